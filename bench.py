@@ -1,0 +1,421 @@
+"""Benchmark of the sparse-INT4 decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): BASELINE config 1 — 28 stacked layers, each with its own seeded K/V
+(fp16, ~N(0,1), four fixed K channels x8), batch 1, 24 query / 8 KV heads, head_dim 128,
+32 768 tokens of context in pages of 16 (2048 pages), retention 0.25 + first and last page;
+one decode step = for every layer: page scores from the INT4 metadata -> top-k + compact
+index -> split-K sparse attention over the selected packed pages.  Data are synthetic.
+With N > 1 every rank runs the same workload on its own independent sequence (batch
+sharding, no collective in the data path): weak scaling.
+
+Prints ONE JSON line (rank 0).  `value` is tokens/s with the cache resident in HBM and the
+step replayed from a CUDA graph; `e2e` is the same step driven through the Python API with
+host buffers (H2D of the new token's q/k/v, pack-on-append, attention incl. the tail, D2H of
+the outputs inside the timed region); `roofline` is for the attention kernel; `cpu_baseline`
+is the CPU oracle port of the same chain on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(layers=28, B=1, Hq=24, Hkv=8, D=128, ctx=32768, page=16, retention=0.25, sinks=1, window=1)
+PAGE_ATTN_BYTES = 1024 + 512 + 1024 + 64      # K payload, K scale+min rows, V payload, V scale+min
+
+
+# --------------------------------------------------------------------------- helpers
+
+def seeds(layer):
+    base = 1000 * 1 + 10 * layer
+    return base, base + 1, base + 2
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- CPU oracle arm
+
+def cpu_chain_setup(n_layers, cfg, threads):
+    """Seeded inputs for n_layers on the host, quantised by the oracle (not timed)."""
+    import numpy as np
+    import torch
+    import oracle
+    oracle.set_num_threads(threads)
+    layers = []
+    for li in range(n_layers):
+        sk, sv, sq = seeds(li)
+        K = torch.from_numpy(np.random.default_rng(sk).standard_normal((cfg["B"], cfg["Hkv"], cfg["ctx"], cfg["D"]), dtype=np.float32))
+        K[..., [3, 17, 64, 100]] *= 8.0
+        V = torch.from_numpy(np.random.default_rng(sv).standard_normal((cfg["B"], cfg["Hkv"], cfg["ctx"], cfg["D"]), dtype=np.float32))
+        Q = torch.from_numpy(np.random.default_rng(sq).standard_normal((cfg["B"], cfg["Hq"], 1, cfg["D"]), dtype=np.float32)).half()
+        kv = oracle.quantize_k_int4(K.half(), cfg["page"]) + oracle.quantize_v_int4(V.half())
+        layers.append((Q, kv))
+    return layers
+
+
+def cpu_chain_step(layers, cfg):
+    """One pass of the hot path per layer on the CPU oracle: scores -> select -> compact -> attention."""
+    import oracle
+    P = cfg["ctx"] // cfg["page"]
+    k_max = math.ceil(cfg["retention"] * P)
+    bucket = k_max + cfg["sinks"] + cfg["window"]
+    for Q, kv in layers:
+        s = oracle.page_scores_int4_fast(Q, kv[1], kv[2])
+        m = oracle.select_pages_vectorized(s, cfg["retention"], cfg["sinks"], cfg["window"], k_max_static=k_max)
+        c = oracle.build_compact_selection(m, bucket)
+        oracle.sparse_attn_int4(Q, *kv, selected_page_ids=c, page_size=cfg["page"])
+
+
+def time_cpu_chain(cfg, sample_layers, reps, threads):
+    layers = cpu_chain_setup(sample_layers, cfg, threads)
+    cpu_chain_step(layers, cfg)  # warm-up
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        cpu_chain_step(layers, cfg)
+        ts.append(time.perf_counter() - t0)
+    per_layer = statistics.median(ts) / sample_layers
+    return per_layer, ts
+
+
+def run_reference(args):
+    """The reference arm: the CPU port of the reference's eager chain on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = dict(CFG)
+    threads = os.cpu_count() or 1
+    sample = 2
+    layers = cpu_chain_setup(sample, cfg, threads)
+    for _ in range(max(args.warmup, 1)):
+        cpu_chain_step(layers, cfg)
+    ts = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        cpu_chain_step(layers, cfg)
+        ts.append(time.perf_counter() - t0)
+    per_layer = sum(ts) / len(ts) / sample
+    ms_step = per_layer * cfg["layers"] * 1e3
+    val = 1e3 / ms_step
+    sample_txt = f"{sample} of {cfg['layers']} layers per step (scores+select+compact+attention), time scaled x{cfg['layers'] // sample}"
+    print(json.dumps({
+        "impl": "reference", "metric": "sparse-INT4 decode tokens/s at 32k ctx", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 accumulate over int4 KV (f64 in the port)",
+        "data": "synthetic", "config": workload_config(cfg, 1),
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample_txt},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(cfg, n_gpus):
+    return {"workload": "BASELINE config 1: 28 layers x (page scores -> top-k+compact -> sparse INT4 attention), batch 1 per GPU",
+            "layers": cfg["layers"], "batch_per_gpu": cfg["B"], "q_heads": cfg["Hq"], "kv_heads": cfg["Hkv"],
+            "head_dim": cfg["D"], "context": cfg["ctx"], "page_size": cfg["page"], "retention": cfg["retention"],
+            "sinks": cfg["sinks"], "window_pages": cfg["window"], "sharding": f"batch x{n_gpus} (independent sequences)",
+            "l2": "inputs larger than L2 (1.15 GB cache, ~1 GB touched per step)"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from flashquest_b200 import _lib
+    from flashquest_b200.cache.persistent_int4 import PersistentInt4KVCache
+    from flashquest_b200.eager.decode_step import QuestDecodeInt4
+    _lib.lib()   # fail loudly here if the CUDA library is missing
+
+    cfg = dict(CFG)
+    if args.layers:
+        cfg["layers"] = args.layers
+    if args.ctx:
+        cfg["ctx"] = args.ctx
+    Lr, B, Hq, Hkv, D, S, page = cfg["layers"], cfg["B"], cfg["Hq"], cfg["Hkv"], cfg["D"], cfg["ctx"], cfg["page"]
+    extra = 256   # room for the tokens appended by the end-to-end run
+    cache = PersistentInt4KVCache(batch_size=B, num_layers=Lr, num_kv_heads=Hkv, head_dim=D, max_seq_len=S + extra,
+                                  page_size=page, device=dev, dtype=torch.float16)
+    qs = []
+    for li in range(Lr):
+        sk, sv, sq = seeds(li + 100 * rank)
+        g = torch.Generator(device=dev)
+        K = torch.randn(B, Hkv, S, D, device=dev, generator=g.manual_seed(sk))
+        K[..., [3, 17, 64, 100]] *= 8.0
+        V = torch.randn(B, Hkv, S, D, device=dev, generator=g.manual_seed(sv))
+        cache.update_quantized(K.half(), V.half(), li)           # bulk pack-on-append
+        qs.append(torch.randn(B, Hq, 1, D, device=dev, generator=g.manual_seed(sq)).half())
+        del K, V
+    step = QuestDecodeInt4(cache, num_q_heads=Hq, retention=cfg["retention"], num_sinks=cfg["sinks"],
+                           window_pages=cfg["window"], q_dtype=torch.float16)
+    Q = torch.stack(qs)       # (L,B,Hq,1,D)
+
+    def one_step():
+        for li in range(Lr):
+            step.attend(Q[li], li)
+
+    # ---- warm-up (eager), then capture the whole step in a CUDA graph ----
+    one_step()
+    torch.cuda.synchronize()
+    launches_per_step = step.launches
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        one_step()
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        one_step()
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- timed region: K graph replays, CUDA events ----
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+        # keep the GPU busy a little longer so the 200 ms sampler sees the loaded clocks
+        t_end = time.time() + 0.7
+        while time.time() < t_end:
+            graph.replay()
+        torch.cuda.synchronize()
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * B * 1e3 / ms_step
+    status = _lib.lib().fq_device_status()
+
+    # ---- roofline of the dominant kernel (attention): back-to-back launches of it alone ----
+    from flashquest_b200._lib import check, dtype_code, lib, ptr, stream_ptr
+    L = lib()
+
+    def attn_only():
+        for li in range(Lr):
+            q3 = Q[li].reshape(B, Hq, D)
+            Ks, Km, Kp, Vp, Vs, Vm = (cache.K_scale[li], cache.K_mn[li], cache.K_packed[li], cache.V_packed[li],
+                                      cache.V_scale[li], cache.V_mn[li])
+            comp, O = step.compact[li], step.O[li]
+            check(L.fq_sparse_decode_int4(
+                ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1), ptr(Kp), Kp.stride(0), Kp.stride(1),
+                ptr(Ks), ptr(Km), Ks.stride(0), Ks.stride(1), Ks.stride(2), ptr(Vp), Vp.stride(0), Vp.stride(1),
+                ptr(Vs), ptr(Vm), Vs.stride(0), Vs.stride(1), ptr(comp), comp.stride(0), comp.stride(1), step.bucket,
+                None, None, 1, 0, 0, 0, 0, B, Hq, Hkv, S, S // page, D, page, step.sm_scale,
+                ptr(O), O.stride(0), O.stride(1), ptr(step.lse[li]), ptr(step.workspace[li]), step.workspace.shape[1],
+                step.n_split, stream_ptr(dev)))
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g2):
+        attn_only()
+    for _ in range(3):
+        g2.replay()
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for _ in range(args.steps):
+        g2.replay()
+    a1.record()
+    torch.cuda.synchronize()
+    attn_us = a0.elapsed_time(a1) * 1e3 / (args.steps * Lr)
+    # algorithmic bytes: union over the query heads of a KV group of the selected pages
+    n_rep = Hq // Hkv
+    P = S // page
+    union_pages = per_head_pages = 0
+    for li in range(Lr):
+        ids = step.compact[li].long()                                 # (B,Hq,bucket)
+        m = torch.zeros(B, Hq, P + 1, dtype=torch.bool, device=dev)
+        m.scatter_(2, torch.where(ids >= 0, ids, torch.full_like(ids, P)), True)
+        m = m[:, :, :P]
+        per_head_pages += int(m.sum())
+        union_pages += int(m.view(B, Hkv, n_rep, P).any(dim=2).sum())
+    alg_bytes = union_pages * PAGE_ATTN_BYTES / Lr
+    peak, peak_kind = measured_peak()
+    achieved = alg_bytes / (attn_us * 1e-6) / 1e9
+    traffic = None
+    try:
+        with open(os.path.join(ROOT, "profiles", "attention_int4_traffic.json")) as f:
+            traffic = json.load(f).get("dram_bytes_per_launch_config1")
+    except Exception:
+        pass
+    roofline = {"bound": "hbm", "kernel": "sparse_decode_int4_kernel", "achieved": achieved, "peak": peak,
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+                "algorithmic_bytes_per_launch": alg_bytes, "per_head_bytes_per_launch": per_head_pages * PAGE_ATTN_BYTES / Lr,
+                "avg_launch_us": attn_us, "frac_of_8TBs": achieved / 8000.0}
+
+    # ---- end to end through the Python API with host buffers ----
+    e2e = run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier)
+
+    # ---- CPU baseline (rank 0, N = 1 only) ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        per_layer, ts = time_cpu_chain(dict(CFG), 2, 3, threads)
+        cpu = {"value": 1.0 / (per_layer * CFG["layers"]), "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"2 of 28 layers x 3 repetitions of scores+select+compact+attention on the C oracle, scaled to 28 layers"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "sparse-INT4 decode tokens/s at 32k ctx", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32 accumulate over int4 KV, fp16 Q/O", "data": "synthetic",
+            "config": workload_config(cfg, world), "clocks": clk.summary(), "e2e": e2e,
+            "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu,
+            "device_status": status,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier):
+    """Per step and layer: pinned host q/k/v of the new token -> device, pack-on-append,
+    score/select/attend incl. the staged tail; one D2H read of all layers' outputs."""
+    Lr, B, Hq, Hkv, D = cfg["layers"], cfg["B"], cfg["Hq"], cfg["Hkv"], cfg["D"]
+    n = args.steps + max(args.warmup, 3)
+    g = torch.Generator().manual_seed(7)
+    hq = torch.randn(n, Lr, B, Hq, 1, D, generator=g).half().pin_memory()
+    hk = torch.randn(n, Lr, B, Hkv, 1, D, generator=g).half().pin_memory()
+    hv = torch.randn(n, Lr, B, Hkv, 1, D, generator=g).half().pin_memory()
+    out_host = torch.empty(Lr, B, Hq, D, dtype=torch.float16).pin_memory()
+    dq = torch.empty(Lr, B, Hq, 1, D, dtype=torch.float16, device=dev)
+    dk = torch.empty(Lr, B, Hkv, 1, D, dtype=torch.float16, device=dev)
+    dv = torch.empty(Lr, B, Hkv, 1, D, dtype=torch.float16, device=dev)
+
+    def one(i):
+        dq.copy_(hq[i], non_blocking=True)
+        dk.copy_(hk[i], non_blocking=True)
+        dv.copy_(hv[i], non_blocking=True)
+        for li in range(Lr):
+            cache.update_quantized(dk[li], dv[li], li)
+            step.attend(dq[li], li)
+        out_host.copy_(step.O, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    w = max(args.warmup, 3)
+    for i in range(w):
+        one(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(w, n):
+        one(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    h2d = hq[0].numel() * 2 + hk[0].numel() * 2 + hv[0].numel() * 2
+    return {"value": world * B * 1e3 / (ms / args.steps), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": ms / args.steps,
+            "path": "pinned host q/k/v -> PersistentInt4KVCache.update_quantized + QuestDecodeInt4.attend per layer -> host O"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures)")
+    ap.add_argument("--ctx", type=int, default=0, help="override the context length (small captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

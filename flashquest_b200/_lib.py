@@ -1,0 +1,102 @@
+"""ctypes binding of libflashquest_b200.so (the C ABI declared in include/flashquest_b200.h).
+
+The library is the only compute path of this package: if it is missing or cannot be loaded
+every operator raises; there is no eager / CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_int64, c_size_t, c_void_p
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libflashquest_b200.so")
+
+FQ_F32, FQ_F16, FQ_BF16 = 0, 1, 2
+_DTYPE_CODE = {torch.float32: FQ_F32, torch.float16: FQ_F16, torch.bfloat16: FQ_BF16}
+
+_lib = None
+
+I, L, P, F, Z = c_int, c_int64, c_void_p, c_float, c_size_t
+
+_PROTOTYPES = {
+    "fq_last_error_string": (ctypes.c_char_p, []),
+    "fq_version": (ctypes.c_char_p, []),
+    "fq_device_status": (I, []),
+    "fq_quantize_kv_int4": (I, [P, P, L, L, L, I, P, P, L, L, L, I, I, I, I, I, I, I,
+                                P, P, L, L, L, P, P, L, L, L, P, P, L, L, L, P, P, L, L, L, P]),
+    "fq_dequantize_int4": (I, [P, L, L, L, P, P, L, L, L, I, I, I, I, I, I, P, L, L, L, P]),
+    "fq_page_scores_int4": (I, [P, I, L, L, P, P, L, L, L, I, I, I, I, I, P, L, L, P]),
+    "fq_select_pages": (I, [P, L, L, I, I, I, P, F, I, I, I, P, L, L, P, L, L, I, P, P]),
+    "fq_build_compact": (I, [P, L, L, I, P, L, I, P]),
+    "fq_sparse_decode_workspace_bytes": (Z, [I, I, I, I]),
+    "fq_sparse_decode_default_splits": (I, [I, I, I, I]),
+    "fq_sparse_decode_int4": (I, [P, I, L, L, P, L, L, P, P, L, L, L, P, L, L, P, P, L, L,
+                                  P, L, L, I, P, P, I, L, L, L, I,
+                                  I, I, I, I, I, I, I, F, P, L, L, P, P, Z, I, P]),
+}
+
+# entry points added by later sources register themselves here (name -> (restype, argtypes))
+EXTRA_PROTOTYPES: dict = {}
+
+
+class FlashQuestError(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded shared library; raises if it has not been built (python -m flashquest_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FlashQuestError(
+                f"{LIB_PATH} is missing: build it with `python -m flashquest_b200.build` "
+                "(nvcc, sm_100a).  flashquest_b200 has no fallback path.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in {**_PROTOTYPES, **EXTRA_PROTOTYPES}.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def exported_symbols():
+    return sorted({**_PROTOTYPES, **EXTRA_PROTOTYPES})
+
+
+def check(rc: int, exc=FlashQuestError):
+    if rc != 0:
+        msg = lib().fq_last_error_string().decode()
+        if rc in (-1, -4) and exc is FlashQuestError:
+            exc = ValueError if rc == -1 else NotImplementedError
+        raise exc(msg)
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}; expected float32, float16 or bfloat16") from None
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise FlashQuestError("flashquest_b200 operators take CUDA tensors (no CPU path)")
+
+
+def ptr(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def stream_ptr(device=None):
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def inner_contiguous(t: torch.Tensor) -> torch.Tensor:
+    """Strided views are taken as they are as long as the last dimension is dense."""
+    if t.dim() > 0 and t.shape[-1] > 1 and t.stride(-1) != 1:
+        return t.contiguous()
+    return t

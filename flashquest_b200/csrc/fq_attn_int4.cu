@@ -1,0 +1,713 @@
+// Sparse decode attention over selected packed INT4 pages: GQA, split-K, LSE merge.
+//
+// Work unit = one chunk of TOK tokens of one selected page (TOK = 16, or 8 for page 8):
+//   K payload TOK*D/2 B, V payload TOK*D/2 B, K scale + K min rows 2*D*2 B, V scale + V min
+//   2*TOK*2 B  (2624 B at D = 128, TOK = 16).
+// Grid = (n_split, H_q, B); a CTA walks a contiguous slice of the row's compact page list.
+// Inside a CTA every QUARTER WARP (8 lanes) owns one unit at a time, so a 4-warp CTA has 16
+// units in flight.  Units are staged into shared memory with bulk asynchronous copies
+// (cp.async.bulk + mbarrier complete_tx); the six copies of a unit are issued by six lanes
+// of the quarter warp that will consume it.  Staging is single-buffered per warp (42 KB per
+// CTA): four CTAs = 16 warps stay resident per SM, and the copy latency of one warp is
+// covered by the arithmetic of the other fifteen rather than by a deeper per-warp pipeline,
+// because the arithmetic (ALU-pipe nibble extraction) needs the occupancy anyway.  By
+// default a CTA gets one 16-unit iteration, so the hardware CTA scheduler balances the load.
+//
+// Arithmetic (CUDA cores, fp32 accumulation, no tensor cores: M is 1):
+//   q.k = sum_d (q_d*sc_d)*code_d + sum_d q_d*mn_d      (scale folded into q once per page)
+//   o_d = sum_t (p_t*vs_t)*code_td + sum_t p_t*vm_t     (min folded into one scalar)
+// A 4-bit code is turned into an fp32 operand with ONE integer instruction: the nibble is
+// masked in place and the word reinterpreted as an fp32 (sub)normal, whose value is
+// code * 2^(4k-149) for nibble k = 0..5 (bits 0..23 of an fp32 read as an integer times
+// 2^-149, across the subnormal/normal boundary).  The power of two is folded into the
+// multiplier (pre-scaled by 2^100 to stay in range).  The top byte gives (c6 + 16*c7) and c7
+// with one shift each; the multiplier of c7 is corrected by -16*m6.
+// A lane owns D/8 channels of every token: K dot products are reduced across the 8 lanes
+// with a transposing shuffle (14 shuffles for 16 tokens); the V accumulation needs no
+// reduction at all.  Softmax runs in base 2 with sm_scale*log2(e) folded into q.
+//
+// Split-K: each CTA writes (m, l, acc[D]) to the workspace and takes a ticket; the CTA that
+// draws the last ticket of its row merges the partials in split order and writes O / LSE.
+// No CTA ever waits for another one.
+#include "fq_common.cuh"
+
+namespace fq {
+
+#ifndef FQ_ATT_WARPS
+#define FQ_ATT_WARPS 4
+#endif
+#ifndef FQ_ATT_STAGES
+#define FQ_ATT_STAGES 1
+#endif
+constexpr int ATT_WARPS = FQ_ATT_WARPS;
+constexpr int ATT_THREADS = ATT_WARPS * 32;
+constexpr int ATT_STAGES = FQ_ATT_STAGES;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr unsigned WAIT_SPIN_LIMIT = 1u << 24;   // bounded wait on a stage; then give up
+
+struct AttnParams {
+    const void* Q; int64_t q_sb, q_sh;
+    const uint8_t* K_packed; int64_t kp_sb, kp_sh;
+    const uint16_t *K_scale, *K_mn; int64_t km_sb, km_sh, km_sp;
+    const uint8_t* V_packed; int64_t vp_sb, vp_sh;
+    const uint16_t *V_scale, *V_mn; int64_t vm_sb, vm_sh;
+    const int32_t* compact; int64_t cp_sb, cp_sh; int bucket;
+    const void *K_tail, *V_tail; int tail_dtype; int64_t tl_sb, tl_sh, tl_ss; int tail_len;
+    int B, Hq, Hkv, S_kv, P, page, cpp_log2;
+    float sm_scale;
+    void* O; int64_t o_sb, o_sh;
+    float* lse;
+    int* tickets; float* partials; int n_split;
+    int* status;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// global -> shared bulk copy; completion is counted in bytes on the mbarrier.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---------------------------------------------------------------- unit layout in shared memory
+template <int D, int TOK>
+struct UnitLayout {
+    static constexpr int ROW = D / 2;               // packed bytes per token
+    static constexpr int K_OFF = 0;
+    static constexpr int V_OFF = TOK * ROW;
+    static constexpr int KS_OFF = 2 * TOK * ROW;    // K scale row (D bf16)
+    static constexpr int KM_OFF = KS_OFF + 2 * D;   // K min row
+    static constexpr int VS_OFF = KM_OFF + 2 * D;   // V scale (TOK bf16)
+    static constexpr int VM_OFF = VS_OFF + 2 * TOK;
+    static constexpr int BYTES = VM_OFF + 2 * TOK;  // 2624 (D=128,TOK=16): = 64 mod 128, so two
+                                                    // quarter warps hit disjoint bank halves
+    static constexpr int STRIDE = (BYTES + 15) & ~15;
+};
+
+// Multiplier pre-scale for channel j (j mod 8 = nibble index) so that
+// (code as masked fp32 bits) * mult = code * value * 2^-49.
+__device__ __forceinline__ float pow2i(int n) { return __int_as_float((127 + n) << 23); }
+__device__ __forceinline__ float nib_scale(int k) {
+    // nibble k <= 5 is read as code*2^(4k-149); nibbles 6,7 (after a shift) as *2^-149
+    return k <= 5 ? pow2i(100 - 4 * k) : pow2i(100);
+}
+__device__ __forceinline__ float nib_unscale(int k) { return k <= 5 ? pow2i(49 - 4 * k) : pow2i(49); }
+
+// eight codes of one 32-bit word as fp32 operands (see the header comment)
+__device__ __forceinline__ void nib8(uint32_t w, float (&f)[8]) {
+    f[0] = __uint_as_float(w & 0x0000000fu);
+    f[1] = __uint_as_float(w & 0x000000f0u);
+    f[2] = __uint_as_float(w & 0x00000f00u);
+    f[3] = __uint_as_float(w & 0x0000f000u);
+    f[4] = __uint_as_float(w & 0x000f0000u);
+    f[5] = __uint_as_float(w & 0x00f00000u);
+    f[6] = __uint_as_float(w >> 24);   // c6 + 16*c7
+    f[7] = __uint_as_float(w >> 28);   // c7
+}
+
+// Transposing reduction over the 8 lanes of a quarter warp: in: N partial sums per lane,
+// out: lane l holds the full sums of tokens (N/8)*l .. (N/8)*l + N/8-1 in s[0..N/8).
+template <int N>
+__device__ __forceinline__ void qw_transpose_reduce(float (&s)[N], int l, unsigned qmask) {
+    static_assert(N == 8 || N == 16, "N");
+    {
+        const bool up = l & 4;
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            const float send = up ? s[i] : s[i + N / 2];
+            const float keep = up ? s[i + N / 2] : s[i];
+            s[i] = keep + __shfl_xor_sync(qmask, send, 4);
+        }
+    }
+    {
+        const bool up = l & 2;
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            const float send = up ? s[i] : s[i + N / 4];
+            const float keep = up ? s[i + N / 4] : s[i];
+            s[i] = keep + __shfl_xor_sync(qmask, send, 2);
+        }
+    }
+    {
+        const bool up = l & 1;
+#pragma unroll
+        for (int i = 0; i < N / 8; ++i) {
+            const float send = up ? s[i] : s[i + N / 8];
+            const float keep = up ? s[i + N / 8] : s[i];
+            s[i] = keep + __shfl_xor_sync(qmask, send, 1);
+        }
+    }
+}
+
+__device__ __forceinline__ float qw_sum(float v, unsigned qmask) {
+    v += __shfl_xor_sync(qmask, v, 4);
+    v += __shfl_xor_sync(qmask, v, 2);
+    v += __shfl_xor_sync(qmask, v, 1);
+    return v;
+}
+__device__ __forceinline__ float qw_max(float v, unsigned qmask) {
+    v = fmaxf(v, __shfl_xor_sync(qmask, v, 4));
+    v = fmaxf(v, __shfl_xor_sync(qmask, v, 2));
+    v = fmaxf(v, __shfl_xor_sync(qmask, v, 1));
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float ld_as_f32(const void* p, int64_t i) { return Dt<T>::to_f32(static_cast<const T*>(p)[i]); }
+
+// ---------------------------------------------------------------- the kernel
+template <typename QT, int D, int TOK>
+__global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnParams p) {
+    using L = UnitLayout<D, TOK>;
+    constexpr int DPL = D / 8;        // channels per lane
+    constexpr int WPL = DPL / 8;      // 32-bit words per lane per token
+    constexpr int TPL = TOK / 8;      // tokens per lane after the reduction
+    constexpr int NSTATE = ATT_WARPS * 4 + ATT_WARPS;   // quarter-warp states + per-warp tail states
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    // [stages][warps][4 units] staging | mbarriers | pv broadcast | merge area (aliases staging)
+    unsigned char* stage_base = smem;
+    constexpr int STAGING_BYTES = ATT_STAGES * ATT_WARPS * 4 * L::STRIDE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGING_BYTES);            // [warps][stages]
+    float* pv_bcast = reinterpret_cast<float*>(smem + STAGING_BYTES + ATT_WARPS * ATT_STAGES * 8);  // [warps*4][TOK]
+    float* st_m = pv_bcast + ATT_WARPS * 4 * TOK;   // [NSTATE]
+    float* st_l = st_m + NSTATE;                    // [NSTATE]
+    float* st_acc = reinterpret_cast<float*>(smem);  // [NSTATE][D], reuses the staging area after the loop
+
+    const int split = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+    const int n_rep = p.Hq / p.Hkv, hkv = hq / n_rep;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, qw = lane >> 3, l = lane & 7;
+    const unsigned qmask = 0xffu << (8 * qw);
+
+    // ---- slice of the compact list owned by this CTA, in units ----
+    const int cpp_log2 = p.cpp_log2;                    // log2(chunks (units) per page)
+    const int slots_per_split = (p.bucket + p.n_split - 1) / p.n_split;
+    const int slot_begin = split * slots_per_split;
+    const int slot_end = min(p.bucket, slot_begin + slots_per_split);
+    const int n_units = max(0, slot_end - slot_begin) << cpp_log2;
+    constexpr int units_per_iter = ATT_WARPS * 4;
+    const int n_iter = (n_units + units_per_iter - 1) / units_per_iter;
+    const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
+
+    uint64_t* my_bars = bars + warp * ATT_STAGES;
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < ATT_STAGES; ++s) mbar_init(&my_bars[s], 4);   // one arrival per quarter warp
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    const uint8_t* Kp = p.K_packed + b * p.kp_sb + hkv * p.kp_sh;
+    const uint8_t* Vp = p.V_packed + b * p.vp_sb + hkv * p.vp_sh;
+    const uint16_t* Ks = p.K_scale + b * p.km_sb + hkv * p.km_sh;
+    const uint16_t* Km = p.K_mn + b * p.km_sb + hkv * p.km_sh;
+    const uint16_t* Vs = p.V_scale + b * p.vm_sb + hkv * p.vm_sh;
+    const uint16_t* Vm = p.V_mn + b * p.vm_sb + hkv * p.vm_sh;
+
+    // Unit handled by this quarter warp in iteration `it`: page id, first token, valid tokens.
+    auto unit_of = [&](int it, int& page_id, int& tok0, int& n_tok) {
+        const int u = it * units_per_iter + warp * 4 + qw;
+        page_id = -1; tok0 = 0; n_tok = 0;
+        if (u < n_units) {
+            const int pg = __ldg(list + slot_begin + (u >> cpp_log2));
+            if (pg >= 0 && pg < p.P) {
+                tok0 = pg * p.page + (u & ((1 << cpp_log2) - 1)) * TOK;
+                n_tok = min(TOK, p.S_kv - tok0);
+                if (n_tok > 0) page_id = pg; else n_tok = 0;
+            }
+        }
+    };
+
+    unsigned char* my_unit = stage_base + (warp * 4 + qw) * L::STRIDE;
+    uint64_t* bar = &my_bars[0];
+    auto issue = [&](int page_id, int tok0, int n_tok) {
+        if (page_id < 0) {
+            if (l == 0) mbar_arrive(bar);
+            return;
+        }
+        const unsigned payload = (unsigned)n_tok * L::ROW;
+        const bool full = n_tok == TOK;
+        if (l == 0) {
+            const unsigned tx = 2u * payload + 4u * D + (full ? 4u * TOK : 0u);
+            mbar_arrive_expect_tx(bar, tx);
+        }
+        if (l == 0) bulk_g2s(my_unit + L::K_OFF, Kp + (int64_t)tok0 * L::ROW, payload, bar);
+        else if (l == 1) bulk_g2s(my_unit + L::V_OFF, Vp + (int64_t)tok0 * L::ROW, payload, bar);
+        else if (l == 2) bulk_g2s(my_unit + L::KS_OFF, Ks + (int64_t)page_id * p.km_sp, 2 * D, bar);
+        else if (l == 3) bulk_g2s(my_unit + L::KM_OFF, Km + (int64_t)page_id * p.km_sp, 2 * D, bar);
+        else if (l == 4 && full) bulk_g2s(my_unit + L::VS_OFF, Vs + tok0, 2 * TOK, bar);
+        else if (l == 5 && full) bulk_g2s(my_unit + L::VM_OFF, Vm + tok0, 2 * TOK, bar);
+    };
+
+    // per quarter-warp online-softmax state (all in base 2)
+    float m_run = -INFINITY;          // running max
+    float l_part = 0.f;               // this lane's share of the denominator
+    float mn_part = 0.f;              // this lane's share of sum_t p_t * vm_t
+    float2 acc[DPL / 2];
+#pragma unroll
+    for (int j = 0; j < DPL / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+
+    bool timed_out = false;
+    int issued = 0;   // iterations whose copies have been started
+    int page_id = -1, tok0 = 0, n_tok = 0;
+    if (n_iter > 0) {   // start the first copies before anything else: q is loaded under their latency
+        unit_of(0, page_id, tok0, n_tok);
+        issue(page_id, tok0, n_tok);
+        issued = 1;
+    }
+
+    // ---- q slice of this lane, pre-multiplied by sm_scale*log2(e) and the nibble scale ----
+    float qn[DPL];    // for the K codes
+    float qr[DPL];    // plain q*sm_scale*log2e, for q.mn
+    {
+        const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + DPL * l;
+        const float c = p.sm_scale * LOG2E;
+#pragma unroll
+        for (int j = 0; j < DPL; j += 8) {
+            float v[8];
+            load8<QT>(qp + j, v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                qr[j + e] = v[e] * c;
+                qn[j + e] = qr[j + e] * nib_scale(e);
+            }
+        }
+    }
+
+    for (int it = 0; it < n_iter; ++it) {
+        if (it > 0) {
+            unit_of(it, page_id, tok0, n_tok);
+            __syncwarp();          // every lane is done reading the previous unit
+            fence_proxy_async();
+            issue(page_id, tok0, n_tok);
+            issued = it + 1;
+        }
+        const unsigned parity = (unsigned)it & 1u;
+        {
+            unsigned spins = 0;
+            while (!mbar_try_wait(bar, parity)) {
+                if (++spins > WAIT_SPIN_LIMIT) { timed_out = true; break; }
+            }
+        }
+        if (__any_sync(0xffffffffu, timed_out)) { timed_out = true; break; }
+        if (page_id < 0) continue;                 // uniform inside the quarter warp
+        const unsigned char* u = my_unit;
+
+        // ---------------- K: fold the page scale into q; q.mn ----------------
+        float qs[DPL];
+        float qmn = 0.f;
+#pragma unroll
+        for (int j = 0; j < DPL; j += 8) {
+            const uint4 s4 = *reinterpret_cast<const uint4*>(u + L::KS_OFF + 2 * (DPL * l + j));
+            const uint4 m4 = *reinterpret_cast<const uint4*>(u + L::KM_OFF + 2 * (DPL * l + j));
+            const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w}, mw[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                qs[j + 2 * e] = qn[j + 2 * e] * bf16_lo(sw[e]);
+                qs[j + 2 * e + 1] = qn[j + 2 * e + 1] * bf16_hi(sw[e]);
+                qmn = fmaf(qr[j + 2 * e], bf16_lo(mw[e]), qmn);
+                qmn = fmaf(qr[j + 2 * e + 1], bf16_hi(mw[e]), qmn);
+            }
+            qs[j + 7] = fmaf(-16.f, qs[j + 6], qs[j + 7]);   // c7 rides on (c6 + 16 c7)
+        }
+        qmn = qw_sum(qmn, qmask);
+
+        float sdot[TOK];
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) {
+            float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int wd = 0; wd < WPL; ++wd) {
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(u + L::K_OFF + t * L::ROW + 4 * (WPL * l + wd));
+                float f[8];
+                nib8(w, f);
+#pragma unroll
+                for (int e = 0; e < 8; e += 2)
+                    a = __ffma2_rn(make_float2(f[e], f[e + 1]), make_float2(qs[8 * wd + e], qs[8 * wd + e + 1]), a);
+            }
+            sdot[t] = a.x + a.y;
+        }
+        qw_transpose_reduce<TOK>(sdot, l, qmask);
+
+        // ---------------- softmax for this lane's TPL tokens ----------------
+        const float UNS = 5.62949953421312e14f;   // 2^49
+        float x[TPL], vs[TPL], vm[TPL];
+        float pmax = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < TPL; ++i) {
+            const int t = TPL * l + i;
+            const bool valid = t < n_tok;
+            x[i] = valid ? fmaf(sdot[i], UNS, qmn) : -INFINITY;
+            pmax = fmaxf(pmax, x[i]);
+            if (n_tok == TOK) {
+                vs[i] = bf16_lo(*reinterpret_cast<const uint16_t*>(u + L::VS_OFF + 2 * t));
+                vm[i] = bf16_lo(*reinterpret_cast<const uint16_t*>(u + L::VM_OFF + 2 * t));
+            } else {   // ragged last chunk: metadata straight from global memory
+                vs[i] = valid ? bf16_lo(Vs[tok0 + t]) : 0.f;
+                vm[i] = valid ? bf16_lo(Vm[tok0 + t]) : 0.f;
+            }
+        }
+        pmax = qw_max(pmax, qmask);
+        const float m_new = fmaxf(m_run, pmax);     // finite: the unit has at least one valid token
+        const float alpha = ex2(m_run - m_new);     // ex2(-inf) = 0 on the first unit
+        m_run = m_new;
+        float* pvb = pv_bcast + (warp * 4 + qw) * TOK;
+        l_part *= alpha;
+        mn_part *= alpha;
+#pragma unroll
+        for (int i = 0; i < TPL; ++i) {
+            const float pr = ex2(x[i] - m_new);
+            l_part += pr;
+            mn_part = fmaf(pr, vm[i], mn_part);
+            pvb[TPL * l + i] = pr * vs[i] * 1.2676506002282294e30f;   // * 2^100
+        }
+        __syncwarp(qmask);
+
+        // ---------------- V ----------------
+        const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+        for (int j = 0; j < DPL / 2; ++j) acc[j] = __fmul2_rn(acc[j], alpha2);
+#pragma unroll
+        for (int t4 = 0; t4 < TOK; t4 += 4) {
+            const float4 pv4 = *reinterpret_cast<const float4*>(pvb + t4);
+            const float pv[4] = {pv4.x, pv4.y, pv4.z, pv4.w};
+#pragma unroll
+            for (int tt = 0; tt < 4; ++tt) {
+                const int t = t4 + tt;
+                const float2 pp = make_float2(pv[tt], pv[tt]);
+#pragma unroll
+                for (int wd = 0; wd < WPL; ++wd) {
+                    const uint32_t w = *reinterpret_cast<const uint32_t*>(u + L::V_OFF + t * L::ROW + 4 * (WPL * l + wd));
+                    float f[8];
+                    nib8(w, f);
+#pragma unroll
+                    for (int e = 0; e < 8; e += 2)
+                        acc[4 * wd + e / 2] = __ffma2_rn(make_float2(f[e], f[e + 1]), pp, acc[4 * wd + e / 2]);
+                }
+            }
+        }
+        __syncwarp(qmask);   // pv_bcast is rewritten in the next iteration
+    }
+
+    if (timed_out) {
+        if (lane == 0) atomicExch(p.status, FQ_ERR_TIMEOUT);
+        // copies still in flight target this CTA's shared memory: wait (bounded) for every
+        // stage that was issued before leaving, so the CTA does not exit under them.
+        if (issued > 0) {
+            unsigned spins = 0;
+            while (!mbar_try_wait(bar, (unsigned)(issued - 1) & 1u)) {
+                if (++spins > WAIT_SPIN_LIMIT) break;
+            }
+        }
+    }
+
+    // ---------------- un-scale the V accumulators of this quarter warp ----------------
+    float o[DPL];
+    {
+        const float l_q = qw_sum(l_part, qmask);
+        const float mn_q = qw_sum(mn_part, qmask);
+#pragma unroll
+        for (int wd = 0; wd < WPL; ++wd) {
+            float a[8];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) { a[e] = acc[4 * wd + e / 2].x; a[e + 1] = acc[4 * wd + e / 2].y; }
+            a[6] = fmaf(-16.f, a[7], a[6]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[8 * wd + e] = fmaf(a[e], nib_unscale(e), mn_q);
+        }
+        l_part = l_q;
+    }
+
+    // ---------------- tail: dense attention over the staged (unquantised) tokens ----------------
+    // Done by the CTA of split 0; warp w takes tail tokens w, w+WARPS, ...; lane owns D/32 channels.
+    constexpr int TD = D / 32;
+    float tm = -INFINITY, tl = 0.f, tacc[TD];
+#pragma unroll
+    for (int j = 0; j < TD; ++j) tacc[j] = 0.f;
+    if (split == 0 && p.tail_len > 0) {
+        float qt[TD];
+        const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + TD * lane;
+#pragma unroll
+        for (int j = 0; j < TD; ++j) qt[j] = Dt<QT>::to_f32(qp[j]) * (p.sm_scale * LOG2E);
+        for (int t = warp; t < p.tail_len; t += ATT_WARPS) {
+            const int64_t ro = b * p.tl_sb + hkv * p.tl_sh + (int64_t)t * p.tl_ss + TD * lane;
+            float kv[TD], vv[TD];
+#pragma unroll
+            for (int j = 0; j < TD; ++j) {
+                if (p.tail_dtype == FQ_BF16) {
+                    kv[j] = ld_as_f32<__nv_bfloat16>(p.K_tail, ro + j);
+                    vv[j] = ld_as_f32<__nv_bfloat16>(p.V_tail, ro + j);
+                } else {
+                    kv[j] = ld_as_f32<__half>(p.K_tail, ro + j);
+                    vv[j] = ld_as_f32<__half>(p.V_tail, ro + j);
+                }
+            }
+            float sdt = 0.f;
+#pragma unroll
+            for (int j = 0; j < TD; ++j) sdt = fmaf(qt[j], kv[j], sdt);
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) sdt += __shfl_xor_sync(0xffffffffu, sdt, off);
+            const float mnew = fmaxf(tm, sdt);
+            const float al = ex2(tm - mnew);
+            const float pr = ex2(sdt - mnew);
+            tl = tl * al + pr;
+#pragma unroll
+            for (int j = 0; j < TD; ++j) tacc[j] = fmaf(pr, vv[j], tacc[j] * al);
+            tm = mnew;
+        }
+    }
+
+    // ---------------- CTA merge of all states through shared memory ----------------
+    __syncthreads();   // every warp is done with the staging area (st_acc aliases it)
+    {
+        const int sid = warp * 4 + qw;
+        if (l == 0) { st_m[sid] = m_run; st_l[sid] = l_part; }
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) st_acc[sid * D + DPL * l + j] = o[j];
+        const int tsid = ATT_WARPS * 4 + warp;
+        if (lane == 0) { st_m[tsid] = tm; st_l[tsid] = tl; }
+#pragma unroll
+        for (int j = 0; j < TD; ++j) st_acc[tsid * D + TD * lane + j] = tacc[j];
+    }
+    __syncthreads();
+    float m_cta = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NSTATE; ++i) m_cta = fmaxf(m_cta, st_m[i]);
+    float l_cta = 0.f;
+    float acc_d = 0.f;           // thread d < D owns output channel d
+    if (m_cta != -INFINITY) {
+#pragma unroll
+        for (int i = 0; i < NSTATE; ++i) {
+            const float wgt = ex2(st_m[i] - m_cta);   // 0 for empty states
+            l_cta = fmaf(st_l[i], wgt, l_cta);
+            if (tid < D) acc_d = fmaf(st_acc[i * D + tid], wgt, acc_d);
+        }
+    }
+
+    QT* Op = static_cast<QT*>(p.O) + b * p.o_sb + hq * p.o_sh;
+    const int row = b * p.Hq + hq;
+    if (p.n_split == 1) {
+        if (tid < D) Op[tid] = from_f32<QT>(l_cta > 0.f ? acc_d / l_cta : 0.f);
+        if (tid == 0 && p.lse) p.lse[row] = l_cta > 0.f ? (m_cta + log2f(l_cta)) * LN2 : -INFINITY;
+        return;
+    }
+
+    // ---------------- split-K: publish the partial, last ticket merges ----------------
+    float* part = p.partials + ((int64_t)row * p.n_split + split) * (D + 2);
+    if (tid < D) part[2 + tid] = acc_d;
+    if (tid == 0) { part[0] = m_cta; part[1] = l_cta; }
+    __threadfence();
+    __syncthreads();
+    __shared__ int s_ticket;
+    if (tid == 0) s_ticket = atomicAdd(&p.tickets[row], 1);
+    __syncthreads();
+    if (s_ticket != p.n_split - 1) return;
+    __threadfence();
+    // The partials of this row are merged in split order with every load independent of the
+    // others (a dependent chain of L2 round trips here would cost more than the attention).
+    const float* parts = p.partials + (int64_t)row * p.n_split * (D + 2);
+    float* mw = reinterpret_cast<float*>(smem);            // [n_split] max, then weight
+    float* lw = mw + p.n_split;                             // [n_split] denominators
+    __shared__ float s_red[ATT_WARPS];
+    float m_loc = -INFINITY;
+    for (int i = tid; i < p.n_split; i += ATT_THREADS) {
+        const float mi = __ldcg(parts + (int64_t)i * (D + 2));
+        mw[i] = mi;
+        lw[i] = __ldcg(parts + (int64_t)i * (D + 2) + 1);
+        m_loc = fmaxf(m_loc, mi);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, off));
+    if (lane == 0) s_red[warp] = m_loc;
+    __syncthreads();
+    float m_all = s_red[0];
+#pragma unroll
+    for (int w = 1; w < ATT_WARPS; ++w) m_all = fmaxf(m_all, s_red[w]);
+    float l_all = 0.f, o_all = 0.f;
+    if (m_all != -INFINITY) {
+        for (int i = tid; i < p.n_split; i += ATT_THREADS) mw[i] = ex2(mw[i] - m_all);
+        __syncthreads();
+        for (int i = 0; i < p.n_split; ++i) l_all = fmaf(lw[i], mw[i], l_all);
+        if (tid < D) {
+            const float* col = parts + 2 + tid;
+            int i = 0;
+            for (; i + 8 <= p.n_split; i += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = __ldcg(col + (int64_t)(i + j) * (D + 2));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o_all = fmaf(v[j], mw[i + j], o_all);
+            }
+            for (; i < p.n_split; ++i) o_all = fmaf(__ldcg(col + (int64_t)i * (D + 2)), mw[i], o_all);
+        }
+    }
+    if (tid < D) Op[tid] = from_f32<QT>(l_all > 0.f ? o_all / l_all : 0.f);
+    if (tid == 0) {
+        if (p.lse) p.lse[row] = l_all > 0.f ? (m_all + log2f(l_all)) * LN2 : -INFINITY;
+        p.tickets[row] = 0;   // leave the workspace ready for the next call
+    }
+}
+
+template <int D, int TOK>
+static constexpr size_t attn_smem_bytes() {
+    using L = UnitLayout<D, TOK>;
+    constexpr int NSTATE = ATT_WARPS * 4 + ATT_WARPS;
+    size_t staging = (size_t)ATT_STAGES * ATT_WARPS * 4 * L::STRIDE;
+    size_t merge = (size_t)NSTATE * D * 4;
+    size_t front = staging > merge ? staging : merge;
+    return front + ATT_WARPS * ATT_STAGES * 8 + (size_t)ATT_WARPS * 4 * TOK * 4 + 2 * NSTATE * 4;
+}
+
+template <typename QT, int D, int TOK>
+static int launch_attn(const AttnParams& p, cudaStream_t st) {
+    constexpr size_t smem = attn_smem_bytes<D, TOK>();
+    static_assert((size_t)ATT_STAGES * ATT_WARPS * 4 * UnitLayout<D, TOK>::STRIDE >=
+                  (size_t)(ATT_WARPS * 5) * D * 4, "merge area must fit in the staging area");
+    auto kern = sparse_decode_int4_kernel<QT, D, TOK>;
+    if (smem > 48 * 1024 - 256) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "fq_sparse_decode_int4: cannot reserve %zu B of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    dim3 grid((unsigned)p.n_split, (unsigned)p.Hq, (unsigned)p.B);
+    kern<<<grid, ATT_THREADS, smem, st>>>(p);
+    return FQ_OK;
+}
+
+}  // namespace fq
+
+extern "C" size_t fq_sparse_decode_workspace_bytes(int B, int Hq, int D, int n_split) {
+    if (B <= 0 || Hq <= 0 || D <= 0 || n_split <= 1) return 0;
+    size_t tickets = ((size_t)B * Hq * 4 + 255) & ~(size_t)255;
+    return tickets + (size_t)B * Hq * n_split * (D + 2) * 4;
+}
+
+extern "C" int fq_sparse_decode_default_splits(int B, int Hq, int bucket, int page) {
+    if (B <= 0 || Hq <= 0 || bucket <= 0 || page <= 0) return 1;
+    const int tok = page >= 16 ? 16 : 8;
+    const long cpp = page / tok;
+    const long units = (long)bucket * cpp;
+    const long rows = (long)B * Hq;
+    const long per_iter = fq::ATT_WARPS * 4;
+    const long total_iters = (units + per_iter - 1) / per_iter;    // per row
+    // One 16-unit iteration per CTA lets the hardware scheduler balance the load; only when
+    // that would mean more than ~8 waves of CTAs (148 SMs x 4 resident) give a CTA several.
+    long iters_per_cta = (rows * total_iters) / (148L * 4 * 8);
+    if (iters_per_cta < 1) iters_per_cta = 1;
+    long n_split = (total_iters + iters_per_cta - 1) / iters_per_cta;
+    if (n_split > bucket) n_split = bucket;
+    if (n_split < 1) n_split = 1;
+    if (n_split > 1024) n_split = 1024;
+    return (int)n_split;
+}
+
+extern "C" int fq_sparse_decode_int4(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss,
+    int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, float* lse,
+    void* workspace, size_t workspace_bytes, int n_split, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_sparse_decode_int4";
+    FQ_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && S_kv >= 0 && P >= 0 && bucket >= 0 && tail_len >= 0, FQ_ERR_ARG, "%s: bad sizes", fn);
+    FQ_CHECK_ARG(B <= 65535 && Hq <= 65535, FQ_ERR_ARG, "%s: B and H_q must be <= 65535", fn);
+    FQ_CHECK_ARG(Hq % Hkv == 0, FQ_ERR_ARG, "%s: H_q=%d must be divisible by H_kv=%d", fn, Hq, Hkv);
+    FQ_CHECK_ARG(D == 64 || D == 128, FQ_ERR_UNSUPPORTED, "%s: head_dim=%d not in (64, 128)", fn, D);
+    FQ_CHECK_ARG(page == 8 || page == 16 || page == 32 || page == 64 || page == 128, FQ_ERR_UNSUPPORTED,
+                 "%s: page_size=%d not in (8, 16, 32, 64, 128)", fn, page);
+    FQ_CHECK_ARG(q_dtype == FQ_F16 || q_dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: Q must be fp16 or bf16 (code %d)", fn, q_dtype);
+    FQ_CHECK_ARG(Q && O, FQ_ERR_ARG, "%s: null Q or O", fn);
+    FQ_CHECK_ARG(n_split >= 1 && n_split <= 1024, FQ_ERR_ARG, "%s: n_split=%d must be in [1, 1024]", fn, n_split);
+    const bool have_pages = bucket > 0 && P > 0 && S_kv > 0;
+    if (have_pages) {
+        FQ_CHECK_ARG(K_packed && V_packed && K_scale && K_mn && V_scale && V_mn && compact, FQ_ERR_ARG, "%s: null cache pointer", fn);
+        FQ_CHECK_ARG((int64_t)P * page >= S_kv, FQ_ERR_ARG, "%s: %d pages of %d tokens do not cover S_kv=%d", fn, P, page, S_kv);
+        FQ_CHECK_ARG(aligned(K_packed, 16) && aligned(V_packed, 16) && kp_sb % 16 == 0 && kp_sh % 16 == 0 && vp_sb % 16 == 0 && vp_sh % 16 == 0,
+                     FQ_ERR_ALIGN, "%s: packed K/V (b,h) slabs must be 16-byte aligned", fn);
+        FQ_CHECK_ARG(aligned(K_scale, 16) && aligned(K_mn, 16) && km_sb % 8 == 0 && km_sh % 8 == 0 && km_sp % 8 == 0,
+                     FQ_ERR_ALIGN, "%s: K metadata rows must be 16-byte aligned", fn);
+        FQ_CHECK_ARG(aligned(V_scale, 16) && aligned(V_mn, 16) && vm_sb % 8 == 0 && vm_sh % 8 == 0,
+                     FQ_ERR_ALIGN, "%s: V metadata (b,h) rows must be 16-byte aligned", fn);
+    }
+    if (tail_len > 0) {
+        FQ_CHECK_ARG(K_tail && V_tail, FQ_ERR_ARG, "%s: null tail pointer", fn);
+        FQ_CHECK_ARG(tail_dtype == FQ_F16 || tail_dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: tail must be fp16 or bf16", fn);
+    }
+    const int64_t qa = 8;
+    FQ_CHECK_ARG(aligned(Q, 16) && q_sb % qa == 0 && q_sh % qa == 0, FQ_ERR_ALIGN, "%s: Q rows must be 16-byte aligned", fn);
+
+    AttnParams p;
+    p.Q = Q; p.q_sb = q_sb; p.q_sh = q_sh;
+    p.K_packed = K_packed; p.kp_sb = kp_sb; p.kp_sh = kp_sh;
+    p.K_scale = static_cast<const uint16_t*>(K_scale); p.K_mn = static_cast<const uint16_t*>(K_mn);
+    p.km_sb = km_sb; p.km_sh = km_sh; p.km_sp = km_sp;
+    p.V_packed = V_packed; p.vp_sb = vp_sb; p.vp_sh = vp_sh;
+    p.V_scale = static_cast<const uint16_t*>(V_scale); p.V_mn = static_cast<const uint16_t*>(V_mn);
+    p.vm_sb = vm_sb; p.vm_sh = vm_sh;
+    p.compact = compact; p.cp_sb = cp_sb; p.cp_sh = cp_sh; p.bucket = have_pages ? bucket : 0;
+    p.K_tail = K_tail; p.V_tail = V_tail; p.tail_dtype = tail_dtype; p.tl_sb = tl_sb; p.tl_sh = tl_sh; p.tl_ss = tl_ss;
+    p.tail_len = tail_len;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S_kv = S_kv; p.P = P; p.page = page;
+    {
+        const int cpp = page >= 16 ? page / 16 : 1;
+        p.cpp_log2 = 0;
+        while ((1 << p.cpp_log2) < cpp) ++p.cpp_log2;
+    }
+    p.sm_scale = sm_scale;
+    p.O = O; p.o_sb = o_sb; p.o_sh = o_sh; p.lse = lse;
+    if (n_split > p.bucket) n_split = p.bucket > 0 ? p.bucket : 1;
+    p.n_split = n_split;
+    p.tickets = nullptr; p.partials = nullptr;
+    p.status = device_status_ptr();
+    if (p.status == nullptr) return FQ_ERR_CUDA;
+    if (n_split > 1) {
+        const size_t need = fq_sparse_decode_workspace_bytes(B, Hq, D, n_split);
+        FQ_CHECK_ARG(workspace && workspace_bytes >= need, FQ_ERR_WORKSPACE, "%s: workspace of %zu B needed, %zu given", fn, need, workspace_bytes);
+        FQ_CHECK_ARG(aligned(workspace, 16), FQ_ERR_ALIGN, "%s: workspace must be 16-byte aligned", fn);
+        p.tickets = static_cast<int*>(workspace);
+        p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + (((size_t)B * Hq * 4 + 255) & ~(size_t)255));
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc;
+    const bool tok8 = page == 8;
+#define FQ_ATT(QT)                                                              \
+    (D == 128 ? (tok8 ? launch_attn<QT, 128, 8>(p, st) : launch_attn<QT, 128, 16>(p, st)) \
+              : (tok8 ? launch_attn<QT, 64, 8>(p, st) : launch_attn<QT, 64, 16>(p, st)))
+    if (q_dtype == FQ_F16) rc = FQ_ATT(__half);
+    else rc = FQ_ATT(__nv_bfloat16);
+#undef FQ_ATT
+    if (rc != FQ_OK) return rc;
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}

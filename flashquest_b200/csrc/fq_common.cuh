@@ -1,0 +1,95 @@
+// Shared device/host helpers for the flashquest_b200 kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/flashquest_b200.h"
+
+namespace fq {
+
+// ---- error reporting (thread-local message behind fq_last_error_string) ----
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+#define FQ_CHECK_ARG(cond, code, ...)              \
+    do {                                           \
+        if (!(cond)) return fq::fail((code), __VA_ARGS__); \
+    } while (0)
+
+#define FQ_CHECK_LAUNCH(name)                                                        \
+    do {                                                                             \
+        cudaError_t e__ = cudaGetLastError();                                        \
+        if (e__ != cudaSuccess)                                                      \
+            return fq::fail(FQ_ERR_CUDA, "%s: launch failed: %s", (name), cudaGetErrorString(e__)); \
+    } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Device-side status word of the current device: kernels that wait (mbarrier) record a
+// timeout there instead of spinning forever; fq_device_status() reads and clears it.
+// Returns nullptr (with the error string set) if the address cannot be resolved.
+int* device_status_ptr();
+
+// ---- dtype traits ----
+template <typename T> struct Dt;
+template <> struct Dt<float> {
+    static constexpr int code = FQ_F32;
+    __device__ static float to_f32(float v) { return v; }
+    __device__ static float rn(float v) { return v; }  // round to T, back to fp32
+};
+template <> struct Dt<__half> {
+    static constexpr int code = FQ_F16;
+    __device__ static float to_f32(__half v) { return __half2float(v); }
+    __device__ static float rn(float v) { return __half2float(__float2half_rn(v)); }
+};
+template <> struct Dt<__nv_bfloat16> {
+    static constexpr int code = FQ_BF16;
+    __device__ static float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static float rn(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+__device__ __forceinline__ float bf16_lo(uint32_t x) { return __uint_as_float(x << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t x) { return __uint_as_float(x & 0xffff0000u); }
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// 16-byte read-only load of 8 16-bit elements / 4 fp32 elements.
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// Convert 8 consecutive elements starting at p (16-byte aligned) to fp32.  Plain (coherent)
+// loads: the quantiser reads a staging buffer that the same kernel later rewrites.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(p);
+    float4 b = *(reinterpret_cast<const float4*>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    v[0] = bf16_lo(u.x); v[1] = bf16_hi(u.x); v[2] = bf16_lo(u.y); v[3] = bf16_hi(u.y);
+    v[4] = bf16_lo(u.z); v[5] = bf16_hi(u.z); v[6] = bf16_lo(u.w); v[7] = bf16_hi(u.w);
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* p, float (&v)[8]) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+}  // namespace fq

@@ -1,0 +1,171 @@
+// Page scores read straight from the INT4 K metadata.
+//
+// score[b,hq,p] = sum_d q[d]*K_mn[p,d] + 15 * sum_d relu(q[d])*K_scale[p,d]
+//
+// HBM-bound: the only real traffic is the metadata, 2*D*2 bytes per (kv head, page), read
+// exactly once and shared by all query heads of the GQA group.  Eight lanes (a quarter
+// warp) own one page: each lane issues 16-byte loads of 8 channels, the eight lanes of a
+// page read 128 contiguous bytes per instruction and the four quarter-warps read four
+// consecutive pages, so every warp load is one contiguous 512-byte run.  Each lane keeps
+// its slice of q for all NR query heads in registers; the per-page reduction is a 3-step
+// xor shuffle inside the quarter warp.
+#include "fq_common.cuh"
+
+namespace fq {
+
+constexpr int SCORE_THREADS = 128;            // 16 pages per CTA iteration
+constexpr int SCORE_PAGES_PER_CTA = 32;       // 2 iterations per CTA
+
+// NR = query heads handled per pass (<= 4), CH = 8-channel chunks per lane (D = 64*CH, or
+// D = 32 with CH = 1 where lanes 4..7 hold no chunk).
+template <typename QT, int NR, int CH>
+__global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
+    const QT* __restrict__ Q, int64_t q_sb, int64_t q_sh,
+    const uint16_t* __restrict__ K_scale, const uint16_t* __restrict__ K_mn,
+    int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int Hq, int Hkv, int P, int D, int head_off,
+    float* __restrict__ scores, int64_t sc_sb, int64_t sc_sh) {
+    const int b = blockIdx.z, hkv = blockIdx.y;
+    const int n_rep = Hq / Hkv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int l = lane & 7, qw = lane >> 3;
+    const int n_chunks = D >> 3;
+    const int nr = min(NR, n_rep - head_off);   // heads actually present in this pass
+
+    float q[NR][CH][8];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int hq = hkv * n_rep + head_off + min(r, nr - 1);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int chunk = l + 8 * c;
+            if (chunk < n_chunks) {
+                load8<QT>(Q + b * q_sb + hq * q_sh + 8 * chunk, q[r][c]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) q[r][c][e] = 0.f;
+            }
+        }
+    }
+
+    const int p_base = blockIdx.x * SCORE_PAGES_PER_CTA;
+    const uint16_t* sc_base = K_scale + b * km_sb + hkv * km_sh;
+    const uint16_t* mn_base = K_mn + b * km_sb + hkv * km_sh;
+#pragma unroll 2
+    for (int it = 0; it < SCORE_PAGES_PER_CTA / 16; ++it) {
+        const int p = p_base + it * 16 + warp * 4 + qw;
+        const bool live = p < P;
+        float t1[NR], t2[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { t1[r] = 0.f; t2[r] = 0.f; }
+        if (live) {
+            uint4 m4[CH], s4[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                const int chunk = l + 8 * c;
+                if (chunk < n_chunks) {
+                    m4[c] = ldg16(mn_base + (int64_t)p * km_sp + 8 * chunk);
+                    s4[c] = ldg16(sc_base + (int64_t)p * km_sp + 8 * chunk);
+                } else {
+                    m4[c] = make_uint4(0, 0, 0, 0);
+                    s4[c] = make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                const uint32_t mw[4] = {m4[c].x, m4[c].y, m4[c].z, m4[c].w};
+                const uint32_t sw[4] = {s4[c].x, s4[c].y, s4[c].z, s4[c].w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float mn = (e & 1) ? bf16_hi(mw[e >> 1]) : bf16_lo(mw[e >> 1]);
+                    const float sc = (e & 1) ? bf16_hi(sw[e >> 1]) : bf16_lo(sw[e >> 1]);
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) {
+                        const float qv = q[r][c][e];
+                        t1[r] = __fmaf_rn(qv, mn, t1[r]);
+                        t2[r] = __fmaf_rn(fmaxf(qv, 0.f), sc, t2[r]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int off = 4; off >= 1; off >>= 1) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                t1[r] = __fadd_rn(t1[r], __shfl_xor_sync(0xffffffffu, t1[r], off));
+                t2[r] = __fadd_rn(t2[r], __shfl_xor_sync(0xffffffffu, t2[r], off));
+            }
+        }
+        if (live && l < nr) {
+            float v1 = t1[0], v2 = t2[0];
+#pragma unroll
+            for (int r = 1; r < NR; ++r) {
+                if (l == r) { v1 = t1[r]; v2 = t2[r]; }
+            }
+            const int hq = hkv * n_rep + head_off + l;
+            scores[b * sc_sb + hq * sc_sh + p] = __fadd_rn(v1, __fmul_rn(v2, 15.0f));
+        }
+    }
+}
+
+template <typename QT, int NR>
+static void launch_scores(int CH, dim3 grid, cudaStream_t st, const void* Q, int64_t q_sb, int64_t q_sh,
+                          const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+                          int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh) {
+#define FQ_LAUNCH_SC(CHV)                                                                              \
+    page_scores_kernel<QT, NR, CHV><<<grid, SCORE_THREADS, 0, st>>>(                                   \
+        static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),                  \
+        static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh)
+    if (CH == 1) FQ_LAUNCH_SC(1);
+    else if (CH == 2) FQ_LAUNCH_SC(2);
+    else FQ_LAUNCH_SC(4);
+#undef FQ_LAUNCH_SC
+}
+
+template <typename QT>
+static void launch_scores_nr(int nr, int CH, dim3 grid, cudaStream_t st, const void* Q, int64_t q_sb, int64_t q_sh,
+                             const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+                             int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh) {
+#define FQ_ARGS CH, grid, st, Q, q_sb, q_sh, K_scale, K_mn, km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh
+    if (nr == 1) launch_scores<QT, 1>(FQ_ARGS);
+    else if (nr == 2) launch_scores<QT, 2>(FQ_ARGS);
+    else if (nr == 3) launch_scores<QT, 3>(FQ_ARGS);
+    else launch_scores<QT, 4>(FQ_ARGS);
+#undef FQ_ARGS
+}
+
+}  // namespace fq
+
+extern "C" int fq_page_scores_int4(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int B, int Hq, int Hkv, int P, int D,
+    float* scores, int64_t sc_sb, int64_t sc_sh, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_page_scores_int4";
+    FQ_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && P >= 0, FQ_ERR_ARG, "%s: bad sizes", fn);
+    FQ_CHECK_ARG(Hq % Hkv == 0, FQ_ERR_ARG, "%s: H_q=%d must be divisible by H_kv=%d", fn, Hq, Hkv);
+    FQ_CHECK_ARG(D == 32 || D == 64 || D == 128 || D == 256, FQ_ERR_UNSUPPORTED, "%s: head_dim %d not in {32,64,128,256}", fn, D);
+    FQ_CHECK_ARG(q_dtype == FQ_F32 || q_dtype == FQ_F16 || q_dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: dtype code %d", fn, q_dtype);
+    if (P == 0) return FQ_OK;
+    FQ_CHECK_ARG(Q && K_scale && K_mn && scores, FQ_ERR_ARG, "%s: null pointer", fn);
+    const int64_t qa = q_dtype == FQ_F32 ? 4 : 8;
+    FQ_CHECK_ARG(q_sb % qa == 0 && q_sh % qa == 0 && aligned(Q, 16), FQ_ERR_ALIGN, "%s: Q rows must be 16-byte aligned", fn);
+    FQ_CHECK_ARG(km_sb % 8 == 0 && km_sh % 8 == 0 && km_sp % 8 == 0 && aligned(K_scale, 16) && aligned(K_mn, 16),
+                 FQ_ERR_ALIGN, "%s: K metadata rows must be 16-byte aligned", fn);
+    const int n_rep = Hq / Hkv;
+    const int CH = D <= 64 ? 1 : D / 64;
+    dim3 grid((unsigned)((P + SCORE_PAGES_PER_CTA - 1) / SCORE_PAGES_PER_CTA), (unsigned)Hkv, (unsigned)B);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // query heads of a group are served four at a time (one pass over the metadata per four)
+    for (int off = 0; off < n_rep; off += 4) {
+        const int nr = n_rep - off < 4 ? n_rep - off : 4;
+#define FQ_ARGS nr, CH, grid, st, Q, q_sb, q_sh, K_scale, K_mn, km_sb, km_sh, km_sp, Hq, Hkv, P, D, off, scores, sc_sb, sc_sh
+        if (q_dtype == FQ_F32) launch_scores_nr<float>(FQ_ARGS);
+        else if (q_dtype == FQ_F16) launch_scores_nr<__half>(FQ_ARGS);
+        else launch_scores_nr<__nv_bfloat16>(FQ_ARGS);
+#undef FQ_ARGS
+        FQ_CHECK_LAUNCH(fn);
+    }
+    return FQ_OK;
+}

@@ -1,0 +1,108 @@
+"""Decode-branch dispatcher for the persistent INT4 cache: score -> select -> attend.
+
+Host-side counterpart of the decode branch of make_quest_persistent_forward
+(flashquest/eager/llama_persistent_patch.py:202-245): static k_max / BUCKET_MAX computed
+once (:77-85), per-head retention from a head pattern (:214-219), page scores from the
+metadata, top-k + compact index, sparse attention over the selected pages, and the staged
+tail merged in the same softmax.  Three kernel launches per layer, no allocation per step
+(all outputs preallocated), so a whole multi-layer step can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .._lib import check, dtype_code, lib, ptr, stream_ptr
+
+
+class QuestDecodeInt4:
+    def __init__(self, cache, *, num_q_heads: int, retention: float = 0.20, num_sinks: int = 4,
+                 window_pages: int = 2, head_pattern_layer: torch.Tensor | None = None,
+                 q_dtype=torch.bfloat16, n_split: int | None = None):
+        if getattr(cache, "kv_bits", None) != 4:
+            raise NotImplementedError(f"QuestDecodeInt4 only supports kv_bits=4; got {getattr(cache, 'kv_bits', None)}")
+        if not (0.0 <= float(retention) <= 1.0):
+            raise ValueError(f"scalar retention must be in [0, 1]; got {retention}")
+        self.cache = cache
+        self.Hq = num_q_heads
+        self.Hkv = cache.num_kv_heads
+        if self.Hq % self.Hkv != 0:
+            raise ValueError(f"H_q={self.Hq} must be divisible by H_kv={self.Hkv}")
+        self.D = cache.head_dim
+        self.page = cache.page_size
+        self.B = cache.batch_size
+        self.retention = float(retention)
+        self.num_sinks = int(num_sinks)
+        self.window_pages = int(window_pages)
+        # eager/llama_persistent_patch.py:77-85
+        P_max = cache.max_seq_len // self.page
+        self.k_max_static = math.ceil(self.retention * P_max)
+        self.bucket = max(1, self.k_max_static + self.num_sinks + self.window_pages)
+        dev = cache.K_packed.device
+        self.device = dev
+        self.q_dtype = q_dtype
+        self.sm_scale = 1.0 / math.sqrt(self.D)
+        self.retention_per_q = None
+        if head_pattern_layer is not None:
+            # retrieval heads keep `retention`, streaming heads 0 (:214-219)
+            n_rep = self.Hq // self.Hkv
+            pat = head_pattern_layer.to(dev).bool().repeat_interleave(n_rep)
+            self.retention_per_q = torch.where(pat, torch.full((self.Hq,), self.retention, device=dev),
+                                               torch.zeros(self.Hq, device=dev)).float().contiguous()
+        L = cache.num_layers
+        self.scores = torch.empty(L, self.B, self.Hq, max(P_max, 1), dtype=torch.float32, device=dev)
+        self.compact = torch.empty(L, self.B, self.Hq, self.bucket, dtype=torch.int32, device=dev)
+        self.O = torch.empty(L, self.B, self.Hq, self.D, dtype=q_dtype, device=dev)
+        self.lse = torch.empty(L, self.B, self.Hq, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            self.n_split = n_split or lib().fq_sparse_decode_default_splits(self.B, self.Hq, self.bucket, self.page)
+            nbytes = lib().fq_sparse_decode_workspace_bytes(self.B, self.Hq, self.D, self.n_split)
+        # one split-K workspace per layer: launches of different layers may overlap in a graph
+        self.ws_bytes = (nbytes + 255) // 256 * 256
+        self.workspace = torch.zeros(L, max(self.ws_bytes, 256), dtype=torch.uint8, device=dev)
+        self.launches = 0
+
+    def attend(self, q: torch.Tensor, layer_idx: int):
+        """q (B,H_q,1,D) or (B,H_q,D), the cache's dtype family (fp16/bf16).  Returns views
+        (O (B,H_q,1,D), lse (B,H_q,1)) of preallocated per-layer buffers."""
+        c = self.cache
+        seen = c._seen_tokens[layer_idx]
+        page = self.page
+        partial_len = seen % page
+        completed = seen - partial_len
+        P = completed // page
+        q3 = q.reshape(self.B, self.Hq, self.D)
+        li = layer_idx
+        L = lib()
+        st = stream_ptr(self.device)
+        scores, compact = self.scores[li], self.compact[li]
+        Ks, Km = c.K_scale[li], c.K_mn[li]
+        if P > 0:
+            check(L.fq_page_scores_int4(
+                ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1),
+                ptr(Ks), ptr(Km), Ks.stride(0), Ks.stride(1), Ks.stride(2),
+                self.B, self.Hq, self.Hkv, P, self.D, ptr(scores), scores.stride(0), scores.stride(1), st))
+            check(L.fq_select_pages(
+                ptr(scores), scores.stride(0), scores.stride(1), self.B, self.Hq, P,
+                ptr(self.retention_per_q), self.retention, min(self.k_max_static, P), self.num_sinks,
+                self.window_pages, None, 0, 0, ptr(compact), compact.stride(0), compact.stride(1), self.bucket,
+                None, st))
+            self.launches += 2
+        Kp, Vp, Vs, Vm = c.K_packed[li], c.V_packed[li], c.V_scale[li], c.V_mn[li]
+        Kt, Vt = c.K_partial[li], c.V_partial[li]
+        O, lse = self.O[li], self.lse[li]
+        check(L.fq_sparse_decode_int4(
+            ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1),
+            ptr(Kp), Kp.stride(0), Kp.stride(1),
+            ptr(Ks), ptr(Km), Ks.stride(0), Ks.stride(1), Ks.stride(2),
+            ptr(Vp), Vp.stride(0), Vp.stride(1),
+            ptr(Vs), ptr(Vm), Vs.stride(0), Vs.stride(1),
+            ptr(compact), compact.stride(0), compact.stride(1), self.bucket if P > 0 else 0,
+            ptr(Kt) if partial_len else None, ptr(Vt) if partial_len else None, dtype_code(Kt),
+            Kt.stride(0), Kt.stride(1), Kt.stride(2), partial_len,
+            self.B, self.Hq, self.Hkv, completed, P, self.D, page, self.sm_scale,
+            ptr(O), O.stride(0), O.stride(1), ptr(lse),
+            ptr(self.workspace[li]), self.workspace.shape[1], self.n_split, st))
+        self.launches += 1
+        return O.unsqueeze(2), lse.unsqueeze(2)

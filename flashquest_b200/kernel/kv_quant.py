@@ -1,0 +1,121 @@
+"""INT4 KV quantisation primitives — CUDA counterparts of flashquest/kernel/kv_quant.py.
+
+Same names, argument order, return tuples and error messages as the reference functions
+(kernel/kv_quant.py:152-215); results are bit-identical to the reference's CPU path.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from .._lib import check, dtype_code, inner_contiguous, lib, ptr, require_cuda, stream_ptr
+
+
+def _strides3(t):
+    """(b, h, row) element strides of a (B, H, rows, inner) or (B, H, rows) tensor."""
+    return t.stride(0), t.stride(1), t.stride(2)
+
+
+def quantize_kv_int4_into(K_new, V_new, page_size, n_quant, *, K_packed=None, K_scale=None, K_mn=None,
+                          V_packed=None, V_scale=None, V_mn=None, K_head=None, V_head=None, n_head=0,
+                          stage_K=None, stage_V=None):
+    """One launch of fq_quantize_kv_int4: quantise the first n_quant tokens of the stream
+    head[:n_head] ++ new, writing into the given (possibly strided) output views, and copy
+    the left-over tokens into the staging views.  This is the page-flush step of
+    PersistentInt4KVCache.update_quantized (cache/persistent_int4.py:94-130) as one kernel."""
+    ref = K_new if K_new is not None else V_new
+    require_cuda(ref)
+    B, H, n_new, D = ref.shape
+    if D % 2 != 0:
+        raise ValueError(f"quantize_k_int4 requires even head_dim; got {D}")
+    K_new = inner_contiguous(K_new) if K_new is not None else None
+    V_new = inner_contiguous(V_new) if V_new is not None else None
+    src = K_new if K_new is not None else V_new
+    if K_new is not None and V_new is not None and _strides3(K_new) != _strides3(V_new):
+        V_new = V_new.contiguous()
+        K_new = K_new.contiguous()
+        src = K_new
+    hd = K_head if K_head is not None else V_head
+    pk = K_packed if K_packed is not None else V_packed
+    st = stage_K if stage_K is not None else stage_V
+    z3 = (0, 0, 0)
+    hs = _strides3(hd) if hd is not None else z3
+    ns = _strides3(src)
+    ps = _strides3(pk) if pk is not None else z3
+    ks = _strides3(K_scale) if K_scale is not None else z3
+    vs = _strides3(V_scale) if V_scale is not None else z3
+    ss = _strides3(st) if st is not None else z3
+    with torch.cuda.device(ref.device):
+        check(lib().fq_quantize_kv_int4(
+            ptr(K_head), ptr(V_head), *hs, int(n_head),
+            ptr(K_new), ptr(V_new), *ns, int(n_new),
+            dtype_code(ref), B, H, D, int(page_size), int(n_quant),
+            ptr(K_packed), ptr(V_packed), *ps,
+            ptr(K_scale), ptr(K_mn), *ks,
+            ptr(V_scale), ptr(V_mn), *vs,
+            ptr(stage_K), ptr(stage_V), *ss,
+            stream_ptr(ref.device)))
+
+
+def quantize_k_int4(K: torch.Tensor, page_size: int):
+    """KIVI-style asymmetric INT4 K quant, packed 2-per-byte along head_dim
+    (kernel/kv_quant.py:152).
+
+    Returns (K_packed (B,H,S,D//2) uint8, scale (B,H,num_pages,D) bf16, mn (B,H,num_pages,D) bf16).
+    """
+    B, H, S, D = K.shape
+    if D % 2 != 0:
+        raise ValueError(f"quantize_k_int4 requires even head_dim; got {D}")
+    require_cuda(K)
+    P = (S + page_size - 1) // page_size
+    K_packed = torch.empty(B, H, S, D // 2, dtype=torch.uint8, device=K.device)
+    scale = torch.empty(B, H, P, D, dtype=torch.bfloat16, device=K.device)
+    mn = torch.empty(B, H, P, D, dtype=torch.bfloat16, device=K.device)
+    if S > 0:
+        quantize_kv_int4_into(K, None, page_size, S, K_packed=K_packed, K_scale=scale, K_mn=mn)
+    return K_packed, scale, mn
+
+
+def quantize_v_int4(V: torch.Tensor):
+    """Per-token V quant, packed 2-per-byte along head_dim (kernel/kv_quant.py:189).
+
+    Returns (V_packed (B,H,S,D//2) uint8, scale (B,H,S,1) bf16, mn (B,H,S,1) bf16).
+    """
+    if V.shape[-1] % 2 != 0:
+        raise ValueError(f"quantize_v_int4 requires even head_dim; got {V.shape[-1]}")
+    require_cuda(V)
+    B, H, S, D = V.shape
+    V_packed = torch.empty(B, H, S, D // 2, dtype=torch.uint8, device=V.device)
+    scale = torch.empty(B, H, S, 1, dtype=torch.bfloat16, device=V.device)
+    mn = torch.empty(B, H, S, 1, dtype=torch.bfloat16, device=V.device)
+    if S > 0:
+        # page size only groups tokens into warps here; V metadata is per token
+        quantize_kv_int4_into(None, V, 16, S, V_packed=V_packed, V_scale=scale, V_mn=mn)
+    return V_packed, scale, mn
+
+
+def _dequantize_int4(packed, scale, mn, page_size, per_page):
+    require_cuda(packed, scale, mn)
+    B, H, S, Dp = packed.shape
+    D = Dp * 2
+    packed = inner_contiguous(packed)
+    scale, mn = inner_contiguous(scale), inner_contiguous(mn)
+    if _strides3(scale) != _strides3(mn):
+        scale, mn = scale.contiguous(), mn.contiguous()
+    out = torch.empty(B, H, S, D, dtype=torch.bfloat16, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(lib().fq_dequantize_int4(
+            ptr(packed), *_strides3(packed), ptr(scale), ptr(mn), *_strides3(scale),
+            1 if per_page else 0, B, H, S, D, int(page_size),
+            ptr(out), *_strides3(out), stream_ptr(packed.device)))
+    return out
+
+
+def dequantize_k_int4(K_packed, scale, mn, page_size: int) -> torch.Tensor:
+    """Inverse of quantize_k_int4 (kernel/kv_quant.py:174).  Returns bf16."""
+    return _dequantize_int4(K_packed, scale, mn, page_size, True)
+
+
+def dequantize_v_int4(V_packed, scale, mn) -> torch.Tensor:
+    """Inverse of quantize_v_int4 (kernel/kv_quant.py:208).  Returns bf16."""
+    return _dequantize_int4(V_packed, scale, mn, 1, False)

@@ -1,0 +1,176 @@
+/*
+ * flashquest_b200 — C ABI of the B200 (sm_100a) sparse-decode kernels.
+ *
+ * The reference (flashquest) is pure Python: its "operator interface" is a set of
+ * Python call signatures.  Every entry point below replaces one of those functions (the
+ * reference file:line is cited beside each) and is what a ctypes/cffi binding on the
+ * reference side would call.  Conventions:
+ *   - all pointers are DEVICE pointers unless stated; nothing here allocates or frees
+ *     device memory, and nothing synchronises the stream;
+ *   - tensors are described by pointer + element strides of the outer dimensions; the
+ *     innermost dimension is always contiguous;
+ *   - dtype codes: FQ_F32 / FQ_F16 / FQ_BF16;
+ *   - `stream` is a cudaStream_t passed as void*;
+ *   - return value: 0 on success, a negative FQ_ERR_* otherwise; the message of the last
+ *     failure on the calling thread is returned by fq_last_error_string().  Invalid
+ *     arguments are rejected on the host; no kernel traps or asserts on the device.
+ */
+#ifndef FLASHQUEST_B200_H
+#define FLASHQUEST_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FQ_F32 0
+#define FQ_F16 1
+#define FQ_BF16 2
+
+#define FQ_OK 0
+#define FQ_ERR_ARG (-1)         /* bad shape / size / null pointer */
+#define FQ_ERR_DTYPE (-2)       /* unsupported dtype code */
+#define FQ_ERR_ALIGN (-3)       /* pointer or stride alignment not met */
+#define FQ_ERR_UNSUPPORTED (-4) /* head_dim / page_size outside the built set */
+#define FQ_ERR_CUDA (-5)        /* CUDA runtime error at launch */
+#define FQ_ERR_WORKSPACE (-6)   /* workspace too small */
+#define FQ_ERR_TIMEOUT (-7)     /* a bounded device-side wait gave up (see fq_device_status) */
+
+const char* fq_last_error_string(void);
+const char* fq_version(void);
+
+/* Reads and clears the device-side status word of the current device (synchronises the
+ * device).  0 = no kernel reported a problem; FQ_ERR_TIMEOUT = a bounded wait on an
+ * asynchronous copy ran out and the kernel returned early. */
+int fq_device_status(void);
+
+/* ------------------------------------------------------------------------------------
+ * INT4 KV quantisation ("pack on append").
+ * Replaces quantize_k_int4 (kernel/kv_quant.py:152-171), quantize_v_int4 (:189-205) and
+ * the page-flush part of PersistentInt4KVCache.update_quantized
+ * (cache/persistent_int4.py:94-130), bit-exactly.
+ *
+ * The token stream of every (b,h) is  head[0:n_head] ++ new[0:n_new]  (the staged partial
+ * page followed by the new tokens; n_head = 0 for a plain quantize call).  Its first
+ * n_quant tokens are quantised: K per page and channel (scale,min in the INPUT dtype, codes
+ * from fp32 division, round-half-even), V per token in fp32; two codes per byte, low nibble =
+ * even channel.  A ragged last page (n_quant % page != 0) takes min/max over its valid
+ * tokens only.  Outputs are written at token 0 / page 0 of the given pointers — pass
+ * pointers already offset into the cache.  Stream token t >= n_quant is left in staging row
+ * t - n_quant of stage_K/stage_V (unless those pointers are NULL); the head may BE the
+ * staging buffer: with n_quant == 0 its tokens stay where they are and the new ones follow.
+ * K or V (and their outputs) may be NULL to quantise only the other one.
+ *
+ *   K_head,V_head : (B,H,n_head,D) dtype, strides hd_sb,hd_sh,hd_ss (elements)
+ *   K_new, V_new  : (B,H,n_new,D)  dtype, strides nw_sb,nw_sh,nw_ss
+ *   K_packed,V_packed : (B,H,n_quant,D/2) u8, strides pk_sb,pk_sh,pk_ss (bytes)
+ *   K_scale,K_mn  : (B,H,ceil(n_quant/page),D) bf16, strides km_sb,km_sh,km_sp
+ *   V_scale,V_mn  : (B,H,n_quant) bf16, strides vm_sb,vm_sh,vm_ss
+ *   stage_K,stage_V : (B,H,page,D) dtype, strides st_sb,st_sh,st_ss
+ * D must be 8,16,...,256 with D/8 a power of two; rows 16-byte aligned.
+ */
+int fq_quantize_kv_int4(
+    const void* K_head, const void* V_head, int64_t hd_sb, int64_t hd_sh, int64_t hd_ss, int n_head,
+    const void* K_new, const void* V_new, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    int dtype, int B, int H, int D, int page, int n_quant,
+    uint8_t* K_packed, uint8_t* V_packed, int64_t pk_sb, int64_t pk_sh, int64_t pk_ss,
+    void* K_scale, void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    void* V_scale, void* V_mn, int64_t vm_sb, int64_t vm_sh, int64_t vm_ss,
+    void* stage_K, void* stage_V, int64_t st_sb, int64_t st_sh, int64_t st_ss,
+    void* stream);
+
+/* dequantize_k_int4 / dequantize_v_int4 (kernel/kv_quant.py:174-186, :208-215):
+ * out = bf16(code*scale + mn), used by the prefill branch
+ * (eager/llama_persistent_patch.py:196-201).  per_page != 0: metadata (B,H,P,D) (K);
+ * else (B,H,S) (V).  out (B,H,S,D) bf16 with strides o_sb,o_sh,o_ss. */
+int fq_dequantize_int4(
+    const uint8_t* packed, int64_t pk_sb, int64_t pk_sh, int64_t pk_ss,
+    const void* scale, const void* mn, int64_t m_sb, int64_t m_sh, int64_t m_s2,
+    int per_page, int B, int H, int S, int D, int page,
+    void* out, int64_t o_sb, int64_t o_sh, int64_t o_ss, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Page scores from INT4 metadata.
+ * Replaces page_scores_int4_fast (eager/criticality.py:128-163) for S_q == 1:
+ *   score[b,hq,p] = sum_d q*K_mn[p,d] + 15 * sum_d relu(q)*K_scale[p,d]   (fp32)
+ * One pass over the metadata serves all query heads of a KV group.  Summation order is
+ * fixed, so results are reproducible bit for bit: channels are cut into chunks of 8; lane l
+ * (0..7) owns chunks l, l+8, ... and accumulates them in ascending order with fused
+ * multiply-adds from zero; the eight lane sums combine as ((p0+p4)+(p2+p6))+((p1+p5)+(p3+p7));
+ * the product by 15 and the final add are separate roundings.
+ *   Q (B,Hq,D) dtype q_dtype strides q_sb,q_sh; K_scale,K_mn (B,Hkv,P,D) bf16 strides
+ *   km_sb,km_sh,km_sp; scores (B,Hq,P) fp32 strides sc_sb,sc_sh.  D in {32,64,128,256}.
+ */
+int fq_page_scores_int4(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int B, int Hq, int Hkv, int P, int D,
+    float* scores, int64_t sc_sb, int64_t sc_sh, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Top-k page selection with static k_max, sinks and window; optional compact index.
+ * Replaces select_pages_vectorized (eager/selection.py:65-126) and
+ * build_compact_selection (:129-164).
+ *   k_h = clamp(ceil(fp32(r_h) * P), 0, P) with r_h = retention_per_head[h] (device fp32,
+ *   length H) or the scalar `retention` when that pointer is NULL; the k_max largest
+ *   scores are found and the first min(k_h,k_max) kept; pages [0,min(sinks,P)) and
+ *   [P-min(window,P),P) are forced on.  Ties between equal scores: the lower page index
+ *   wins (torch.topk leaves this unspecified).
+ * Outputs (each optional, NULL to skip):
+ *   mask    (B,H,P) u8 0/1, strides mk_sb,mk_sh
+ *   compact (B,H,bucket) int32: selected ids in DESCENDING order, truncated to bucket,
+ *           padded with -1 (exactly build_compact_selection's output), strides cp_sb,cp_sh
+ *   count   (B,H) int32: number of selected pages (contiguous)
+ */
+int fq_select_pages(
+    const float* scores, int64_t sc_sb, int64_t sc_sh, int B, int H, int P,
+    const float* retention_per_head, float retention, int k_max, int sinks, int window,
+    uint8_t* mask, int64_t mk_sb, int64_t mk_sh,
+    int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    int32_t* count, void* stream);
+
+/* build_compact_selection (eager/selection.py:129-164) on an existing mask.
+ * mask (rows,P) u8 with row stride mk_sr; compact (rows,bucket) int32 with stride cp_sr. */
+int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
+                     int32_t* compact, int64_t cp_sr, int bucket, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Sparse decode attention over selected packed INT4 pages (GQA, split-K, LSE merge).
+ * Replaces flash_attn_sparse_int4_fwd_compact (kernel/sparse_int4_fwd_compact.py:153-244)
+ * and, with a compact list built from the mask, flash_attn_sparse_int4_fwd
+ * (kernel/sparse_int4_fwd.py:160-248); with a tail it also covers
+ * _bf16_dense_attn_with_lse + _merge_two_attentions
+ * (eager/llama_persistent_patch.py:30-61) in the same softmax.
+ *
+ *   Q (B,Hq,D) q_dtype (F16|BF16), strides q_sb,q_sh;  O same dtype, strides o_sb,o_sh
+ *   K_packed,V_packed (B,Hkv,S_kv,D/2) u8, strides in bytes; token stride must be D/2
+ *   K_scale,K_mn (B,Hkv,P,D) bf16;  V_scale,V_mn (B,Hkv,S_kv) bf16 (token stride 1)
+ *   compact (B,Hq,bucket) int32 page ids; ids < 0 or >= P are skipped (order irrelevant)
+ *   K_tail,V_tail (B,Hkv,tail_len,D) tail_dtype (F16|BF16) or NULL with tail_len = 0
+ *   lse (B,Hq) fp32 in nats or NULL.  Nothing attended => O = 0, lse = -inf.
+ *   n_split: CTAs per (b,hq) row (1..1024); with n_split > 1 `workspace` must hold
+ *   fq_sparse_decode_workspace_bytes(...) bytes whose first B*Hq*4 bytes were zeroed once
+ *   (the kernel leaves them zero again); concurrent calls must not share a workspace.
+ * D in {64,128}; page in {8,16,32,64,128}.  Page rows must be 16-byte aligned.
+ */
+size_t fq_sparse_decode_workspace_bytes(int B, int Hq, int D, int n_split);
+int fq_sparse_decode_default_splits(int B, int Hq, int bucket, int page);
+int fq_sparse_decode_int4(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss,
+    int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, float* lse,
+    void* workspace, size_t workspace_bytes, int n_split, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHQUEST_B200_H */
