@@ -375,8 +375,7 @@ def run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier):
         dk.copy_(hk[i], non_blocking=True)
         dv.copy_(hv[i], non_blocking=True)
         for li in range(Lr):
-            cache.update_quantized(dk[li], dv[li], li)
-            step.attend(dq[li], li)
+            step.step(dk[li], dv[li], dq[li], li)       # append + score + select + attend, one call
         out_host.copy_(step.O, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -398,7 +397,7 @@ def run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier):
     h2d = hq[0].numel() * 2 + hk[0].numel() * 2 + hv[0].numel() * 2
     return {"value": world * B * 1e3 / (ms / args.steps), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": ms / args.steps,
-            "path": "pinned host q/k/v -> PersistentInt4KVCache.update_quantized + QuestDecodeInt4.attend per layer -> host O"}
+            "path": "pinned host q/k/v -> QuestDecodeInt4.step (fq_decode_layer_int4: append+score+select+attend) per layer -> host O"}
 
 
 def main():

@@ -38,6 +38,26 @@ _PROTOTYPES = {
                                   I, I, I, I, I, I, I, F, P, L, L, P, P, Z, I, P]),
 }
 
+
+
+class Int4CacheDesc(ctypes.Structure):
+    """struct fq_int4_cache (include/flashquest_b200.h)."""
+    _fields_ = [("K_packed", P), ("V_packed", P), ("pk_sl", L), ("pk_sb", L), ("pk_sh", L), ("pk_ss", L),
+                ("K_scale", P), ("K_mn", P), ("km_sl", L), ("km_sb", L), ("km_sh", L), ("km_sp", L),
+                ("V_scale", P), ("V_mn", P), ("vm_sl", L), ("vm_sb", L), ("vm_sh", L),
+                ("K_partial", P), ("V_partial", P), ("pt_sl", L), ("pt_sb", L), ("pt_sh", L), ("pt_ss", L),
+                ("kv_dtype", I), ("L", I), ("B", I), ("Hkv", I), ("D", I), ("page", I), ("max_seq_len", I)]
+
+
+class DecodeParams(ctypes.Structure):
+    """struct fq_decode_params (include/flashquest_b200.h)."""
+    _fields_ = [("Hq", I), ("retention_per_head", P), ("retention", F), ("k_max_static", I), ("sinks", I),
+                ("window", I), ("bucket", I), ("sm_scale", F), ("n_split", I)]
+
+
+_PROTOTYPES["fq_decode_layer_int4"] = (I, [ctypes.POINTER(Int4CacheDesc), I, I, P, P, L, L, L, I, P, I, L, L,
+                                          ctypes.POINTER(DecodeParams), P, P, P, P, P, Z, P])
+
 # entry points added by later sources register themselves here (name -> (restype, argtypes))
 EXTRA_PROTOTYPES: dict = {}
 

@@ -2,16 +2,21 @@
 //
 // Work unit = one chunk of TOK tokens of one selected page (TOK = 16, or 8 for page 8):
 //   K payload TOK*D/2 B, V payload TOK*D/2 B, K scale + K min rows 2*D*2 B, V scale + V min
-//   2*TOK*2 B  (2624 B at D = 128, TOK = 16).
+//   2*TOK*2 B  (2624 B at D = 128, TOK = 16).  The two payloads (1 KB each) are staged in
+//   shared memory by bulk copies; the small metadata pieces go straight to registers with
+//   ordinary 16-byte / 4-byte loads issued at the same moment (a bulk copy per 32-byte piece
+//   costs the copy engine as much as a 1 KB one).
 // Grid = (n_split, H_q, B); a CTA walks a contiguous slice of the row's compact page list.
-// Inside a CTA every QUARTER WARP (8 lanes) owns one unit at a time, so a 4-warp CTA has 16
-// units in flight.  Units are staged into shared memory with bulk asynchronous copies
-// (cp.async.bulk + mbarrier complete_tx); the six copies of a unit are issued by six lanes
-// of the quarter warp that will consume it.  Staging is single-buffered per warp (42 KB per
-// CTA): four CTAs = 16 warps stay resident per SM, and the copy latency of one warp is
-// covered by the arithmetic of the other fifteen rather than by a deeper per-warp pipeline,
-// because the arithmetic (ALU-pipe nibble extraction) needs the occupancy anyway.  By
-// default a CTA gets one 16-unit iteration, so the hardware CTA scheduler balances the load.
+// A CTA has ATT_WARPS consumer warps and one producer warp.  Every QUARTER WARP (8 lanes) of
+// a consumer warp owns one unit at a time, so a CTA works on 4*ATT_WARPS units per iteration.
+// The producer warp stages the payloads into shared memory with bulk asynchronous copies
+// (cp.async.bulk + mbarrier complete_tx), ATT_STAGES iterations deep: the copy engine back-
+// pressures the issuing thread for as long as the transfer lasts, so the issue must not sit
+// in the warps that do the arithmetic.  Per (consumer warp, stage) there is a "full" barrier
+// (the producer's expect_tx arrivals + the copies' bytes) and an "empty" barrier (the
+// consumer warp's release).  The launch is sized so that all CTAs are resident at once; every
+// byte of the selection is then requested in the first microsecond and streams in at HBM
+// speed while the consumers work through the units in arrival order.
 //
 // Arithmetic (CUDA cores, fp32 accumulation, no tensor cores: M is 1):
 //   q.k = sum_d (q_d*sc_d)*code_d + sum_d q_d*mn_d      (scale folded into q once per page)
@@ -29,22 +34,32 @@
 // Split-K: each CTA writes (m, l, acc[D]) to the workspace and takes a ticket; the CTA that
 // draws the last ticket of its row merges the partials in split order and writes O / LSE.
 // No CTA ever waits for another one.
+#include <type_traits>
+
 #include "fq_common.cuh"
 
 namespace fq {
 
 #ifndef FQ_ATT_WARPS
-#define FQ_ATT_WARPS 4
+#define FQ_ATT_WARPS 6      // consumer warps per CTA (one more warp issues the copies)
 #endif
 #ifndef FQ_ATT_STAGES
-#define FQ_ATT_STAGES 1
+#define FQ_ATT_STAGES 2
+#endif
+#ifndef FQ_ATT_CTAS_PER_SM
+#define FQ_ATT_CTAS_PER_SM 2
 #endif
 constexpr int ATT_WARPS = FQ_ATT_WARPS;
-constexpr int ATT_THREADS = ATT_WARPS * 32;
+constexpr int ATT_THREADS = (ATT_WARPS + 1) * 32;   // consumers + the producer warp
 constexpr int ATT_STAGES = FQ_ATT_STAGES;
+constexpr int ATT_CTAS_PER_SM = FQ_ATT_CTAS_PER_SM;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
-constexpr unsigned WAIT_SPIN_LIMIT = 1u << 24;   // bounded wait on a stage; then give up
+#ifdef FQ_DEBUG_WAIT
+constexpr unsigned WAIT_SPIN_LIMIT = 1u << 16;
+#else
+constexpr unsigned WAIT_SPIN_LIMIT = 1u << 24;
+#endif   // bounded wait on a stage; then give up
 
 struct AttnParams {
     const void* Q; int64_t q_sb, q_sh;
@@ -95,19 +110,41 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+#ifdef FQ_DEBUG_WAIT
+__device__ int g_dbg[32];
+#define FQ_PROG(v) do { if (lane == 0) s_prog[warp] = (v); } while (0)
+#else
+#define FQ_PROG(v) do {} while (0)
+#endif
+#ifdef FQ_ATT_TRACE
+// Debug build only: per-CTA phase timestamps (globaltimer, ns) for timeline analysis.
+__device__ unsigned long long g_trace[4096 * 8];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define FQ_TRACE(slot)                                                                        \
+    do {                                                                                      \
+        if (threadIdx.x == 0) {                                                               \
+            const int cta__ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); \
+            if (cta__ < 4096) g_trace[cta__ * 8 + (slot)] = gtime();                          \
+        }                                                                                     \
+    } while (0)
+#else
+#define FQ_TRACE(slot) do {} while (0)
+#endif
+
 // ---------------------------------------------------------------- unit layout in shared memory
 template <int D, int TOK>
 struct UnitLayout {
     static constexpr int ROW = D / 2;               // packed bytes per token
     static constexpr int K_OFF = 0;
     static constexpr int V_OFF = TOK * ROW;
-    static constexpr int KS_OFF = 2 * TOK * ROW;    // K scale row (D bf16)
-    static constexpr int KM_OFF = KS_OFF + 2 * D;   // K min row
-    static constexpr int VS_OFF = KM_OFF + 2 * D;   // V scale (TOK bf16)
-    static constexpr int VM_OFF = VS_OFF + 2 * TOK;
-    static constexpr int BYTES = VM_OFF + 2 * TOK;  // 2624 (D=128,TOK=16): = 64 mod 128, so two
-                                                    // quarter warps hit disjoint bank halves
-    static constexpr int STRIDE = (BYTES + 15) & ~15;
+    static constexpr int BYTES = 2 * TOK * ROW;
+    // stride = 64 mod 128 bytes, so the four quarter warps of a warp hit disjoint bank halves
+    // pairwise (two wavefronts for a 256-byte warp read, the minimum)
+    static constexpr int STRIDE = (BYTES % 128 == 0) ? BYTES + 64 : ((BYTES + 15) & ~15);
 };
 
 // Multiplier pre-scale for channel j (j mod 8 = nibble index) so that
@@ -121,6 +158,17 @@ __device__ __forceinline__ float nib_unscale(int k) { return k <= 5 ? pow2i(49 -
 
 // eight codes of one 32-bit word as fp32 operands (see the header comment)
 __device__ __forceinline__ void nib8(uint32_t w, float (&f)[8]) {
+#ifdef FQ_EXPERIMENT_NORMALS
+    f[0] = __uint_as_float((w & 0x0000000fu) | 0x3f800000u);
+    f[1] = __uint_as_float((w & 0x000000f0u) | 0x3f800000u);
+    f[2] = __uint_as_float((w & 0x00000f00u) | 0x3f800000u);
+    f[3] = __uint_as_float((w & 0x0000f000u) | 0x3f800000u);
+    f[4] = __uint_as_float((w & 0x000f0000u) | 0x3f800000u);
+    f[5] = __uint_as_float((w & 0x00700000u) | 0x3f800000u);
+    f[6] = __uint_as_float((w >> 24) | 0x3f800000u);
+    f[7] = __uint_as_float((w >> 28) | 0x3f800000u);
+    return;
+#endif
     f[0] = __uint_as_float(w & 0x0000000fu);
     f[1] = __uint_as_float(w & 0x000000f0u);
     f[2] = __uint_as_float(w & 0x00000f00u);
@@ -182,28 +230,53 @@ template <typename T>
 __device__ __forceinline__ float ld_as_f32(const void* p, int64_t i) { return Dt<T>::to_f32(static_cast<const T*>(p)[i]); }
 
 // ---------------------------------------------------------------- the kernel
+template <int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (N > 0) {
+        static_for<N - 1>(f);
+        f(std::integral_constant<int, N - 1>{});
+    }
+}
+
+// What a quarter warp knows about a unit besides its payload.
+template <int DPL, int TPL>
+struct UnitCtx {
+    int page_id, tok0, n_tok;             // page_id < 0: nothing to do in this slot
+    uint4 ks[DPL / 8], km[DPL / 8];       // this lane's DPL channels of the K scale / min rows (bf16)
+    uint32_t vs_raw, vm_raw;              // V scale / min of this lane's TPL tokens, bf16 bits (token i in half i)
+};
+
 template <typename QT, int D, int TOK>
-__global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnParams p) {
+__global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_int4_kernel(AttnParams p) {
     using L = UnitLayout<D, TOK>;
     constexpr int DPL = D / 8;        // channels per lane
     constexpr int WPL = DPL / 8;      // 32-bit words per lane per token
     constexpr int TPL = TOK / 8;      // tokens per lane after the reduction
     constexpr int NSTATE = ATT_WARPS * 4 + ATT_WARPS;   // quarter-warp states + per-warp tail states
+    constexpr int NBARS = 2 * ATT_WARPS * ATT_STAGES;
 
     extern __shared__ __align__(128) unsigned char smem[];
-    // [stages][warps][4 units] staging | mbarriers | pv broadcast | merge area (aliases staging)
+    // [stages][warps][4 units] staging | mbarriers | pv broadcast | states; the merge area
+    // aliases the staging area once the main loop is over
     unsigned char* stage_base = smem;
     constexpr int STAGING_BYTES = ATT_STAGES * ATT_WARPS * 4 * L::STRIDE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGING_BYTES);            // [warps][stages]
-    float* pv_bcast = reinterpret_cast<float*>(smem + STAGING_BYTES + ATT_WARPS * ATT_STAGES * 8);  // [warps*4][TOK]
-    float* st_m = pv_bcast + ATT_WARPS * 4 * TOK;   // [NSTATE]
+    uint64_t* full_bars = reinterpret_cast<uint64_t*>(smem + STAGING_BYTES);       // [warps][stages]
+    uint64_t* empty_bars = full_bars + ATT_WARPS * ATT_STAGES;                     // [warps][stages]
+    float* pv_bcast = reinterpret_cast<float*>(smem + STAGING_BYTES + NBARS * 8);  // [warps*4][TOK]
+    float* st_m = pv_bcast + ATT_WARPS * 4 * TOK;   // [NSTATE] running max, then merge weight
     float* st_l = st_m + NSTATE;                    // [NSTATE]
-    float* st_acc = reinterpret_cast<float*>(smem);  // [NSTATE][D], reuses the staging area after the loop
+    float* st_acc = reinterpret_cast<float*>(smem);  // [NSTATE][D]
 
     const int split = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
     const int n_rep = p.Hq / p.Hkv, hkv = hq / n_rep;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, qw = lane >> 3, l = lane & 7;
     const unsigned qmask = 0xffu << (8 * qw);
+    const bool is_producer = warp == ATT_WARPS;
+#ifdef FQ_DEBUG_WAIT
+    __shared__ volatile int s_prog[ATT_WARPS + 1];
+    if (lane == 0) s_prog[warp] = -1;
+#endif
+    FQ_TRACE(0);
 
     // ---- slice of the compact list owned by this CTA, in units ----
     const int cpp_log2 = p.cpp_log2;                    // log2(chunks (units) per page)
@@ -215,13 +288,14 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
     const int n_iter = (n_units + units_per_iter - 1) / units_per_iter;
     const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
 
-    uint64_t* my_bars = bars + warp * ATT_STAGES;
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < ATT_STAGES; ++s) mbar_init(&my_bars[s], 4);   // one arrival per quarter warp
+    if (tid == 0) {
+        for (int i = 0; i < ATT_WARPS * ATT_STAGES; ++i) {
+            mbar_init(&full_bars[i], 4);    // one arrival per unit of the warp
+            mbar_init(&empty_bars[i], 1);   // the consumer warp's release
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncwarp();
+    __syncthreads();
 
     const uint8_t* Kp = p.K_packed + b * p.kp_sb + hkv * p.kp_sh;
     const uint8_t* Vp = p.V_packed + b * p.vp_sb + hkv * p.vp_sh;
@@ -230,9 +304,9 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
     const uint16_t* Vs = p.V_scale + b * p.vm_sb + hkv * p.vm_sh;
     const uint16_t* Vm = p.V_mn + b * p.vm_sb + hkv * p.vm_sh;
 
-    // Unit handled by this quarter warp in iteration `it`: page id, first token, valid tokens.
-    auto unit_of = [&](int it, int& page_id, int& tok0, int& n_tok) {
-        const int u = it * units_per_iter + warp * 4 + qw;
+    // unit uu (0..units_per_iter) of iteration it -> page id (or -1), first token, valid tokens
+    auto locate = [&](int it, int uu, int& page_id, int& tok0, int& n_tok) {
+        const int u = it * units_per_iter + uu;
         page_id = -1; tok0 = 0; n_tok = 0;
         if (u < n_units) {
             const int pg = __ldg(list + slot_begin + (u >> cpp_log2));
@@ -244,189 +318,256 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
         }
     };
 
-    unsigned char* my_unit = stage_base + (warp * 4 + qw) * L::STRIDE;
-    uint64_t* bar = &my_bars[0];
-    auto issue = [&](int page_id, int tok0, int n_tok) {
-        if (page_id < 0) {
-            if (l == 0) mbar_arrive(bar);
-            return;
-        }
-        const unsigned payload = (unsigned)n_tok * L::ROW;
-        const bool full = n_tok == TOK;
-        if (l == 0) {
-            const unsigned tx = 2u * payload + 4u * D + (full ? 4u * TOK : 0u);
-            mbar_arrive_expect_tx(bar, tx);
-        }
-        if (l == 0) bulk_g2s(my_unit + L::K_OFF, Kp + (int64_t)tok0 * L::ROW, payload, bar);
-        else if (l == 1) bulk_g2s(my_unit + L::V_OFF, Vp + (int64_t)tok0 * L::ROW, payload, bar);
-        else if (l == 2) bulk_g2s(my_unit + L::KS_OFF, Ks + (int64_t)page_id * p.km_sp, 2 * D, bar);
-        else if (l == 3) bulk_g2s(my_unit + L::KM_OFF, Km + (int64_t)page_id * p.km_sp, 2 * D, bar);
-        else if (l == 4 && full) bulk_g2s(my_unit + L::VS_OFF, Vs + tok0, 2 * TOK, bar);
-        else if (l == 5 && full) bulk_g2s(my_unit + L::VM_OFF, Vm + tok0, 2 * TOK, bar);
-    };
-
-    // per quarter-warp online-softmax state (all in base 2)
+    // per quarter-warp online-softmax state (all in base 2); the producer warp keeps the
+    // neutral element
     float m_run = -INFINITY;          // running max
     float l_part = 0.f;               // this lane's share of the denominator
     float mn_part = 0.f;              // this lane's share of sum_t p_t * vm_t
     float2 acc[DPL / 2];
 #pragma unroll
     for (int j = 0; j < DPL / 2; ++j) acc[j] = make_float2(0.f, 0.f);
-
     bool timed_out = false;
-    int issued = 0;   // iterations whose copies have been started
-    int page_id = -1, tok0 = 0, n_tok = 0;
-    if (n_iter > 0) {   // start the first copies before anything else: q is loaded under their latency
-        unit_of(0, page_id, tok0, n_tok);
-        issue(page_id, tok0, n_tok);
-        issued = 1;
-    }
 
-    // ---- q slice of this lane, pre-multiplied by sm_scale*log2(e) and the nibble scale ----
-    float qn[DPL];    // for the K codes
-    float qr[DPL];    // plain q*sm_scale*log2e, for q.mn
-    {
-        const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + DPL * l;
-        const float c = p.sm_scale * LOG2E;
+    if (is_producer) {
+        // =========================== producer warp ===========================
+        // Lane j handles unit j of the iteration: it waits for the consumer's release of the
+        // stage, announces the bytes and issues both payload copies.  One lane per unit: a lane
+        // that only issued the second copy could fall two barrier phases behind when a unit is
+        // empty (no bytes are awaited then), and a parity wait cannot see that.
+        for (int it = 0; it < n_iter && !timed_out; ++it) {
+            const int s_ = it % ATT_STAGES;
 #pragma unroll
-        for (int j = 0; j < DPL; j += 8) {
-            float v[8];
-            load8<QT>(qp + j, v);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                qr[j + e] = v[e] * c;
-                qn[j + e] = qr[j + e] * nib_scale(e);
+            for (int u0 = 0; u0 < units_per_iter; u0 += 32) {
+                const int uu = u0 + lane;
+                if (uu < units_per_iter) {
+                    const int w = uu >> 2, q = uu & 3;
+                    uint64_t* full = &full_bars[w * ATT_STAGES + s_];
+                    if (it >= ATT_STAGES) {     // wait until the consumer warp has released the stage
+                        const unsigned par = (unsigned)(it / ATT_STAGES - 1) & 1u;
+                        unsigned spins = 0;
+                        while (!mbar_try_wait(&empty_bars[w * ATT_STAGES + s_], par)) {
+                            if (++spins > WAIT_SPIN_LIMIT) { timed_out = true; break; }
+                        }
+                    }
+                    if (!timed_out) {
+                        int page_id, tok0, n_tok;
+                        locate(it, uu, page_id, tok0, n_tok);
+                        if (page_id >= 0) {
+                            unsigned char* dst = stage_base + ((s_ * ATT_WARPS + w) * 4 + q) * L::STRIDE;
+                            const unsigned payload = (unsigned)n_tok * L::ROW;
+                            mbar_arrive_expect_tx(full, 2u * payload);
+                            bulk_g2s(dst + L::K_OFF, Kp + (int64_t)tok0 * L::ROW, payload, full);
+                            bulk_g2s(dst + L::V_OFF, Vp + (int64_t)tok0 * L::ROW, payload, full);
+                        } else {
+                            mbar_arrive(full);
+                        }
+                    }
+                }
             }
+            timed_out = __any_sync(0xffffffffu, timed_out);
         }
-    }
+#ifdef FQ_DEBUG_WAIT
+        if (timed_out && lane == 0) atomicExch(p.status, -7000);
+#else
+        if (timed_out && lane == 0) atomicExch(p.status, FQ_ERR_TIMEOUT);
+#endif
+    } else {
+        // =========================== consumer warps ===========================
+        UnitCtx<DPL, TPL> ctx[2];     // metadata of the unit in hand and of the next one
+        auto load_ctx = [&](auto SC, int it) {
+            constexpr int S = decltype(SC)::value;
+            UnitCtx<DPL, TPL>& c = ctx[S];
+            locate(it, warp * 4 + qw, c.page_id, c.tok0, c.n_tok);
+            c.vs_raw = 0u; c.vm_raw = 0u;
+            if (c.page_id < 0) return;
+            const uint16_t* ksr = Ks + (int64_t)c.page_id * p.km_sp + DPL * l;
+            const uint16_t* kmr = Km + (int64_t)c.page_id * p.km_sp + DPL * l;
+#pragma unroll
+            for (int j = 0; j < DPL / 8; ++j) {
+                c.ks[j] = ldg16(ksr + 8 * j);
+                c.km[j] = ldg16(kmr + 8 * j);
+            }
+            if (c.n_tok == TOK && TPL == 2) {
+                c.vs_raw = __ldg(reinterpret_cast<const uint32_t*>(Vs + c.tok0 + 2 * l));
+                c.vm_raw = __ldg(reinterpret_cast<const uint32_t*>(Vm + c.tok0 + 2 * l));
+            } else {   // ragged last chunk (or one token per lane): per-token loads
+#pragma unroll
+                for (int i = 0; i < TPL; ++i) {
+                    const int t = TPL * l + i;
+                    if (t < c.n_tok) {
+                        c.vs_raw |= (uint32_t)__ldg(Vs + c.tok0 + t) << (16 * i);
+                        c.vm_raw |= (uint32_t)__ldg(Vm + c.tok0 + t) << (16 * i);
+                    }
+                }
+            }
+        };
+        if (n_iter > 0) load_ctx(std::integral_constant<int, 0>{}, 0);
+        FQ_TRACE(1);
 
-    for (int it = 0; it < n_iter; ++it) {
-        if (it > 0) {
-            unit_of(it, page_id, tok0, n_tok);
-            __syncwarp();          // every lane is done reading the previous unit
-            fence_proxy_async();
-            issue(page_id, tok0, n_tok);
-            issued = it + 1;
-        }
-        const unsigned parity = (unsigned)it & 1u;
+        // ---- q slice of this lane, pre-multiplied by sm_scale*log2(e) and the nibble scale ----
+        float qn[DPL];    // for the K codes
+        float qr[DPL];    // plain q*sm_scale*log2e, for q.mn
         {
-            unsigned spins = 0;
-            while (!mbar_try_wait(bar, parity)) {
-                if (++spins > WAIT_SPIN_LIMIT) { timed_out = true; break; }
+            const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + DPL * l;
+            const float c = p.sm_scale * LOG2E;
+#pragma unroll
+            for (int j = 0; j < DPL; j += 8) {
+                float v[8];
+                load8<QT>(qp + j, v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    qr[j + e] = v[e] * c;
+                    qn[j + e] = qr[j + e] * nib_scale(e);
+                }
             }
         }
-        if (__any_sync(0xffffffffu, timed_out)) { timed_out = true; break; }
-        if (page_id < 0) continue;                 // uniform inside the quarter warp
-        const unsigned char* u = my_unit;
-
-        // ---------------- K: fold the page scale into q; q.mn ----------------
-        float qs[DPL];
-        float qmn = 0.f;
-#pragma unroll
-        for (int j = 0; j < DPL; j += 8) {
-            const uint4 s4 = *reinterpret_cast<const uint4*>(u + L::KS_OFF + 2 * (DPL * l + j));
-            const uint4 m4 = *reinterpret_cast<const uint4*>(u + L::KM_OFF + 2 * (DPL * l + j));
-            const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w}, mw[4] = {m4.x, m4.y, m4.z, m4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                qs[j + 2 * e] = qn[j + 2 * e] * bf16_lo(sw[e]);
-                qs[j + 2 * e + 1] = qn[j + 2 * e + 1] * bf16_hi(sw[e]);
-                qmn = fmaf(qr[j + 2 * e], bf16_lo(mw[e]), qmn);
-                qmn = fmaf(qr[j + 2 * e + 1], bf16_hi(mw[e]), qmn);
-            }
-            qs[j + 7] = fmaf(-16.f, qs[j + 6], qs[j + 7]);   // c7 rides on (c6 + 16 c7)
-        }
-        qmn = qw_sum(qmn, qmask);
-
-        float sdot[TOK];
-#pragma unroll
-        for (int t = 0; t < TOK; ++t) {
-            float2 a = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int wd = 0; wd < WPL; ++wd) {
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(u + L::K_OFF + t * L::ROW + 4 * (WPL * l + wd));
-                float f[8];
-                nib8(w, f);
-#pragma unroll
-                for (int e = 0; e < 8; e += 2)
-                    a = __ffma2_rn(make_float2(f[e], f[e + 1]), make_float2(qs[8 * wd + e], qs[8 * wd + e + 1]), a);
-            }
-            sdot[t] = a.x + a.y;
-        }
-        qw_transpose_reduce<TOK>(sdot, l, qmask);
-
-        // ---------------- softmax for this lane's TPL tokens ----------------
-        const float UNS = 5.62949953421312e14f;   // 2^49
-        float x[TPL], vs[TPL], vm[TPL];
-        float pmax = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < TPL; ++i) {
-            const int t = TPL * l + i;
-            const bool valid = t < n_tok;
-            x[i] = valid ? fmaf(sdot[i], UNS, qmn) : -INFINITY;
-            pmax = fmaxf(pmax, x[i]);
-            if (n_tok == TOK) {
-                vs[i] = bf16_lo(*reinterpret_cast<const uint16_t*>(u + L::VS_OFF + 2 * t));
-                vm[i] = bf16_lo(*reinterpret_cast<const uint16_t*>(u + L::VM_OFF + 2 * t));
-            } else {   // ragged last chunk: metadata straight from global memory
-                vs[i] = valid ? bf16_lo(Vs[tok0 + t]) : 0.f;
-                vm[i] = valid ? bf16_lo(Vm[tok0 + t]) : 0.f;
-            }
-        }
-        pmax = qw_max(pmax, qmask);
-        const float m_new = fmaxf(m_run, pmax);     // finite: the unit has at least one valid token
-        const float alpha = ex2(m_run - m_new);     // ex2(-inf) = 0 on the first unit
-        m_run = m_new;
         float* pvb = pv_bcast + (warp * 4 + qw) * TOK;
-        l_part *= alpha;
-        mn_part *= alpha;
-#pragma unroll
-        for (int i = 0; i < TPL; ++i) {
-            const float pr = ex2(x[i] - m_new);
-            l_part += pr;
-            mn_part = fmaf(pr, vm[i], mn_part);
-            pvb[TPL * l + i] = pr * vs[i] * 1.2676506002282294e30f;   // * 2^100
-        }
-        __syncwarp(qmask);
+        FQ_TRACE(2);
 
-        // ---------------- V ----------------
-        const float2 alpha2 = make_float2(alpha, alpha);
+        // One unit: K dot products, softmax update, V accumulation (see the header comment).
+        auto compute_unit = [&](const unsigned char* u, const UnitCtx<DPL, TPL>& c, auto&& prefetch) {
+            // ---------------- K: fold the page scale into q; q.mn ----------------
+            float qs[DPL];
+            float qmn = 0.f;
 #pragma unroll
-        for (int j = 0; j < DPL / 2; ++j) acc[j] = __fmul2_rn(acc[j], alpha2);
+            for (int j = 0; j < DPL; j += 8) {
+                const uint4 s4 = c.ks[j / 8];
+                const uint4 m4 = c.km[j / 8];
+                const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w}, mw[4] = {m4.x, m4.y, m4.z, m4.w};
 #pragma unroll
-        for (int t4 = 0; t4 < TOK; t4 += 4) {
-            const float4 pv4 = *reinterpret_cast<const float4*>(pvb + t4);
-            const float pv[4] = {pv4.x, pv4.y, pv4.z, pv4.w};
+                for (int e = 0; e < 4; ++e) {
+                    qs[j + 2 * e] = qn[j + 2 * e] * bf16_lo(sw[e]);
+                    qs[j + 2 * e + 1] = qn[j + 2 * e + 1] * bf16_hi(sw[e]);
+                    qmn = fmaf(qr[j + 2 * e], bf16_lo(mw[e]), qmn);
+                    qmn = fmaf(qr[j + 2 * e + 1], bf16_hi(mw[e]), qmn);
+                }
+                qs[j + 7] = fmaf(-16.f, qs[j + 6], qs[j + 7]);   // c7 rides on (c6 + 16 c7)
+            }
+            qmn = qw_sum(qmn, qmask);
+            prefetch();
+
+            float sdot[TOK];
 #pragma unroll
-            for (int tt = 0; tt < 4; ++tt) {
-                const int t = t4 + tt;
-                const float2 pp = make_float2(pv[tt], pv[tt]);
+            for (int t = 0; t < TOK; ++t) {
+                float2 a = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int wd = 0; wd < WPL; ++wd) {
-                    const uint32_t w = *reinterpret_cast<const uint32_t*>(u + L::V_OFF + t * L::ROW + 4 * (WPL * l + wd));
+                    const uint32_t w = *reinterpret_cast<const uint32_t*>(u + L::K_OFF + t * L::ROW + 4 * (WPL * l + wd));
                     float f[8];
                     nib8(w, f);
 #pragma unroll
                     for (int e = 0; e < 8; e += 2)
-                        acc[4 * wd + e / 2] = __ffma2_rn(make_float2(f[e], f[e + 1]), pp, acc[4 * wd + e / 2]);
+                        a = __ffma2_rn(make_float2(f[e], f[e + 1]), make_float2(qs[8 * wd + e], qs[8 * wd + e + 1]), a);
+                }
+                sdot[t] = a.x + a.y;
+            }
+            qw_transpose_reduce<TOK>(sdot, l, qmask);
+
+            // ---------------- softmax for this lane's TPL tokens ----------------
+            const float UNS = 5.62949953421312e14f;   // 2^49
+            float x[TPL];
+            float pmax = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < TPL; ++i) {
+                const bool valid = TPL * l + i < c.n_tok;
+                x[i] = valid ? fmaf(sdot[i], UNS, qmn) : -INFINITY;
+                pmax = fmaxf(pmax, x[i]);
+            }
+            pmax = qw_max(pmax, qmask);
+            const float m_new = fmaxf(m_run, pmax);     // finite: the unit has at least one valid token
+            const float alpha = ex2(m_run - m_new);     // ex2(-inf) = 0 on the first unit
+            m_run = m_new;
+            l_part *= alpha;
+            mn_part *= alpha;
+#pragma unroll
+            for (int i = 0; i < TPL; ++i) {
+                const float pr = ex2(x[i] - m_new);
+                const float vsi = i == 0 ? bf16_lo(c.vs_raw) : bf16_hi(c.vs_raw);
+                const float vmi = i == 0 ? bf16_lo(c.vm_raw) : bf16_hi(c.vm_raw);
+                l_part += pr;
+                mn_part = fmaf(pr, vmi, mn_part);
+                pvb[TPL * l + i] = pr * vsi * 1.2676506002282294e30f;   // * 2^100
+            }
+            __syncwarp(qmask);
+
+            // ---------------- V ----------------
+            const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+            for (int j = 0; j < DPL / 2; ++j) acc[j] = __fmul2_rn(acc[j], alpha2);
+#pragma unroll
+            for (int t4 = 0; t4 < TOK; t4 += 4) {
+                const float4 pv4 = *reinterpret_cast<const float4*>(pvb + t4);
+                const float pv[4] = {pv4.x, pv4.y, pv4.z, pv4.w};
+#pragma unroll
+                for (int tt = 0; tt < 4; ++tt) {
+                    const int t = t4 + tt;
+                    const float2 pp = make_float2(pv[tt], pv[tt]);
+#pragma unroll
+                    for (int wd = 0; wd < WPL; ++wd) {
+                        const uint32_t w = *reinterpret_cast<const uint32_t*>(u + L::V_OFF + t * L::ROW + 4 * (WPL * l + wd));
+                        float f[8];
+                        nib8(w, f);
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2)
+                            acc[4 * wd + e / 2] = __ffma2_rn(make_float2(f[e], f[e + 1]), pp, acc[4 * wd + e / 2]);
+                    }
                 }
             }
-        }
-        __syncwarp(qmask);   // pv_bcast is rewritten in the next iteration
-    }
+            __syncwarp(qmask);   // pv_bcast is rewritten by the next unit
+        };
 
-    if (timed_out) {
-        if (lane == 0) atomicExch(p.status, FQ_ERR_TIMEOUT);
-        // copies still in flight target this CTA's shared memory: wait (bounded) for every
-        // stage that was issued before leaving, so the CTA does not exit under them.
-        if (issued > 0) {
+
+        // ---- main loop: wait for the stage, consume it, release it to the producer ----
+        for (int it0 = 0; it0 < n_iter && !timed_out; it0 += 2) {
+            static_for<2>([&](auto SC) {
+                constexpr int S = decltype(SC)::value;
+                const int it = it0 + S;
+                if (it >= n_iter || timed_out) return;
+                const int s_ = it % ATT_STAGES;
+                const unsigned parity = (unsigned)(it / ATT_STAGES) & 1u;
+                unsigned spins = 0;
+                bool gave_up = false;
+                FQ_PROG(10 * it + 1);
+                while (!mbar_try_wait(&full_bars[warp * ATT_STAGES + s_], parity)) {
+                    if (++spins > WAIT_SPIN_LIMIT) { gave_up = true; break; }
+                }
+#ifdef FQ_DEBUG_WAIT
+                if (gave_up) atomicExch(p.status, -(8000 + it * 10 + warp));
+#endif
+                if (__any_sync(0xffffffffu, gave_up)) { timed_out = true; return; }
+                if (it == 0) FQ_TRACE(3);
+                FQ_PROG(10 * it + 2);
+                // the next unit's metadata is requested while this unit is being worked on
+                auto prefetch = [&]() {
+                    if (it + 1 < n_iter) load_ctx(std::integral_constant<int, 1 - S>{}, it + 1);
+                };
+                if (ctx[S].page_id >= 0)                   // uniform inside the quarter warp
+                    compute_unit(stage_base + ((s_ * ATT_WARPS + warp) * 4 + qw) * L::STRIDE, ctx[S], prefetch);
+                else
+                    prefetch();
+                __syncwarp();                              // every lane is done reading this stage
+                fence_proxy_async();
+                if (lane == 0) mbar_arrive(&empty_bars[warp * ATT_STAGES + s_]);
+                FQ_PROG(10 * it + 3);
+            });
+        }
+        if (timed_out && lane == 0) atomicExch(p.status, FQ_ERR_TIMEOUT);
+    }
+    // A CTA that gave up may still have copies in flight into its shared memory; the producer
+    // only ever runs ATT_STAGES iterations ahead of the consumers, and the grid-level timeout
+    // is reported through the status word.  Wait (bounded) for the full barriers of the last
+    // iterations before the staging area is reused.
+    timed_out = __syncthreads_or(timed_out);
+    if (timed_out && !is_producer) {
+        for (int it2 = max(0, n_iter - ATT_STAGES); it2 < n_iter; ++it2) {
             unsigned spins = 0;
-            while (!mbar_try_wait(bar, (unsigned)(issued - 1) & 1u)) {
-                if (++spins > WAIT_SPIN_LIMIT) break;
+            while (!mbar_try_wait(&full_bars[warp * ATT_STAGES + it2 % ATT_STAGES], (unsigned)(it2 / ATT_STAGES) & 1u)) {
+                if (++spins > (WAIT_SPIN_LIMIT >> 4)) break;
             }
         }
     }
 
+    FQ_TRACE(4);
     // ---------------- un-scale the V accumulators of this quarter warp ----------------
     float o[DPL];
     {
@@ -450,7 +591,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
     float tm = -INFINITY, tl = 0.f, tacc[TD];
 #pragma unroll
     for (int j = 0; j < TD; ++j) tacc[j] = 0.f;
-    if (split == 0 && p.tail_len > 0) {
+    if (split == 0 && p.tail_len > 0 && !is_producer) {
         float qt[TD];
         const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + TD * lane;
 #pragma unroll
@@ -485,7 +626,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
 
     // ---------------- CTA merge of all states through shared memory ----------------
     __syncthreads();   // every warp is done with the staging area (st_acc aliases it)
-    {
+    if (!is_producer) {
         const int sid = warp * 4 + qw;
         if (l == 0) { st_m[sid] = m_run; st_l[sid] = l_part; }
 #pragma unroll
@@ -496,20 +637,30 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
         for (int j = 0; j < TD; ++j) st_acc[tsid * D + TD * lane + j] = tacc[j];
     }
     __syncthreads();
-    float m_cta = -INFINITY;
+    // warp 0 turns the per-state maxima into merge weights once; then thread d sums channel d
+    static_assert(NSTATE <= 32, "one lane per state");
+    __shared__ float s_mcta, s_lcta;
+    if (warp == 0) {
+        const float mi = lane < NSTATE ? st_m[lane] : -INFINITY;
+        float mx = mi;
 #pragma unroll
-    for (int i = 0; i < NSTATE; ++i) m_cta = fmaxf(m_cta, st_m[i]);
-    float l_cta = 0.f;
+        for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        const float wgt = (mx == -INFINITY) ? 0.f : ex2(mi - mx);   // 0 for empty states
+        float lsum = lane < NSTATE ? st_l[lane] * wgt : 0.f;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
+        if (lane < NSTATE) st_m[lane] = wgt;
+        if (lane == 0) { s_mcta = mx; s_lcta = lsum; }
+    }
+    __syncthreads();
+    const float m_cta = s_mcta, l_cta = s_lcta;
     float acc_d = 0.f;           // thread d < D owns output channel d
-    if (m_cta != -INFINITY) {
+    if (tid < D) {
 #pragma unroll
-        for (int i = 0; i < NSTATE; ++i) {
-            const float wgt = ex2(st_m[i] - m_cta);   // 0 for empty states
-            l_cta = fmaf(st_l[i], wgt, l_cta);
-            if (tid < D) acc_d = fmaf(st_acc[i * D + tid], wgt, acc_d);
-        }
+        for (int i = 0; i < NSTATE; ++i) acc_d = fmaf(st_acc[i * D + tid], st_m[i], acc_d);
     }
 
+    FQ_TRACE(5);
     QT* Op = static_cast<QT*>(p.O) + b * p.o_sb + hq * p.o_sh;
     const int row = b * p.Hq + hq;
     if (p.n_split == 1) {
@@ -522,19 +673,28 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
     float* part = p.partials + ((int64_t)row * p.n_split + split) * (D + 2);
     if (tid < D) part[2 + tid] = acc_d;
     if (tid == 0) { part[0] = m_cta; part[1] = l_cta; }
-    __threadfence();
-    __syncthreads();
+    __syncthreads();           // the CTA's stores are ordered before thread 0's fence below
     __shared__ int s_ticket;
-    if (tid == 0) s_ticket = atomicAdd(&p.tickets[row], 1);
+    if (tid == 0) {
+        __threadfence();       // one device-scope fence per CTA (cumulative over the barrier)
+        s_ticket = atomicAdd(&p.tickets[row], 1);
+        __threadfence();
+    }
     __syncthreads();
+    FQ_TRACE(6);
     if (s_ticket != p.n_split - 1) return;
-    __threadfence();
     // The partials of this row are merged in split order with every load independent of the
     // others (a dependent chain of L2 round trips here would cost more than the attention).
     const float* parts = p.partials + (int64_t)row * p.n_split * (D + 2);
     float* mw = reinterpret_cast<float*>(smem);            // [n_split] max, then weight
     float* lw = mw + p.n_split;                             // [n_split] denominators
-    __shared__ float s_red[ATT_WARPS];
+    __shared__ float s_red[ATT_WARPS + 1];
+    constexpr int PRE = 16;    // partial accumulators requested up front, with the maxima
+    float pre[PRE];
+    if (tid < D) {
+#pragma unroll
+        for (int i = 0; i < PRE; ++i) pre[i] = i < p.n_split ? __ldcg(parts + (int64_t)i * (D + 2) + 2 + tid) : 0.f;
+    }
     float m_loc = -INFINITY;
     for (int i = tid; i < p.n_split; i += ATT_THREADS) {
         const float mi = __ldcg(parts + (int64_t)i * (D + 2));
@@ -548,7 +708,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
     __syncthreads();
     float m_all = s_red[0];
 #pragma unroll
-    for (int w = 1; w < ATT_WARPS; ++w) m_all = fmaxf(m_all, s_red[w]);
+    for (int w = 1; w < ATT_WARPS + 1; ++w) m_all = fmaxf(m_all, s_red[w]);
     float l_all = 0.f, o_all = 0.f;
     if (m_all != -INFINITY) {
         for (int i = tid; i < p.n_split; i += ATT_THREADS) mw[i] = ex2(mw[i] - m_all);
@@ -556,7 +716,9 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
         for (int i = 0; i < p.n_split; ++i) l_all = fmaf(lw[i], mw[i], l_all);
         if (tid < D) {
             const float* col = parts + 2 + tid;
-            int i = 0;
+#pragma unroll
+            for (int i = 0; i < PRE; ++i) o_all = fmaf(pre[i], i < p.n_split ? mw[i] : 0.f, o_all);
+            int i = PRE;
             for (; i + 8 <= p.n_split; i += 8) {
                 float v[8];
 #pragma unroll
@@ -572,6 +734,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_decode_int4_kernel(AttnPar
         if (p.lse) p.lse[row] = l_all > 0.f ? (m_all + log2f(l_all)) * LN2 : -INFINITY;
         p.tickets[row] = 0;   // leave the workspace ready for the next call
     }
+    FQ_TRACE(7);
 }
 
 template <int D, int TOK>
@@ -581,7 +744,7 @@ static constexpr size_t attn_smem_bytes() {
     size_t staging = (size_t)ATT_STAGES * ATT_WARPS * 4 * L::STRIDE;
     size_t merge = (size_t)NSTATE * D * 4;
     size_t front = staging > merge ? staging : merge;
-    return front + ATT_WARPS * ATT_STAGES * 8 + (size_t)ATT_WARPS * 4 * TOK * 4 + 2 * NSTATE * 4;
+    return front + 2 * ATT_WARPS * ATT_STAGES * 8 + (size_t)ATT_WARPS * 4 * TOK * 4 + 2 * NSTATE * 4;
 }
 
 template <typename QT, int D, int TOK>
@@ -601,6 +764,20 @@ static int launch_attn(const AttnParams& p, cudaStream_t st) {
 
 }  // namespace fq
 
+#ifdef FQ_DEBUG_WAIT
+extern "C" int fq_debug_read_dbg(int* dst) {
+    int rc = (int)cudaMemcpyFromSymbol(dst, fq::g_dbg, sizeof(int) * 32);
+    int zero[32] = {0};
+    cudaMemcpyToSymbol(fq::g_dbg, zero, sizeof(zero));
+    return rc;
+}
+#endif
+#ifdef FQ_ATT_TRACE
+extern "C" int fq_debug_read_trace(unsigned long long* dst, int n) {
+    return (int)cudaMemcpyFromSymbol(dst, fq::g_trace, sizeof(unsigned long long) * n);
+}
+#endif
+
 extern "C" size_t fq_sparse_decode_workspace_bytes(int B, int Hq, int D, int n_split) {
     if (B <= 0 || Hq <= 0 || D <= 0 || n_split <= 1) return 0;
     size_t tickets = ((size_t)B * Hq * 4 + 255) & ~(size_t)255;
@@ -615,11 +792,10 @@ extern "C" int fq_sparse_decode_default_splits(int B, int Hq, int bucket, int pa
     const long rows = (long)B * Hq;
     const long per_iter = fq::ATT_WARPS * 4;
     const long total_iters = (units + per_iter - 1) / per_iter;    // per row
-    // One 16-unit iteration per CTA lets the hardware scheduler balance the load; only when
-    // that would mean more than ~8 waves of CTAs (148 SMs x 4 resident) give a CTA several.
-    long iters_per_cta = (rows * total_iters) / (148L * 4 * 8);
-    if (iters_per_cta < 1) iters_per_cta = 1;
-    long n_split = (total_iters + iters_per_cta - 1) / iters_per_cta;
+    // All CTAs resident at once (148 SMs x ATT_CTAS_PER_SM): the producers then request the
+    // first STAGES iterations of every CTA immediately and the memory latency is paid once.
+    long n_split = (148L * fq::ATT_CTAS_PER_SM) / rows;
+    if (n_split > total_iters) n_split = total_iters;
     if (n_split > bucket) n_split = bucket;
     if (n_split < 1) n_split = 1;
     if (n_split > 1024) n_split = 1024;

@@ -1,0 +1,72 @@
+// Host-side chaining of the four kernels of one decode step of one layer on a persistent
+// INT4 cache: pack-on-append, page scores, top-k + compact index, sparse attention with the
+// staged tail.  No device code of its own; it exists so that a caller pays one foreign call
+// per layer instead of four plus the slicing arithmetic.
+#include "fq_common.cuh"
+
+extern "C" int fq_decode_layer_int4(
+    const fq_int4_cache* c, int layer, int seen,
+    const void* K_new, const void* V_new, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const fq_decode_params* prm,
+    float* scores, int32_t* compact, void* O, float* lse,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_decode_layer_int4";
+    FQ_CHECK_ARG(c && prm, FQ_ERR_ARG, "%s: null descriptor", fn);
+    FQ_CHECK_ARG(layer >= 0 && layer < c->L, FQ_ERR_ARG, "%s: layer_idx %d out of range [0, %d)", fn, layer, c->L);
+    FQ_CHECK_ARG(seen >= 0 && n_new >= 0 && seen + n_new <= c->max_seq_len, FQ_ERR_ARG,
+                 "%s: seen+new=%d exceeds max_seq_len=%d", fn, seen + n_new, c->max_seq_len);
+    FQ_CHECK_ARG(c->kv_dtype == FQ_F16 || c->kv_dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: cache dtype code %d", fn, c->kv_dtype);
+    const int page = c->page, D = c->D, B = c->B, Hkv = c->Hkv, Hq = prm->Hq;
+    const size_t esz = 2;
+    const int partial_len = seen % page;
+    const int total = partial_len + n_new;
+    const int n_quant = (total / page) * page;
+    const int tok_start = seen - partial_len;
+    const int pg_start = tok_start / page;
+
+    uint8_t* Kp = c->K_packed + layer * c->pk_sl;
+    uint8_t* Vp = c->V_packed + layer * c->pk_sl;
+    uint16_t* Ks = static_cast<uint16_t*>(c->K_scale) + layer * c->km_sl;
+    uint16_t* Km = static_cast<uint16_t*>(c->K_mn) + layer * c->km_sl;
+    uint16_t* Vs = static_cast<uint16_t*>(c->V_scale) + layer * c->vm_sl;
+    uint16_t* Vm = static_cast<uint16_t*>(c->V_mn) + layer * c->vm_sl;
+    char* Kt = static_cast<char*>(c->K_partial) + layer * c->pt_sl * esz;
+    char* Vt = static_cast<char*>(c->V_partial) + layer * c->pt_sl * esz;
+
+    int rc;
+    if (n_new > 0) {
+        rc = fq_quantize_kv_int4(
+            Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, partial_len,
+            K_new, V_new, nw_sb, nw_sh, nw_ss, n_new,
+            c->kv_dtype, B, Hkv, D, page, n_quant,
+            Kp + (int64_t)tok_start * c->pk_ss, Vp + (int64_t)tok_start * c->pk_ss, c->pk_sb, c->pk_sh, c->pk_ss,
+            Ks + (int64_t)pg_start * c->km_sp, Km + (int64_t)pg_start * c->km_sp, c->km_sb, c->km_sh, c->km_sp,
+            Vs + tok_start, Vm + tok_start, c->vm_sb, c->vm_sh, 1,
+            Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, stream);
+        if (rc != FQ_OK) return rc;
+    }
+    const int now = seen + n_new;
+    const int tail = now % page;
+    const int completed = now - tail;
+    const int P = completed / page;
+    if (P > 0) {
+        rc = fq_page_scores_int4(Q, q_dtype, q_sb, q_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
+                                 B, Hq, Hkv, P, D, scores, (int64_t)Hq * P, P, stream);
+        if (rc != FQ_OK) return rc;
+        const int k_max = prm->k_max_static < P ? prm->k_max_static : P;
+        rc = fq_select_pages(scores, (int64_t)Hq * P, P, B, Hq, P, prm->retention_per_head, prm->retention,
+                             k_max, prm->sinks, prm->window, nullptr, 0, 0,
+                             compact, (int64_t)Hq * prm->bucket, prm->bucket, prm->bucket, nullptr, stream);
+        if (rc != FQ_OK) return rc;
+    }
+    int n_split = prm->n_split > 0 ? prm->n_split : fq_sparse_decode_default_splits(B, Hq, prm->bucket, page);
+    return fq_sparse_decode_int4(
+        Q, q_dtype, q_sb, q_sh, Kp, c->pk_sb, c->pk_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
+        Vp, c->pk_sb, c->pk_sh, Vs, Vm, c->vm_sb, c->vm_sh,
+        compact, (int64_t)Hq * prm->bucket, prm->bucket, P > 0 ? prm->bucket : 0,
+        tail ? Kt : nullptr, tail ? Vt : nullptr, c->kv_dtype, c->pt_sb, c->pt_sh, c->pt_ss, tail,
+        B, Hq, Hkv, completed, P, D, page, prm->sm_scale,
+        O, (int64_t)Hq * D, D, lse, workspace, workspace_bytes, n_split, stream);
+}

@@ -32,6 +32,29 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
     const int n_chunks = D >> 3;
     const int nr = min(NR, n_rep - head_off);   // heads actually present in this pass
 
+    // Metadata loads of every page this quarter warp will score are issued first, the q loads
+    // after them, so the two global-memory latencies overlap instead of adding up.
+    constexpr int ITERS = SCORE_PAGES_PER_CTA / 16;
+    const int p_base = blockIdx.x * SCORE_PAGES_PER_CTA;
+    const uint16_t* sc_base = K_scale + b * km_sb + hkv * km_sh;
+    const uint16_t* mn_base = K_mn + b * km_sb + hkv * km_sh;
+    uint4 m4[ITERS][CH], s4[ITERS][CH];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int p = p_base + it * 16 + warp * 4 + qw;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int chunk = l + 8 * c;
+            if (p < P && chunk < n_chunks) {
+                m4[it][c] = ldg16(mn_base + (int64_t)p * km_sp + 8 * chunk);
+                s4[it][c] = ldg16(sc_base + (int64_t)p * km_sp + 8 * chunk);
+            } else {
+                m4[it][c] = make_uint4(0, 0, 0, 0);
+                s4[it][c] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    }
+
     float q[NR][CH][8];
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
@@ -48,33 +71,18 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
         }
     }
 
-    const int p_base = blockIdx.x * SCORE_PAGES_PER_CTA;
-    const uint16_t* sc_base = K_scale + b * km_sb + hkv * km_sh;
-    const uint16_t* mn_base = K_mn + b * km_sb + hkv * km_sh;
-#pragma unroll 2
-    for (int it = 0; it < SCORE_PAGES_PER_CTA / 16; ++it) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
         const int p = p_base + it * 16 + warp * 4 + qw;
         const bool live = p < P;
         float t1[NR], t2[NR];
 #pragma unroll
         for (int r = 0; r < NR; ++r) { t1[r] = 0.f; t2[r] = 0.f; }
-        if (live) {
-            uint4 m4[CH], s4[CH];
+        {
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
-                const int chunk = l + 8 * c;
-                if (chunk < n_chunks) {
-                    m4[c] = ldg16(mn_base + (int64_t)p * km_sp + 8 * chunk);
-                    s4[c] = ldg16(sc_base + (int64_t)p * km_sp + 8 * chunk);
-                } else {
-                    m4[c] = make_uint4(0, 0, 0, 0);
-                    s4[c] = make_uint4(0, 0, 0, 0);
-                }
-            }
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                const uint32_t mw[4] = {m4[c].x, m4[c].y, m4[c].z, m4[c].w};
-                const uint32_t sw[4] = {s4[c].x, s4[c].y, s4[c].z, s4[c].w};
+                const uint32_t mw[4] = {m4[it][c].x, m4[it][c].y, m4[it][c].z, m4[it][c].w};
+                const uint32_t sw[4] = {s4[it][c].x, s4[it][c].y, s4[it][c].z, s4[it][c].w};
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const float mn = (e & 1) ? bf16_hi(mw[e >> 1]) : bf16_lo(mw[e >> 1]);

@@ -2,19 +2,24 @@
 //
 // One CTA per (batch, head) row of P fp32 scores.  The row is read from global memory ONCE
 // (all loads in flight together) and kept in shared memory as order-preserving 32-bit keys;
-// every later pass runs out of shared memory.  The k-th largest key is found with a 4-pass,
-// 8-bit-digit radix select (one private 256-bin histogram per warp in shared memory, plain
-// shared atomics, a warp whose 32 digits are all equal adds once); the selected set is
-// { key > T } plus the
-// lowest-indexed pages with key == T until k are taken.  Output positions come from warp
-// ballots and a block-level scan, so the compact list is produced directly (descending page
-// id, -1 padded) without a sort.  Latency-bound, not bandwidth-bound: P*4 bytes in,
-// P + 4*bucket bytes out.  Rows too long for shared memory (P > 40960) re-read global memory.
+// every later pass runs out of shared memory.  The k-th largest key T is found by
+// distribution select: the keys still in play span [lo, hi]; they are counted into 2048
+// equal-width bins of that span (plain shared-memory atomics), a block scan from the top
+// finds the bin holding rank k, and the span shrinks to that bin.  Two rounds usually leave a
+// handful of candidates, which are ranked directly; a span of width 1 ends the search too, so
+// at most three rounds are needed for any input (ties, infinities, NaNs included).
+// The selected set is { key > T } plus the lowest-indexed pages with key == T until k are
+// taken.  Output positions come from warp ballots and a block-level scan, so the compact
+// list is produced directly (descending page id, -1 padded) without a sort.
+// Latency-bound, not bandwidth-bound: P*4 bytes in, P + 4*bucket bytes out.  Rows too long
+// for shared memory (P > 49152) re-read global memory in every pass.
 #include "fq_common.cuh"
 
 namespace fq {
 
 constexpr int SEL_MAX_WARPS = 32;
+constexpr int SEL_BINS = 2048;
+constexpr int SEL_CAND_MAX = 128;
 
 // larger float -> larger key; -0 folds onto +0; NaN with a clear sign bit sorts above +inf.
 __device__ __forceinline__ uint32_t score_key(float f) {
@@ -24,11 +29,14 @@ __device__ __forceinline__ uint32_t score_key(float f) {
 }
 
 struct SelShared {
-    unsigned hist[256];
+    unsigned hist[SEL_BINS];
+    unsigned cand[SEL_CAND_MAX];
     unsigned warp_tot[SEL_MAX_WARPS];
-    unsigned prefix;      // key bits fixed so far
-    unsigned remaining;   // rank still to find inside the current prefix bucket
-    unsigned misc[4];
+    unsigned warp_min[SEL_MAX_WARPS];
+    unsigned warp_max[SEL_MAX_WARPS];
+    unsigned sel_bin, above, cnt;     // result of one histogram round
+    unsigned ncand;
+    unsigned T, need_eq, eq_total;    // result of the search
 };
 
 // Exclusive scan of one value per warp (value valid on every lane of the warp).
@@ -57,18 +65,31 @@ __global__ void select_pages_kernel(
     int32_t* __restrict__ compact, int64_t cp_sb, int64_t cp_sh, int bucket,
     int32_t* __restrict__ count) {
     __shared__ SelShared sh;
-    extern __shared__ unsigned s_dyn[];
-    unsigned* s_hist = s_dyn;                                   // [nwarps][256] private histograms
-    unsigned* s_keys = s_dyn + (blockDim.x >> 5) * 256;         // [P] keys (SMEM_KEYS only)
+    extern __shared__ unsigned s_keys[];                        // [P] keys (SMEM_KEYS only)
     const int b = blockIdx.y, h = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int T_ = blockDim.x;
     const float* row = scores + b * sc_sb + h * sc_sh;
-    if (SMEM_KEYS) {
-#pragma unroll 4
-        for (int i = tid; i < P; i += blockDim.x) s_keys[i] = score_key(__ldg(row + i));
-        __syncthreads();
-    }
     auto key_at = [&](int i) -> unsigned { return SMEM_KEYS ? s_keys[i] : score_key(row[i]); };
+
+    // ---- load the row once; block min / max of the keys ----
+    unsigned kmin = 0xffffffffu, kmax = 0u;
+#pragma unroll 4
+    for (int i = tid; i < P; i += T_) {
+        const unsigned key = score_key(__ldg(row + i));
+        if (SMEM_KEYS) s_keys[i] = key;
+        kmin = min(kmin, key);
+        kmax = max(kmax, key);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, off));
+        kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, off));
+    }
+    if (lane == 0) { sh.warp_min[warp] = kmin; sh.warp_max[warp] = kmax; }
+    __syncthreads();
+    unsigned lo = sh.warp_min[0], hi = sh.warp_max[0];
+    for (int w = 1; w < nwarps; ++w) { lo = min(lo, sh.warp_min[w]); hi = max(hi, sh.warp_max[w]); }
 
     // k_h = clamp(ceil(fp32(r) * fp32(P)), 0, P), then capped by the static k_max
     const float r = retention_per_head ? retention_per_head[h] : retention;
@@ -77,66 +98,80 @@ __global__ void select_pages_kernel(
     k = min(k, min(k_max, P));
     const int ns = min(sinks, P), nw = min(window, P);
 
-    // ---- radix select of the k-th largest key (only when 0 < k < P) ----
+    // ---- distribution select of the k-th largest key (only when 0 < k < P) ----
     unsigned T = 0u;           // threshold key
     unsigned need_eq = 0u;     // how many pages with key == T are kept
+    unsigned eq_total = 0u;    // how many pages have key == T
     if (k > 0 && k < P) {
-        if (tid == 0) { sh.prefix = 0u; sh.remaining = (unsigned)k; }
-        for (int shift = 24; shift >= 0; shift -= 8) {
-            unsigned* my_hist = s_hist + warp * 256;
-            for (int i = tid; i < nwarps * 256; i += blockDim.x) s_hist[i] = 0u;
-            __syncthreads();
-            const unsigned prefix = sh.prefix;
-            const unsigned hi_mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            const int P_round = (P + 31) & ~31;   // whole warps stay converged for the vote
-            for (int i = tid; i < P_round; i += blockDim.x) {
-                const bool in = i < P;
-                const unsigned key = in ? key_at(i) : 0u;
-                const bool cand = in && ((key & hi_mask) == prefix);
-                const unsigned digit = cand ? ((key >> shift) & 255u) : 256u;
-                int same = 0;
-                __match_all_sync(0xffffffffu, digit, &same);
-                if (same) {
-                    if (cand && lane == 0) atomicAdd(&my_hist[digit], 32u);
-                } else if (cand) {
-                    atomicAdd(&my_hist[digit], 1u);
+        unsigned remaining = (unsigned)k;   // rank (1 = largest) still to find inside [lo, hi]
+        unsigned in_range = (unsigned)P;    // number of keys inside [lo, hi]
+        const int bpt = SEL_BINS / T_;      // bins per thread in the scan (T_ is 128..1024)
+        for (int round = 0; round < 4; ++round) {
+            const unsigned width = hi - lo;
+            if (width == 0u) { T = lo; need_eq = remaining; eq_total = in_range; break; }
+            if (in_range <= (unsigned)SEL_CAND_MAX) {
+                // ---- few candidates left: rank them directly ----
+                if (tid == 0) sh.ncand = 0u;
+                __syncthreads();
+                for (int i = tid; i < P; i += T_) {
+                    const unsigned key = key_at(i);
+                    if (key >= lo && key <= hi) sh.cand[atomicAdd(&sh.ncand, 1u)] = key;
                 }
-            }
-            __syncthreads();
-            for (int i = tid; i < 256; i += blockDim.x) {
-                unsigned c = 0u;
-                for (int w = 0; w < nwarps; ++w) c += s_hist[w * 256 + i];
-                sh.hist[i] = c;
-            }
-            __syncthreads();
-            if (warp == 0) {
-                // scan bins from the top: find the bin where the cumulative count reaches `remaining`
-                const unsigned rem = sh.remaining;
-                unsigned c[8], s = 0u;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { c[j] = sh.hist[255 - (lane * 8 + j)]; s += c[j]; }
-                unsigned incl = s;
-#pragma unroll
-                for (int off = 1; off < 32; off <<= 1) {
-                    unsigned n = __shfl_up_sync(0xffffffffu, incl, off);
-                    if (lane >= off) incl += n;
-                }
-                unsigned run = incl - s;   // pages in bins above this lane's bins
-                if (run < rem && incl >= rem) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (run < rem && run + c[j] >= rem) {
-                            sh.prefix = prefix | ((unsigned)(255 - (lane * 8 + j)) << shift);
-                            sh.remaining = rem - run;
-                        }
-                        run += c[j];
+                __syncthreads();
+                const unsigned c = sh.ncand;
+                for (unsigned i = tid; i < c; i += T_) {
+                    const unsigned v = sh.cand[i];
+                    unsigned g = 0u, ge = 0u;
+                    for (unsigned j = 0; j < c; ++j) {
+                        const unsigned o = sh.cand[j];
+                        g += o > v;
+                        ge += o >= v;
                     }
+                    if (g < remaining && remaining <= ge) { sh.T = v; sh.need_eq = remaining - g; sh.eq_total = ge - g; }
+                }
+                __syncthreads();
+                T = sh.T; need_eq = sh.need_eq; eq_total = sh.eq_total;
+                break;
+            }
+            const int nb = 32 - __clz(width);
+            const int shift = nb > 11 ? nb - 11 : 0;           // (width >> shift) <= 2047
+            for (int i = tid; i < SEL_BINS; i += T_) sh.hist[i] = 0u;
+            __syncthreads();
+            for (int i = tid; i < P; i += T_) {
+                const unsigned key = key_at(i);
+                if (key >= lo && key <= hi) atomicAdd(&sh.hist[(key - lo) >> shift], 1u);
+            }
+            __syncthreads();
+            // scan from the top bin down: thread t owns bins 2047 - (t*bpt + j)
+            unsigned own = 0u;
+            for (int j = 0; j < bpt; ++j) own += sh.hist[SEL_BINS - 1 - (tid * bpt + j)];
+            unsigned incl = own;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                unsigned n = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += n;
+            }
+            unsigned tot_unused;
+            const unsigned wprefix = block_warp_scan(__shfl_sync(0xffffffffu, incl, 31), sh, &tot_unused);
+            unsigned run = wprefix + incl - own;               // keys in bins above this thread's bins
+            if (run < remaining && remaining <= run + own) {
+                for (int j = 0; j < bpt; ++j) {
+                    const int bin = SEL_BINS - 1 - (tid * bpt + j);
+                    const unsigned c = sh.hist[bin];
+                    if (run < remaining && remaining <= run + c) { sh.sel_bin = (unsigned)bin; sh.above = run; sh.cnt = c; }
+                    run += c;
                 }
             }
             __syncthreads();
+            const unsigned bin = sh.sel_bin;
+            remaining -= sh.above;
+            in_range = sh.cnt;
+            const unsigned new_lo = lo + (bin << shift);
+            const unsigned new_hi = (bin == (width >> shift)) ? hi : new_lo + ((1u << shift) - 1u);
+            lo = new_lo;
+            hi = new_hi;
+            if (shift == 0) { T = lo; need_eq = remaining; eq_total = in_range; break; }
         }
-        T = sh.prefix;
-        need_eq = sh.remaining;   // 1 <= need_eq <= #(key == T)
     }
     const bool take_all = k >= P;
     const bool take_none = k <= 0;
@@ -147,15 +182,18 @@ __global__ void select_pages_kernel(
     const int w_end = min(P, w_begin + per_warp);
 
     // pass A: pages with key == T in this warp's run
-    unsigned eq_before = 0u, eq_total = 0u;
-    if (!take_all && !take_none) {
+    // (skipped when every page with key == T is kept: then "selected" is simply key >= T)
+    unsigned eq_before = 0u;
+    const bool rank_ties = !take_all && !take_none && need_eq < eq_total;
+    if (rank_ties) {
         unsigned cnt = 0u;
         for (int i0 = w_begin; i0 < w_end; i0 += 32) {
             const int i = i0 + lane;
             const bool eq = i < w_end && key_at(i) == T;
             cnt += __popc(__ballot_sync(0xffffffffu, eq));
         }
-        eq_before = block_warp_scan(cnt, sh, &eq_total);
+        unsigned eq_tot_unused;
+        eq_before = block_warp_scan(cnt, sh, &eq_tot_unused);
     }
 
     // pass B: selected pages in this warp's run
@@ -173,7 +211,7 @@ __global__ void select_pages_kernel(
         const unsigned eq_ballot = __ballot_sync(0xffffffffu, eq);
         if (eq) {
             const unsigned rank = eq_run + __popc(eq_ballot & ((1u << lane) - 1u));
-            sel = rank < need_eq;
+            sel = rank_ties ? (rank < need_eq) : true;
         }
         eq_run += __popc(eq_ballot);
         if (valid && (i < ns || i >= P - nw)) sel = true;
@@ -249,7 +287,7 @@ __global__ void build_compact_kernel(const uint8_t* __restrict__ mask, int64_t m
 }
 
 static int select_threads(int P) { return P <= 512 ? 128 : (P <= 1024 ? 256 : (P <= 4096 ? 512 : 1024)); }
-constexpr int SEL_SMEM_MAX_P = 40960;   // 160 KB of keys + 32 KB of histograms
+constexpr int SEL_SMEM_MAX_P = 49152;   // 192 KB of keys
 
 }  // namespace fq
 
@@ -271,8 +309,8 @@ extern "C" int fq_select_pages(
     dim3 grid((unsigned)H, (unsigned)B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (P <= SEL_SMEM_MAX_P) {
-        const size_t smem = (size_t)P * 4 + (size_t)(select_threads(P) / 32) * 1024;
-        if (smem > 40 * 1024) {
+        const size_t smem = (size_t)P * 4;
+        if (smem > 36 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(select_pages_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve %zu B of shared memory: %s", fn, smem, cudaGetErrorString(e));
         }
@@ -280,7 +318,7 @@ extern "C" int fq_select_pages(
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
             mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count);
     } else {
-        select_pages_kernel<false><<<grid, select_threads(P), (select_threads(P) / 32) * 1024, st>>>(
+        select_pages_kernel<false><<<grid, select_threads(P), 0, st>>>(
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
             mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count);
     }

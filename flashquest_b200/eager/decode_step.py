@@ -9,11 +9,12 @@ tail merged in the same softmax.  Three kernel launches per layer, no allocation
 """
 from __future__ import annotations
 
+import ctypes
 import math
 
 import torch
 
-from .._lib import check, dtype_code, lib, ptr, stream_ptr
+from .._lib import DecodeParams, Int4CacheDesc, check, dtype_code, lib, ptr, stream_ptr
 
 
 class QuestDecodeInt4:
@@ -62,6 +63,44 @@ class QuestDecodeInt4:
         self.ws_bytes = (nbytes + 255) // 256 * 256
         self.workspace = torch.zeros(L, max(self.ws_bytes, 256), dtype=torch.uint8, device=dev)
         self.launches = 0
+        # descriptors for the one-call-per-layer entry point
+        c = cache
+        self._cdesc = Int4CacheDesc(
+            c.K_packed.data_ptr(), c.V_packed.data_ptr(), *c.K_packed.stride()[:4],
+            c.K_scale.data_ptr(), c.K_mn.data_ptr(), *c.K_scale.stride()[:4],
+            c.V_scale.data_ptr(), c.V_mn.data_ptr(), *c.V_scale.stride()[:3],
+            c.K_partial.data_ptr(), c.V_partial.data_ptr(), *c.K_partial.stride()[:4],
+            dtype_code(c.K_partial), c.num_layers, self.B, self.Hkv, self.D, self.page, c.max_seq_len)
+        self._prm = DecodeParams(
+            self.Hq, self.retention_per_q.data_ptr() if self.retention_per_q is not None else None, self.retention,
+            self.k_max_static, self.num_sinks, self.window_pages, self.bucket, self.sm_scale, self.n_split)
+
+    def step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor, layer_idx: int):
+        """Append k_new, v_new (B,H_kv,n,D) to the layer and attend with q (B,H_q,1,D) in ONE
+        foreign call (fq_decode_layer_int4): what cache.update_quantized followed by attend()
+        does, without the per-call slicing.  Tensors must have the cache's dtype."""
+        c = self.cache
+        if layer_idx < 0 or layer_idx >= c.num_layers:
+            raise IndexError(f"layer_idx {layer_idx} out of range [0, {c.num_layers})")
+        seen = c._seen_tokens[layer_idx]
+        n_new = k_new.shape[2]
+        if seen + n_new > c.max_seq_len:
+            raise RuntimeError(f"PersistentInt4KVCache: seen+new={seen + n_new} exceeds max_seq_len={c.max_seq_len}")
+        if k_new.dtype != c.dtype or v_new.dtype != c.dtype:
+            k_new, v_new = k_new.to(c.dtype), v_new.to(c.dtype)
+        if k_new.stride(3) != 1 or v_new.stride() != k_new.stride():
+            k_new, v_new = k_new.contiguous(), v_new.contiguous()
+        q3 = q.reshape(self.B, self.Hq, self.D)
+        O, lse = self.O[layer_idx], self.lse[layer_idx]
+        check(lib().fq_decode_layer_int4(
+            ctypes.byref(self._cdesc), layer_idx, seen,
+            ptr(k_new), ptr(v_new), k_new.stride(0), k_new.stride(1), k_new.stride(2), n_new,
+            ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1), ctypes.byref(self._prm),
+            ptr(self.scores[layer_idx]), ptr(self.compact[layer_idx]), ptr(O), ptr(lse),
+            ptr(self.workspace[layer_idx]), self.workspace.shape[1], stream_ptr(self.device)))
+        c._seen_tokens[layer_idx] = seen + n_new
+        self.launches += 4
+        return O.unsqueeze(2), lse.unsqueeze(2)
 
     def attend(self, q: torch.Tensor, layer_idx: int):
         """q (B,H_q,1,D) or (B,H_q,D), the cache's dtype family (fp16/bf16).  Returns views

@@ -12,15 +12,21 @@ _SUPPORTED_HEAD_DIMS = (64, 128)
 _workspaces: dict = {}
 
 
-def _workspace(device, nbytes: int):
-    """Split-K scratch, one per (device, stream): the kernel expects the ticket words at its
-    start to be zero before the first use and leaves them zero after every call."""
+def _workspace(device, nbytes: int, rows: int):
+    """Split-K scratch, one per (device, stream).  The kernel expects the ticket words at its
+    start (one per (batch, head) row) to be zero before a call and leaves them zero after it;
+    that only holds while the row count stays the same, because the partial results of a
+    call with fewer rows land where a call with more rows keeps its tickets.  So the ticket
+    region is cleared whenever the row count changes."""
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
-    ws = _workspaces.get(key)
+    ws, last_rows = _workspaces.get(key, (None, -1))
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+        last_rows = rows
+    if last_rows != rows:
+        ws[: (rows * 4 + 255) // 256 * 256].zero_()
+    _workspaces[key] = (ws, rows)
     return ws
 
 
@@ -101,7 +107,7 @@ def sparse_decode_int4(Q, K_packed, K_scale, K_mn, V_packed, V_scale, V_mn, sel_
         ws_bytes = 0
         if n_split > 1:
             ws_bytes = lib().fq_sparse_decode_workspace_bytes(B, H_q, D, n_split)
-            ws = _workspace(dev, ws_bytes)
+            ws = _workspace(dev, ws_bytes, B * H_q)
         check(lib().fq_sparse_decode_int4(
             ptr(Q_2d), dtype_code(Q_2d), Q_2d.stride(0), Q_2d.stride(1),
             ptr(K_packed), K_packed.stride(0), K_packed.stride(1),

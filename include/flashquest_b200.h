@@ -170,6 +170,54 @@ int fq_sparse_decode_int4(
     void* O, int64_t o_sb, int64_t o_sh, float* lse,
     void* workspace, size_t workspace_bytes, int n_split, void* stream);
 
+/* ------------------------------------------------------------------------------------
+ * One decode step of one layer on a persistent INT4 cache: append + score + select + attend.
+ * Replaces, in one host call and four launches, what the reference's patched forward does
+ * per layer and step around the projections (eager/llama_persistent_patch.py:193-245):
+ * cache.update_quantized (cache/persistent_int4.py:69-132), page_scores_int4_fast,
+ * select_pages_vectorized + build_compact_selection, the sparse kernel, the partial-page
+ * tail attention and the LSE merge.
+ *
+ * fq_int4_cache describes the storage of PersistentInt4KVCache (cache/persistent_int4.py:46-61):
+ * base pointers of layer 0 and element strides of the (layer, batch, head, row) axes; the
+ * innermost axis is dense.  `seen` is the number of tokens in the layer BEFORE this call
+ * (the reference keeps it in _seen_tokens); the call appends n_new tokens and attends over
+ * seen + n_new tokens with S_q = 1.
+ */
+typedef struct fq_int4_cache {
+    uint8_t* K_packed; uint8_t* V_packed;          /* (L,B,H,S,D/2) u8 */
+    int64_t pk_sl, pk_sb, pk_sh, pk_ss;            /* bytes */
+    void* K_scale; void* K_mn;                     /* (L,B,H,P,D) bf16 */
+    int64_t km_sl, km_sb, km_sh, km_sp;
+    void* V_scale; void* V_mn;                     /* (L,B,H,S) bf16, token stride 1 */
+    int64_t vm_sl, vm_sb, vm_sh;
+    void* K_partial; void* V_partial;              /* (L,B,H,page,D) kv_dtype */
+    int64_t pt_sl, pt_sb, pt_sh, pt_ss;
+    int kv_dtype;                                  /* FQ_F16 | FQ_BF16 */
+    int L, B, Hkv, D, page, max_seq_len;
+} fq_int4_cache;
+
+typedef struct fq_decode_params {
+    int Hq;
+    const float* retention_per_head;               /* device, length Hq, or NULL */
+    float retention;
+    int k_max_static, sinks, window, bucket;       /* bucket = k_max_static + sinks + window */
+    float sm_scale;
+    int n_split;                                   /* 0: fq_sparse_decode_default_splits */
+} fq_decode_params;
+
+/* K_new,V_new (B,Hkv,n_new,D) kv_dtype with strides nw_sb,nw_sh,nw_ss; Q (B,Hq,D) q_dtype;
+ * scores (B,Hq,P_max) fp32 and compact (B,Hq,bucket) int32 are caller-provided scratch, dense;
+ * O (B,Hq,D) q_dtype dense, lse (B,Hq) fp32 or NULL; workspace as for fq_sparse_decode_int4.
+ * Fails with FQ_ERR_ARG if seen + n_new exceeds max_seq_len or layer is out of range. */
+int fq_decode_layer_int4(
+    const fq_int4_cache* cache, int layer, int seen,
+    const void* K_new, const void* V_new, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const fq_decode_params* params,
+    float* scores, int32_t* compact, void* O, float* lse,
+    void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -196,3 +196,32 @@ def test_full_size_invariances(att):
     Ow, lw = oracle.sparse_attn_int4(Q.cpu()[:, heads], *[t[:, :1] for t in cpu], selection_mask=mask.cpu()[:, heads], page_size=page)
     _close(base[:, heads], lbase[:, heads], Ow, lw, torch.float16)
     assert att.status() == 0
+
+
+def test_many_ctas_with_refills_and_empty_trailing_units(att):
+    """A grid larger than the GPU, several pipeline refills per CTA and last iterations whose
+    units are partly empty (regression: an empty unit must not let a copy-issuing lane fall two
+    barrier phases behind the consumers)."""
+    from flashquest_b200.kernel.kv_quant import quantize_k_int4, quantize_v_int4
+    B, Hq, Hkv, S, D, page = 16, 24, 8, 4096, 128, 16
+    g = torch.Generator(device="cuda").manual_seed(9)
+    K = torch.randn(B, Hkv, S, D, device="cuda", generator=g).half()
+    V = torch.randn(B, Hkv, S, D, device="cuda", generator=g).half()
+    Q = torch.randn(B, Hq, 1, D, device="cuda", generator=g).half()
+    kv = quantize_k_int4(K, page) + quantize_v_int4(V)
+    cpu = [t[:1, :1].cpu() for t in kv]
+    for bucket in (77, 130, 200):
+        comp = torch.stack([torch.randperm(S // page, device="cuda", generator=g)[:bucket]
+                            for _ in range(B * Hq)]).reshape(B, Hq, 1, bucket).int()
+        outs = []
+        for n_split in (1, 2, 5):
+            for _ in range(3):
+                O, lse = att.compact(Q, *kv, selected_page_ids=comp, page_size=page, n_split=n_split)
+            torch.cuda.synchronize()
+            assert att.status() == 0, (bucket, n_split)
+            outs.append((O, lse))
+        for O, lse in outs[1:]:
+            assert (O.float() - outs[0][0].float()).abs().max() <= 1e-3
+            assert (lse - outs[0][1]).abs().max() <= 1e-4
+        Ow, lw = oracle.sparse_attn_int4(Q[:1, :3].cpu(), *cpu, selected_page_ids=comp[:1, :3].cpu(), page_size=page)
+        _close(outs[0][0][:1, :3], outs[0][1][:1, :3], Ow, lw, torch.float16)

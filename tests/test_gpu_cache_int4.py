@@ -96,9 +96,13 @@ def test_decode_step_dispatcher_matches_oracle(Cache):
                            head_pattern_layer=pattern, q_dtype=torch.float16)
     cache.update_quantized(K[:, :, :S0].cuda(), V[:, :, :S0].cuda(), 1)
     for t in range(S0, S0 + 2 * page + 2):
-        cache.update_quantized(K[:, :, t:t + 1].cuda(), V[:, :, t:t + 1].cuda(), 1)
         Q = torch.randn(B, Hq, 1, D, generator=torch.Generator().manual_seed(t)).half()
-        O, lse = step.attend(Q.cuda(), 1)
+        if t % 2 == 0:      # two equivalent routes: separate calls, or the one-call layer step
+            cache.update_quantized(K[:, :, t:t + 1].cuda(), V[:, :, t:t + 1].cuda(), 1)
+            O, lse = step.attend(Q.cuda(), 1)
+        else:
+            O, lse = step.step(K[:, :, t:t + 1].cuda(), V[:, :, t:t + 1].cuda(), Q.cuda(), 1)
+        assert cache.get_seq_length(1) == t + 1
         seen = t + 1
         n = seen - seen % page
         kv = oracle.quantize_k_int4(K[:, :, :n], page) + oracle.quantize_v_int4(V[:, :, :n])
@@ -110,9 +114,12 @@ def test_decode_step_dispatcher_matches_oracle(Cache):
         assert (O.float().cpu() - Ow).abs().max() < 2e-3, t
         assert (lse.cpu() - lw).abs().max() < 1e-3, t
     # empty cache: tail-only attention
-    cache.update_quantized(K[:, :, :3].cuda(), V[:, :, :3].cuda(), 0)
     Q = torch.randn(B, Hq, 1, D, generator=torch.Generator().manual_seed(1)).half()
-    O, lse = step.attend(Q.cuda(), 0)
+    O, lse = step.step(K[:, :, :3].cuda(), V[:, :, :3].cuda(), Q.cuda(), 0)
     Ow, lw = oracle.sparse_attn_int4(Q, *kv, selected_page_ids=torch.full((B, Hq, 1, 1), -1, dtype=torch.int32),
                                      page_size=page, K_partial=K[:, :, :3], V_partial=V[:, :, :3])
     assert (O.float().cpu() - Ow).abs().max() < 2e-3 and (lse.cpu() - lw).abs().max() < 1e-3
+    with pytest.raises(IndexError, match="layer_idx"):
+        step.step(K[:, :, :1].cuda(), V[:, :, :1].cuda(), Q.cuda(), 5)
+    with pytest.raises(RuntimeError, match="exceeds.*max_seq_len"):
+        step.step(K[:, :, :512].cuda(), V[:, :, :512].cuda(), Q.cuda(), 0)
