@@ -55,6 +55,9 @@ class DecodeParams(ctypes.Structure):
                 ("window", I), ("bucket", I), ("sm_scale", F), ("n_split", I)]
 
 
+_PROTOTYPES["fq_sparse_decode_int4_static"] = (I, [P, I, L, L, P, L, L, P, P, L, L, L, P, L, L, P, P, L, L,
+                                                  P, L, L, I, P, P, I, L, L, L, I,
+                                                  I, I, I, I, I, I, I, F, P, L, L, P, I, P])
 _PROTOTYPES["fq_decode_layer_int4"] = (I, [ctypes.POINTER(Int4CacheDesc), I, I, P, P, L, L, L, I, P, I, L, L,
                                           ctypes.POINTER(DecodeParams), P, P, P, P, P, Z, P])
 

@@ -887,3 +887,82 @@ extern "C" int fq_sparse_decode_int4(
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
+
+namespace fq {
+
+// ---------------------------------------------------------------------------------------
+// Split-K attention for callers that cannot hand over a workspace.
+//
+// Some hosts of this library have no way to obtain device memory at the point where they
+// call it: a binding from a runtime that owns no CUDA allocator, a serving loop that must
+// not touch cudaMalloc/cudaFree because those calls synchronise the whole device, a plugin
+// that is only given its inputs and outputs.  For them the split-K scratch (tickets +
+// per-split partial results) lives in this fixed array, which every GPU that loads the
+// library carries from load until the process exits.
+constexpr size_t FQ_STATIC_SCRATCH_BYTES = FQ_SPARSE_DECODE_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[FQ_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name
+// is only a handle for the runtime, not a device pointer, so the address is looked up once
+// per device (with that device current) and remembered.
+static void* static_scratch_ptr() {
+    constexpr int MAX_DEV = 64;
+    static void* ptrs[MAX_DEV] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= MAX_DEV) {
+        set_error("fq_sparse_decode_int4_static: cannot identify the current device");
+        return nullptr;
+    }
+    if (ptrs[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            set_error("fq_sparse_decode_int4_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        ptrs[dev] = ptr;
+    }
+    return ptrs[dev];
+}
+
+}  // namespace fq
+
+extern "C" int fq_sparse_decode_int4_static(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss,
+    int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, float* lse, int n_split, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_sparse_decode_int4_static";
+    FQ_CHECK_ARG(B > 0 && Hq > 0 && D > 0, FQ_ERR_ARG, "%s: bad sizes", fn);
+    if (n_split <= 0) n_split = fq_sparse_decode_default_splits(B, Hq, bucket, page);
+    FQ_CHECK_ARG(n_split <= 1024, FQ_ERR_ARG, "%s: n_split=%d must be at most 1024", fn, n_split);
+    const size_t need = fq_sparse_decode_workspace_bytes(B, Hq, D, n_split);
+    FQ_CHECK_ARG(need <= FQ_STATIC_SCRATCH_BYTES, FQ_ERR_WORKSPACE,
+                 "%s: B=%d x H_q=%d x n_split=%d x head_dim=%d needs %zu B of scratch, the built-in array holds %zu B; "
+                 "lower n_split or use fq_sparse_decode_int4 with a workspace of your own",
+                 fn, B, Hq, n_split, D, need, (size_t)FQ_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    if (n_split > 1) {
+        scratch = static_scratch_ptr();
+        if (scratch == nullptr) return FQ_ERR_CUDA;
+        // The array keeps whatever the previous call left in it; the per-row ticket words are
+        // the only part the kernel needs to find at zero.
+        const size_t tickets = ((size_t)B * Hq * 4 + 255) & ~(size_t)255;
+        cudaError_t e = cudaMemsetAsync(scratch, 0, tickets, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: clearing the tickets failed: %s", fn, cudaGetErrorString(e));
+    }
+    return fq_sparse_decode_int4(
+        Q, q_dtype, q_sb, q_sh, K_packed, kp_sb, kp_sh, K_scale, K_mn, km_sb, km_sh, km_sp,
+        V_packed, vp_sb, vp_sh, V_scale, V_mn, vm_sb, vm_sh, compact, cp_sb, cp_sh, bucket,
+        K_tail, V_tail, tail_dtype, tl_sb, tl_sh, tl_ss, tail_len,
+        B, Hq, Hkv, S_kv, P, D, page, sm_scale, O, o_sb, o_sh, lse,
+        scratch, n_split > 1 ? (size_t)FQ_STATIC_SCRATCH_BYTES : 0, n_split, stream);
+}

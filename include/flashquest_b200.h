@@ -170,6 +170,35 @@ int fq_sparse_decode_int4(
     void* O, int64_t o_sb, int64_t o_sh, float* lse,
     void* workspace, size_t workspace_bytes, int n_split, void* stream);
 
+/* Sparse decode attention with built-in scratch: same computation and arguments as
+ * fq_sparse_decode_int4, minus the workspace.  It has no counterpart in the reference; it
+ * exists for hosts that cannot supply device memory when they call in (a language binding
+ * without a CUDA allocator, a loop that must stay clear of cudaMalloc/cudaFree because they
+ * stall the device, a plugin that only receives its inputs and outputs).  The split-K scratch
+ * is a fixed array of FQ_SPARSE_DECODE_STATIC_SCRATCH_BYTES inside the library, resident on
+ * every GPU that loads it until the process ends.  The call allocates and frees nothing.
+ *   - Limit: fq_sparse_decode_workspace_bytes(B,Hq,D,n_split) must not exceed the array
+ *     (4 MiB: e.g. B*Hq*n_split <= 8000 at D = 128); larger requests return
+ *     FQ_ERR_WORKSPACE and touch nothing.  n_split <= 0 picks the default split count.
+ *   - The first call on a device looks up the array's device address; make that call
+ *     outside any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents; the entry
+ *     point clears the ticket words it needs at zero on `stream` before launching.  Two calls
+ *     whose work overlaps on the GPU (different streams) corrupt each other: serialise them.
+ */
+#define FQ_SPARSE_DECODE_STATIC_SCRATCH_BYTES (4u << 20)
+int fq_sparse_decode_int4_static(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss,
+    int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, float* lse, int n_split, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * One decode step of one layer on a persistent INT4 cache: append + score + select + attend.
  * Replaces, in one host call and four launches, what the reference's patched forward does
