@@ -55,6 +55,12 @@ class DecodeParams(ctypes.Structure):
                 ("window", I), ("bucket", I), ("sm_scale", F), ("n_split", I)]
 
 
+_PROTOTYPES["fq_wht"] = (I, [P, P, I, L, I, P])
+_PROTOTYPES["fq_quantize_turbo"] = (I, [P, L, L, L, I, P, L, L, L, I, I, I, I, I, I, P, L, L, L, P, L, L, L, P, L, L, L, P])
+_PROTOTYPES["fq_dequantize_turbo"] = (I, [P, L, L, L, P, L, L, L, P, L, L, L, I, I, I, I, P, L, L, L, P])
+_PROTOTYPES["fq_sparse_decode_turbo"] = (I, [P, I, L, L, P, L, L, L, P, L, L, L, P, L, L, P, L, L, L, P, L, L, L, P, L, L,
+                                            P, L, L, I, I, I, I, I, I, I, I, F, P, L, L, P, P, Z, I, P])
+_PROTOTYPES["fq_lse_merge"] = (I, [P, P, I, I, L, I, P, P, P])
 _PROTOTYPES["fq_sparse_decode_int4_static"] = (I, [P, I, L, L, P, L, L, P, P, L, L, L, P, L, L, P, P, L, L,
                                                   P, L, L, I, P, P, I, L, L, L, I,
                                                   I, I, I, I, I, I, I, F, P, L, L, P, I, P])

@@ -55,11 +55,7 @@ constexpr int ATT_STAGES = FQ_ATT_STAGES;
 constexpr int ATT_CTAS_PER_SM = FQ_ATT_CTAS_PER_SM;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
-#ifdef FQ_DEBUG_WAIT
-constexpr unsigned WAIT_SPIN_LIMIT = 1u << 16;
-#else
-constexpr unsigned WAIT_SPIN_LIMIT = 1u << 24;
-#endif   // bounded wait on a stage; then give up
+constexpr unsigned WAIT_SPIN_LIMIT = 1u << 24;   // bounded wait on a stage; then give up
 
 struct AttnParams {
     const void* Q; int64_t q_sb, q_sh;
@@ -110,12 +106,6 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-#ifdef FQ_DEBUG_WAIT
-__device__ int g_dbg[32];
-#define FQ_PROG(v) do { if (lane == 0) s_prog[warp] = (v); } while (0)
-#else
-#define FQ_PROG(v) do {} while (0)
-#endif
 #ifdef FQ_ATT_TRACE
 // Debug build only: per-CTA phase timestamps (globaltimer, ns) for timeline analysis.
 __device__ unsigned long long g_trace[4096 * 8];
@@ -158,17 +148,6 @@ __device__ __forceinline__ float nib_unscale(int k) { return k <= 5 ? pow2i(49 -
 
 // eight codes of one 32-bit word as fp32 operands (see the header comment)
 __device__ __forceinline__ void nib8(uint32_t w, float (&f)[8]) {
-#ifdef FQ_EXPERIMENT_NORMALS
-    f[0] = __uint_as_float((w & 0x0000000fu) | 0x3f800000u);
-    f[1] = __uint_as_float((w & 0x000000f0u) | 0x3f800000u);
-    f[2] = __uint_as_float((w & 0x00000f00u) | 0x3f800000u);
-    f[3] = __uint_as_float((w & 0x0000f000u) | 0x3f800000u);
-    f[4] = __uint_as_float((w & 0x000f0000u) | 0x3f800000u);
-    f[5] = __uint_as_float((w & 0x00700000u) | 0x3f800000u);
-    f[6] = __uint_as_float((w >> 24) | 0x3f800000u);
-    f[7] = __uint_as_float((w >> 28) | 0x3f800000u);
-    return;
-#endif
     f[0] = __uint_as_float(w & 0x0000000fu);
     f[1] = __uint_as_float(w & 0x000000f0u);
     f[2] = __uint_as_float(w & 0x00000f00u);
@@ -272,10 +251,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, qw = lane >> 3, l = lane & 7;
     const unsigned qmask = 0xffu << (8 * qw);
     const bool is_producer = warp == ATT_WARPS;
-#ifdef FQ_DEBUG_WAIT
-    __shared__ volatile int s_prog[ATT_WARPS + 1];
-    if (lane == 0) s_prog[warp] = -1;
-#endif
     FQ_TRACE(0);
 
     // ---- slice of the compact list owned by this CTA, in units ----
@@ -366,11 +341,7 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
             }
             timed_out = __any_sync(0xffffffffu, timed_out);
         }
-#ifdef FQ_DEBUG_WAIT
-        if (timed_out && lane == 0) atomicExch(p.status, -7000);
-#else
         if (timed_out && lane == 0) atomicExch(p.status, FQ_ERR_TIMEOUT);
-#endif
     } else {
         // =========================== consumer warps ===========================
         UnitCtx<DPL, TPL> ctx[2];     // metadata of the unit in hand and of the next one
@@ -527,16 +498,11 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
                 const unsigned parity = (unsigned)(it / ATT_STAGES) & 1u;
                 unsigned spins = 0;
                 bool gave_up = false;
-                FQ_PROG(10 * it + 1);
                 while (!mbar_try_wait(&full_bars[warp * ATT_STAGES + s_], parity)) {
                     if (++spins > WAIT_SPIN_LIMIT) { gave_up = true; break; }
                 }
-#ifdef FQ_DEBUG_WAIT
-                if (gave_up) atomicExch(p.status, -(8000 + it * 10 + warp));
-#endif
                 if (__any_sync(0xffffffffu, gave_up)) { timed_out = true; return; }
                 if (it == 0) FQ_TRACE(3);
-                FQ_PROG(10 * it + 2);
                 // the next unit's metadata is requested while this unit is being worked on
                 auto prefetch = [&]() {
                     if (it + 1 < n_iter) load_ctx(std::integral_constant<int, 1 - S>{}, it + 1);
@@ -548,7 +514,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
                 __syncwarp();                              // every lane is done reading this stage
                 fence_proxy_async();
                 if (lane == 0) mbar_arrive(&empty_bars[warp * ATT_STAGES + s_]);
-                FQ_PROG(10 * it + 3);
             });
         }
         if (timed_out && lane == 0) atomicExch(p.status, FQ_ERR_TIMEOUT);
@@ -764,14 +729,6 @@ static int launch_attn(const AttnParams& p, cudaStream_t st) {
 
 }  // namespace fq
 
-#ifdef FQ_DEBUG_WAIT
-extern "C" int fq_debug_read_dbg(int* dst) {
-    int rc = (int)cudaMemcpyFromSymbol(dst, fq::g_dbg, sizeof(int) * 32);
-    int zero[32] = {0};
-    cudaMemcpyToSymbol(fq::g_dbg, zero, sizeof(zero));
-    return rc;
-}
-#endif
 #ifdef FQ_ATT_TRACE
 extern "C" int fq_debug_read_trace(unsigned long long* dst, int n) {
     return (int)cudaMemcpyFromSymbol(dst, fq::g_trace, sizeof(unsigned long long) * n);

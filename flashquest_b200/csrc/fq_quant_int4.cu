@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
         const int t0 = page_idx * p.page;
         const int n_tok = min(p.page, p.n_quant - t0);
         // ---------------- K: per page, per channel ----------------
-        if (p.K_packed != nullptr) {
+        if (p.K_scale != nullptr) {      // K_packed may be NULL: metadata only
             float mn[8], mx[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) { mn[i] = INFINITY; mx[i] = -INFINITY; }
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
                 *reinterpret_cast<uint4*>(p.K_scale + mo) = make_uint4(s4[0], s4[1], s4[2], s4[3]);
                 *reinterpret_cast<uint4*>(p.K_mn + mo) = make_uint4(m4[0], m4[1], m4[2], m4[3]);
             }
-            for (int tt = ti; tt < n_tok; tt += TPI) {
+            for (int tt = ti; tt < n_tok && p.K_packed != nullptr; tt += TPI) {
                 float v[8];
                 load8<T>(stream_row<T>(Kh, Kn, p, b, h, t0 + tt) + 8 * c, v);
                 uint32_t w = 0;
@@ -241,9 +241,9 @@ extern "C" int fq_quantize_kv_int4(
     FQ_CHECK_ARG(n_head == 0 || n_quant == 0 || n_head < page, FQ_ERR_ARG,
                  "%s: a staged head (%d tokens) must be shorter than a page (%d)", fn, n_head, page);
     FQ_CHECK_ARG(dtype == FQ_F32 || dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: dtype code %d", fn, dtype);
-    const bool doK = K_packed != nullptr, doV = V_packed != nullptr;
+    const bool doK = K_packed != nullptr || K_scale != nullptr, doV = V_packed != nullptr;
     if (n_quant > 0) {
-        FQ_CHECK_ARG(doK || doV, FQ_ERR_ARG, "%s: neither K_packed nor V_packed given", fn);
+        FQ_CHECK_ARG(doK || doV, FQ_ERR_ARG, "%s: neither K nor V outputs given", fn);
         FQ_CHECK_ARG(!doK || (K_scale && K_mn && (K_new || n_new == 0)), FQ_ERR_ARG, "%s: K outputs/inputs missing", fn);
         FQ_CHECK_ARG(!doV || (V_scale && V_mn && (V_new || n_new == 0)), FQ_ERR_ARG, "%s: V outputs/inputs missing", fn);
     }

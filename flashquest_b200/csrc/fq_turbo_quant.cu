@@ -1,0 +1,280 @@
+// Walsh-Hadamard rotation and TurboQuant K3-V3 packing (3-bit Lloyd-Max codes in a 1-bit and
+// a 2-bit plane, per-token RMS scale).
+//
+// One warp owns one token row of D values; lane l holds the D/32 consecutive values starting
+// at l*D/32.  The butterfly stages with a stride inside a lane are register-only, the others
+// exchange with lane ^ (stride / values-per-lane) by shuffle.  Every stage is rounded to the
+// tensor's dtype exactly as the reference's eager ops do (kernel/wht.py:26-41), so results are
+// bit-identical.  HBM-bound: D*sizeof(T) in, 3*D/8 + 2 bytes out per token.
+#include "fq_common.cuh"
+
+namespace fq {
+
+// kernel/kv_quant.py:225-229
+__device__ __constant__ float c_turbo_codebook[8] = {-2.1519f, -1.3439f, -0.7560f, -0.2451f,
+                                                     0.2451f, 0.7560f, 1.3439f, 2.1519f};
+
+// In-place WHT of the row spread over the warp: v[j] is element lane*EPL + j.
+template <typename T, int EPL>
+__device__ __forceinline__ void wht_lanes(float (&v)[EPL], int lane, int D) {
+#pragma unroll
+    for (int h = 1; h < EPL; h <<= 1) {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            if ((j & h) == 0) {
+                const float a = v[j], b = v[j + h];
+                v[j] = Dt<T>::rn(__fadd_rn(a, b));
+                v[j + h] = Dt<T>::rn(__fsub_rn(a, b));
+            }
+        }
+    }
+    for (int h = EPL; h < D; h <<= 1) {
+        const int lo = h / EPL;                 // partner lane distance
+        const bool upper = (lane & lo) != 0;    // this lane holds the "b" half of the pair
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], lo);
+            v[j] = upper ? Dt<T>::rn(__fsub_rn(other, v[j])) : Dt<T>::rn(__fadd_rn(v[j], other));
+        }
+    }
+    const float cd = (float)sqrt((double)D);    // the divisor the reference uses: fp32(math.sqrt(D))
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = Dt<T>::rn(__fdiv_rn(v[j], cd));
+}
+
+template <typename T, int EPL>
+__device__ __forceinline__ void load_row(const T* row, int lane, int D, float (&v)[EPL]) {
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int i = lane * EPL + j;
+        v[j] = i < D ? Dt<T>::to_f32(row[i]) : 0.f;
+    }
+}
+
+// wht_along_head_dim (kernel/wht.py:17): rows of D values, dtype preserved.
+template <typename T, int EPL>
+__global__ void __launch_bounds__(128) wht_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n_rows, int D) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    float v[EPL];
+    load_row<T, EPL>(x + row * D, lane, D, v);
+    wht_lanes<T, EPL>(v, lane, D);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int i = lane * EPL + j;
+        if (i < D) out[row * D + i] = from_f32<T>(v[j]);
+    }
+}
+
+struct TurboParams {
+    const void *head, *nw;                       // token stream: head[0:n_head] ++ new
+    int64_t hd_sb, hd_sh, hd_ss, nw_sb, nw_sh, nw_ss;
+    int n_head, n_quant, D;
+    uint8_t *msb, *lsb;                          // (B,H,n,D/8), (B,H,n,D/4)
+    int64_t ms_sb, ms_sh, ms_ss, ls_sb, ls_sh, ls_ss;
+    uint16_t* scale;                             // (B,H,n) bf16
+    int64_t sc_sb, sc_sh, sc_ss;
+};
+
+// quantize_k_turbo / quantize_v_turbo without the raw page metadata
+// (kernel/kv_quant.py:327-405): rot = WHT(x) in x's dtype; s = max(sqrt(mean(rot^2)), 1e-6) in
+// fp32 (lane partial sums in ascending order, then an xor butterfly 16,8,4,2,1);
+// idx = first index of min |rot/s - c_j|; planes per kv_quant.py:253-279.
+template <typename T, int EPL>
+__global__ void __launch_bounds__(128) turbo_quant_kernel(TurboParams p) {
+    __shared__ uint8_t s_idx[4][1024];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= p.n_quant) return;
+    const int D = p.D;
+    const T* row = t < p.n_head
+        ? static_cast<const T*>(p.head) + b * p.hd_sb + h * p.hd_sh + (int64_t)t * p.hd_ss
+        : static_cast<const T*>(p.nw) + b * p.nw_sb + h * p.nw_sh + (int64_t)(t - p.n_head) * p.nw_ss;
+    float v[EPL];
+    load_row<T, EPL>(row, lane, D, v);
+    wht_lanes<T, EPL>(v, lane, D);
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) a = __fmaf_rn(v[j], v[j], a);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, off));
+    const float s = fmaxf(__fsqrt_rn(__fdiv_rn(a, (float)D)), 1e-6f);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int i = lane * EPL + j;
+        if (i < D) {
+            const float y = __fdiv_rn(v[j], s);
+            int best = 0;
+            float bd = fabsf(__fsub_rn(y, c_turbo_codebook[0]));
+#pragma unroll
+            for (int k = 1; k < 8; ++k) {
+                const float dk = fabsf(__fsub_rn(y, c_turbo_codebook[k]));
+                if (dk < bd) { bd = dk; best = k; }
+            }
+            s_idx[warp][i] = (uint8_t)best;
+        }
+    }
+    __syncwarp();
+    uint8_t* msb = p.msb + b * p.ms_sb + h * p.ms_sh + (int64_t)t * p.ms_ss;
+    uint8_t* lsb = p.lsb + b * p.ls_sb + h * p.ls_sh + (int64_t)t * p.ls_ss;
+    for (int k = lane; k < D / 8; k += 32) {
+        unsigned m = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m |= (unsigned)((s_idx[warp][8 * k + i] >> 2) & 1) << i;
+        msb[k] = (uint8_t)m;
+    }
+    for (int k = lane; k < D / 4; k += 32) {
+        unsigned m = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) m |= (unsigned)(s_idx[warp][4 * k + i] & 3) << (2 * i);
+        lsb[k] = (uint8_t)m;
+    }
+    if (lane == 0) p.scale[b * p.sc_sb + h * p.sc_sh + (int64_t)t * p.sc_ss] = f32_to_bf16_bits(s);
+}
+
+// dequantize_k_turbo / dequantize_v_turbo (kernel/kv_quant.py:366-378, :408-420):
+// codebook[idx] * scale in fp32, WHT in fp32, cast to bf16.
+template <int EPL>
+__global__ void __launch_bounds__(128) turbo_dequant_kernel(
+    const uint8_t* __restrict__ msb, int64_t ms_sb, int64_t ms_sh, int64_t ms_ss,
+    const uint8_t* __restrict__ lsb, int64_t ls_sb, int64_t ls_sh, int64_t ls_ss,
+    const uint16_t* __restrict__ scale, int64_t sc_sb, int64_t sc_sh, int64_t sc_ss,
+    int S, int D, uint16_t* __restrict__ out, int64_t o_sb, int64_t o_sh, int64_t o_ss) {
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= S) return;
+    const uint8_t* mrow = msb + b * ms_sb + h * ms_sh + (int64_t)t * ms_ss;
+    const uint8_t* lrow = lsb + b * ls_sb + h * ls_sh + (int64_t)t * ls_ss;
+    const float s = bf16_lo(scale[b * sc_sb + h * sc_sh + (int64_t)t * sc_ss]);
+    float v[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int i = lane * EPL + j;
+        v[j] = 0.f;
+        if (i < D) {
+            const unsigned m = (mrow[i >> 3] >> (i & 7)) & 1u;
+            const unsigned l2 = (lrow[i >> 2] >> (2 * (i & 3))) & 3u;
+            v[j] = __fmul_rn(c_turbo_codebook[(m << 2) | l2], s);
+        }
+    }
+    wht_lanes<float, EPL>(v, lane, D);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int i = lane * EPL + j;
+        if (i < D) out[b * o_sb + h * o_sh + (int64_t)t * o_ss + i] = f32_to_bf16_bits(v[j]);
+    }
+}
+
+template <typename T>
+static int launch_wht(const void* x, void* out, int64_t n_rows, int D, cudaStream_t st) {
+    const int epl = D >= 32 ? D / 32 : 1;
+    const unsigned blocks = (unsigned)((n_rows + 3) / 4);
+#define FQ_W(E) wht_kernel<T, E><<<blocks, 128, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(out), n_rows, D)
+    switch (epl) {
+        case 1: FQ_W(1); break;
+        case 2: FQ_W(2); break;
+        case 4: FQ_W(4); break;
+        case 8: FQ_W(8); break;
+        case 16: FQ_W(16); break;
+        default: FQ_W(32); break;
+    }
+#undef FQ_W
+    return FQ_OK;
+}
+
+template <typename T>
+static void launch_turbo(const TurboParams& p, dim3 grid, cudaStream_t st) {
+    const int epl = p.D >= 32 ? p.D / 32 : 1;
+#define FQ_T(E) turbo_quant_kernel<T, E><<<grid, 128, 0, st>>>(p)
+    switch (epl) {
+        case 1: FQ_T(1); break;
+        case 2: FQ_T(2); break;
+        case 4: FQ_T(4); break;
+        case 8: FQ_T(8); break;
+        case 16: FQ_T(16); break;
+        default: FQ_T(32); break;
+    }
+#undef FQ_T
+}
+
+}  // namespace fq
+
+extern "C" int fq_wht(const void* x, void* out, int dtype, int64_t n_rows, int D, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_wht";
+    FQ_CHECK_ARG(D > 0 && (D & (D - 1)) == 0, FQ_ERR_ARG, "%s: head_dim must be a positive power of 2, got %d", fn, D);
+    FQ_CHECK_ARG(D <= 1024, FQ_ERR_UNSUPPORTED, "%s: head_dim %d above 1024", fn, D);
+    FQ_CHECK_ARG(n_rows >= 0 && (n_rows == 0 || (x && out)), FQ_ERR_ARG, "%s: bad arguments", fn);
+    if (n_rows == 0) return FQ_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == FQ_F32) launch_wht<float>(x, out, n_rows, D, st);
+    else if (dtype == FQ_F16) launch_wht<__half>(x, out, n_rows, D, st);
+    else if (dtype == FQ_BF16) launch_wht<__nv_bfloat16>(x, out, n_rows, D, st);
+    else return fail(FQ_ERR_DTYPE, "%s: dtype code %d", fn, dtype);
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+
+extern "C" int fq_quantize_turbo(
+    const void* head, int64_t hd_sb, int64_t hd_sh, int64_t hd_ss, int n_head,
+    const void* nw, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    int dtype, int B, int H, int D, int n_quant,
+    uint8_t* msb, int64_t ms_sb, int64_t ms_sh, int64_t ms_ss,
+    uint8_t* lsb, int64_t ls_sb, int64_t ls_sh, int64_t ls_ss,
+    void* scale, int64_t sc_sb, int64_t sc_sh, int64_t sc_ss, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_quantize_turbo";
+    FQ_CHECK_ARG(B > 0 && H > 0 && n_head >= 0 && n_new >= 0 && n_quant >= 0 && n_quant <= n_head + n_new, FQ_ERR_ARG, "%s: bad sizes", fn);
+    FQ_CHECK_ARG(D % 8 == 0, FQ_ERR_ARG, "%s: requires head_dim multiple of 8; got %d", fn, D);
+    FQ_CHECK_ARG(D > 0 && (D & (D - 1)) == 0, FQ_ERR_ARG, "%s: head_dim must be a positive power of 2, got %d", fn, D);
+    FQ_CHECK_ARG(D <= 1024, FQ_ERR_UNSUPPORTED, "%s: head_dim %d above 1024", fn, D);
+    FQ_CHECK_ARG(dtype == FQ_F32 || dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: dtype code %d", fn, dtype);
+    if (n_quant == 0) return FQ_OK;
+    FQ_CHECK_ARG(msb && lsb && scale && (nw || n_new == 0) && (head || n_head == 0), FQ_ERR_ARG, "%s: null pointer", fn);
+    FQ_CHECK_ARG(B <= 65535 && H <= 65535, FQ_ERR_ARG, "%s: B and H must be <= 65535", fn);
+    TurboParams p;
+    p.head = head; p.nw = nw; p.hd_sb = hd_sb; p.hd_sh = hd_sh; p.hd_ss = hd_ss;
+    p.nw_sb = nw_sb; p.nw_sh = nw_sh; p.nw_ss = nw_ss; p.n_head = n_head; p.n_quant = n_quant; p.D = D;
+    p.msb = msb; p.lsb = lsb; p.ms_sb = ms_sb; p.ms_sh = ms_sh; p.ms_ss = ms_ss; p.ls_sb = ls_sb; p.ls_sh = ls_sh; p.ls_ss = ls_ss;
+    p.scale = static_cast<uint16_t*>(scale); p.sc_sb = sc_sb; p.sc_sh = sc_sh; p.sc_ss = sc_ss;
+    dim3 grid((unsigned)((n_quant + 3) / 4), (unsigned)H, (unsigned)B);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == FQ_F32) launch_turbo<float>(p, grid, st);
+    else if (dtype == FQ_F16) launch_turbo<__half>(p, grid, st);
+    else launch_turbo<__nv_bfloat16>(p, grid, st);
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+
+extern "C" int fq_dequantize_turbo(
+    const uint8_t* msb, int64_t ms_sb, int64_t ms_sh, int64_t ms_ss,
+    const uint8_t* lsb, int64_t ls_sb, int64_t ls_sh, int64_t ls_ss,
+    const void* scale, int64_t sc_sb, int64_t sc_sh, int64_t sc_ss,
+    int B, int H, int S, int D, void* out, int64_t o_sb, int64_t o_sh, int64_t o_ss, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_dequantize_turbo";
+    FQ_CHECK_ARG(B > 0 && H > 0 && S >= 0, FQ_ERR_ARG, "%s: bad sizes", fn);
+    FQ_CHECK_ARG(D >= 8 && (D & (D - 1)) == 0 && D <= 1024, FQ_ERR_UNSUPPORTED, "%s: head_dim %d must be a power of 2 in [8, 1024]", fn, D);
+    if (S == 0) return FQ_OK;
+    FQ_CHECK_ARG(msb && lsb && scale && out, FQ_ERR_ARG, "%s: null pointer", fn);
+    FQ_CHECK_ARG(B <= 65535 && H <= 65535, FQ_ERR_ARG, "%s: B and H must be <= 65535", fn);
+    dim3 grid((unsigned)((S + 3) / 4), (unsigned)H, (unsigned)B);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int epl = D >= 32 ? D / 32 : 1;
+#define FQ_D(E) turbo_dequant_kernel<E><<<grid, 128, 0, st>>>(msb, ms_sb, ms_sh, ms_ss, lsb, ls_sb, ls_sh, ls_ss, \
+        static_cast<const uint16_t*>(scale), sc_sb, sc_sh, sc_ss, S, D, static_cast<uint16_t*>(out), o_sb, o_sh, o_ss)
+    switch (epl) {
+        case 1: FQ_D(1); break;
+        case 2: FQ_D(2); break;
+        case 4: FQ_D(4); break;
+        case 8: FQ_D(8); break;
+        case 16: FQ_D(16); break;
+        default: FQ_D(32); break;
+    }
+#undef FQ_D
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}

@@ -119,3 +119,79 @@ def dequantize_k_int4(K_packed, scale, mn, page_size: int) -> torch.Tensor:
 def dequantize_v_int4(V_packed, scale, mn) -> torch.Tensor:
     """Inverse of quantize_v_int4 (kernel/kv_quant.py:208).  Returns bf16."""
     return _dequantize_int4(V_packed, scale, mn, 1, False)
+
+
+# === TurboQuant K3-V3 (kernel/kv_quant.py:225-420) ===
+
+K_TURBO_CODEBOOK_VALUES = (-2.1519, -1.3439, -0.7560, -0.2451, 0.2451, 0.7560, 1.3439, 2.1519)
+
+
+def quantize_turbo_into(x_new, n_quant, *, msb, lsb, scale, head=None, n_head=0):
+    """One launch of fq_quantize_turbo over the stream head[:n_head] ++ x_new, writing planes
+    and scales into (possibly strided) views."""
+    require_cuda(x_new)
+    B, H, n_new, D = x_new.shape
+    x_new = inner_contiguous(x_new)
+    z3 = (0, 0, 0)
+    hs = _strides3(head) if head is not None else z3
+    with torch.cuda.device(x_new.device):
+        check(lib().fq_quantize_turbo(
+            ptr(head), *hs, int(n_head), ptr(x_new), *_strides3(x_new), int(n_new),
+            dtype_code(x_new), B, H, D, int(n_quant),
+            ptr(msb), *_strides3(msb), ptr(lsb), *_strides3(lsb), ptr(scale), *_strides3(scale),
+            stream_ptr(x_new.device)))
+
+
+def _quantize_turbo(x: torch.Tensor, name: str):
+    B, H, S, D = x.shape
+    if D % 8 != 0:
+        raise ValueError(f"{name} requires head_dim multiple of 8; got {D}")
+    require_cuda(x)
+    msb = torch.empty(B, H, S, D // 8, dtype=torch.uint8, device=x.device)
+    lsb = torch.empty(B, H, S, D // 4, dtype=torch.uint8, device=x.device)
+    scale = torch.empty(B, H, S, 1, dtype=torch.bfloat16, device=x.device)
+    if S > 0:
+        quantize_turbo_into(x, S, msb=msb, lsb=lsb, scale=scale)
+    return msb, lsb, scale
+
+
+def quantize_k_turbo(K: torch.Tensor, page_size: int):
+    """TurboQuant K: WHT -> per-token RMS scale -> 3-bit Lloyd-Max -> bit-split planes, plus
+    the un-rotated per-page (scale, mn) used for page scoring (kernel/kv_quant.py:327).
+
+    Returns (K_msb (B,H,S,D/8) u8, K_lsb (B,H,S,D/4) u8, K_scale_turbo (B,H,S,1) bf16,
+             K_scale_raw (B,H,P,D) bf16, K_mn_raw (B,H,P,D) bf16)."""
+    B, H, S, D = K.shape
+    msb, lsb, scale = _quantize_turbo(K, "quantize_k_turbo")
+    P = (S + page_size - 1) // page_size
+    sr = torch.empty(B, H, P, D, dtype=torch.bfloat16, device=K.device)
+    mr = torch.empty(B, H, P, D, dtype=torch.bfloat16, device=K.device)
+    if S > 0:
+        quantize_kv_int4_into(K, None, page_size, S, K_scale=sr, K_mn=mr)     # metadata only
+    return msb, lsb, scale, sr, mr
+
+
+def quantize_v_turbo(V: torch.Tensor):
+    """TurboQuant V (K3-V3): same coding as K, no page metadata (kernel/kv_quant.py:381)."""
+    return _quantize_turbo(V, "quantize_v_turbo")
+
+
+def dequantize_k_turbo(K_msb, K_lsb, K_scale_turbo, head_dim: int) -> torch.Tensor:
+    """Inverse: planes -> codebook -> * scale -> inverse WHT -> bf16 (kernel/kv_quant.py:366)."""
+    require_cuda(K_msb, K_lsb, K_scale_turbo)
+    B, H, S, Dm = K_msb.shape
+    if Dm * 8 != head_dim:
+        raise ValueError(f"_unpack_bit_split: msb last axis {Dm} * 8 != head_dim {head_dim}")
+    if K_lsb.shape[-1] * 4 != head_dim:
+        raise ValueError(f"_unpack_bit_split: lsb last axis {K_lsb.shape[-1]} * 4 != head_dim {head_dim}")
+    K_msb, K_lsb = inner_contiguous(K_msb), inner_contiguous(K_lsb)
+    sc = K_scale_turbo
+    out = torch.empty(B, H, S, head_dim, dtype=torch.bfloat16, device=K_msb.device)
+    with torch.cuda.device(K_msb.device):
+        check(lib().fq_dequantize_turbo(
+            ptr(K_msb), *_strides3(K_msb), ptr(K_lsb), *_strides3(K_lsb), ptr(sc), *_strides3(sc),
+            B, H, S, head_dim, ptr(out), *_strides3(out), stream_ptr(K_msb.device)))
+    return out
+
+
+dequantize_v_turbo = dequantize_k_turbo

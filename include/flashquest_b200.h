@@ -61,7 +61,9 @@ int fq_device_status(void);
  * pointers already offset into the cache.  Stream token t >= n_quant is left in staging row
  * t - n_quant of stage_K/stage_V (unless those pointers are NULL); the head may BE the
  * staging buffer: with n_quant == 0 its tokens stay where they are and the new ones follow.
- * K or V (and their outputs) may be NULL to quantise only the other one.
+ * K or V (and their outputs) may be NULL to quantise only the other one; K_packed alone may
+ * be NULL to get only the per-page K metadata (what quantize_k_turbo keeps for scoring,
+ * kernel/kv_quant.py:355).
  *
  *   K_head,V_head : (B,H,n_head,D) dtype, strides hd_sb,hd_sh,hd_ss (elements)
  *   K_new, V_new  : (B,H,n_new,D)  dtype, strides nw_sb,nw_sh,nw_ss
@@ -198,6 +200,68 @@ int fq_sparse_decode_int4_static(
     int tail_len,
     int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
     void* O, int64_t o_sb, int64_t o_sh, float* lse, int n_split, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * TurboQuant K3-V3: Walsh-Hadamard rotation, 3-bit Lloyd-Max codes in bit planes.
+ *
+ * fq_wht — wht_along_head_dim (kernel/wht.py:17-41): normalised WHT along the last axis of
+ * n_rows dense rows of D values (D a power of two <= 1024), every butterfly stage and the
+ * final division by sqrt(D) rounded to `dtype` as the reference's eager ops do (bit-exact).
+ */
+int fq_wht(const void* x, void* out, int dtype, int64_t n_rows, int D, void* stream);
+
+/* quantize_k_turbo / quantize_v_turbo without the raw page metadata
+ * (kernel/kv_quant.py:327-405).  Token stream head[0:n_head] ++ new[0:n_new] as in
+ * fq_quantize_kv_int4; its first n_quant tokens are rotated (WHT in the input dtype), scaled
+ * by their RMS (fp32: each of 32 lanes sums the squares of its D/32 consecutive values in
+ * ascending order with fused multiply-adds, the lane sums combine by an xor butterfly
+ * 16,8,4,2,1; then /D, sqrt, clamp at 1e-6), coded to the nearest of the 8 codebook values
+ * (first index on ties) and split into planes: bit i of msb byte k = (idx[8k+i] >> 2) & 1,
+ * bits 2i..2i+1 of lsb byte k = idx[4k+i] & 3.  Bit-exact against the reference except where
+ * the summation order of the RMS moves a value across a code boundary.
+ *   msb (B,H,n_quant,D/8) u8, lsb (B,H,n_quant,D/4) u8, scale (B,H,n_quant) bf16.
+ * The per-page K metadata that quantize_k_turbo also returns (kv_quant.py:355) and the
+ * staging of left-over tokens come from fq_quantize_kv_int4 with K_packed = V_packed = NULL. */
+int fq_quantize_turbo(
+    const void* head, int64_t hd_sb, int64_t hd_sh, int64_t hd_ss, int n_head,
+    const void* nw, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    int dtype, int B, int H, int D, int n_quant,
+    uint8_t* msb, int64_t ms_sb, int64_t ms_sh, int64_t ms_ss,
+    uint8_t* lsb, int64_t ls_sb, int64_t ls_sh, int64_t ls_ss,
+    void* scale, int64_t sc_sb, int64_t sc_sh, int64_t sc_ss, void* stream);
+
+/* dequantize_k_turbo / dequantize_v_turbo (kernel/kv_quant.py:366-378, :408-420):
+ * codebook[idx]*scale in fp32, WHT in fp32, result bf16 (B,H,S,D) in the raw basis. */
+int fq_dequantize_turbo(
+    const uint8_t* msb, int64_t ms_sb, int64_t ms_sh, int64_t ms_ss,
+    const uint8_t* lsb, int64_t ls_sb, int64_t ls_sh, int64_t ls_ss,
+    const void* scale, int64_t sc_sb, int64_t sc_sh, int64_t sc_ss,
+    int B, int H, int S, int D, void* out, int64_t o_sb, int64_t o_sh, int64_t o_ss, void* stream);
+
+/* Sparse decode attention over K3-V3 planes in the ROTATED basis: the kernel part of
+ * flash_attn_sparse_turbo_fwd (kernel/sparse_turbo_fwd.py:110-346).  The caller rotates Q
+ * with fq_wht before and O after, as the reference wrapper does (:305, :343-344).
+ * Q_rot, O_rot (B,Hq,D) fp16|bf16; planes and scales as produced by fq_quantize_turbo
+ * (scale token stride 1); compact, lse, workspace, n_split as for fq_sparse_decode_int4.
+ * D in {64,128}; page a multiple of 16. */
+int fq_sparse_decode_turbo(
+    const void* Q_rot, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_msb, int64_t km_sb, int64_t km_sh, int64_t km_ss,
+    const uint8_t* K_lsb, int64_t kl_sb, int64_t kl_sh, int64_t kl_ss,
+    const void* K_scale, int64_t ks_sb, int64_t ks_sh,
+    const uint8_t* V_msb, int64_t vm_sb, int64_t vm_sh, int64_t vm_ss,
+    const uint8_t* V_lsb, int64_t vl_sb, int64_t vl_sh, int64_t vl_ss,
+    const void* V_scale, int64_t vs_sb, int64_t vs_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O_rot, int64_t o_sb, int64_t o_sh, float* lse,
+    void* workspace, size_t workspace_bytes, int n_split, void* stream);
+
+/* _merge_two_attentions (eager/llama_persistent_patch.py:50-61) for n partial results that
+ * share Q: O_parts (n,rows,D) dtype, lse_parts (n,rows) fp32 nats -> O (rows,D) dtype,
+ * lse (rows) fp32 or NULL.  Rows whose parts are all empty (lse = -inf) give O = 0. */
+int fq_lse_merge(const void* O_parts, const float* lse_parts, int dtype, int n, int64_t rows, int D,
+                 void* O, float* lse, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * One decode step of one layer on a persistent INT4 cache: append + score + select + attend.
