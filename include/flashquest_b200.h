@@ -264,6 +264,27 @@ int fq_lse_merge(const void* O_parts, const float* lse_parts, int dtype, int n, 
                  void* O, float* lse, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * AWQ W4A16 GEMV, several projections of the same input fused in one launch.
+ * Replaces fused_qkv_proj / fused_gate_up_proj (kernel/fused_proj.py:18-53), which in the
+ * reference call AutoAWQ 0.2.9 modules one after the other (third party, not part of the
+ * reference tree: parity is against a restatement of AutoAWQ's published GEMM format, not
+ * against reference outputs).  Layout per quant/awq_layout.py:18-44: qweight (K, N/8) int32,
+ * scales (K/G, N) fp16, qzeros (K/G, N/8) int32; w = (code - zero) * scale; `interleaved` != 0:
+ * nibble i of an int32 holds column 8c + {0,2,4,6,1,3,5,7}[i] (AutoAWQ GEMM order), else 8c + i.
+ *   x (M,K) fp16 dense, 1 <= M <= 8; arrays of n_proj (<= 4) HOST arrays holding device
+ *   pointers / sizes; bias NULL, or n_proj entries each NULL or (N[i]) fp16, added in fp32
+ *   before the rounding to fp16; y[i] (M,N[i]) fp16 dense.  fp32 accumulation.
+ *   k_split > 1 needs fq_awq_gemv_workspace_bytes(M, sum N, k_split) bytes whose leading
+ *   ticket words are zero (left zero again); k_split <= 0 is not accepted — ask
+ *   fq_awq_gemv_default_splits. */
+size_t fq_awq_gemv_workspace_bytes(int M, int N_total, int k_split);
+int fq_awq_gemv_default_splits(int K, int N_total, int group);
+int fq_awq_gemv(
+    const void* x, int M, int K, int group, int n_proj,
+    const int32_t* const* qweight, const void* const* scales, const int32_t* const* qzeros, const void* const* bias,
+    const int* N, void* const* y, int interleaved, void* workspace, size_t workspace_bytes, int k_split, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * One decode step of one layer on a persistent INT4 cache: append + score + select + attend.
  * Replaces, in one host call and four launches, what the reference's patched forward does
  * per layer and step around the projections (eager/llama_persistent_patch.py:193-245):

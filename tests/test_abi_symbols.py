@@ -1,0 +1,51 @@
+"""The shared library loads without a GPU and exports every function the header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "flashquest_b200.h")
+
+
+def _declared():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_path():
+    names = _declared()
+    for want in ("fq_quantize_kv_int4", "fq_page_scores_int4", "fq_select_pages", "fq_build_compact",
+                 "fq_sparse_decode_int4", "fq_sparse_decode_turbo", "fq_lse_merge", "fq_awq_gemv"):
+        assert want in names
+
+
+def test_library_exports_every_declared_symbol():
+    from flashquest_b200 import build
+    path = build.LIB
+    if not os.path.exists(path):
+        pytest.skip("library not built (python -m flashquest_b200.build)")
+    so = ctypes.CDLL(path)
+    missing = [n for n in _declared() if not hasattr(so, n)]
+    assert not missing, missing
+
+
+def test_bindings_cover_the_header():
+    from flashquest_b200 import _lib
+    assert sorted(_lib._PROTOTYPES) == _declared()
+
+
+def test_host_only_entry_points_answer_without_a_gpu():
+    from flashquest_b200 import build
+    path = build.LIB
+    if not os.path.exists(path):
+        pytest.skip("library not built")
+    so = ctypes.CDLL(path)
+    so.fq_version.restype = ctypes.c_char_p
+    assert so.fq_version()
+    so.fq_awq_gemv_workspace_bytes.restype = ctypes.c_size_t
+    assert so.fq_awq_gemv_workspace_bytes(1, 5120, 1) == 0
+    assert so.fq_awq_gemv_workspace_bytes(1, 5120, 4) >= 4 * 5120 * 4
+    assert 1 <= so.fq_awq_gemv_default_splits(3072, 5120, 128) <= 24
