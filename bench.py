@@ -22,6 +22,7 @@ import argparse
 import json
 import math
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -172,7 +173,7 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": "sparse-INT4 decode tokens/s at 32k ctx", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 accumulate over int4 KV (f64 in the port)",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
         "data": "synthetic", "config": workload_config(cfg, 1),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample_txt},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -180,11 +181,12 @@ def run_reference(args):
 
 
 def workload_config(cfg, n_gpus):
-    return {"workload": "BASELINE config 1: 28 layers x (page scores -> top-k+compact -> sparse INT4 attention), batch 1 per GPU",
+    name = "BASELINE config 1" if (cfg["layers"], cfg["B"], cfg["ctx"]) == (CFG["layers"], CFG["B"], CFG["ctx"]) else "variant of BASELINE config 1"
+    return {"workload": f"{name}: {cfg['layers']} layers x (page scores -> top-k+compact -> sparse INT4 attention), batch {cfg['B']} per GPU",
             "layers": cfg["layers"], "batch_per_gpu": cfg["B"], "q_heads": cfg["Hq"], "kv_heads": cfg["Hkv"],
             "head_dim": cfg["D"], "context": cfg["ctx"], "page_size": cfg["page"], "retention": cfg["retention"],
             "sinks": cfg["sinks"], "window_pages": cfg["window"], "sharding": f"batch x{n_gpus} (independent sequences)",
-            "l2": "inputs larger than L2 (1.15 GB cache, ~1 GB touched per step)"}
+            "l2": "inputs larger than L2 (%.2f GB cache)" % (cfg["layers"] * cfg["B"] * cfg["Hkv"] * cfg["ctx"] * (cfg["D"] + 2 * cfg["D"] * 2 // cfg["page"] + 4) / 1e9)}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -211,6 +213,8 @@ def run_ours(args):
         cfg["layers"] = args.layers
     if args.ctx:
         cfg["ctx"] = args.ctx
+    if args.batch:
+        cfg["B"] = args.batch
     Lr, B, Hq, Hkv, D, S, page = cfg["layers"], cfg["B"], cfg["Hq"], cfg["Hkv"], cfg["D"], cfg["ctx"], cfg["page"]
     extra = 256   # room for the tokens appended by the end-to-end run
     cache = PersistentInt4KVCache(batch_size=B, num_layers=Lr, num_kv_heads=Hkv, head_dim=D, max_seq_len=S + extra,
@@ -321,12 +325,15 @@ def run_ours(args):
     alg_bytes = union_pages * PAGE_ATTN_BYTES / Lr
     peak, peak_kind = measured_peak()
     achieved = alg_bytes / (attn_us * 1e-6) / 1e9
+    # DRAM bytes per launch from the committed ncu summary (config 1 only)
     traffic = None
-    try:
-        with open(os.path.join(ROOT, "profiles", "attention_int4_traffic.json")) as f:
-            traffic = json.load(f).get("dram_bytes_per_launch_config1")
-    except Exception:
-        pass
+    if (Lr, B, S) == (CFG["layers"], CFG["B"], CFG["ctx"]) or args.layers:
+        try:
+            with open(os.path.join(ROOT, "profiles", "sparse_decode_int4_config1.md")) as f:
+                mt = re.search(r"dram_bytes_per_launch:\s*(\d+)", f.read())
+            traffic = int(mt.group(1)) if mt and B == CFG["B"] and S == CFG["ctx"] else None
+        except OSError:
+            pass
     roofline = {"bound": "hbm", "kernel": "sparse_decode_int4_kernel", "achieved": achieved, "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                 "algorithmic_bytes_per_launch": alg_bytes, "per_head_bytes_per_launch": per_head_pages * PAGE_ATTN_BYTES / Lr,
@@ -347,7 +354,7 @@ def run_ours(args):
         print(json.dumps({
             "metric": "sparse-INT4 decode tokens/s at 32k ctx", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp32 accumulate over int4 KV, fp16 Q/O", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(cfg, world), "clocks": clk.summary(), "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu,
             "device_status": status,
@@ -400,6 +407,60 @@ def run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier):
             "path": "pinned host q/k/v -> QuestDecodeInt4.step (fq_decode_layer_int4: append+score+select+attend) per layer -> host O"}
 
 
+
+# --------------------------------------------------------------------------- secondary workload: AWQ GEMV
+
+def run_awq(args):
+    """AWQ W4A16 GEMV on the Llama-3.2-3B projection shapes (BASELINE config 3's linears): a CUDA
+    graph of 28 launches over 28 distinct seeded weight sets (1.5 GB, nothing served from L2)."""
+    import torch
+    from flashquest_b200 import _lib
+    from flashquest_b200.kernel.fused_proj import awq_gemv_fused
+    from flashquest_b200.quant import AWQLinear
+    _lib.lib()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    layers, group = 28, 128
+    peak, peak_kind = measured_peak()
+
+    def linear(K, N, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), dtype=torch.int32, device=dev, generator=g)
+        qz = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // group, N // 8), dtype=torch.int32, device=dev, generator=g)
+        sc = (torch.rand(K // group, N, device=dev, generator=g) * 0.019 + 0.001).half()
+        return AWQLinear(qw, sc, qz, group_size=group)
+
+    rows = []
+    for name, K, Ns in (("qkv", 3072, (3072, 1024, 1024)), ("gate_up", 3072, (8192, 8192)),
+                        ("down", 8192, (3072,)), ("o", 3072, (3072,))):
+        for M in (1, 4, 8):
+            projs = [[linear(K, N, 7 * li + i) for i, N in enumerate(Ns)] for li in range(layers)]
+            x = torch.randn(1, M, K, device=dev).half()
+            for pj in projs:
+                awq_gemv_fused(x, pj)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for pj in projs:
+                    awq_gemv_fused(x, pj)
+            for _ in range(max(args.warmup, 3)):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (args.steps * layers)
+            nbytes = sum(K * N // 2 + (K // group) * N * 2 + (K // group) * N // 2 for N in Ns)
+            rows.append({"proj": name, "M": M, "us_per_launch": round(us, 2), "bytes": nbytes,
+                         "GBs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / peak, 3)})
+            del projs, g
+    print(json.dumps({"metric": "AWQ W4A16 GEMV weight bytes per second", "unit": "GB/s", "workload": "awq",
+                      "peak": peak, "peak_kind": peak_kind, "steps": args.steps, "rows": rows,
+                      "device_status": _lib.lib().fq_device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -408,10 +469,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures)")
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (small captures)")
+    ap.add_argument("--batch", type=int, default=0, help="override the batch per GPU (profiles of batched shapes)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "awq"],
+                    help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "awq":
+        run_awq(args)
     else:
         run_ours(args)
 
