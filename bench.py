@@ -230,7 +230,7 @@ def run_ours(args):
         qs.append(torch.randn(B, Hq, 1, D, device=dev, generator=g.manual_seed(sq)).half())
         del K, V
     step = QuestDecodeInt4(cache, num_q_heads=Hq, retention=cfg["retention"], num_sinks=cfg["sinks"],
-                           window_pages=cfg["window"], q_dtype=torch.float16)
+                           window_pages=cfg["window"], q_dtype=torch.float16, n_split=args.n_split or None)
     Q = torch.stack(qs)       # (L,B,Hq,1,D)
 
     def one_step():
@@ -381,8 +381,7 @@ def run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier):
         dq.copy_(hq[i], non_blocking=True)
         dk.copy_(hk[i], non_blocking=True)
         dv.copy_(hv[i], non_blocking=True)
-        for li in range(Lr):
-            step.step(dk[li], dv[li], dq[li], li)       # append + score + select + attend, one call
+        step.step_all(dk, dv, dq)                      # every layer: append + score + select + attend
         out_host.copy_(step.O, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -404,7 +403,7 @@ def run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier):
     h2d = hq[0].numel() * 2 + hk[0].numel() * 2 + hv[0].numel() * 2
     return {"value": world * B * 1e3 / (ms / args.steps), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": ms / args.steps,
-            "path": "pinned host q/k/v -> QuestDecodeInt4.step (fq_decode_layer_int4: append+score+select+attend) per layer -> host O"}
+            "path": "pinned host q/k/v -> QuestDecodeInt4.step_all (fq_decode_step_int4: append+score+select+attend per layer) -> host O"}
 
 
 
@@ -470,6 +469,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small captures)")
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (small captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per GPU (profiles of batched shapes)")
+    ap.add_argument("--n-split", type=int, default=0, help="override the split-K factor of the attention kernel")
     ap.add_argument("--workload", default="decode", choices=["decode", "awq"],
                     help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

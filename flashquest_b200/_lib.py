@@ -70,6 +70,9 @@ _PROTOTYPES["fq_sparse_decode_int4_static"] = (I, [P, I, L, L, P, L, L, P, P, L,
 _PROTOTYPES["fq_decode_layer_int4"] = (I, [ctypes.POINTER(Int4CacheDesc), I, I, P, P, L, L, L, I, P, I, L, L,
                                           ctypes.POINTER(DecodeParams), P, P, P, P, P, Z, P])
 
+_PROTOTYPES["fq_decode_step_int4"] = (I, [ctypes.POINTER(Int4CacheDesc), I, P, P, P, L, L, L, L, I, P, I, L, L, L,
+                                         ctypes.POINTER(DecodeParams), Z, P, L, P, L, P, L, P, L, P, Z, Z, P])
+
 # entry points added by later sources register themselves here (name -> (restype, argtypes))
 EXTRA_PROTOTYPES: dict = {}
 

@@ -1,6 +1,7 @@
 // Error reporting, version and device status word of the C ABI.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "fq_common.cuh"
 
@@ -21,6 +22,14 @@ int fail(int code, const char* fmt, ...) {
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
     return code;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("FQ_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 
 __device__ int g_fq_status = 0;

@@ -36,18 +36,20 @@
 // No CTA ever waits for another one.
 #include <type_traits>
 
+#include <cstdlib>
+
 #include "fq_common.cuh"
 
 namespace fq {
 
 #ifndef FQ_ATT_WARPS
-#define FQ_ATT_WARPS 6      // consumer warps per CTA (one more warp issues the copies)
+#define FQ_ATT_WARPS 4      // consumer warps per CTA (one more warp issues the copies)
 #endif
 #ifndef FQ_ATT_STAGES
 #define FQ_ATT_STAGES 2
 #endif
 #ifndef FQ_ATT_CTAS_PER_SM
-#define FQ_ATT_CTAS_PER_SM 2
+#define FQ_ATT_CTAS_PER_SM 3
 #endif
 constexpr int ATT_WARPS = FQ_ATT_WARPS;
 constexpr int ATT_THREADS = (ATT_WARPS + 1) * 32;   // consumers + the producer warp
@@ -144,6 +146,7 @@ __device__ __forceinline__ float nib_scale(int k) {
     // nibble k <= 5 is read as code*2^(4k-149); nibbles 6,7 (after a shift) as *2^-149
     return k <= 5 ? pow2i(100 - 4 * k) : pow2i(100);
 }
+__device__ __forceinline__ float nib_descale(int k) { return k <= 5 ? pow2i(4 * k - 100) : pow2i(-100); }   // 1 / nib_scale
 __device__ __forceinline__ float nib_unscale(int k) { return k <= 5 ? pow2i(49 - 4 * k) : pow2i(49); }
 
 // eight codes of one 32-bit word as fp32 operands (see the header comment)
@@ -156,6 +159,15 @@ __device__ __forceinline__ void nib8(uint32_t w, float (&f)[8]) {
     f[5] = __uint_as_float(w & 0x00f00000u);
     f[6] = __uint_as_float(w >> 24);   // c6 + 16*c7
     f[7] = __uint_as_float(w >> 28);   // c7
+}
+
+// N consecutive 32-bit words from shared memory with the widest load (N = 1, 2, 4)
+template <int N>
+__device__ __forceinline__ void ld_words(const unsigned char* p, uint32_t (&w)[N]) {
+    static_assert(N == 1 || N == 2 || N == 4, "words per lane");
+    if constexpr (N == 1) { w[0] = *reinterpret_cast<const uint32_t*>(p); }
+    else if constexpr (N == 2) { const uint2 v = *reinterpret_cast<const uint2*>(p); w[0] = v.x; w[1] = v.y; }
+    else { const uint4 v = *reinterpret_cast<const uint4*>(p); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
 }
 
 // Transposing reduction over the 8 lanes of a quarter warp: in: N partial sums per lane,
@@ -231,6 +243,10 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     constexpr int DPL = D / 8;        // channels per lane
     constexpr int WPL = DPL / 8;      // 32-bit words per lane per token
     constexpr int TPL = TOK / 8;      // tokens per lane after the reduction
+#ifndef FQ_ATT_KT
+#define FQ_ATT_KT 1
+#endif
+    constexpr int KT = FQ_ATT_KT;     // tokens whose K dot products are interleaved
     constexpr int NSTATE = ATT_WARPS * 4 + ATT_WARPS;   // quarter-warp states + per-warp tail states
     constexpr int NBARS = 2 * ATT_WARPS * ATT_STAGES;
 
@@ -271,6 +287,8 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait();        // the page list (and, in the fused step, the freshly packed page) come from the previous kernels
+    pdl_trigger();
 
     const uint8_t* Kp = p.K_packed + b * p.kp_sb + hkv * p.kp_sh;
     const uint8_t* Vp = p.V_packed + b * p.vp_sb + hkv * p.vp_sh;
@@ -344,10 +362,8 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         if (timed_out && lane == 0) atomicExch(p.status, FQ_ERR_TIMEOUT);
     } else {
         // =========================== consumer warps ===========================
-        UnitCtx<DPL, TPL> ctx[2];     // metadata of the unit in hand and of the next one
-        auto load_ctx = [&](auto SC, int it) {
-            constexpr int S = decltype(SC)::value;
-            UnitCtx<DPL, TPL>& c = ctx[S];
+        UnitCtx<DPL, TPL> ctx_cur, ctx_nxt;     // metadata of the unit in hand and of the next one
+        auto load_ctx = [&](UnitCtx<DPL, TPL>& c, int it) {
             locate(it, warp * 4 + qw, c.page_id, c.tok0, c.n_tok);
             c.vs_raw = 0u; c.vm_raw = 0u;
             if (c.page_id < 0) return;
@@ -355,9 +371,18 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
             const uint16_t* kmr = Km + (int64_t)c.page_id * p.km_sp + DPL * l;
 #pragma unroll
             for (int j = 0; j < DPL / 8; ++j) {
+#ifdef FQ_EXP_NOMETA
+                c.ks[j] = make_uint4(0x3c003c00u + c.page_id, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u);
+                c.km[j] = make_uint4(0x3c003c00u, 0x3c003c00u + c.tok0, 0x3c003c00u, 0x3c003c00u);
+#else
                 c.ks[j] = ldg16(ksr + 8 * j);
                 c.km[j] = ldg16(kmr + 8 * j);
+#endif
             }
+#ifdef FQ_EXP_NOMETA
+            c.vs_raw = 0x3c003c00u + c.tok0; c.vm_raw = 0x3c003c00u;
+            return;
+#endif
             if (c.n_tok == TOK && TPL == 2) {
                 c.vs_raw = __ldg(reinterpret_cast<const uint32_t*>(Vs + c.tok0 + 2 * l));
                 c.vm_raw = __ldg(reinterpret_cast<const uint32_t*>(Vm + c.tok0 + 2 * l));
@@ -372,12 +397,12 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
                 }
             }
         };
-        if (n_iter > 0) load_ctx(std::integral_constant<int, 0>{}, 0);
+        ctx_cur.page_id = -1; ctx_nxt.page_id = -1;
+        if (n_iter > 0) load_ctx(ctx_cur, 0);
         FQ_TRACE(1);
 
         // ---- q slice of this lane, pre-multiplied by sm_scale*log2(e) and the nibble scale ----
-        float qn[DPL];    // for the K codes
-        float qr[DPL];    // plain q*sm_scale*log2e, for q.mn
+        float qn[DPL];    // q*sm_scale*log2e times the nibble pre-scale (a power of two)
         {
             const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + DPL * l;
             const float c = p.sm_scale * LOG2E;
@@ -386,10 +411,7 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
                 float v[8];
                 load8<QT>(qp + j, v);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    qr[j + e] = v[e] * c;
-                    qn[j + e] = qr[j + e] * nib_scale(e);
-                }
+                for (int e = 0; e < 8; ++e) qn[j + e] = v[e] * c * nib_scale(e);
             }
         }
         float* pvb = pv_bcast + (warp * 4 + qw) * TOK;
@@ -409,8 +431,9 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
                 for (int e = 0; e < 4; ++e) {
                     qs[j + 2 * e] = qn[j + 2 * e] * bf16_lo(sw[e]);
                     qs[j + 2 * e + 1] = qn[j + 2 * e + 1] * bf16_hi(sw[e]);
-                    qmn = fmaf(qr[j + 2 * e], bf16_lo(mw[e]), qmn);
-                    qmn = fmaf(qr[j + 2 * e + 1], bf16_hi(mw[e]), qmn);
+                    // q.mn with the pre-scaled q: the power of two moves to mn, the product is the same
+                    qmn = fmaf(qn[j + 2 * e], bf16_lo(mw[e]) * nib_descale(2 * e), qmn);
+                    qmn = fmaf(qn[j + 2 * e + 1], bf16_hi(mw[e]) * nib_descale(2 * e + 1), qmn);
                 }
                 qs[j + 7] = fmaf(-16.f, qs[j + 6], qs[j + 7]);   // c7 rides on (c6 + 16 c7)
             }
@@ -418,19 +441,29 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
             prefetch();
 
             float sdot[TOK];
+            // KT tokens at a time, one accumulator pair each: KT independent fma chains
 #pragma unroll
-            for (int t = 0; t < TOK; ++t) {
-                float2 a = make_float2(0.f, 0.f);
+            for (int t0 = 0; t0 < TOK; t0 += KT) {
+                uint32_t w[KT][WPL];
+#pragma unroll
+                for (int tt = 0; tt < KT; ++tt) ld_words<WPL>(u + L::K_OFF + (t0 + tt) * L::ROW + 4 * WPL * l, w[tt]);
+                float2 a[KT];
+#pragma unroll
+                for (int tt = 0; tt < KT; ++tt) a[tt] = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int wd = 0; wd < WPL; ++wd) {
-                    const uint32_t w = *reinterpret_cast<const uint32_t*>(u + L::K_OFF + t * L::ROW + 4 * (WPL * l + wd));
-                    float f[8];
-                    nib8(w, f);
+                    float f[KT][8];
 #pragma unroll
-                    for (int e = 0; e < 8; e += 2)
-                        a = __ffma2_rn(make_float2(f[e], f[e + 1]), make_float2(qs[8 * wd + e], qs[8 * wd + e + 1]), a);
+                    for (int tt = 0; tt < KT; ++tt) nib8(w[tt][wd], f[tt]);
+#pragma unroll
+                    for (int e = 0; e < 8; e += 2) {
+                        const float2 q2 = make_float2(qs[8 * wd + e], qs[8 * wd + e + 1]);
+#pragma unroll
+                        for (int tt = 0; tt < KT; ++tt) a[tt] = __ffma2_rn(make_float2(f[tt][e], f[tt][e + 1]), q2, a[tt]);
+                    }
                 }
-                sdot[t] = a.x + a.y;
+#pragma unroll
+                for (int tt = 0; tt < KT; ++tt) sdot[t0 + tt] = a[tt].x + a[tt].y;
             }
             qw_transpose_reduce<TOK>(sdot, l, qmask);
 
@@ -473,11 +506,12 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
                 for (int tt = 0; tt < 4; ++tt) {
                     const int t = t4 + tt;
                     const float2 pp = make_float2(pv[tt], pv[tt]);
+                    uint32_t wv[WPL];
+                    ld_words<WPL>(u + L::V_OFF + t * L::ROW + 4 * WPL * l, wv);
 #pragma unroll
                     for (int wd = 0; wd < WPL; ++wd) {
-                        const uint32_t w = *reinterpret_cast<const uint32_t*>(u + L::V_OFF + t * L::ROW + 4 * (WPL * l + wd));
                         float f[8];
-                        nib8(w, f);
+                        nib8(wv[wd], f);
 #pragma unroll
                         for (int e = 0; e < 8; e += 2)
                             acc[4 * wd + e / 2] = __ffma2_rn(make_float2(f[e], f[e + 1]), pp, acc[4 * wd + e / 2]);
@@ -489,32 +523,28 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
 
 
         // ---- main loop: wait for the stage, consume it, release it to the producer ----
-        for (int it0 = 0; it0 < n_iter && !timed_out; it0 += 2) {
-            static_for<2>([&](auto SC) {
-                constexpr int S = decltype(SC)::value;
-                const int it = it0 + S;
-                if (it >= n_iter || timed_out) return;
-                const int s_ = it % ATT_STAGES;
-                const unsigned parity = (unsigned)(it / ATT_STAGES) & 1u;
-                unsigned spins = 0;
-                bool gave_up = false;
-                while (!mbar_try_wait(&full_bars[warp * ATT_STAGES + s_], parity)) {
-                    if (++spins > WAIT_SPIN_LIMIT) { gave_up = true; break; }
-                }
-                if (__any_sync(0xffffffffu, gave_up)) { timed_out = true; return; }
-                if (it == 0) FQ_TRACE(3);
-                // the next unit's metadata is requested while this unit is being worked on
-                auto prefetch = [&]() {
-                    if (it + 1 < n_iter) load_ctx(std::integral_constant<int, 1 - S>{}, it + 1);
-                };
-                if (ctx[S].page_id >= 0)                   // uniform inside the quarter warp
-                    compute_unit(stage_base + ((s_ * ATT_WARPS + warp) * 4 + qw) * L::STRIDE, ctx[S], prefetch);
-                else
-                    prefetch();
-                __syncwarp();                              // every lane is done reading this stage
-                fence_proxy_async();
-                if (lane == 0) mbar_arrive(&empty_bars[warp * ATT_STAGES + s_]);
-            });
+        for (int it = 0; it < n_iter && !timed_out; ++it) {
+            const int s_ = it % ATT_STAGES;
+            const unsigned parity = (unsigned)(it / ATT_STAGES) & 1u;
+            unsigned spins = 0;
+            bool gave_up = false;
+            while (!mbar_try_wait(&full_bars[warp * ATT_STAGES + s_], parity)) {
+                if (++spins > WAIT_SPIN_LIMIT) { gave_up = true; break; }
+            }
+            if (__any_sync(0xffffffffu, gave_up)) { timed_out = true; break; }
+            if (it == 0) FQ_TRACE(3);
+            // the next unit's metadata is requested while this unit is being worked on
+            auto prefetch = [&]() {
+                if (it + 1 < n_iter) load_ctx(ctx_nxt, it + 1);
+            };
+            if (ctx_cur.page_id >= 0)                  // uniform inside the quarter warp
+                compute_unit(stage_base + ((s_ * ATT_WARPS + warp) * 4 + qw) * L::STRIDE, ctx_cur, prefetch);
+            else
+                prefetch();
+            __syncwarp();                              // every lane is done reading this stage
+            fence_proxy_async();
+            if (lane == 0) mbar_arrive(&empty_bars[warp * ATT_STAGES + s_]);
+            ctx_cur = ctx_nxt;
         }
         if (timed_out && lane == 0) atomicExch(p.status, FQ_ERR_TIMEOUT);
     }
@@ -718,12 +748,18 @@ static int launch_attn(const AttnParams& p, cudaStream_t st) {
     static_assert((size_t)ATT_STAGES * ATT_WARPS * 4 * UnitLayout<D, TOK>::STRIDE >=
                   (size_t)(ATT_WARPS * 5) * D * 4, "merge area must fit in the staging area");
     auto kern = sparse_decode_int4_kernel<QT, D, TOK>;
-    if (smem > 48 * 1024 - 256) {
+    constexpr int MAX_DEV = 64;
+    static bool prepared[MAX_DEV] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return fail(FQ_ERR_CUDA, "fq_sparse_decode_int4: cannot identify the current device");
+    if (!prepared[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "fq_sparse_decode_int4: cannot reserve %zu B of shared memory: %s", smem, cudaGetErrorString(e));
+        prepared[dev] = true;
     }
     dim3 grid((unsigned)p.n_split, (unsigned)p.Hq, (unsigned)p.B);
-    kern<<<grid, ATT_THREADS, smem, st>>>(p);
+    cudaError_t e = launch_k(kern, grid, dim3(ATT_THREADS), smem, st, p);
+    if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "fq_sparse_decode_int4: launch failed: %s", cudaGetErrorString(e));
     return FQ_OK;
 }
 

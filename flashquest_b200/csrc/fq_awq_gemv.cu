@@ -97,7 +97,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
     const int n_chunks = g_end - g_begin;
     const int G = p.group;
 
-    auto issue = [&](int chunk) {
+    // weights of a chunk (they never change: safe to request before the previous kernel is done)
+    auto issue_w = [&](int chunk) {
         const int g = g_begin + chunk, st = chunk % GEMV_STAGES;
         uint32_t* dst = s_w + st * GEMV_STAGE_WORDS;
         const int32_t* src = pr.qweight + (int64_t)g * G * npk + pk0;
@@ -117,7 +118,10 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
                 for (int r = r0; r < G; r += 4, d += 4 * GEMV_PACKS, sp += 4 * (int64_t)npk) cp_async4(d, sp);
             }
         }
-        // activations of the group, fp16 as they are: M rows of G halves (16-byte pieces)
+    };
+    // activations of the group, fp16 as they are: M rows of G halves (16-byte pieces)
+    auto issue_x = [&](int chunk) {
+        const int g = g_begin + chunk, st = chunk % GEMV_STAGES;
         for (int i = tid; i < M * (G / 8); i += GEMV_THREADS) {
             const int m = i / (G / 8), q = i % (G / 8);
             if (m < p.M) cp_async16(s_xh + (st * M + m) * GEMV_ROWS + q * 8, p.x + (int64_t)m * p.K + (int64_t)g * G + q * 8);
@@ -125,9 +129,14 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
     };
 
 #pragma unroll
+    for (int s = 0; s < GEMV_STAGES - 1; ++s)
+        if (s < n_chunks) issue_w(s);
+    pdl_wait();        // x comes from the previous kernel
+    pdl_trigger();
+#pragma unroll
     for (int s = 0; s < GEMV_STAGES - 1; ++s) {
-        if (s < n_chunks) issue(s);
-        cp_async_commit();
+        if (s < n_chunks) issue_x(s);
+        cp_async_commit();      // the first group also holds the weights of the later prologue stages: waits are only stricter
     }
 
     float yacc[M][8];
@@ -146,7 +155,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
         }
         cp_async_wait<GEMV_STAGES - 2>();
         __syncthreads();                 // chunk ch has landed for everybody; chunk ch-1 is consumed
-        if (ch + GEMV_STAGES - 1 < n_chunks) issue(ch + GEMV_STAGES - 1);
+        if (ch + GEMV_STAGES - 1 < n_chunks) { issue_w(ch + GEMV_STAGES - 1); issue_x(ch + GEMV_STAGES - 1); }
         cp_async_commit();
         // x of the group: fp16 -> fp32 * 2^100, duplicated; sum per row of x (fixed order)
         if (warp < M) {
@@ -375,7 +384,7 @@ extern "C" int fq_awq_gemv(
             if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve %zu B of shared memory: %s", fn, smem, cudaGetErrorString(e)); \
             if (dev >= 0 && dev < 64) attr_set[dev] = true;                                                  \
         }                                                                                                    \
-        awq_gemv_kernel<MV><<<grid, GEMV_THREADS, smem, st>>>(p);                                            \
+        launch_k(awq_gemv_kernel<MV>, grid, dim3(GEMV_THREADS), smem, st, p);                                          \
     } while (0)
     if (Mp == 1) FQ_GEMV(1);
     else if (Mp == 2) FQ_GEMV(2);

@@ -25,6 +25,32 @@ int fail(int code, const char* fmt, ...);
             return fq::fail(FQ_ERR_CUDA, "%s: launch failed: %s", (name), cudaGetErrorString(e__)); \
     } while (0)
 
+// ---- programmatic dependent launch ----
+// Every kernel of the decode chain is launched with programmatic stream serialisation: its
+// CTAs may become resident while the previous kernel of the stream is still draining, run
+// their prologue (index arithmetic, barrier set-up, loads of data that is older than the
+// previous kernel) and block in pdl_wait() until the previous kernel has completed and its
+// writes are visible.  pdl_trigger() comes right after the wait in every kernel, so at most
+// two kernels of a chain overlap and whatever a kernel reads before its wait must have been
+// written at least two kernels earlier.  FQ_PDL=0 in the environment turns the attribute off.
+bool pdl_enabled();
+
+template <typename... KP, typename... A>
+inline cudaError_t launch_k(void (*kernel)(KP...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at{};
+    at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &at; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<A&&>(args)...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // Device-side status word of the current device: kernels that wait (mbarrier) record a

@@ -70,3 +70,32 @@ extern "C" int fq_decode_layer_int4(
         B, Hq, Hkv, completed, P, D, page, prm->sm_scale,
         O, (int64_t)Hq * D, D, lse, workspace, workspace_bytes, n_split, stream);
 }
+
+extern "C" int fq_decode_step_int4(
+    const fq_int4_cache* c, int n_layers, const int* seen,
+    const void* K_new, const void* V_new, int64_t nw_sl, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    const void* Q, int q_dtype, int64_t q_sl, int64_t q_sb, int64_t q_sh,
+    const fq_decode_params* prm, size_t prm_stride,
+    float* scores, int64_t sc_sl, int32_t* compact, int64_t cp_sl, void* O, int64_t o_sl, float* lse, int64_t lse_sl,
+    void* workspace, size_t ws_sl, size_t workspace_bytes, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_decode_step_int4";
+    FQ_CHECK_ARG(c && prm && seen, FQ_ERR_ARG, "%s: null descriptor", fn);
+    FQ_CHECK_ARG(n_layers >= 0 && n_layers <= c->L, FQ_ERR_ARG, "%s: %d layers, the cache has %d", fn, n_layers, c->L);
+    FQ_CHECK_ARG(n_layers <= 1 || ws_sl >= workspace_bytes, FQ_ERR_WORKSPACE,
+                 "%s: the per-layer workspaces overlap (stride %zu B < %zu B)", fn, ws_sl, workspace_bytes);
+    const size_t kv_esz = 2, q_esz = q_dtype == FQ_F32 ? 4 : 2;
+    for (int l = 0; l < n_layers; ++l) {
+        const fq_decode_params* pl = reinterpret_cast<const fq_decode_params*>(reinterpret_cast<const char*>(prm) + (size_t)l * prm_stride);
+        const int rc = fq_decode_layer_int4(
+            c, l, seen[l],
+            K_new ? static_cast<const char*>(K_new) + (size_t)l * nw_sl * kv_esz : nullptr,
+            V_new ? static_cast<const char*>(V_new) + (size_t)l * nw_sl * kv_esz : nullptr, nw_sb, nw_sh, nw_ss, n_new,
+            static_cast<const char*>(Q) + (size_t)l * q_sl * q_esz, q_dtype, q_sb, q_sh, pl,
+            scores + l * sc_sl, compact + l * cp_sl, static_cast<char*>(O) + (size_t)l * o_sl * q_esz,
+            lse ? lse + l * lse_sl : nullptr,
+            workspace ? static_cast<char*>(workspace) + (size_t)l * ws_sl : nullptr, workspace_bytes, stream);
+        if (rc != FQ_OK) return rc;
+    }
+    return FQ_OK;
+}

@@ -51,6 +51,8 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
     const T* Kn = static_cast<const T*>(p.K_new);
     const T* Vh = static_cast<const T*>(p.V_head);
     const T* Vn = static_cast<const T*>(p.V_new);
+    pdl_wait();        // inputs and the staging rows may come from the previous kernel
+    pdl_trigger();
 
     if (page_idx < p.n_pages) {
         const int t0 = page_idx * p.page;
@@ -276,9 +278,9 @@ extern "C" int fq_quantize_kv_int4(
 
     dim3 grid((unsigned)max(1, (p.n_pages + 3) / 4), (unsigned)H, (unsigned)B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == FQ_F32) quant_int4_kernel<float><<<grid, 128, 0, st>>>(p);
-    else if (dtype == FQ_F16) quant_int4_kernel<__half><<<grid, 128, 0, st>>>(p);
-    else quant_int4_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(p);
+    if (dtype == FQ_F32) launch_k(quant_int4_kernel<float>, grid, dim3(128), 0, st, p);
+    else if (dtype == FQ_F16) launch_k(quant_int4_kernel<__half>, grid, dim3(128), 0, st, p);
+    else launch_k(quant_int4_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, p);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }

@@ -31,6 +31,8 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
     const int l = lane & 7, qw = lane >> 3;
     const int n_chunks = D >> 3;
     const int nr = min(NR, n_rep - head_off);   // heads actually present in this pass
+    pdl_wait();        // Q and the newest metadata row come from the kernels before this one
+    pdl_trigger();
 
     // Metadata loads of every page this quarter warp will score are issued first, the q loads
     // after them, so the two global-memory latencies overlap instead of adding up.
@@ -121,9 +123,9 @@ static void launch_scores(int CH, dim3 grid, cudaStream_t st, const void* Q, int
                           const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
                           int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh) {
 #define FQ_LAUNCH_SC(CHV)                                                                              \
-    page_scores_kernel<QT, NR, CHV><<<grid, SCORE_THREADS, 0, st>>>(                                   \
-        static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),                  \
-        static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh)
+    launch_k(page_scores_kernel<QT, NR, CHV>, grid, dim3(SCORE_THREADS), 0, st,                        \
+             static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),             \
+             static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh)
     if (CH == 1) FQ_LAUNCH_SC(1);
     else if (CH == 2) FQ_LAUNCH_SC(2);
     else FQ_LAUNCH_SC(4);

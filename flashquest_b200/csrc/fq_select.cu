@@ -71,6 +71,8 @@ __global__ void select_pages_kernel(
     const int T_ = blockDim.x;
     const float* row = scores + b * sc_sb + h * sc_sh;
     auto key_at = [&](int i) -> unsigned { return SMEM_KEYS ? s_keys[i] : score_key(row[i]); };
+    pdl_wait();        // the scores come from the previous kernel
+    pdl_trigger();
 
     // ---- load the row once; block min / max of the keys ----
     unsigned kmin = 0xffffffffu, kmax = 0u;
@@ -314,11 +316,11 @@ extern "C" int fq_select_pages(
             cudaError_t e = cudaFuncSetAttribute(select_pages_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve %zu B of shared memory: %s", fn, smem, cudaGetErrorString(e));
         }
-        select_pages_kernel<true><<<grid, select_threads(P), smem, st>>>(
+        launch_k(select_pages_kernel<true>, grid, dim3(select_threads(P)), smem, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
             mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count);
     } else {
-        select_pages_kernel<false><<<grid, select_threads(P), 0, st>>>(
+        launch_k(select_pages_kernel<false>, grid, dim3(select_threads(P)), 0, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
             mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count);
     }

@@ -102,6 +102,38 @@ class QuestDecodeInt4:
         self.launches += 4
         return O.unsqueeze(2), lse.unsqueeze(2)
 
+    def step_all(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor):
+        """step() for every layer in ONE foreign call (fq_decode_step_int4): k_new, v_new
+        (L,B,H_kv,n,D) in the cache's dtype, q (L,B,H_q,1,D).  For callers that hold all layers'
+        projections at once (stacked independent layers); returns (O (L,B,H_q,1,D), lse (L,B,H_q,1))."""
+        c = self.cache
+        Ln = c.num_layers
+        n_new = k_new.shape[3]
+        if k_new.shape[0] != Ln or q.shape[0] != Ln:
+            raise ValueError(f"expected {Ln} layers, got {k_new.shape[0]} / {q.shape[0]}")
+        for li in range(Ln):
+            if c._seen_tokens[li] + n_new > c.max_seq_len:
+                raise RuntimeError(f"PersistentInt4KVCache: seen+new={c._seen_tokens[li] + n_new} exceeds max_seq_len={c.max_seq_len}")
+        if k_new.dtype != c.dtype or v_new.dtype != c.dtype:
+            k_new, v_new = k_new.to(c.dtype), v_new.to(c.dtype)
+        if k_new.stride(4) != 1 or v_new.stride() != k_new.stride():
+            k_new, v_new = k_new.contiguous(), v_new.contiguous()
+        q4 = q.reshape(Ln, self.B, self.Hq, self.D)
+        if q4.stride(3) != 1:
+            q4 = q4.contiguous()
+        seen = (ctypes.c_int * Ln)(*c._seen_tokens[:Ln])
+        check(lib().fq_decode_step_int4(
+            ctypes.byref(self._cdesc), Ln, seen,
+            ptr(k_new), ptr(v_new), k_new.stride(0), k_new.stride(1), k_new.stride(2), k_new.stride(3), n_new,
+            ptr(q4), dtype_code(q4), q4.stride(0), q4.stride(1), q4.stride(2), ctypes.byref(self._prm), 0,
+            ptr(self.scores), self.scores.stride(0), ptr(self.compact), self.compact.stride(0),
+            ptr(self.O), self.O.stride(0), ptr(self.lse), self.lse.stride(0),
+            ptr(self.workspace), self.workspace.stride(0), self.workspace.shape[1], stream_ptr(self.device)))
+        for li in range(Ln):
+            c._seen_tokens[li] += n_new
+        self.launches += 4 * Ln
+        return self.O.unsqueeze(3), self.lse.unsqueeze(3)
+
     def attend(self, q: torch.Tensor, layer_idx: int):
         """q (B,H_q,1,D) or (B,H_q,D), the cache's dtype family (fp16/bf16).  Returns views
         (O (B,H_q,1,D), lse (B,H_q,1)) of preallocated per-layer buffers."""

@@ -332,6 +332,23 @@ int fq_decode_layer_int4(
     float* scores, int32_t* compact, void* O, float* lse,
     void* workspace, size_t workspace_bytes, void* stream);
 
+/* fq_decode_layer_int4 for layers [0, n_layers) in one foreign call — the layer loop of the
+ * caller (the decoder-layer loop around eager/llama_persistent_patch.py:164-305, or
+ * BASELINE-style stacked independent layers) without one host round trip per layer.  Every
+ * per-layer array is addressed as base + layer * stride: K_new/V_new stride nw_sl, Q stride q_sl
+ * (elements), scores stride sc_sl, compact stride cp_sl, O stride o_sl, lse stride lse_sl
+ * (elements), workspace stride ws_sl (bytes; each layer needs its own split-K workspace).
+ * seen[layer] (host array) is the number of tokens already in that layer; params is one
+ * struct for all layers (params_stride 0) or an array of structs params_stride bytes apart.
+ * Stops at the first failing layer and returns its error. */
+int fq_decode_step_int4(
+    const fq_int4_cache* cache, int n_layers, const int* seen,
+    const void* K_new, const void* V_new, int64_t nw_sl, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    const void* Q, int q_dtype, int64_t q_sl, int64_t q_sb, int64_t q_sh,
+    const fq_decode_params* params, size_t params_stride,
+    float* scores, int64_t sc_sl, int32_t* compact, int64_t cp_sl, void* O, int64_t o_sl, float* lse, int64_t lse_sl,
+    void* workspace, size_t ws_sl, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import oracle
-from tests._util import bit_equal, make_kv
+from tests._util import bit_equal, make_kv, make_q
 
 pytestmark = pytest.mark.gpu
 
@@ -123,3 +123,34 @@ def test_decode_step_dispatcher_matches_oracle(Cache):
         step.step(K[:, :, :1].cuda(), V[:, :, :1].cuda(), Q.cuda(), 5)
     with pytest.raises(RuntimeError, match="exceeds.*max_seq_len"):
         step.step(K[:, :, :512].cuda(), V[:, :, :512].cuda(), Q.cuda(), 0)
+
+
+def test_step_all_equals_per_layer_steps():
+    """fq_decode_step_int4 (all layers in one call) == fq_decode_layer_int4 layer by layer, bit for bit,
+    with layers at different lengths (one of them crossing a page boundary)."""
+    from flashquest_b200.cache.persistent_int4 import PersistentInt4KVCache
+    from flashquest_b200.eager.decode_step import QuestDecodeInt4
+    B, Hq, Hkv, D, page, Ln = 1, 6, 2, 128, 16, 3
+    outs = []
+    for mode in ("all", "each"):
+        cache = PersistentInt4KVCache(batch_size=B, num_layers=Ln, num_kv_heads=Hkv, head_dim=D, max_seq_len=256,
+                                      page_size=page, device="cuda", dtype=torch.float16)
+        step = QuestDecodeInt4(cache, num_q_heads=Hq, retention=0.5, num_sinks=1, window_pages=1, q_dtype=torch.float16)
+        for li, s0 in enumerate((95, 64, 130)):
+            cache.update_quantized(make_kv(60 + li, (B, Hkv, s0, D), torch.float16).cuda(),
+                                   make_kv(70 + li, (B, Hkv, s0, D), torch.float16, outliers=()).cuda(), li)
+        res = []
+        for t in range(3):
+            k = make_kv(80 + t, (Ln, B, Hkv, 1, D), torch.float16).cuda()
+            v = make_kv(90 + t, (Ln, B, Hkv, 1, D), torch.float16, outliers=()).cuda()
+            q = make_q(100 + t, (Ln, B, Hq, 1, D), torch.float16).cuda()
+            if mode == "all":
+                O, lse = step.step_all(k, v, q)
+                res.append((O.clone(), lse.clone()))
+            else:
+                Os, ls = zip(*[tuple(x.clone() for x in step.step(k[li], v[li], q[li], li)) for li in range(Ln)])
+                res.append((torch.stack(Os), torch.stack(ls)))
+        assert [cache.get_seq_length(li) for li in range(Ln)] == [98, 67, 133]
+        outs.append(res)
+    for (Oa, la), (Oe, le) in zip(*outs):
+        assert torch.equal(Oa, Oe) and torch.equal(la, le)
