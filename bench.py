@@ -460,6 +460,82 @@ def run_awq(args):
                       "device_status": _lib.lib().fq_device_status()}))
 
 
+# --------------------------------------------------------------------------- secondary workload: TurboQuant
+
+def run_turbo(args):
+    """BASELINE config 2: TurboQuant K3-V3, context 32k, batch 16 (overridable), 24/8 heads, D 128,
+    retention 0.25: pack-on-append throughput of a bulk append and the sparse decode attention."""
+    import torch
+    from flashquest_b200 import _lib
+    from flashquest_b200.eager.criticality import page_scores_int4_fast
+    from flashquest_b200.eager.selection import select_pages_vectorized
+    from flashquest_b200.kernel.kv_quant import quantize_k_turbo, quantize_v_turbo
+    from flashquest_b200.kernel.sparse_turbo_fwd import flash_attn_sparse_turbo_fwd
+    _lib.lib()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, Hq, Hkv, D, S, page = args.batch or 16, 24, 8, 128, args.ctx or 32768, 16
+    peak, peak_kind = measured_peak()
+    g = torch.Generator(device=dev).manual_seed(11)
+
+    def heavy(shape):            # N(0,1) with Student-t (df 3) outliers on 8 of the 128 channels
+        x = torch.randn(shape, device=dev, generator=g)
+        t = torch.randn(shape[:-1] + (8,), device=dev, generator=g)
+        chi = torch.randn(shape[:-1] + (8, 3), device=dev, generator=g).pow(2).sum(-1).div(3).sqrt()
+        x[..., [3, 17, 29, 41, 64, 77, 100, 119]] = t / chi
+        return x.half()
+
+    kv, times = [], []
+    for b in range(B):           # one sequence at a time keeps the fp16 source small
+        K, V = heavy((1, Hkv, S, D)), heavy((1, Hkv, S, D))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        qk = quantize_k_turbo(K, page)
+        qv = quantize_v_turbo(V)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        kv.append(qk + qv)
+        del K, V
+    pack_ms = statistics.median(times[1:] or times)
+    in_bytes = 2 * Hkv * S * D * 2
+    out_bytes = 2 * Hkv * S * (D // 8 + D // 4 + 2) + 2 * Hkv * (S // page) * D * 2
+    cat = [torch.cat([k[i] for k in kv]) for i in range(8)]
+    del kv
+    K_msb, K_lsb, K_st, K_sr, K_mr, V_msb, V_lsb, V_st = cat
+    Q = torch.randn(B, Hq, 1, D, device=dev, generator=g).half()
+    mask = select_pages_vectorized(page_scores_int4_fast(Q, K_sr, K_mr), 0.25, 1, 1)
+
+    def attend():
+        return flash_attn_sparse_turbo_fwd(Q, K_msb, K_lsb, K_st, V_msb, V_lsb, V_st, selection_mask=mask, page_size=page)
+
+    for _ in range(max(args.warmup, 3)):
+        attend()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        attend()
+    e1.record()
+    torch.cuda.synchronize()
+    attn_us = e0.elapsed_time(e1) * 1e3 / args.steps
+    per_tok = 2 * (D // 8 + D // 4 + 2)
+    n_rep = Hq // Hkv
+    per_head = int(mask.sum()) * page * per_tok
+    union = int(mask.view(B, Hkv, n_rep, -1).any(2).sum()) * page * per_tok
+    print(json.dumps({
+        "metric": "TurboQuant K3-V3: pack-on-append and sparse decode attention", "workload": "turbo",
+        "config": {"batch": B, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "context": S, "page_size": page, "retention": 0.25},
+        "pack": {"ms_per_sequence": pack_ms, "tokens_per_s": S / (pack_ms * 1e-3), "GBs": (in_bytes + out_bytes) / (pack_ms * 1e-3) / 1e9,
+                 "frac": (in_bytes + out_bytes) / (pack_ms * 1e-3) / 1e9 / peak,
+                 "what": "quantize_k_turbo (planes + scales + page metadata) and quantize_v_turbo of one 32k sequence"},
+        "attention": {"us_per_call": attn_us, "union_bytes": union, "per_head_bytes": per_head,
+                      "GBs_union": union / attn_us / 1e3, "frac": union / attn_us / 1e3 / peak,
+                      "what": "flash_attn_sparse_turbo_fwd: WHT of Q, compact list, attention, inverse WHT (4 launches)"},
+        "peak": peak, "peak_kind": peak_kind, "device_status": _lib.lib().fq_device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -470,7 +546,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (small captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per GPU (profiles of batched shapes)")
     ap.add_argument("--n-split", type=int, default=0, help="override the split-K factor of the attention kernel")
-    ap.add_argument("--workload", default="decode", choices=["decode", "awq"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo"],
                     help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -478,6 +554,8 @@ def main():
         run_reference(args)
     elif args.workload == "awq":
         run_awq(args)
+    elif args.workload == "turbo":
+        run_turbo(args)
     else:
         run_ours(args)
 

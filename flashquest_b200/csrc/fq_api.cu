@@ -24,12 +24,12 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-bool pdl_enabled() {
-    static const bool on = [] {
+bool pdl_enabled(int kind) {
+    static const int mask = [] {
         const char* e = getenv("FQ_PDL");
-        return !(e && e[0] == '0');
+        return e ? atoi(e) : (PDL_SCORES | PDL_ATTN | PDL_QUANT | PDL_GEMV);
     }();
-    return on;
+    return (mask & kind) != 0;
 }
 
 __device__ int g_fq_status = 0;

@@ -269,12 +269,12 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     const bool is_producer = warp == ATT_WARPS;
     FQ_TRACE(0);
 
-    // ---- slice of the compact list owned by this CTA, in units ----
+    // ---- units of the compact list owned by this CTA ----
+    // Units are dealt round-robin to the splits (unit g belongs to split g % n_split), so a
+    // list with its valid entries at the front and -1 padding behind them stays balanced.
     const int cpp_log2 = p.cpp_log2;                    // log2(chunks (units) per page)
-    const int slots_per_split = (p.bucket + p.n_split - 1) / p.n_split;
-    const int slot_begin = split * slots_per_split;
-    const int slot_end = min(p.bucket, slot_begin + slots_per_split);
-    const int n_units = max(0, slot_end - slot_begin) << cpp_log2;
+    const int total_units = p.bucket << cpp_log2;
+    const int n_units = split < total_units ? (total_units - split + p.n_split - 1) / p.n_split : 0;
     constexpr int units_per_iter = ATT_WARPS * 4;
     const int n_iter = (n_units + units_per_iter - 1) / units_per_iter;
     const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
@@ -302,9 +302,10 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         const int u = it * units_per_iter + uu;
         page_id = -1; tok0 = 0; n_tok = 0;
         if (u < n_units) {
-            const int pg = __ldg(list + slot_begin + (u >> cpp_log2));
+            const int g = u * p.n_split + split;
+            const int pg = __ldg(list + (g >> cpp_log2));
             if (pg >= 0 && pg < p.P) {
-                tok0 = pg * p.page + (u & ((1 << cpp_log2) - 1)) * TOK;
+                tok0 = pg * p.page + (g & ((1 << cpp_log2) - 1)) * TOK;
                 n_tok = min(TOK, p.S_kv - tok0);
                 if (n_tok > 0) page_id = pg; else n_tok = 0;
             }
@@ -758,7 +759,7 @@ static int launch_attn(const AttnParams& p, cudaStream_t st) {
         prepared[dev] = true;
     }
     dim3 grid((unsigned)p.n_split, (unsigned)p.Hq, (unsigned)p.B);
-    cudaError_t e = launch_k(kern, grid, dim3(ATT_THREADS), smem, st, p);
+    cudaError_t e = launch_k(PDL_ATTN, kern, grid, dim3(ATT_THREADS), smem, st, p);
     if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "fq_sparse_decode_int4: launch failed: %s", cudaGetErrorString(e));
     return FQ_OK;
 }

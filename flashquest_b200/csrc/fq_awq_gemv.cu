@@ -384,7 +384,7 @@ extern "C" int fq_awq_gemv(
             if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve %zu B of shared memory: %s", fn, smem, cudaGetErrorString(e)); \
             if (dev >= 0 && dev < 64) attr_set[dev] = true;                                                  \
         }                                                                                                    \
-        launch_k(awq_gemv_kernel<MV>, grid, dim3(GEMV_THREADS), smem, st, p);                                          \
+        launch_k(PDL_GEMV, awq_gemv_kernel<MV>, grid, dim3(GEMV_THREADS), smem, st, p);                                          \
     } while (0)
     if (Mp == 1) FQ_GEMV(1);
     else if (Mp == 2) FQ_GEMV(2);

@@ -32,17 +32,20 @@ int fail(int code, const char* fmt, ...);
 // previous kernel) and block in pdl_wait() until the previous kernel has completed and its
 // writes are visible.  pdl_trigger() comes right after the wait in every kernel, so at most
 // two kernels of a chain overlap and whatever a kernel reads before its wait must have been
-// written at least two kernels earlier.  FQ_PDL=0 in the environment turns the attribute off.
-bool pdl_enabled();
+// written at least two kernels earlier.  FQ_PDL=<bit mask of PDL_*> in the environment selects which kernels get the attribute (0 = none);
+// by default all but the selection kernel, which measured 3 us slower per launch when it was
+// made resident early beside the scoring kernel.
+bool pdl_enabled(int kind);
+enum { PDL_SCORES = 1, PDL_SELECT = 2, PDL_ATTN = 4, PDL_QUANT = 8, PDL_GEMV = 16 };
 
 template <typename... KP, typename... A>
-inline cudaError_t launch_k(void (*kernel)(KP...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+inline cudaError_t launch_k(int kind, void (*kernel)(KP...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at{};
     at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &at; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.attrs = &at; cfg.numAttrs = pdl_enabled(kind) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<A&&>(args)...);
 }
 

@@ -278,9 +278,9 @@ extern "C" int fq_quantize_kv_int4(
 
     dim3 grid((unsigned)max(1, (p.n_pages + 3) / 4), (unsigned)H, (unsigned)B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == FQ_F32) launch_k(quant_int4_kernel<float>, grid, dim3(128), 0, st, p);
-    else if (dtype == FQ_F16) launch_k(quant_int4_kernel<__half>, grid, dim3(128), 0, st, p);
-    else launch_k(quant_int4_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, p);
+    if (dtype == FQ_F32) launch_k(PDL_QUANT, quant_int4_kernel<float>, grid, dim3(128), 0, st, p);
+    else if (dtype == FQ_F16) launch_k(PDL_QUANT, quant_int4_kernel<__half>, grid, dim3(128), 0, st, p);
+    else launch_k(PDL_QUANT, quant_int4_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, p);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }

@@ -123,7 +123,7 @@ static void launch_scores(int CH, dim3 grid, cudaStream_t st, const void* Q, int
                           const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
                           int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh) {
 #define FQ_LAUNCH_SC(CHV)                                                                              \
-    launch_k(page_scores_kernel<QT, NR, CHV>, grid, dim3(SCORE_THREADS), 0, st,                        \
+    launch_k(PDL_SCORES, page_scores_kernel<QT, NR, CHV>, grid, dim3(SCORE_THREADS), 0, st,                        \
              static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),             \
              static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh)
     if (CH == 1) FQ_LAUNCH_SC(1);

@@ -316,11 +316,11 @@ extern "C" int fq_select_pages(
             cudaError_t e = cudaFuncSetAttribute(select_pages_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve %zu B of shared memory: %s", fn, smem, cudaGetErrorString(e));
         }
-        launch_k(select_pages_kernel<true>, grid, dim3(select_threads(P)), smem, st,
+        launch_k(PDL_SELECT, select_pages_kernel<true>, grid, dim3(select_threads(P)), smem, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
             mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count);
     } else {
-        launch_k(select_pages_kernel<false>, grid, dim3(select_threads(P)), 0, st,
+        launch_k(PDL_SELECT, select_pages_kernel<false>, grid, dim3(select_threads(P)), 0, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
             mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count);
     }

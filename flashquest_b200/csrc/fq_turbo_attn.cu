@@ -2,19 +2,21 @@
 // n-way LSE merge of partial attention results.
 //
 // Per selected 16-token unit the kernel reads 16 x (D/8 + D/4 + 2) bytes for K and the same
-// for V (1600 B at D = 128).  One warp owns one unit at a time.  K phase: lane = (token,
-// half of the channels); the 3-bit index of a channel is assembled from the two planes and the
-// codebook value is fetched from a lane-private column of a shared-memory table (no bank
-// conflicts); the two halves of a token meet by one shuffle.  V phase: lane = D/32 channels of
-// every token.  Softmax in base 2, fp32 accumulation, split-K partials merged by the CTA
-// that draws the last ticket of its row (no CTA waits for another).
-// This first version loads straight from global memory (no staging pipeline) and is bound by
-// the shared-memory table look-ups, not by HBM.
+// for V (1600 B at D = 128).  One warp owns one unit at a time and stages the next one into
+// its own double buffer with cp.async while it works.  A lane owns 8 channels (one byte of
+// the msb plane, two of the lsb plane) of every NTP-th token.  Decoding is a table look-up:
+// two neighbouring channels form a 6-bit index (2 msb bits, 4 lsb bits) into a table of
+// codebook PAIRS, replicated per lane so that a warp's 64-bit loads never collide; one
+// fma.rn.f32x2 then covers both channels (K: times the q pair, V: times the softmax weight).
+// Per-token dot products meet in a transposing shuffle reduction; softmax in base 2, fp32
+// accumulation, split-K partials merged by the CTA that draws the last ticket of its row (no
+// CTA waits for another).  Bound by the ALU/LSU work of the index assembly and look-ups
+// (about 3 instructions per 3-bit element), not by HBM.
 #include "fq_common.cuh"
 
 namespace fq {
 
-constexpr int TQ_WARPS = 4;
+constexpr int TQ_WARPS = 8;
 constexpr int TQ_THREADS = TQ_WARPS * 32;
 constexpr float TQ_LOG2E = 1.4426950408889634f;
 constexpr float TQ_LN2 = 0.6931471805599453f;
@@ -29,6 +31,7 @@ struct TurboAttnParams {
     float sm_scale;
     void* O; int64_t o_sb, o_sh; float* lse;
     int* tickets; float* partials; int n_split;
+    int fast;            // planes are token-contiguous and 16-byte aligned: 16-byte async copies
 };
 
 __device__ __forceinline__ float tq_ex2(float x) {
@@ -36,35 +39,82 @@ __device__ __forceinline__ float tq_ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ void tq_cp16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+
+// Transposing reduction of N partial sums per lane over the L lanes (L = 2N) that share a
+// token group: afterwards lane c holds the complete sum of value index c >> 1 in s[0].
+template <int N, int L>
+__device__ __forceinline__ void tq_reduce(float (&s)[N], int c) {
+    static_assert(L == 2 * N, "lanes per token");
+    if constexpr (N >= 8) {
+        const bool up = c & (L / 2);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[i] = (up ? s[i + 4] : s[i]) + __shfl_xor_sync(0xffffffffu, up ? s[i] : s[i + 4], L / 2);
+    }
+    if constexpr (N >= 4) {
+        constexpr int H = N >= 8 ? L / 4 : L / 2;
+        const bool up = c & H;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) s[i] = (up ? s[i + 2] : s[i]) + __shfl_xor_sync(0xffffffffu, up ? s[i] : s[i + 2], H);
+    }
+    {
+        const bool up = c & 2;
+        s[0] = (up ? s[1] : s[0]) + __shfl_xor_sync(0xffffffffu, up ? s[0] : s[1], 2);
+    }
+    s[0] += __shfl_xor_sync(0xffffffffu, s[0], 1);
+}
 
 template <typename QT, int D>
 __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAttnParams p) {
     constexpr int TOK = 16;
-    constexpr int HALF = D / 2;          // channels per lane in the K phase
-    constexpr int EV = D / 32;           // channels per lane in the V phase
-    constexpr int NSTATE = TQ_WARPS;
-    __shared__ float s_cb[8 * 32];       // codebook, one column per lane
-    __shared__ float s_q[D + 2];         // q * sm_scale * log2(e); second half shifted by one bank
-    __shared__ float s_m[NSTATE], s_l[NSTATE], s_acc[NSTATE][D];
+    constexpr int LPT = D / 8;           // lanes per token, 8 channels each
+    constexpr int NTP = 32 / LPT;        // tokens a warp works on at once
+    constexpr int TPL = TOK / NTP;       // tokens per lane
+    constexpr int MROW = D / 8, LROW = D / 4;
+    constexpr int KM_OFF = 0, KL_OFF = TOK * MROW, VM_OFF = KL_OFF + TOK * LROW, VL_OFF = VM_OFF + TOK * MROW;
+    constexpr int UNIT_BYTES = VL_OFF + TOK * LROW;
+    static_assert(TPL * 2 == LPT, "the reduction leaves one token per lane pair");
+    __shared__ __align__(16) float2 s_lut[64 * 32];                       // [pair index][lane]
+    __shared__ __align__(16) unsigned char s_stage[TQ_WARPS][2][UNIT_BYTES];
+    __shared__ float s_m[TQ_WARPS], s_l[TQ_WARPS], s_acc[TQ_WARPS][D];
     __shared__ int s_ticket;
 
     const int split = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
     const int n_rep = p.Hq / p.Hkv, hkv = hq / n_rep;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float cb[8] = {-2.1519f, -1.3439f, -0.7560f, -0.2451f, 0.2451f, 0.7560f, 1.3439f, 2.1519f};
-    for (int i = tid; i < 8 * 32; i += TQ_THREADS) s_cb[i] = cb[i >> 5];
+    const int tp = lane / LPT, c = lane % LPT;
     {
-        const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh;
-        for (int d = tid; d < D; d += TQ_THREADS) s_q[d + (d >= HALF ? 1 : 0)] = Dt<QT>::to_f32(qp[d]) * (p.sm_scale * TQ_LOG2E);
+        const float cb[8] = {-2.1519f, -1.3439f, -0.7560f, -0.2451f, 0.2451f, 0.7560f, 1.3439f, 2.1519f};
+        // pair index = (msb_b msb_a) << 4 | (lsb_b << 2) | lsb_a for the channels a (even) and b = a + 1
+        for (int i = tid; i < 64 * 32; i += TQ_THREADS) {
+            const int e = i >> 5;
+            const int ia = (((e >> 4) & 1) << 2) | (e & 3), ib = (((e >> 5) & 1) << 2) | ((e >> 2) & 3);
+            float va = 0.f, vb = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { va = ia == k ? cb[k] : va; vb = ib == k ? cb[k] : vb; }
+            s_lut[i] = make_float2(va, vb);
+        }
     }
     __syncthreads();
-    const float* cbl = s_cb + lane;      // cbl[idx * 32]
+    pdl_wait();        // the rotated Q and the page list come from the kernels before this one
+    pdl_trigger();
+    const unsigned char* lutl = reinterpret_cast<const unsigned char*>(s_lut) + lane * 8;
 
+    float2 q2[4];      // this lane's 8 channels of q * sm_scale * log2(e)
+    {
+        const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + 8 * c;
+        const float sc = p.sm_scale * TQ_LOG2E;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q2[j] = make_float2(Dt<QT>::to_f32(qp[2 * j]) * sc, Dt<QT>::to_f32(qp[2 * j + 1]) * sc);
+    }
+
+    // Units are dealt round-robin to the splits (unit g belongs to split g % n_split): a list
+    // whose valid entries sit at the front and padding at the back stays balanced.
     const int cpp = p.page / TOK;
-    const int slots_per_split = (p.bucket + p.n_split - 1) / p.n_split;
-    const int slot_begin = split * slots_per_split;
-    const int slot_end = min(p.bucket, slot_begin + slots_per_split);
-    const int n_units = max(0, slot_end - slot_begin) * cpp;
+    const int total_units = p.bucket * cpp;
+    const int n_units = split < total_units ? (total_units - split + p.n_split - 1) / p.n_split : 0;   // of this CTA
     const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
 
     const uint8_t* Kmsb = p.K_msb + b * p.km_sb + hkv * p.km_sh;
@@ -74,75 +124,139 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
     const uint16_t* Ksc = p.K_scale + b * p.ks_sb + hkv * p.ks_sh;
     const uint16_t* Vsc = p.V_scale + b * p.vs_sb + hkv * p.vs_sh;
 
-    float m_run = -INFINITY, l_run = 0.f, acc[EV];
-#pragma unroll
-    for (int j = 0; j < EV; ++j) acc[j] = 0.f;
+    const int t_mine = NTP * (c >> 1) + tp;      // the token whose logit ends up in this lane
 
-    const int tk = lane >> 1, hh = lane & 1;            // K phase: token, channel half
-    const float* qh = s_q + hh * (HALF + 1);
-    for (int u = warp; u < n_units; u += TQ_WARPS) {
-        const int pg = __ldg(list + slot_begin + u / cpp);
-        if (pg < 0 || pg >= p.P) continue;              // warp-uniform
-        const int tok0 = pg * p.page + (u % cpp) * TOK;
-        const int n_tok = min(TOK, p.S_kv - tok0);
-        if (n_tok <= 0) continue;
-        // ---------------- K ----------------
-        float x = -INFINITY;
-        {
-            const bool valid = tk < n_tok;
-            float dot = 0.f;
-            if (valid) {
-                const uint32_t* mw = reinterpret_cast<const uint32_t*>(Kmsb + (int64_t)(tok0 + tk) * p.km_ss + hh * (D / 16));
-                const uint32_t* lw = reinterpret_cast<const uint32_t*>(Klsb + (int64_t)(tok0 + tk) * p.kl_ss + hh * (D / 8));
-#pragma unroll
-                for (int w = 0; w < HALF / 32; ++w) {       // 32 channels per msb word
-                    const uint32_t m = __ldg(mw + w);
-                    const uint32_t l0 = __ldg(lw + 2 * w), l1 = __ldg(lw + 2 * w + 1);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const uint32_t lo = i < 16 ? (l0 >> (2 * i)) & 3u : (l1 >> (2 * (i - 16))) & 3u;
-                        const uint32_t idx = (((m >> i) & 1u) << 2) | lo;
-                        dot = fmaf(qh[32 * w + i], cbl[idx * 32], dot);
-                    }
-                }
+    // unit -> first token and number of valid tokens (0: nothing to do)
+    auto locate = [&](int u, int& tok0, int& n_tok) {
+        tok0 = 0; n_tok = 0;
+        const int g = u * p.n_split + split;
+        const int pg = __ldg(list + g / cpp);
+        if (pg < 0 || pg >= p.P) return;
+        tok0 = pg * p.page + (g % cpp) * TOK;
+        n_tok = max(0, min(TOK, p.S_kv - tok0));
+    };
+    // bring a unit into a staging buffer; scales of this lane's token come back in registers
+    auto stage = [&](unsigned char* buf, int tok0, int n_tok, float& ks, float& vs) {
+        ks = 0.f; vs = 0.f;
+        if (n_tok <= 0) return;
+        if (t_mine < n_tok) { ks = bf16_lo(__ldg(Ksc + tok0 + t_mine)); vs = bf16_lo(__ldg(Vsc + tok0 + t_mine)); }
+        if (p.fast && n_tok == TOK) {
+            constexpr int CM = TOK * MROW / 16, CL = TOK * LROW / 16;    // 16-byte pieces per plane
+            for (int i = lane; i < 2 * (CM + CL); i += 32) {
+                if (i < CM) tq_cp16(buf + KM_OFF + 16 * i, Kmsb + (int64_t)tok0 * MROW + 16 * i);
+                else if (i < CM + CL) tq_cp16(buf + KL_OFF + 16 * (i - CM), Klsb + (int64_t)tok0 * LROW + 16 * (i - CM));
+                else if (i < 2 * CM + CL) tq_cp16(buf + VM_OFF + 16 * (i - CM - CL), Vmsb + (int64_t)tok0 * MROW + 16 * (i - CM - CL));
+                else tq_cp16(buf + VL_OFF + 16 * (i - 2 * CM - CL), Vlsb + (int64_t)tok0 * LROW + 16 * (i - 2 * CM - CL));
             }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            if (valid) x = dot * bf16_lo(__ldg(Ksc + tok0 + tk));
-        }
-        float pmax = x;
-#pragma unroll
-        for (int off = 16; off >= 2; off >>= 1) pmax = fmaxf(pmax, __shfl_xor_sync(0xffffffffu, pmax, off));
-        const float m_new = fmaxf(m_run, pmax);
-        const float alpha = tq_ex2(m_run - m_new);
-        const float pr = tq_ex2(x - m_new);                 // both lanes of a token hold the same value
-        float psum = hh == 0 ? pr : 0.f;
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, off);
-        l_run = l_run * alpha + psum;
-        m_run = m_new;
-        const float pv_mine = (tk < n_tok) ? pr * bf16_lo(__ldg(Vsc + tok0 + tk)) : 0.f;
-        // ---------------- V ----------------
-#pragma unroll
-        for (int j = 0; j < EV; ++j) acc[j] *= alpha;
-        const int d0 = lane * EV;
-        for (int t = 0; t < n_tok; ++t) {
-            const float pv = __shfl_sync(0xffffffffu, pv_mine, 2 * t);
-            const uint32_t mb = __ldg(Vmsb + (int64_t)(tok0 + t) * p.vm_ss + (d0 >> 3));
-            const uint32_t lb = __ldg(Vlsb + (int64_t)(tok0 + t) * p.vl_ss + (d0 >> 2));
-#pragma unroll
-            for (int j = 0; j < EV; ++j) {
-                const int d = d0 + j;
-                const uint32_t idx = (((mb >> (d & 7)) & 1u) << 2) | ((lb >> (2 * (d & 3))) & 3u);
-                acc[j] = fmaf(pv, cbl[idx * 32], acc[j]);
+        } else {
+            // ragged last unit or strided planes: byte copies of the valid tokens only
+            for (int i = lane; i < n_tok * MROW; i += 32) {
+                const int t = i / MROW, x = i % MROW;
+                buf[KM_OFF + i] = Kmsb[(int64_t)(tok0 + t) * p.km_ss + x];
+                buf[VM_OFF + i] = Vmsb[(int64_t)(tok0 + t) * p.vm_ss + x];
+            }
+            for (int i = lane; i < n_tok * LROW; i += 32) {
+                const int t = i / LROW, x = i % LROW;
+                buf[KL_OFF + i] = Klsb[(int64_t)(tok0 + t) * p.kl_ss + x];
+                buf[VL_OFF + i] = Vlsb[(int64_t)(tok0 + t) * p.vl_ss + x];
             }
         }
+    };
+    // codebook pair of channels (2j, 2j+1) of this lane: M = msb byte << 12, Lw = lsb halfword << 8
+    auto pair_at = [&](uint32_t M, uint32_t Lw, int j) -> float2 {
+        const uint32_t off = ((M >> (2 * j)) & 0x3000u) | ((Lw >> (4 * j)) & 0x0f00u);
+        return *reinterpret_cast<const float2*>(lutl + off);
+    };
+
+    float m_run = -INFINITY, l_run = 0.f;
+    float2 acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = make_float2(0.f, 0.f);
+
+    int cur_tok0 = 0, cur_n = 0;
+    float cur_ks = 0.f, cur_vs = 0.f;
+    if (warp < n_units) {
+        locate(warp, cur_tok0, cur_n);
+        stage(s_stage[warp][0], cur_tok0, cur_n, cur_ks, cur_vs);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    int it = 0;
+    for (int u = warp; u < n_units; u += TQ_WARPS, ++it) {
+        int nxt_tok0 = 0, nxt_n = 0;
+        float nxt_ks = 0.f, nxt_vs = 0.f;
+        if (u + TQ_WARPS < n_units) {
+            locate(u + TQ_WARPS, nxt_tok0, nxt_n);
+            stage(s_stage[warp][(it + 1) & 1], nxt_tok0, nxt_n, nxt_ks, nxt_vs);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncwarp();
+        if (cur_n > 0) {                                   // warp-uniform
+            const unsigned char* buf = s_stage[warp][it & 1];
+            // ---------------- K ----------------
+            float dots[TPL];
+#pragma unroll
+            for (int k = 0; k < TPL; ++k) {
+                const int t = NTP * k + tp;
+                const uint32_t M = (uint32_t)buf[KM_OFF + t * MROW + c] << 12;
+                const uint32_t Lw = (uint32_t)*reinterpret_cast<const uint16_t*>(buf + KL_OFF + t * LROW + 2 * c) << 8;
+                float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) a = __ffma2_rn(pair_at(M, Lw, j), q2[j], a);
+                dots[k] = a.x + a.y;
+            }
+            tq_reduce<TPL, LPT>(dots, c);
+            const bool valid = t_mine < cur_n;
+            const float x = valid ? dots[0] * cur_ks : -INFINITY;
+            float pmax = x;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) pmax = fmaxf(pmax, __shfl_xor_sync(0xffffffffu, pmax, off));
+            const float m_new = fmaxf(m_run, pmax);            // finite: the unit has a valid token
+            const float alpha = tq_ex2(m_run - m_new);
+            const float pr = valid ? tq_ex2(x - m_new) : 0.f;
+            float psum = (c & 1) ? 0.f : pr;                   // every token sits in two lanes
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, off);
+            l_run = l_run * alpha + psum;
+            m_run = m_new;
+            const float pv_mine = pr * cur_vs;
+            // ---------------- V ----------------
+            const float2 al2 = make_float2(alpha, alpha);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = __fmul2_rn(acc[j], al2);
+#pragma unroll
+            for (int k = 0; k < TPL; ++k) {
+                const int t = NTP * k + tp;
+                const float pv = __shfl_sync(0xffffffffu, pv_mine, tp * LPT + 2 * k);
+                const float2 pv2 = make_float2(pv, pv);
+                const uint32_t M = (uint32_t)buf[VM_OFF + t * MROW + c] << 12;
+                const uint32_t Lw = (uint32_t)*reinterpret_cast<const uint16_t*>(buf + VL_OFF + t * LROW + 2 * c) << 8;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j] = __ffma2_rn(pair_at(M, Lw, j), pv2, acc[j]);
+            }
+        }
+        __syncwarp();                                      // the buffer is refilled in the next iteration
+        cur_tok0 = nxt_tok0; cur_n = nxt_n; cur_ks = nxt_ks; cur_vs = nxt_vs;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // ---------------- CTA merge ----------------
-    if (lane == 0) { s_m[warp] = m_run; s_l[warp] = l_run; }
+    // the token phases of a warp hold partial sums of the same channels
 #pragma unroll
-    for (int j = 0; j < EV; ++j) s_acc[warp][lane * EV + j] = acc[j];
+    for (int off = LPT; off < 32; off <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[j].x += __shfl_xor_sync(0xffffffffu, acc[j].x, off);
+            acc[j].y += __shfl_xor_sync(0xffffffffu, acc[j].y, off);
+        }
+    }
+    if (lane == 0) { s_m[warp] = m_run; s_l[warp] = l_run; }
+    if (tp == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { s_acc[warp][8 * c + 2 * j] = acc[j].x; s_acc[warp][8 * c + 2 * j + 1] = acc[j].y; }
+    }
     __syncthreads();
+    constexpr int NSTATE = TQ_WARPS;
     float m_cta = -INFINITY;
 #pragma unroll
     for (int i = 0; i < NSTATE; ++i) m_cta = fmaxf(m_cta, s_m[i]);
@@ -245,9 +359,6 @@ extern "C" int fq_sparse_decode_turbo(
     if (have_pages) {
         FQ_CHECK_ARG(K_msb && K_lsb && V_msb && V_lsb && K_scale && V_scale && compact, FQ_ERR_ARG, "%s: null cache pointer", fn);
         FQ_CHECK_ARG((int64_t)P * page >= S_kv, FQ_ERR_ARG, "%s: %d pages of %d tokens do not cover S_kv=%d", fn, P, page, S_kv);
-        FQ_CHECK_ARG(aligned(K_msb, 4) && aligned(K_lsb, 4) && aligned(V_msb, 4) && aligned(V_lsb, 4) &&
-                     km_sb % 4 == 0 && km_sh % 4 == 0 && km_ss % 4 == 0 && kl_sb % 4 == 0 && kl_sh % 4 == 0 && kl_ss % 4 == 0,
-                     FQ_ERR_ALIGN, "%s: plane rows must be 4-byte aligned", fn);
     }
     TurboAttnParams p;
     p.Q = Q_rot; p.q_sb = q_sb; p.q_sh = q_sh;
@@ -259,6 +370,12 @@ extern "C" int fq_sparse_decode_turbo(
     p.compact = compact; p.cp_sb = cp_sb; p.cp_sh = cp_sh; p.bucket = have_pages ? bucket : 0;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S_kv = S_kv; p.P = P; p.page = page; p.sm_scale = sm_scale;
     p.O = O_rot; p.o_sb = o_sb; p.o_sh = o_sh; p.lse = lse;
+    {
+        const int mrow = D / 8, lrow = D / 4;
+        auto ok16 = [](const void* q, int64_t a, int64_t b2) { return aligned(q, 16) && a % 16 == 0 && b2 % 16 == 0; };
+        p.fast = have_pages && km_ss == mrow && vm_ss == mrow && kl_ss == lrow && vl_ss == lrow &&
+                 ok16(K_msb, km_sb, km_sh) && ok16(K_lsb, kl_sb, kl_sh) && ok16(V_msb, vm_sb, vm_sh) && ok16(V_lsb, vl_sb, vl_sh);
+    }
     if (n_split > p.bucket) n_split = p.bucket > 0 ? p.bucket : 1;
     p.n_split = n_split; p.tickets = nullptr; p.partials = nullptr;
     if (n_split > 1) {
@@ -270,11 +387,11 @@ extern "C" int fq_sparse_decode_turbo(
     dim3 grid((unsigned)n_split, (unsigned)Hq, (unsigned)B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (q_dtype == FQ_F16) {
-        if (D == 128) sparse_decode_turbo_kernel<__half, 128><<<grid, TQ_THREADS, 0, st>>>(p);
-        else sparse_decode_turbo_kernel<__half, 64><<<grid, TQ_THREADS, 0, st>>>(p);
+        if (D == 128) launch_k(PDL_ATTN, sparse_decode_turbo_kernel<__half, 128>, grid, dim3(TQ_THREADS), 0, st, p);
+        else launch_k(PDL_ATTN, sparse_decode_turbo_kernel<__half, 64>, grid, dim3(TQ_THREADS), 0, st, p);
     } else {
-        if (D == 128) sparse_decode_turbo_kernel<__nv_bfloat16, 128><<<grid, TQ_THREADS, 0, st>>>(p);
-        else sparse_decode_turbo_kernel<__nv_bfloat16, 64><<<grid, TQ_THREADS, 0, st>>>(p);
+        if (D == 128) launch_k(PDL_ATTN, sparse_decode_turbo_kernel<__nv_bfloat16, 128>, grid, dim3(TQ_THREADS), 0, st, p);
+        else launch_k(PDL_ATTN, sparse_decode_turbo_kernel<__nv_bfloat16, 64>, grid, dim3(TQ_THREADS), 0, st, p);
     }
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
