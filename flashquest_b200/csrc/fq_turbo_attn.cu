@@ -127,27 +127,41 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
     const int t_mine = NTP * (c >> 1) + tp;      // the token whose logit ends up in this lane
 
     // unit -> first token and number of valid tokens (0: nothing to do)
-    auto locate = [&](int u, int& tok0, int& n_tok) {
+    // page id of this warp's unit u (-1 past the end); requested two units ahead of its use
+    auto page_of = [&](int u) -> int {
+        return u < n_units ? __ldg(list + (u * p.n_split + split) / cpp) : -1;
+    };
+    auto locate = [&](int u, int pg, int& tok0, int& n_tok) {
         tok0 = 0; n_tok = 0;
-        const int g = u * p.n_split + split;
-        const int pg = __ldg(list + g / cpp);
         if (pg < 0 || pg >= p.P) return;
-        tok0 = pg * p.page + (g % cpp) * TOK;
+        tok0 = pg * p.page + ((u * p.n_split + split) % cpp) * TOK;
         n_tok = max(0, min(TOK, p.S_kv - tok0));
     };
+    // this lane's three 16-byte pieces of a full unit: plane, offset inside the unit, bytes per token
+    const uint8_t* piece_src[3];
+    int piece_dst[3], piece_row[3];
+    {
+        constexpr int CM = TOK * MROW / 16, CL = TOK * LROW / 16;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int i = lane + 32 * r;
+            if (i < CM) { piece_src[r] = Kmsb + 16 * i; piece_dst[r] = KM_OFF + 16 * i; piece_row[r] = MROW; }
+            else if (i < CM + CL) { piece_src[r] = Klsb + 16 * (i - CM); piece_dst[r] = KL_OFF + 16 * (i - CM); piece_row[r] = LROW; }
+            else if (i < 2 * CM + CL) { piece_src[r] = Vmsb + 16 * (i - CM - CL); piece_dst[r] = VM_OFF + 16 * (i - CM - CL); piece_row[r] = MROW; }
+            else if (i < 2 * (CM + CL)) { piece_src[r] = Vlsb + 16 * (i - 2 * CM - CL); piece_dst[r] = VL_OFF + 16 * (i - 2 * CM - CL); piece_row[r] = LROW; }
+            else { piece_src[r] = nullptr; piece_dst[r] = 0; piece_row[r] = 0; }
+        }
+        static_assert(2 * (CM + CL) <= 96, "three pieces per lane cover a unit");
+    }
     // bring a unit into a staging buffer; scales of this lane's token come back in registers
     auto stage = [&](unsigned char* buf, int tok0, int n_tok, float& ks, float& vs) {
         ks = 0.f; vs = 0.f;
         if (n_tok <= 0) return;
         if (t_mine < n_tok) { ks = bf16_lo(__ldg(Ksc + tok0 + t_mine)); vs = bf16_lo(__ldg(Vsc + tok0 + t_mine)); }
         if (p.fast && n_tok == TOK) {
-            constexpr int CM = TOK * MROW / 16, CL = TOK * LROW / 16;    // 16-byte pieces per plane
-            for (int i = lane; i < 2 * (CM + CL); i += 32) {
-                if (i < CM) tq_cp16(buf + KM_OFF + 16 * i, Kmsb + (int64_t)tok0 * MROW + 16 * i);
-                else if (i < CM + CL) tq_cp16(buf + KL_OFF + 16 * (i - CM), Klsb + (int64_t)tok0 * LROW + 16 * (i - CM));
-                else if (i < 2 * CM + CL) tq_cp16(buf + VM_OFF + 16 * (i - CM - CL), Vmsb + (int64_t)tok0 * MROW + 16 * (i - CM - CL));
-                else tq_cp16(buf + VL_OFF + 16 * (i - 2 * CM - CL), Vlsb + (int64_t)tok0 * LROW + 16 * (i - 2 * CM - CL));
-            }
+#pragma unroll
+            for (int r = 0; r < 3; ++r)
+                if (piece_src[r]) tq_cp16(buf + piece_dst[r], piece_src[r] + (int64_t)tok0 * piece_row[r]);
         } else {
             // ragged last unit or strided planes: byte copies of the valid tokens only
             for (int i = lane; i < n_tok * MROW; i += 32) {
@@ -175,8 +189,9 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
 
     int cur_tok0 = 0, cur_n = 0;
     float cur_ks = 0.f, cur_vs = 0.f;
+    int pg_nxt = page_of(warp + TQ_WARPS);               // page of the unit after the first one
     if (warp < n_units) {
-        locate(warp, cur_tok0, cur_n);
+        locate(warp, page_of(warp), cur_tok0, cur_n);
         stage(s_stage[warp][0], cur_tok0, cur_n, cur_ks, cur_vs);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -184,10 +199,12 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
     for (int u = warp; u < n_units; u += TQ_WARPS, ++it) {
         int nxt_tok0 = 0, nxt_n = 0;
         float nxt_ks = 0.f, nxt_vs = 0.f;
+        const int pg_nxt2 = page_of(u + 2 * TQ_WARPS);   // in flight while this unit is worked on
         if (u + TQ_WARPS < n_units) {
-            locate(u + TQ_WARPS, nxt_tok0, nxt_n);
+            locate(u + TQ_WARPS, pg_nxt, nxt_tok0, nxt_n);
             stage(s_stage[warp][(it + 1) & 1], nxt_tok0, nxt_n, nxt_ks, nxt_vs);
         }
+        pg_nxt = pg_nxt2;
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncwarp();
