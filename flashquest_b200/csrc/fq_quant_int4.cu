@@ -25,11 +25,25 @@ struct QuantParams {
     int64_t st_sb, st_sh, st_ss;
 };
 
-__device__ __forceinline__ uint32_t code4(float x, float mn, float sc) {
-    // fp32 subtract, IEEE divide, round-half-even, clamp to 0..15
-    float t = rintf(__fdiv_rn(__fsub_rn(x, mn), sc));
-    t = fminf(fmaxf(t, 0.0f), 15.0f);
-    return (uint32_t)t;
+// Code of one element: rint((x - mn) / sc) clamped to 0..15, where the quotient is the IEEE
+// fp32 quotient (what the reference computes).  The division is replaced by a multiplication
+// with the correctly rounded reciprocal: that product is within 3e-6 of the IEEE quotient for
+// quotients below 16, so both round to the same integer unless the product lies within 2e-5
+// of a half-integer; only then (about 4 elements in 100 000) is the exact division done.
+// Rounding to nearest even through the 1.5 * 2^23 constant.  Returns the code as a float.
+__device__ __forceinline__ float code4f(float x, float mn, float sc, float rsc) {
+    const float d = __fsub_rn(x, mn);
+    const float t = __fmul_rn(d, rsc);
+    float r = __fsub_rn(__fadd_rn(t, 12582912.0f), 12582912.0f);
+    if (!(fabsf(__fsub_rn(t, r)) < 0.49998f) || !(t < 16.0f))     // near a tie, huge, or NaN
+        r = rintf(__fdiv_rn(d, sc));
+    return fminf(fmaxf(r, 0.0f), 15.0f);
+}
+// eight codes -> one 32-bit word, nibble i = code i; two exact fp32 sums of four nibbles each
+__device__ __forceinline__ uint32_t pack8(const float (&q)[8]) {
+    const float lo = fmaf(q[3], 4096.f, fmaf(q[2], 256.f, fmaf(q[1], 16.f, q[0])));
+    const float hi = fmaf(q[7], 4096.f, fmaf(q[6], 256.f, fmaf(q[5], 16.f, q[4])));
+    return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
 template <typename T>
@@ -82,6 +96,9 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
                 float diff = Dt<T>::rn(__fsub_rn(mx[i], mn[i]));
                 sc[i] = fmaxf(Dt<T>::rn(__fdiv_rn(diff, 15.0f)), eps);
             }
+            float rsc[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rsc[i] = __frcp_rn(sc[i]);
             if (ti == 0) {
                 uint32_t s4[4], m4[4];
 #pragma unroll
@@ -96,11 +113,11 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
             for (int tt = ti; tt < n_tok && p.K_packed != nullptr; tt += TPI) {
                 float v[8];
                 load8<T>(stream_row<T>(Kh, Kn, p, b, h, t0 + tt) + 8 * c, v);
-                uint32_t w = 0;
+                float q[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) w |= code4(v[i], mn[i], sc[i]) << (4 * i);
+                for (int i = 0; i < 8; ++i) q[i] = code4f(v[i], mn[i], sc[i], rsc[i]);
                 uint8_t* row = p.K_packed + b * p.pk_sb + h * p.pk_sh + (int64_t)(t0 + tt) * p.pk_ss;
-                *reinterpret_cast<uint32_t*>(row + 4 * c) = w;
+                *reinterpret_cast<uint32_t*>(row + 4 * c) = pack8(q);
             }
         }
         // ---------------- V: per token ----------------
@@ -123,11 +140,12 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
                 }
                 if (live) {
                     float sc = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 15.0f), 1e-6f);
-                    uint32_t w = 0;
+                    const float rsc = __frcp_rn(sc);
+                    float q[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) w |= code4(v[i], lo, sc) << (4 * i);
+                    for (int i = 0; i < 8; ++i) q[i] = code4f(v[i], lo, sc, rsc);
                     uint8_t* row = p.V_packed + b * p.pk_sb + h * p.pk_sh + (int64_t)(t0 + tt) * p.pk_ss;
-                    *reinterpret_cast<uint32_t*>(row + 4 * c) = w;
+                    *reinterpret_cast<uint32_t*>(row + 4 * c) = pack8(q);
                     if (c == 0) {
                         int64_t mo = b * p.vm_sb + h * p.vm_sh + (int64_t)(t0 + tt) * p.vm_ss;
                         p.V_scale[mo] = f32_to_bf16_bits(sc);

@@ -93,3 +93,36 @@ def test_full_size_roundtrip_properties(kvq):
     idx = slice(4096, 4096 + 64)
     w = oracle.quantize_k_int4(K[:, :, idx].cpu(), page)
     assert bit_equal(Kp[:, :, idx].cpu(), w[0]) and bit_equal(Ks[:, :, 256:260].cpu(), w[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_quotients_on_and_next_to_rounding_ties(kvq, dtype):
+    """Scale exactly 1 (values span 0..15): x = k + 0.5 divides to an exact tie (round half to
+    even), and the neighbouring representable values fall just beside it.  Also a large sample
+    of fp32 values whose quotients crowd the half-integers under an awkward scale."""
+    B, H, S, D, page = 1, 2, 64, 128, 16
+    g = torch.Generator().manual_seed(5)
+    base = torch.randint(0, 15, (B, H, S, D), generator=g).float() + 0.5          # k + 0.5
+    eps = {torch.float16: 2.0 ** -8, torch.bfloat16: 2.0 ** -5, torch.float32: 2.0 ** -21}[dtype]
+    jitter = torch.randint(-1, 2, (B, H, S, D), generator=g).float() * eps         # -eps, 0, +eps
+    X = base + jitter
+    X[..., 0] = 0.0      # every token / every page sees the full range 0..15
+    X[..., 1] = 15.0
+    X[:, :, 0::16, :] = 0.0
+    X[:, :, 1::16, :] = 15.0
+    X = X.to(dtype)
+    want = oracle.quantize_k_int4(X, page) + oracle.quantize_v_int4(X)
+    got = kvq.quantize_k_int4(X.cuda(), page) + kvq.quantize_v_int4(X.cuda())
+    for a, b in zip(got, want):
+        assert bit_equal(a.cpu(), b)
+    if dtype == torch.float32:
+        # scale 0.7 / 15: many quotients within a few ulps of k + 0.5
+        k = torch.randint(0, 15, (1, 1, 4096, 128), generator=g).float() + 0.5
+        Y = (k * torch.tensor(0.7 / 15, dtype=torch.float32))
+        Y = torch.nextafter(Y, torch.where(torch.rand(Y.shape, generator=g) < 0.5, torch.zeros(()), torch.ones(()) * 10))
+        Y[..., 0] = 0.0
+        Y[..., 1] = 0.7
+        want = oracle.quantize_v_int4(Y)
+        got = kvq.quantize_v_int4(Y.cuda())
+        for a, b in zip(got, want):
+            assert bit_equal(a.cpu(), b)
