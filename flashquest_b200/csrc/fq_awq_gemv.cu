@@ -10,7 +10,7 @@
 // flight: a CTA owns a tile of 64 int32 column packs (256 B of a weight row, 512 outputs) of ONE
 // projection and a range of quantisation groups; it streams the tile one group (<= 128 rows,
 // 32 KiB) at a time into a 3-stage shared-memory ring with cp.async, so up to 96 KiB per CTA are
-// outstanding whatever the register budget of the arithmetic.  A thread owns one pack
+// outstanding however many registers the arithmetic needs.  A thread owns one pack
 // (8 outputs); the 8 warps are 2 column halves x 4 interleaved row phases.
 // Inside a group the kernel accumulates sum_k x*code in fp32: the nibble is masked in place and
 // reinterpreted as an fp32 (sub)normal, x is pre-scaled by 2^100 and duplicated so that

@@ -44,6 +44,16 @@ __device__ __forceinline__ void wht_lanes(float (&v)[EPL], int lane, int D) {
 
 template <typename T, int EPL>
 __device__ __forceinline__ void load_row(const T* row, int lane, int D, float (&v)[EPL]) {
+    if constexpr (EPL == 4 && sizeof(T) == 2) {
+        // four 16-bit values of a lane in one 8-byte load when the row allows it
+        if ((reinterpret_cast<uintptr_t>(row) & 7) == 0 && D == 128) {
+            const uint2 u = *reinterpret_cast<const uint2*>(row + 4 * lane);
+            const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = Dt<T>::to_f32(e[j]);
+            return;
+        }
+    }
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
         const int i = lane * EPL + j;
@@ -101,35 +111,51 @@ __global__ void __launch_bounds__(128) turbo_quant_kernel(TurboParams p) {
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, off));
     const float s = fmaxf(__fsqrt_rn(__fdiv_rn(a, (float)D)), 1e-6f);
+    // Nearest codebook entry, first index on ties (torch.argmin): the codebook is sorted, so
+    // the winner is one of the two entries around y; which one is decided by the same fp32
+    // distances the reference compares.
+    unsigned idx[EPL];
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
-        const int i = lane * EPL + j;
-        if (i < D) {
-            const float y = __fdiv_rn(v[j], s);
-            int best = 0;
-            float bd = fabsf(__fsub_rn(y, c_turbo_codebook[0]));
-#pragma unroll
-            for (int k = 1; k < 8; ++k) {
-                const float dk = fabsf(__fsub_rn(y, c_turbo_codebook[k]));
-                if (dk < bd) { bd = dk; best = k; }
-            }
-            s_idx[warp][i] = (uint8_t)best;
-        }
+        const float y = __fdiv_rn(v[j], s);
+        int k = y >= c_turbo_codebook[4] ? 4 : 0;
+        k += y >= c_turbo_codebook[k + 2] ? 2 : 0;
+        k += y >= c_turbo_codebook[k + 1] ? 1 : 0;
+        k = min(k, 6);                                        // c_k <= y < c_{k+1}, clamped at both ends
+        const float d0 = fabsf(__fsub_rn(y, c_turbo_codebook[k]));
+        const float d1 = fabsf(__fsub_rn(y, c_turbo_codebook[k + 1]));
+        idx[j] = (unsigned)(k + (d1 < d0 ? 1 : 0));
     }
-    __syncwarp();
     uint8_t* msb = p.msb + b * p.ms_sb + h * p.ms_sh + (int64_t)t * p.ms_ss;
     uint8_t* lsb = p.lsb + b * p.ls_sb + h * p.ls_sh + (int64_t)t * p.ls_ss;
-    for (int k = lane; k < D / 8; k += 32) {
-        unsigned m = 0;
+    if constexpr (EPL == 4) {
+        // lane = channels 4l..4l+3: exactly one byte of the 2-bit plane, half a byte of the 1-bit plane
+        unsigned l8 = 0, m4 = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) m |= (unsigned)((s_idx[warp][8 * k + i] >> 2) & 1) << i;
-        msb[k] = (uint8_t)m;
-    }
-    for (int k = lane; k < D / 4; k += 32) {
-        unsigned m = 0;
+        for (int j = 0; j < 4; ++j) { l8 |= (idx[j] & 3u) << (2 * j); m4 |= ((idx[j] >> 2) & 1u) << j; }
+        const unsigned hi = __shfl_down_sync(0xffffffffu, m4, 1);
+        if (4 * lane < D) lsb[lane] = (uint8_t)l8;
+        if ((lane & 1) == 0 && 4 * lane < D) msb[lane >> 1] = (uint8_t)(m4 | (hi << 4));
+    } else {
+        uint8_t* si = s_idx[warp];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) m |= (unsigned)(s_idx[warp][4 * k + i] & 3) << (2 * i);
-        lsb[k] = (uint8_t)m;
+        for (int j = 0; j < EPL; ++j) {
+            const int i = lane * EPL + j;
+            if (i < D) si[i] = (uint8_t)idx[j];
+        }
+        __syncwarp();
+        for (int k = lane; k < D / 8; k += 32) {
+            unsigned m = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m |= (unsigned)((si[8 * k + i] >> 2) & 1) << i;
+            msb[k] = (uint8_t)m;
+        }
+        for (int k = lane; k < D / 4; k += 32) {
+            unsigned m = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m |= (unsigned)(si[4 * k + i] & 3) << (2 * i);
+            lsb[k] = (uint8_t)m;
+        }
     }
     if (lane == 0) p.scale[b * p.sc_sb + h * p.sc_sh + (int64_t)t * p.sc_ss] = f32_to_bf16_bits(s);
 }
