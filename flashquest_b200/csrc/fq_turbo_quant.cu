@@ -14,9 +14,72 @@ namespace fq {
 __device__ __constant__ float c_turbo_codebook[8] = {-2.1519f, -1.3439f, -0.7560f, -0.2451f,
                                                      0.2451f, 0.7560f, 1.3439f, 2.1519f};
 
+// Packed 16-bit arithmetic for the butterflies.  The reference adds two values of dtype T in
+// T: that is the correctly rounded sum, and so is rn_T(fp32 sum) because rounding first to 24
+// and then to 11 (or 8) bits is innocuous when 24 >= 2*11 + 2; the packed add is the same
+// correctly rounded sum, two values per instruction and no conversions.
+template <typename T> struct Pk2;
+template <> struct Pk2<__half> {
+    using type = __half2;
+    __device__ static type make(float a, float b) { return __floats2half2_rn(a, b); }
+    __device__ static float2 unpack(type x) { return __half22float2(x); }
+};
+template <> struct Pk2<__nv_bfloat16> {
+    using type = __nv_bfloat162;
+    __device__ static type make(float a, float b) { return __floats2bfloat162_rn(a, b); }
+    __device__ static float2 unpack(type x) { return __bfloat1622float2(x); }
+};
+template <typename P2> __device__ __forceinline__ uint32_t p2_bits(P2 x) { return *reinterpret_cast<uint32_t*>(&x); }
+template <typename P2> __device__ __forceinline__ P2 p2_from(uint32_t u) { return *reinterpret_cast<P2*>(&u); }
+
 // In-place WHT of the row spread over the warp: v[j] is element lane*EPL + j.
 template <typename T, int EPL>
 __device__ __forceinline__ void wht_lanes(float (&v)[EPL], int lane, int D) {
+    if constexpr (sizeof(T) == 2 && EPL >= 2) {
+        using P2 = typename Pk2<T>::type;
+        constexpr int NP = EPL / 2;
+        P2 x[NP];
+#pragma unroll
+        for (int i = 0; i < NP; ++i) x[i] = Pk2<T>::make(v[2 * i], v[2 * i + 1]);      // exact: the values are T already
+        // stride 1: (a, b) -> (a + b, a - b)
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const uint32_t u = p2_bits(x[i]);
+            const P2 aa = p2_from<P2>(__byte_perm(u, u, 0x1010));                         // (a, a)
+            const P2 bm = p2_from<P2>(__byte_perm(u, u, 0x3232) ^ 0x80000000u);           // (b, -b)
+            x[i] = __hadd2(aa, bm);
+        }
+        // strides 2 .. EPL/2: whole registers
+#pragma unroll
+        for (int h = 1; h < NP; h <<= 1) {
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                if ((i & h) == 0) {
+                    const P2 a = x[i], b = x[i + h];
+                    x[i] = __hadd2(a, b);
+                    x[i + h] = __hsub2(a, b);
+                }
+            }
+        }
+        // strides >= EPL: partner lane; the upper lane of a pair computes other - mine
+        for (int h = EPL; h < D; h <<= 1) {
+            const int lo = h / EPL;
+            const uint32_t flip = (lane & lo) ? 0x80008000u : 0u;
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                const uint32_t mine = p2_bits(x[i]);
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, lo);
+                x[i] = __hadd2(p2_from<P2>(other), p2_from<P2>(mine ^ flip));
+            }
+        }
+        const float cd = (float)sqrt((double)D);
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const float2 f = Pk2<T>::unpack(x[i]);
+            v[2 * i] = Dt<T>::rn(__fdiv_rn(f.x, cd));
+            v[2 * i + 1] = Dt<T>::rn(__fdiv_rn(f.y, cd));
+        }
+    } else {
 #pragma unroll
     for (int h = 1; h < EPL; h <<= 1) {
 #pragma unroll
@@ -40,6 +103,7 @@ __device__ __forceinline__ void wht_lanes(float (&v)[EPL], int lane, int D) {
     const float cd = (float)sqrt((double)D);    // the divisor the reference uses: fp32(math.sqrt(D))
 #pragma unroll
     for (int j = 0; j < EPL; ++j) v[j] = Dt<T>::rn(__fdiv_rn(v[j], cd));
+    }
 }
 
 template <typename T, int EPL>
@@ -94,9 +158,12 @@ struct TurboParams {
 template <typename T, int EPL>
 __global__ void __launch_bounds__(128) turbo_quant_kernel(TurboParams p) {
     __shared__ uint8_t s_idx[4][1024];
+    __shared__ float s_cb[9];          // the codebook where lanes may index it independently, +inf behind it
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = blockIdx.z, h = blockIdx.y;
     const int t = blockIdx.x * 4 + warp;
+    if (threadIdx.x < 9) s_cb[threadIdx.x] = threadIdx.x < 8 ? c_turbo_codebook[threadIdx.x] : INFINITY;
+    __syncthreads();
     if (t >= p.n_quant) return;
     const int D = p.D;
     const T* row = t < p.n_head
@@ -114,16 +181,20 @@ __global__ void __launch_bounds__(128) turbo_quant_kernel(TurboParams p) {
     // Nearest codebook entry, first index on ties (torch.argmin): the codebook is sorted, so
     // the winner is one of the two entries around y; which one is decided by the same fp32
     // distances the reference compares.
+    auto nearest = [&](float y, float& d0, float& d1) -> int {
+        int k = y >= 0.2451f ? 4 : 0;                          // c_4
+        k += y >= (k ? 1.3439f : -0.7560f) ? 2 : 0;           // c_6 or c_2
+        k += y >= s_cb[k + 1] ? 1 : 0;
+        k = min(k, 6);                                        // c_k <= y < c_{k+1}, clamped at both ends
+        d0 = fabsf(__fsub_rn(y, s_cb[k]));
+        d1 = fabsf(__fsub_rn(y, s_cb[k + 1]));
+        return k;
+    };
     unsigned idx[EPL];
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
-        const float y = __fdiv_rn(v[j], s);
-        int k = y >= c_turbo_codebook[4] ? 4 : 0;
-        k += y >= c_turbo_codebook[k + 2] ? 2 : 0;
-        k += y >= c_turbo_codebook[k + 1] ? 1 : 0;
-        k = min(k, 6);                                        // c_k <= y < c_{k+1}, clamped at both ends
-        const float d0 = fabsf(__fsub_rn(y, c_turbo_codebook[k]));
-        const float d1 = fabsf(__fsub_rn(y, c_turbo_codebook[k + 1]));
+        float d0, d1;
+        const int k = nearest(__fdiv_rn(v[j], s), d0, d1);
         idx[j] = (unsigned)(k + (d1 < d0 ? 1 : 0));
     }
     uint8_t* msb = p.msb + b * p.ms_sb + h * p.ms_sh + (int64_t)t * p.ms_ss;
