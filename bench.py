@@ -342,6 +342,14 @@ def run_ours(args):
     # ---- end to end through the Python API with host buffers ----
     e2e = run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier)
 
+    # ---- the attention kernel at batched shapes (rank 0, N = 1, default workload only) ----
+    batched = None
+    if rank == 0 and world == 1 and not (args.layers or args.ctx or args.batch) and not args.no_batched:
+        del graph, g2
+        cache = step = None
+        torch.cuda.empty_cache()
+        batched = [attention_batched(torch, dev, bn, 10) for bn in (16, 64)]
+
     # ---- CPU baseline (rank 0, N = 1 only) ----
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -356,11 +364,61 @@ def run_ours(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(cfg, world), "clocks": clk.summary(), "e2e": e2e,
-            "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu,
+            "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "attention_batched": batched,
+            "cpu_baseline": cpu,
             "device_status": status,
         }))
     if world > 1:
         dist.destroy_process_group()
+
+
+def attention_batched(torch, dev, Bn, steps):
+    """Attention launch alone at batch Bn (one layer, 32k context each, same selection rule):
+    the shape where the bytes, not the launch chain, set the time."""
+    from flashquest_b200.eager.criticality import page_scores_int4_fast
+    from flashquest_b200.eager.selection import select_pages_compact
+    from flashquest_b200.kernel.kv_quant import quantize_k_int4, quantize_v_int4
+    from flashquest_b200.kernel.sparse_int4_fwd_compact import flash_attn_sparse_int4_fwd_compact
+    Hq, Hkv, D, S, page = CFG["Hq"], CFG["Hkv"], CFG["D"], CFG["ctx"], CFG["page"]
+    g = torch.Generator(device=dev).manual_seed(4242)
+    parts = []
+    for _ in range(Bn):                       # one sequence at a time keeps the fp32 source small
+        K = torch.randn(1, Hkv, S, D, device=dev, generator=g)
+        K[..., [3, 17, 64, 100]] *= 8.0
+        V = torch.randn(1, Hkv, S, D, device=dev, generator=g)
+        parts.append(quantize_k_int4(K.half(), page) + quantize_v_int4(V.half()))
+        del K, V
+    kv = tuple(torch.cat([x[i] for x in parts]) for i in range(6))
+    del parts
+    Q = torch.randn(Bn, Hq, 1, D, device=dev, generator=g).half()
+    k_max = int(CFG["retention"] * (S // page))
+    bucket = k_max + CFG["sinks"] + CFG["window"]
+    comp = select_pages_compact(page_scores_int4_fast(Q, kv[1], kv[2]), CFG["retention"], CFG["sinks"], CFG["window"],
+                                k_max_static=k_max, BUCKET_MAX=bucket)
+
+    def run():
+        return flash_attn_sparse_int4_fwd_compact(Q, *kv, selected_page_ids=comp, page_size=page)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / steps
+    ids = comp.reshape(Bn, Hq, -1).long()
+    P = S // page
+    m = torch.zeros(Bn, Hq, P + 1, dtype=torch.bool, device=dev)
+    m.scatter_(2, torch.where(ids >= 0, ids, torch.full_like(ids, P)), True)
+    m = m[:, :, :P]
+    per_head = int(m.sum()) * PAGE_ATTN_BYTES
+    union = int(m.view(Bn, Hkv, Hq // Hkv, P).any(dim=2).sum()) * PAGE_ATTN_BYTES
+    peak, _ = measured_peak()
+    return {"batch": Bn, "avg_launch_us": us, "union_bytes": union, "per_head_bytes": per_head,
+            "GBs_union": union / us / 1e3, "GBs_per_head": per_head / us / 1e3,
+            "frac_union": union / us / 1e3 / peak, "frac_per_head": per_head / us / 1e3 / peak}
 
 
 def run_e2e(torch, dist, world, dev, cache, step, cfg, args, barrier):
@@ -548,6 +606,7 @@ def main():
     ap.add_argument("--n-split", type=int, default=0, help="override the split-K factor of the attention kernel")
     ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo"],
                     help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
+    ap.add_argument("--no-batched", action="store_true", help="skip the batched-attention leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
