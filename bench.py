@@ -594,6 +594,60 @@ def run_turbo(args):
         "peak": peak, "peak_kind": peak_kind, "device_status": _lib.lib().fq_device_status()}))
 
 
+# --------------------------------------------------------------------------- secondary workload: Llama decode
+
+def run_llama(args):
+    """BASELINE config 3 shape: random-init Llama-3.2-3B architecture with AWQ 4-bit weights, greedy
+    decode with the cache already holding 32 768 tokens per layer.  The cache is filled with seeded
+    synthetic K/V (the prefill path is not built), then `steps` decode steps are timed end to end:
+    embedding gather, 28 x (norms, AWQ GEMVs, RoPE, append + sparse attention, SwiGLU), lm_head, argmax."""
+    import torch
+    from flashquest_b200 import _lib
+    from flashquest_b200.eager.llama_decode import LlamaConfig, LlamaInt4Decoder, random_llama_weights
+    _lib.lib()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    cfg = LlamaConfig()
+    if args.layers:
+        cfg.layers = args.layers
+    S = args.ctx or 32768
+    w = random_llama_weights(cfg, dev, seed=3)
+    dec = LlamaInt4Decoder(cfg, w, batch_size=1, max_seq_len=S + 256, page_size=16, retention=0.25, num_sinks=1, window_pages=1,
+                           device=dev)
+    g = torch.Generator(device=dev)
+    for li in range(cfg.layers):
+        K = torch.randn(1, cfg.kv_heads, S, cfg.head_dim, device=dev, generator=g.manual_seed(2 * li))
+        K[..., [3, 17, 64, 100]] *= 8.0
+        V = torch.randn(1, cfg.kv_heads, S, cfg.head_dim, device=dev, generator=g.manual_seed(2 * li + 1))
+        dec.cache.update_quantized(K.half(), V.half(), li)
+        del K, V
+    ids = torch.tensor([1], dtype=torch.int32, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        ids = dec.decode_step(ids).clone()
+    torch.cuda.synchronize()
+    l0 = dec.launches + dec.attn.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index or 0) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            ids = dec.decode_step(ids).clone()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    wbytes = cfg.layers * sum(K * N // 2 + (K // 128) * N * 2 + (K // 128) * N // 2 for K, N in
+                              ((cfg.hidden, (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim), (cfg.q_heads * cfg.head_dim, cfg.hidden),
+                               (cfg.hidden, 2 * cfg.ffn), (cfg.ffn, cfg.hidden))) + cfg.vocab * cfg.hidden * 2
+    print(json.dumps({
+        "metric": "Llama-3.2-3B-shaped AWQ decode tokens/s at 32k ctx (sparse INT4 attention)", "workload": "llama",
+        "value": 1e3 / ms, "unit": "tokens/s", "ms_per_token": ms, "steps": args.steps,
+        "config": {"hidden": cfg.hidden, "layers": cfg.layers, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
+                   "ffn": cfg.ffn, "vocab": cfg.vocab, "context": S, "retention": 0.25, "weights": "random-init AWQ 4-bit, group 128",
+                   "cache": "synthetic K/V (prefill not built)"},
+        "weight_bytes_per_token": wbytes, "weight_GBs": wbytes / ms / 1e6,
+        "gpu_launches": dec.launches + dec.attn.launches - l0, "clocks": clk.summary(),
+        "device_status": _lib.lib().fq_device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -604,7 +658,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (small captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per GPU (profiles of batched shapes)")
     ap.add_argument("--n-split", type=int, default=0, help="override the split-K factor of the attention kernel")
-    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo", "llama"],
                     help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
     ap.add_argument("--no-batched", action="store_true", help="skip the batched-attention leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -615,6 +669,8 @@ def main():
         run_awq(args)
     elif args.workload == "turbo":
         run_turbo(args)
+    elif args.workload == "llama":
+        run_llama(args)
     else:
         run_ours(args)
 

@@ -1,0 +1,256 @@
+// The small operators around the sparse-decode path in a Llama-shaped decode step: residual
+// add + RMSNorm, rotary embedding of q and k, SwiGLU, the fp16 lm_head GEMV and argmax.
+// They restate what the reference's patched forward inherits from the Hugging Face Llama
+// modules it wraps (flashquest/eager/llama_persistent_patch.py:164-305 calls q/k/v_proj,
+// apply_rotary_pos_emb, o_proj; the decoder layer around it adds the norms, residuals and the
+// MLP), with the same intermediate roundings to fp16.  All are HBM- or latency-bound
+// element-wise / reduction kernels; one launch each, programmatic dependent launch like the
+// rest of the chain.
+#include "fq_common.cuh"
+
+namespace fq {
+
+constexpr int NORM_THREADS = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* s_red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < nw; ++w) t += s_red[w];
+    return t;
+}
+
+// h = a (+ b) in fp16; sum_out = h; y = weight * fp16(h * rsqrt(mean(h^2) + eps))   (one CTA per row)
+__global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(
+    const __half* __restrict__ a, const __half* __restrict__ b, const __half* __restrict__ weight, float eps,
+    int H, __half* __restrict__ sum_out, __half* __restrict__ y) {
+    __shared__ float s_red[NORM_THREADS / 32];
+    extern __shared__ __half s_row[];                 // the row after the add
+    const int64_t row = blockIdx.x;
+    pdl_wait();
+    pdl_trigger();
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
+        __half h = a[row * H + i];
+        if (b) h = __hadd(h, b[row * H + i]);
+        s_row[i] = h;
+        if (sum_out) sum_out[row * H + i] = h;
+        const float f = __half2float(h);
+        ss = fmaf(f, f, ss);
+    }
+    const float var = block_sum(ss, s_red) / (float)H;
+    const float r = rsqrtf(var + eps);
+    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
+        const __half xh = __float2half_rn(__half2float(s_row[i]) * r);
+        y[row * H + i] = __hmul(weight[i], xh);
+    }
+}
+
+// Rotary embedding in place, Hugging Face "rotate_half" convention: for i < D/2
+//   out[i]       = x[i]*cos_i       + (-x[i + D/2])*sin_i
+//   out[i + D/2] = x[i + D/2]*cos_i + ( x[i])*sin_i
+// with cos/sin computed in fp32 from pos * theta^(-2i/D) and rounded to fp16, products and sum in fp16.
+__global__ void __launch_bounds__(128) rope_kernel(__half* __restrict__ q, int64_t q_sb, int64_t q_sh, int Hq,
+                                                   __half* __restrict__ k, int64_t k_sb, int64_t k_sh, int Hkv,
+                                                   int D, int pos, float theta) {
+    const int head = blockIdx.x, b = blockIdx.y;
+    pdl_wait();
+    pdl_trigger();
+    __half* x = head < Hq ? q + b * q_sb + head * q_sh : k + b * k_sb + (head - Hq) * k_sh;
+    const int half = D / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float inv_freq = 1.0f / powf(theta, (float)(2 * i) / (float)D);
+        const float ang = (float)pos * inv_freq;
+        const __half c = __float2half_rn(cosf(ang)), s = __float2half_rn(sinf(ang));
+        const __half x1 = x[i], x2 = x[i + half];
+        x[i] = __hadd(__hmul(x1, c), __hmul(__hneg(x2), s));
+        x[i + half] = __hadd(__hmul(x2, c), __hmul(x1, s));
+    }
+}
+
+// out = fp16(silu(gate)) * up, silu evaluated in fp32
+__global__ void __launch_bounds__(256) swiglu_kernel(const __half2* __restrict__ gate, const __half2* __restrict__ up,
+                                                     int64_t n2, __half2* __restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n2; i += (int64_t)gridDim.x * blockDim.x) {
+        const float2 g = __half22float2(gate[i]);
+        const __half2 a = __floats2half2_rn(g.x / (1.0f + expf(-g.x)), g.y / (1.0f + expf(-g.y)));
+        out[i] = __hmul2(a, up[i]);
+    }
+}
+
+// y[m, n] = sum_k x[m, k] * W[n, k]: fp16 weights (N, K) row-major read once, fp32 accumulation.
+// One warp per output row, x (M <= 8 rows) staged in shared memory as fp32.
+constexpr int GEMVH_WARPS = 8;
+template <int M>
+__global__ void __launch_bounds__(GEMVH_WARPS * 32) gemv_f16_kernel(const __half* __restrict__ x, const __half* __restrict__ W,
+                                                                    int Mrows, int K, int N, __half* __restrict__ y) {
+    extern __shared__ float s_x[];                    // [M][K]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * GEMVH_WARPS + warp;
+    // the weights never change: request the first pieces of the row before the dependency wait
+    uint4 w0 = make_uint4(0, 0, 0, 0);
+    const uint4* wrow = reinterpret_cast<const uint4*>(W + (int64_t)min(n, N - 1) * K);
+    if (lane * 8 < K) w0 = __ldg(wrow + lane);
+    pdl_wait();
+    pdl_trigger();
+    for (int i = threadIdx.x; i < M * K; i += GEMVH_WARPS * 32) {
+        const int m = i / K, kk = i % K;
+        s_x[i] = m < Mrows ? __half2float(x[(int64_t)m * K + kk]) : 0.f;
+    }
+    __syncthreads();
+    if (n >= N) return;
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    for (int c = lane; c * 8 < K; c += 32) {
+        const uint4 w = c == lane ? w0 : __ldg(wrow + c);
+        const __half2* wh = reinterpret_cast<const __half2*>(&w);
+        float wf[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __half22float2(wh[j]); wf[2 * j] = f.x; wf[2 * j + 1] = f.y; }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float4 xa = *reinterpret_cast<const float4*>(s_x + m * K + c * 8);
+            const float4 xb = *reinterpret_cast<const float4*>(s_x + m * K + c * 8 + 4);
+            acc[m] = fmaf(wf[0], xa.x, fmaf(wf[1], xa.y, fmaf(wf[2], xa.z, fmaf(wf[3], xa.w, acc[m]))));
+            acc[m] = fmaf(wf[4], xb.x, fmaf(wf[5], xb.y, fmaf(wf[6], xb.z, fmaf(wf[7], xb.w, acc[m]))));
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], off);
+        if (lane == 0 && m < Mrows) y[(int64_t)m * N + n] = __float2half_rn(acc[m]);
+    }
+}
+
+// index of the first maximum of each row (torch.argmax); one CTA per row
+__global__ void __launch_bounds__(1024) argmax_f16_kernel(const __half* __restrict__ x, int N, int32_t* __restrict__ out) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const int64_t row = blockIdx.x;
+    pdl_wait();
+    pdl_trigger();
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        const float v = __half2float(x[row * N + i]);
+        if (v > best || (v == best && i < bi) || bi == 0x7fffffff) { best = v; bi = i; }
+    }
+    auto better = [](float v, int i, float bv, int b2) { return v > bv || (v == bv && i < b2); };
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? s_v[lane] : -INFINITY;
+        bi = lane < nw ? s_i[lane] : 0x7fffffff;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) out[row] = bi;
+    }
+}
+
+}  // namespace fq
+
+extern "C" int fq_add_rmsnorm(const void* a, const void* b, const void* weight, float eps, int64_t rows, int H,
+                              void* sum_out, void* y, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_add_rmsnorm";
+    FQ_CHECK_ARG(a && weight && y && rows >= 0 && H > 0, FQ_ERR_ARG, "%s: bad arguments", fn);
+    FQ_CHECK_ARG((size_t)H * 2 <= 96 * 1024, FQ_ERR_UNSUPPORTED, "%s: hidden size %d too large", fn, H);
+    if (rows == 0) return FQ_OK;
+    const size_t smem = (size_t)H * 2;
+    if (smem > 40 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));
+    }
+    launch_k(PDL_GEMV, add_rmsnorm_kernel, dim3((unsigned)rows), dim3(NORM_THREADS), smem, static_cast<cudaStream_t>(stream),
+             static_cast<const __half*>(a), static_cast<const __half*>(b), static_cast<const __half*>(weight), eps, H,
+             static_cast<__half*>(sum_out), static_cast<__half*>(y));
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+
+extern "C" int fq_rope(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv,
+                       int B, int D, int pos, float theta, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_rope";
+    FQ_CHECK_ARG(q && k && B > 0 && Hq > 0 && Hkv > 0 && D > 0 && D % 2 == 0 && pos >= 0 && theta > 0.f, FQ_ERR_ARG, "%s: bad arguments", fn);
+    FQ_CHECK_ARG(B <= 65535, FQ_ERR_ARG, "%s: batch %d too large", fn, B);
+    launch_k(PDL_GEMV, rope_kernel, dim3((unsigned)(Hq + Hkv), (unsigned)B), dim3(D / 2 < 128 ? (D / 2 + 31) / 32 * 32 : 128), 0,
+             static_cast<cudaStream_t>(stream), static_cast<__half*>(q), q_sb, q_sh, Hq, static_cast<__half*>(k), k_sb, k_sh, Hkv,
+             D, pos, theta);
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+
+extern "C" int fq_swiglu(const void* gate, const void* up, int64_t n, void* out, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_swiglu";
+    FQ_CHECK_ARG(gate && up && out && n >= 0 && n % 2 == 0, FQ_ERR_ARG, "%s: bad arguments (n must be even)", fn);
+    FQ_CHECK_ARG(aligned(gate, 4) && aligned(up, 4) && aligned(out, 4), FQ_ERR_ALIGN, "%s: tensors must be 4-byte aligned", fn);
+    if (n == 0) return FQ_OK;
+    const int64_t n2 = n / 2;
+    const unsigned blocks = (unsigned)((n2 + 255) / 256 < 148 * 8 ? (n2 + 255) / 256 : 148 * 8);
+    launch_k(PDL_GEMV, swiglu_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __half2*>(gate), static_cast<const __half2*>(up), n2, static_cast<__half2*>(out));
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+
+extern "C" int fq_gemv_f16(const void* x, const void* W, int M, int K, int N, void* y, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_gemv_f16";
+    FQ_CHECK_ARG(x && W && y && N > 0 && K > 0, FQ_ERR_ARG, "%s: bad arguments", fn);
+    FQ_CHECK_ARG(M >= 1 && M <= 8, FQ_ERR_UNSUPPORTED, "%s: M=%d rows; 1..8 are built", fn, M);
+    FQ_CHECK_ARG(K % 8 == 0 && aligned(W, 16) && aligned(x, 2), FQ_ERR_ALIGN, "%s: K must be a multiple of 8 and W 16-byte aligned", fn);
+    const int Mp = M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
+    const size_t smem = (size_t)Mp * K * 4;
+    FQ_CHECK_ARG(smem <= 200 * 1024, FQ_ERR_UNSUPPORTED, "%s: M x K = %d x %d does not fit in shared memory", fn, M, K);
+    dim3 grid((unsigned)((N + GEMVH_WARPS - 1) / GEMVH_WARPS));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define FQ_GH(MV)                                                                                                  \
+    do {                                                                                                           \
+        if (smem > 40 * 1024) {                                                                                    \
+            cudaError_t e = cudaFuncSetAttribute(gemv_f16_kernel<MV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));                   \
+        }                                                                                                          \
+        launch_k(PDL_GEMV, gemv_f16_kernel<MV>, grid, dim3(GEMVH_WARPS * 32), smem, st, static_cast<const __half*>(x), \
+                 static_cast<const __half*>(W), M, K, N, static_cast<__half*>(y));                                 \
+    } while (0)
+    if (Mp == 1) FQ_GH(1);
+    else if (Mp == 2) FQ_GH(2);
+    else if (Mp == 4) FQ_GH(4);
+    else FQ_GH(8);
+#undef FQ_GH
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+
+extern "C" int fq_argmax_f16(const void* x, int64_t rows, int N, int32_t* out, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_argmax_f16";
+    FQ_CHECK_ARG(x && out && rows >= 0 && N > 0, FQ_ERR_ARG, "%s: bad arguments", fn);
+    if (rows == 0) return FQ_OK;
+    launch_k(PDL_GEMV, argmax_f16_kernel, dim3((unsigned)rows), dim3(1024), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __half*>(x), N, out);
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}

@@ -1,0 +1,171 @@
+"""A Llama-shaped decode step on top of the sparse-decode path.
+
+The reference reaches its kernels through a monkey-patched Hugging Face attention forward
+(flashquest/eager/llama_persistent_patch.py:164-305) inside HF's decoder-layer loop; the norms,
+residuals, rotary embedding and the SwiGLU MLP around it are HF's.  This module is that loop
+for one new token per sequence, written against the C ABI: per layer
+
+    add+RMSNorm -> fused AWQ q/k/v GEMV -> RoPE -> append + score + select + sparse attention
+    -> AWQ o GEMV -> add+RMSNorm -> fused AWQ gate/up GEMV -> SwiGLU -> AWQ down GEMV
+
+and after the last layer add+RMSNorm -> fp16 lm_head GEMV -> argmax.  Weights are passed in;
+`random_llama_weights` builds a seeded random-init set of a given architecture (AWQ tensors
+with uniform codes, scales ~ U(0.001, 0.02)), which is what the benchmark uses.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+from .._lib import check, lib, ptr, stream_ptr
+from ..cache.persistent_int4 import PersistentInt4KVCache
+from ..kernel.fused_proj import awq_gemv_fused
+from ..quant import AWQLinear
+from .decode_step import QuestDecodeInt4
+
+
+@dataclass
+class LlamaConfig:
+    hidden: int = 3072
+    layers: int = 28
+    q_heads: int = 24
+    kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 8192
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-5
+    group_size: int = 128
+
+
+@dataclass
+class LlamaLayerWeights:
+    input_norm: torch.Tensor
+    q_proj: AWQLinear
+    k_proj: AWQLinear
+    v_proj: AWQLinear
+    o_proj: AWQLinear
+    post_norm: torch.Tensor
+    gate_proj: AWQLinear
+    up_proj: AWQLinear
+    down_proj: AWQLinear
+
+
+@dataclass
+class LlamaWeights:
+    embed: torch.Tensor                 # (vocab, hidden) fp16
+    layers: List[LlamaLayerWeights] = field(default_factory=list)
+    final_norm: Optional[torch.Tensor] = None
+    lm_head: Optional[torch.Tensor] = None   # (vocab, hidden) fp16
+
+
+def _awq(K, N, group, gen, dev):
+    qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), dtype=torch.int32, device=dev, generator=gen)
+    qz = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // group, N // 8), dtype=torch.int32, device=dev, generator=gen)
+    sc = (torch.rand(K // group, N, device=dev, generator=gen) * 0.019 + 0.001).half()
+    return AWQLinear(qw, sc, qz, group_size=group)
+
+
+def random_llama_weights(cfg: LlamaConfig, device, seed: int = 0, scale_down: float = 1.0) -> LlamaWeights:
+    """Seeded random-init weights of the given architecture.  `scale_down` multiplies the AWQ
+    scales (random 4-bit codes with zero-mean offsets make activations grow layer by layer;
+    tests use it to keep values inside fp16)."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    H, D = cfg.hidden, cfg.head_dim
+    w = LlamaWeights(embed=(torch.randn(cfg.vocab, H, device=dev, generator=g) * 0.02).half())
+
+    def lin(K, N):
+        a = _awq(K, N, cfg.group_size, g, dev)
+        if scale_down != 1.0:
+            a.scales = (a.scales.float() * scale_down).half()
+        return a
+
+    for _ in range(cfg.layers):
+        w.layers.append(LlamaLayerWeights(
+            input_norm=(1.0 + 0.1 * torch.randn(H, device=dev, generator=g)).half(),
+            q_proj=lin(H, cfg.q_heads * D), k_proj=lin(H, cfg.kv_heads * D), v_proj=lin(H, cfg.kv_heads * D),
+            o_proj=lin(cfg.q_heads * D, H),
+            post_norm=(1.0 + 0.1 * torch.randn(H, device=dev, generator=g)).half(),
+            gate_proj=lin(H, cfg.ffn), up_proj=lin(H, cfg.ffn), down_proj=lin(cfg.ffn, H)))
+    w.final_norm = (1.0 + 0.1 * torch.randn(H, device=dev, generator=g)).half()
+    w.lm_head = (torch.randn(cfg.vocab, H, device=dev, generator=g) * 0.02).half()
+    return w
+
+
+class LlamaInt4Decoder:
+    """Greedy decode, one token per call and sequence, over a persistent INT4 cache."""
+
+    def __init__(self, cfg: LlamaConfig, weights: LlamaWeights, *, batch_size: int, max_seq_len: int, page_size: int = 16,
+                 retention: float = 0.25, num_sinks: int = 1, window_pages: int = 1, device="cuda"):
+        self.cfg, self.w = cfg, weights
+        self.dev = torch.device(device)
+        self.B = batch_size
+        self.cache = PersistentInt4KVCache(batch_size=batch_size, num_layers=cfg.layers, num_kv_heads=cfg.kv_heads,
+                                           head_dim=cfg.head_dim, max_seq_len=max_seq_len, page_size=page_size,
+                                           device=self.dev, dtype=torch.float16)
+        self.attn = QuestDecodeInt4(self.cache, num_q_heads=cfg.q_heads, retention=retention, num_sinks=num_sinks,
+                                    window_pages=window_pages, q_dtype=torch.float16)
+        H = cfg.hidden
+        mk = lambda *s: torch.empty(*s, dtype=torch.float16, device=self.dev)
+        self.resid = [mk(batch_size, H), mk(batch_size, H)]      # the residual stream alternates between the two
+        self.normed, self.act = mk(batch_size, H), mk(batch_size, cfg.ffn)
+        self.logits = mk(batch_size, cfg.vocab)
+        self.next_ids = torch.empty(batch_size, dtype=torch.int32, device=self.dev)
+        self.launches = 0
+
+    # -- thin wrappers over the C ABI ------------------------------------------------------
+    def _add_rmsnorm(self, a, b, weight, sum_out, y):
+        check(lib().fq_add_rmsnorm(ptr(a), ptr(b), ptr(weight), self.cfg.rms_eps, a.shape[0], a.shape[1],
+                                   ptr(sum_out), ptr(y), stream_ptr(self.dev)))
+        self.launches += 1
+
+    def _rope(self, q, k, pos):
+        c = self.cfg
+        check(lib().fq_rope(ptr(q), q.stride(0), q.stride(1), c.q_heads, ptr(k), k.stride(0), k.stride(1), c.kv_heads,
+                            self.B, c.head_dim, int(pos), c.rope_theta, stream_ptr(self.dev)))
+        self.launches += 1
+
+    def decode_step(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """token_ids (B,) -> next token ids (B,) int32 (greedy); logits of the step stay in self.logits."""
+        c, w, B = self.cfg, self.w, self.B
+        L = lib()
+        st = stream_ptr(self.dev)
+        pos = self.cache.get_seq_length(0)
+        x = w.embed[token_ids.long()]                            # (B, H) gather: plumbing
+        flip = 0
+
+        def add_norm(x, delta, weight):
+            """x <- x + delta (into the residual buffer that does not hold x); normed <- RMSNorm(x)."""
+            nonlocal flip
+            if delta is None:
+                self._add_rmsnorm(x, None, weight, None, self.normed)
+                return x
+            out = self.resid[flip]
+            flip ^= 1
+            self._add_rmsnorm(x, delta, weight, out, self.normed)
+            return out
+
+        delta = None                                             # output of the previous block, not yet added
+        for li, lw in enumerate(w.layers):
+            x = add_norm(x, delta, lw.input_norm)
+            q, k, v = awq_gemv_fused(self.normed.view(B, 1, -1), (lw.q_proj, lw.k_proj, lw.v_proj))
+            q = q.view(B, c.q_heads, c.head_dim)
+            k = k.view(B, c.kv_heads, c.head_dim)
+            v = v.view(B, c.kv_heads, 1, c.head_dim)
+            self._rope(q, k, pos)
+            O, _ = self.attn.step(k.unsqueeze(2), v, q.unsqueeze(2), li)
+            (attn_out,) = awq_gemv_fused(O.reshape(B, 1, c.q_heads * c.head_dim), (lw.o_proj,))
+            x = add_norm(x, attn_out.view(B, -1), lw.post_norm)
+            gate, up = awq_gemv_fused(self.normed.view(B, 1, -1), (lw.gate_proj, lw.up_proj))
+            check(L.fq_swiglu(ptr(gate), ptr(up), gate.numel(), ptr(self.act), st))
+            (down,) = awq_gemv_fused(self.act.view(B, 1, -1), (lw.down_proj,))
+            delta = down.view(B, -1)
+            self.launches += 5
+        x = add_norm(x, delta, w.final_norm)
+        check(L.fq_gemv_f16(ptr(self.normed), ptr(w.lm_head), B, c.hidden, c.vocab, ptr(self.logits), st))
+        check(L.fq_argmax_f16(ptr(self.logits), B, c.vocab, ptr(self.next_ids), st))
+        self.launches += 2
+        return self.next_ids

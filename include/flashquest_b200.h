@@ -349,6 +349,27 @@ int fq_decode_step_int4(
     float* scores, int64_t sc_sl, int32_t* compact, int64_t cp_sl, void* O, int64_t o_sl, float* lse, int64_t lse_sl,
     void* workspace, size_t ws_sl, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------
+ * The operators around the sparse-decode path in a Llama-shaped decode step.  The reference
+ * inherits them from the Hugging Face modules its patched forward wraps
+ * (eager/llama_persistent_patch.py:164-305: q/k/v_proj, apply_rotary_pos_emb, o_proj; the
+ * decoder layer adds the norms, residuals and the SwiGLU MLP); same fp16 roundings here.
+ * All tensors fp16, dense.
+ *   fq_add_rmsnorm: h = a (+ b if not NULL); sum_out = h (if not NULL); y = weight * fp16(h * rsqrt(mean(h^2)+eps)),
+ *                   rows x H.
+ *   fq_rope:        rotate-half rotary embedding in place on q (B,Hq,D) and k (B,Hkv,D) (element strides sb, sh)
+ *                   at position pos, base theta.
+ *   fq_swiglu:      out = fp16(silu(gate)) * up over n elements (n even).
+ *   fq_gemv_f16:    y (M,N) = x (M,K) @ W(N,K)^T, fp32 accumulation, 1 <= M <= 8 (the lm_head at decode).
+ *   fq_argmax_f16:  index of the first maximum of each row of x (rows,N). */
+int fq_add_rmsnorm(const void* a, const void* b, const void* weight, float eps, int64_t rows, int H,
+                   void* sum_out, void* y, void* stream);
+int fq_rope(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv,
+            int B, int D, int pos, float theta, void* stream);
+int fq_swiglu(const void* gate, const void* up, int64_t n, void* out, void* stream);
+int fq_gemv_f16(const void* x, const void* W, int M, int K, int N, void* y, void* stream);
+int fq_argmax_f16(const void* x, int64_t rows, int N, int32_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,145 @@
+"""The Llama-shaped decode step (norms, rotary embedding, AWQ projections, sparse INT4 attention,
+SwiGLU, lm_head, argmax) against a CPU restatement with Hugging Face's fp16 roundings, built
+from the oracle's AWQ GEMV and attention chain, token by token from an empty cache."""
+import math
+
+import pytest
+import torch
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _rms(x, w, eps):
+    xf = x.float()
+    xh = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).half()
+    return w * xh
+
+
+def _awq(x, lin):
+    return oracle.awq_gemv(x, lin.qweight.cpu(), lin.scales.cpu(), lin.qzeros.cpu(), group_size=lin.group_size).half()
+
+
+def _rope(x, pos, theta):
+    # x (B, H, D) fp16; Hugging Face rotate_half convention with fp16 cos / sin
+    D = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2).float() / D))
+    ang = pos * inv
+    cos = torch.cat([ang, ang]).cos().half()
+    sin = torch.cat([ang, ang]).sin().half()
+    rot = torch.cat([-x[..., D // 2:], x[..., : D // 2]], dim=-1)
+    return x * cos + rot * sin
+
+
+class _Ref:
+    def __init__(self, cfg, w, page, retention, sinks, window, k_max_static):
+        self.cfg, self.w, self.page = cfg, w, page
+        self.sel = (retention, sinks, window, k_max_static)
+        self.K = [None] * cfg.layers
+        self.V = [None] * cfg.layers
+
+    def step(self, ids):
+        c, w = self.cfg, self.w
+        B = ids.shape[0]
+        pos = 0 if self.K[0] is None else self.K[0].shape[2]
+        x = w.embed.cpu()[ids.long()]
+        delta = None
+        for li, lw in enumerate(w.layers):
+            if delta is not None:
+                x = x + delta
+            n = _rms(x, lw.input_norm.cpu(), c.rms_eps)
+            q = _awq(n, lw.q_proj).view(B, c.q_heads, c.head_dim)
+            k = _awq(n, lw.k_proj).view(B, c.kv_heads, c.head_dim)
+            v = _awq(n, lw.v_proj).view(B, c.kv_heads, c.head_dim)
+            q, k = _rope(q, pos, c.rope_theta), _rope(k, pos, c.rope_theta)
+            self.K[li] = k.unsqueeze(2) if self.K[li] is None else torch.cat([self.K[li], k.unsqueeze(2)], 2)
+            self.V[li] = v.unsqueeze(2) if self.V[li] is None else torch.cat([self.V[li], v.unsqueeze(2)], 2)
+            seen = self.K[li].shape[2]
+            nq = seen - seen % self.page
+            Kc, Vc = self.K[li][:, :, :nq], self.V[li][:, :, :nq]
+            kv = oracle.quantize_k_int4(Kc, self.page) + oracle.quantize_v_int4(Vc)
+            r, s, wn, kms = self.sel
+            if nq > 0:
+                sc = oracle.page_scores_int4_fast(q.unsqueeze(2), kv[1], kv[2])
+                mask = oracle.select_pages_vectorized(sc, r, s, wn, k_max_static=kms)
+            else:
+                mask = torch.zeros(B, c.q_heads, 1, 0, dtype=torch.bool)
+            O, _ = oracle.sparse_attn_int4(q.unsqueeze(2), *kv, selection_mask=mask, page_size=self.page,
+                                           K_partial=self.K[li][:, :, nq:], V_partial=self.V[li][:, :, nq:])
+            attn = _awq(O.half().reshape(B, -1), lw.o_proj)
+            x = x + attn
+            n = _rms(x, lw.post_norm.cpu(), c.rms_eps)
+            gate, up = _awq(n, lw.gate_proj), _awq(n, lw.up_proj)
+            act = torch.nn.functional.silu(gate.float()).half() * up
+            delta = _awq(act, lw.down_proj)
+        x = x + delta
+        n = _rms(x, w.final_norm.cpu(), c.rms_eps)
+        return (n.float() @ w.lm_head.cpu().float().T).half()
+
+
+def test_small_ops_match_torch():
+    from flashquest_b200._lib import check, lib, ptr, stream_ptr
+    L = lib()
+    g = torch.Generator().manual_seed(3)
+    dev = torch.device("cuda")
+    st = lambda: stream_ptr(dev)
+    # add + RMSNorm
+    a, b = torch.randn(3, 3072, generator=g).half(), torch.randn(3, 3072, generator=g).half()
+    wt = (1 + 0.1 * torch.randn(3072, generator=g)).half()
+    s_out, y = torch.empty(3, 3072, dtype=torch.float16, device=dev), torch.empty(3, 3072, dtype=torch.float16, device=dev)
+    ad, bd, wd = a.cuda(), b.cuda(), wt.cuda()             # keep the device copies alive across the launch
+    check(L.fq_add_rmsnorm(ptr(ad), ptr(bd), ptr(wd), 1e-5, 3, 3072, ptr(s_out), ptr(y), st()))
+    h = a + b
+    assert torch.equal(s_out.cpu(), h)
+    assert (y.cpu().float() - _rms(h, wt, 1e-5).float()).abs().max() <= 2e-3      # one fp16 ulp at |y| ~ 4
+    # RoPE
+    q, k = torch.randn(2, 6, 128, generator=g).half(), torch.randn(2, 2, 128, generator=g).half()
+    qd, kd = q.cuda(), k.cuda()
+    check(L.fq_rope(ptr(qd), qd.stride(0), qd.stride(1), 6, ptr(kd), kd.stride(0), kd.stride(1), 2, 2, 128, 32767, 500000.0, st()))
+    assert (qd.cpu().float() - _rope(q, 32767, 500000.0).float()).abs().max() <= 6e-3   # sin/cos of a large angle in fp32
+    assert (kd.cpu().float() - _rope(k, 32767, 500000.0).float()).abs().max() <= 6e-3
+    # SwiGLU
+    gt, up = torch.randn(2, 8192, generator=g).half() * 3, torch.randn(2, 8192, generator=g).half()
+    out = torch.empty(2, 8192, dtype=torch.float16, device=dev)
+    gd, ud = gt.cuda(), up.cuda()
+    check(L.fq_swiglu(ptr(gd), ptr(ud), gt.numel(), ptr(out), st()))
+    want = torch.nn.functional.silu(gt.float()).half() * up
+    assert (out.cpu().float() - want.float()).abs().max() <= 4e-3
+    # fp16 GEMV + argmax
+    x, W = torch.randn(3, 512, generator=g).half(), (torch.randn(1000, 512, generator=g) * 0.05).half()
+    yv = torch.empty(3, 1000, dtype=torch.float16, device=dev)
+    xd, Wd = x.cuda(), W.cuda()
+    check(L.fq_gemv_f16(ptr(xd), ptr(Wd), 3, 512, 1000, ptr(yv), st()))
+    ref = (x.float() @ W.float().T)
+    assert (yv.cpu().float() - ref).abs().max() <= 2e-3 * ref.abs().max() + 1e-3
+    idx = torch.empty(3, dtype=torch.int32, device=dev)
+    yv[1, 7] = yv[1].max() ; yv[1, 500] = yv[1, 7]               # a tie: the first index wins
+    check(L.fq_argmax_f16(ptr(yv), 3, 1000, ptr(idx), st()))
+    assert idx.cpu().tolist() == yv.float().argmax(-1).cpu().tolist()
+    assert idx[1].item() == int((yv[1] == yv[1].max()).nonzero()[0])
+
+
+def test_decode_steps_match_cpu_restatement():
+    from flashquest_b200.eager.llama_decode import LlamaConfig, LlamaInt4Decoder, random_llama_weights
+    cfg = LlamaConfig(hidden=256, layers=2, q_heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=512)
+    w = random_llama_weights(cfg, "cuda", seed=1)
+    page, B = 16, 2
+    dec = LlamaInt4Decoder(cfg, w, batch_size=B, max_seq_len=64, page_size=page, retention=0.5, num_sinks=1, window_pages=1)
+    ref = _Ref(cfg, w, page, 0.5, 1, 1, dec.attn.k_max_static)
+    ids = torch.tensor([5, 300], dtype=torch.int32)
+    worst = 0.0
+    for t in range(36):                                   # crosses two page boundaries
+        nxt = dec.decode_step(ids.cuda())
+        got = dec.logits.float().cpu()
+        want = ref.step(ids).float()
+        tol = 3e-2 * want.abs().max().item() + 1e-2
+        err = (got - want).abs().max().item()
+        worst = max(worst, err / tol)
+        assert err <= tol, (t, err, tol)
+        top2 = want.topk(2, dim=-1).values
+        for b in range(B):
+            if (top2[b, 0] - top2[b, 1]).item() > 2 * tol:
+                assert nxt[b].item() == int(want[b].argmax())
+        ids = want.argmax(-1).to(torch.int32)             # both sides continue from the reference's choice
+    assert dec.cache.get_seq_length(0) == 36
