@@ -55,6 +55,35 @@ class DecodeParams(ctypes.Structure):
                 ("window", I), ("bucket", I), ("sm_scale", F), ("n_split", I)]
 
 
+class AwqLinearDesc(ctypes.Structure):
+    """struct fq_awq_linear."""
+    _fields_ = [("qweight", P), ("scales", P), ("qzeros", P), ("bias", P), ("K", I), ("N", I)]
+
+
+class LlamaLayerDesc(ctypes.Structure):
+    """struct fq_llama_layer."""
+    _fields_ = [("input_norm", P), ("q", AwqLinearDesc), ("k", AwqLinearDesc), ("v", AwqLinearDesc), ("o", AwqLinearDesc),
+                ("post_norm", P), ("gate", AwqLinearDesc), ("up", AwqLinearDesc), ("down", AwqLinearDesc)]
+
+
+class LlamaModelDesc(ctypes.Structure):
+    """struct fq_llama_model."""
+    _fields_ = [("hidden", I), ("n_layers", I), ("q_heads", I), ("kv_heads", I), ("head_dim", I), ("ffn", I), ("vocab", I),
+                ("group", I), ("interleaved", I), ("rope_theta", F), ("rms_eps", F),
+                ("layers", ctypes.POINTER(LlamaLayerDesc)), ("final_norm", P), ("lm_head", P)]
+
+
+class LlamaScratchDesc(ctypes.Structure):
+    """struct fq_llama_scratch."""
+    _fields_ = [("resid0", P), ("resid1", P), ("normed", P), ("q", P), ("k", P), ("v", P), ("attn_out", P), ("down", P),
+                ("gate", P), ("up", P), ("act", P), ("logits", P), ("next_ids", P),
+                ("gemv_ws", P * 4), ("gemv_ws_bytes", Z * 4),
+                ("scores", P), ("sc_sl", L), ("compact", P), ("cp_sl", L), ("O", P), ("o_sl", L),
+                ("attn_ws", P), ("attn_ws_sl", Z), ("attn_ws_bytes", Z)]
+
+
+_PROTOTYPES["fq_llama_decode_step"] = (I, [ctypes.POINTER(LlamaModelDesc), ctypes.POINTER(Int4CacheDesc),
+                                          ctypes.POINTER(DecodeParams), P, P, I, ctypes.POINTER(LlamaScratchDesc), P])
 _PROTOTYPES["fq_awq_gemv_workspace_bytes"] = (Z, [I, I, I])
 _PROTOTYPES["fq_awq_gemv_default_splits"] = (I, [I, I, I])
 _PROTOTYPES["fq_awq_gemv"] = (I, [P, I, I, I, I, P, P, P, P, P, P, I, P, Z, I, P])

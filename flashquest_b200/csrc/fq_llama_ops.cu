@@ -254,3 +254,86 @@ extern "C" int fq_argmax_f16(const void* x, int64_t rows, int N, int32_t* out, v
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
+
+extern "C" int fq_llama_decode_step(const fq_llama_model* m, const fq_int4_cache* cache, const fq_decode_params* prm,
+                                    const int* seen, const void* x, int B, const fq_llama_scratch* s, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_llama_decode_step";
+    FQ_CHECK_ARG(m && cache && prm && seen && x && s && m->layers, FQ_ERR_ARG, "%s: null argument", fn);
+    FQ_CHECK_ARG(B >= 1 && B <= 8 && B == cache->B, FQ_ERR_ARG, "%s: batch %d (cache %d); 1..8 sequences are built", fn, B, cache->B);
+    FQ_CHECK_ARG(m->n_layers >= 1 && m->n_layers <= cache->L && m->kv_heads == cache->Hkv && m->head_dim == cache->D &&
+                 m->q_heads == prm->Hq, FQ_ERR_ARG, "%s: model and cache shapes differ", fn);
+    FQ_CHECK_ARG(cache->kv_dtype == FQ_F16, FQ_ERR_DTYPE, "%s: the step computes in fp16; the cache stages dtype code %d", fn, cache->kv_dtype);
+    const int H = m->hidden, D = m->head_dim, Hq = m->q_heads, Hkv = m->kv_heads;
+    const int nq = Hq * D, nkv = Hkv * D;
+    int rc;
+    // split counts of the four GEMV shapes
+    const int ks_qkv = fq_awq_gemv_default_splits(H, nq + 2 * nkv, m->group);
+    const int ks_o = fq_awq_gemv_default_splits(nq, H, m->group);
+    const int ks_gu = fq_awq_gemv_default_splits(H, 2 * m->ffn, m->group);
+    const int ks_dn = fq_awq_gemv_default_splits(m->ffn, H, m->group);
+
+    const void* xin = x;          // residual stream; alternates between the two buffers
+    const void* delta = nullptr;  // output of the previous block, added by the next norm
+    int flip = 0;
+    auto add_norm = [&](const void* w) -> int {
+        void* out = nullptr;
+        if (delta) { out = flip ? s->resid1 : s->resid0; flip ^= 1; }
+        const int r = fq_add_rmsnorm(xin, delta, w, m->rms_eps, B, H, out, s->normed, stream);
+        if (out) xin = out;
+        return r;
+    };
+    for (int l = 0; l < m->n_layers; ++l) {
+        const fq_llama_layer& L = m->layers[l];
+        FQ_CHECK_ARG(L.q.K == H && L.q.N == nq && L.k.N == nkv && L.v.N == nkv && L.o.K == nq && L.o.N == H &&
+                     L.gate.N == m->ffn && L.up.N == m->ffn && L.down.K == m->ffn && L.down.N == H, FQ_ERR_ARG,
+                     "%s: layer %d has unexpected projection shapes", fn, l);
+        if ((rc = add_norm(L.input_norm)) != FQ_OK) return rc;
+        {
+            const int32_t* qw[3] = {L.q.qweight, L.k.qweight, L.v.qweight};
+            const void* sc[3] = {L.q.scales, L.k.scales, L.v.scales};
+            const int32_t* qz[3] = {L.q.qzeros, L.k.qzeros, L.v.qzeros};
+            const void* bs[3] = {L.q.bias, L.k.bias, L.v.bias};
+            const int N[3] = {nq, nkv, nkv};
+            void* y[3] = {s->q, s->k, s->v};
+            rc = fq_awq_gemv(s->normed, B, H, m->group, 3, qw, sc, qz, (bs[0] || bs[1] || bs[2]) ? bs : nullptr, N, y, m->interleaved,
+                             s->gemv_ws[0], s->gemv_ws_bytes[0], ks_qkv, stream);
+            if (rc != FQ_OK) return rc;
+        }
+        if ((rc = fq_rope(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, seen[l], m->rope_theta, stream)) != FQ_OK) return rc;
+        void* Ol = static_cast<char*>(s->O) + (size_t)l * s->o_sl * 2;
+        rc = fq_decode_layer_int4(cache, l, seen[l], s->k, s->v, nkv, D, D, 1, s->q, FQ_F16, nq, D, prm,
+                                  s->scores + l * s->sc_sl, s->compact + l * s->cp_sl, Ol, nullptr,
+                                  static_cast<char*>(s->attn_ws) + (size_t)l * s->attn_ws_sl, s->attn_ws_bytes, stream);
+        if (rc != FQ_OK) return rc;
+        {
+            const int32_t* qw[1] = {L.o.qweight}; const void* sc[1] = {L.o.scales}; const int32_t* qz[1] = {L.o.qzeros};
+            const void* bs[1] = {L.o.bias}; const int N[1] = {H}; void* y[1] = {s->attn_out};
+            rc = fq_awq_gemv(Ol, B, nq, m->group, 1, qw, sc, qz, bs[0] ? bs : nullptr, N, y, m->interleaved,
+                             s->gemv_ws[1], s->gemv_ws_bytes[1], ks_o, stream);
+            if (rc != FQ_OK) return rc;
+        }
+        delta = s->attn_out;
+        if ((rc = add_norm(L.post_norm)) != FQ_OK) return rc;
+        {
+            const int32_t* qw[2] = {L.gate.qweight, L.up.qweight}; const void* sc[2] = {L.gate.scales, L.up.scales};
+            const int32_t* qz[2] = {L.gate.qzeros, L.up.qzeros}; const void* bs[2] = {L.gate.bias, L.up.bias};
+            const int N[2] = {m->ffn, m->ffn}; void* y[2] = {s->gate, s->up};
+            rc = fq_awq_gemv(s->normed, B, H, m->group, 2, qw, sc, qz, (bs[0] || bs[1]) ? bs : nullptr, N, y, m->interleaved,
+                             s->gemv_ws[2], s->gemv_ws_bytes[2], ks_gu, stream);
+            if (rc != FQ_OK) return rc;
+        }
+        if ((rc = fq_swiglu(s->gate, s->up, (int64_t)B * m->ffn, s->act, stream)) != FQ_OK) return rc;
+        {
+            const int32_t* qw[1] = {L.down.qweight}; const void* sc[1] = {L.down.scales}; const int32_t* qz[1] = {L.down.qzeros};
+            const void* bs[1] = {L.down.bias}; const int N[1] = {H}; void* y[1] = {s->down};
+            rc = fq_awq_gemv(s->act, B, m->ffn, m->group, 1, qw, sc, qz, bs[0] ? bs : nullptr, N, y, m->interleaved,
+                             s->gemv_ws[3], s->gemv_ws_bytes[3], ks_dn, stream);
+            if (rc != FQ_OK) return rc;
+        }
+        delta = s->down;
+    }
+    if ((rc = add_norm(m->final_norm)) != FQ_OK) return rc;
+    if ((rc = fq_gemv_f16(s->normed, m->lm_head, B, H, m->vocab, s->logits, stream)) != FQ_OK) return rc;
+    return fq_argmax_f16(s->logits, B, m->vocab, s->next_ids, stream);
+}

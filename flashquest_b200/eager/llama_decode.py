@@ -19,7 +19,9 @@ from typing import List, Optional
 
 import torch
 
-from .._lib import check, lib, ptr, stream_ptr
+import ctypes
+
+from .._lib import (AwqLinearDesc, LlamaLayerDesc, LlamaModelDesc, LlamaScratchDesc, check, lib, ptr, stream_ptr)
 from ..cache.persistent_int4 import PersistentInt4KVCache
 from ..kernel.fused_proj import awq_gemv_fused
 from ..quant import AWQLinear
@@ -115,6 +117,55 @@ class LlamaInt4Decoder:
         self.logits = mk(batch_size, cfg.vocab)
         self.next_ids = torch.empty(batch_size, dtype=torch.int32, device=self.dev)
         self.launches = 0
+        self._build_native()
+
+    def _build_native(self):
+        """Descriptors of the one-call step (fq_llama_decode_step): weights, scratch, split-K workspaces."""
+        c, w, B, a = self.cfg, self.w, self.B, self.attn
+        L = lib()
+
+        def lin(x):
+            return AwqLinearDesc(ptr(x.qweight), ptr(x.scales), ptr(x.qzeros), ptr(x.bias), x.in_features, x.out_features)
+
+        self._layers = (LlamaLayerDesc * c.layers)(*[
+            LlamaLayerDesc(ptr(lw.input_norm), lin(lw.q_proj), lin(lw.k_proj), lin(lw.v_proj), lin(lw.o_proj),
+                           ptr(lw.post_norm), lin(lw.gate_proj), lin(lw.up_proj), lin(lw.down_proj)) for lw in w.layers])
+        inter = int(bool(getattr(w.layers[0].q_proj, "interleaved", True)))
+        self._model = LlamaModelDesc(c.hidden, c.layers, c.q_heads, c.kv_heads, c.head_dim, c.ffn, c.vocab, c.group_size, inter,
+                                     c.rope_theta, c.rms_eps, self._layers, ptr(w.final_norm), ptr(w.lm_head))
+        mk = lambda *s: torch.empty(*s, dtype=torch.float16, device=self.dev)
+        nq, nkv = c.q_heads * c.head_dim, c.kv_heads * c.head_dim
+        self._nat = dict(q=mk(B, nq), k=mk(B, nkv), v=mk(B, nkv), attn_out=mk(B, c.hidden), down=mk(B, c.hidden),
+                         gate=mk(B, c.ffn), up=mk(B, c.ffn))
+        shapes = ((c.hidden, nq + 2 * nkv), (nq, c.hidden), (c.hidden, 2 * c.ffn), (c.ffn, c.hidden))
+        self._gemv_ws = []
+        with torch.cuda.device(self.dev):
+            for K, N in shapes:
+                ks = L.fq_awq_gemv_default_splits(K, N, c.group_size)
+                self._gemv_ws.append(torch.zeros(max(L.fq_awq_gemv_workspace_bytes(B, N, ks), 256), dtype=torch.uint8, device=self.dev))
+        n = self._nat
+        self._scratch = LlamaScratchDesc(
+            ptr(self.resid[0]), ptr(self.resid[1]), ptr(self.normed), ptr(n["q"]), ptr(n["k"]), ptr(n["v"]),
+            ptr(n["attn_out"]), ptr(n["down"]), ptr(n["gate"]), ptr(n["up"]), ptr(self.act), ptr(self.logits), ptr(self.next_ids),
+            (ctypes.c_void_p * 4)(*[ptr(t) for t in self._gemv_ws]), (ctypes.c_size_t * 4)(*[t.numel() for t in self._gemv_ws]),
+            ptr(a.scores), a.scores.stride(0), ptr(a.compact), a.compact.stride(0), ptr(a.O), a.O.stride(0),
+            ptr(a.workspace), a.workspace.stride(0), a.workspace.shape[1])
+
+    def decode_step(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """token_ids (B,) -> next token ids (B,) int32 (greedy), the whole step in one foreign call
+        (fq_llama_decode_step); logits of the step stay in self.logits."""
+        c = self.cache
+        n_l = self.cfg.layers
+        x = self.w.embed[token_ids.long()]                       # (B, H) gather: plumbing
+        seen = (ctypes.c_int * n_l)(*c._seen_tokens[:n_l])
+        if c._seen_tokens[0] + 1 > c.max_seq_len:
+            raise RuntimeError(f"PersistentInt4KVCache: seen+new={c._seen_tokens[0] + 1} exceeds max_seq_len={c.max_seq_len}")
+        check(lib().fq_llama_decode_step(ctypes.byref(self._model), ctypes.byref(self.attn._cdesc), ctypes.byref(self.attn._prm),
+                                         seen, ptr(x), self.B, ctypes.byref(self._scratch), stream_ptr(self.dev)))
+        for li in range(n_l):
+            c._seen_tokens[li] += 1
+        self.launches += 12 * n_l + 3
+        return self.next_ids
 
     # -- thin wrappers over the C ABI ------------------------------------------------------
     def _add_rmsnorm(self, a, b, weight, sum_out, y):
@@ -128,8 +179,8 @@ class LlamaInt4Decoder:
                             self.B, c.head_dim, int(pos), c.rope_theta, stream_ptr(self.dev)))
         self.launches += 1
 
-    def decode_step(self, token_ids: torch.Tensor) -> torch.Tensor:
-        """token_ids (B,) -> next token ids (B,) int32 (greedy); logits of the step stay in self.logits."""
+    def decode_step_per_op(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """The same step issued operator by operator from Python (one foreign call per kernel group)."""
         c, w, B = self.cfg, self.w, self.B
         L = lib()
         st = stream_ptr(self.dev)

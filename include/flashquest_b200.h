@@ -370,6 +370,49 @@ int fq_swiglu(const void* gate, const void* up, int64_t n, void* out, void* stre
 int fq_gemv_f16(const void* x, const void* W, int M, int K, int N, void* y, void* stream);
 int fq_argmax_f16(const void* x, int64_t rows, int N, int32_t* out, void* stream);
 
+/* ------------------------------------------------------------------------------------
+ * One greedy decode step of a Llama-shaped model in ONE foreign call: the decoder-layer loop
+ * around eager/llama_persistent_patch.py:164-305 (Hugging Face's LlamaDecoderLayer / LlamaMLP /
+ * LlamaRMSNorm semantics) issued from native code, 12 launches per layer and no host work
+ * between them.  Per layer: add+RMSNorm, fused AWQ q/k/v GEMV, RoPE, fq_decode_layer_int4
+ * (append + score + select + attend), AWQ o GEMV, add+RMSNorm, fused AWQ gate/up GEMV, SwiGLU,
+ * AWQ down GEMV; then add+RMSNorm, fp16 lm_head GEMV, argmax.  fp16 model, B <= 8 sequences.
+ * All pointers inside the structs are device pointers except `layers` (host array). */
+typedef struct fq_awq_linear {
+    const int32_t* qweight; const void* scales; const int32_t* qzeros; const void* bias;   /* bias may be NULL */
+    int K, N;
+} fq_awq_linear;
+
+typedef struct fq_llama_layer {
+    const void* input_norm; fq_awq_linear q, k, v, o;
+    const void* post_norm; fq_awq_linear gate, up, down;
+} fq_llama_layer;
+
+typedef struct fq_llama_model {
+    int hidden, n_layers, q_heads, kv_heads, head_dim, ffn, vocab, group, interleaved;
+    float rope_theta, rms_eps;
+    const fq_llama_layer* layers;                  /* host array of n_layers entries */
+    const void* final_norm; const void* lm_head;   /* (hidden), (vocab, hidden) fp16 */
+} fq_llama_model;
+
+typedef struct fq_llama_scratch {
+    void *resid0, *resid1, *normed;                /* (B, hidden) fp16 */
+    void *q, *k, *v;                               /* (B, q_heads*D), (B, kv_heads*D) x2 fp16 */
+    void *attn_out, *down;                         /* (B, hidden) fp16 */
+    void *gate, *up, *act;                         /* (B, ffn) fp16 */
+    void* logits; int32_t* next_ids;               /* (B, vocab) fp16, (B) */
+    void* gemv_ws[4]; size_t gemv_ws_bytes[4];     /* split-K scratch of the q/k/v, o, gate/up and down GEMVs, tickets zero */
+    float* scores; int64_t sc_sl;                  /* per layer (B,Hq,P_max) fp32, layer stride in elements */
+    int32_t* compact; int64_t cp_sl;               /* per layer (B,Hq,bucket) */
+    void* O; int64_t o_sl;                         /* per layer (B,Hq,D) fp16 */
+    void* attn_ws; size_t attn_ws_sl, attn_ws_bytes;   /* per layer split-K scratch of the attention, tickets zero */
+} fq_llama_scratch;
+
+/* x (B, hidden) fp16: the embedding rows of this step's tokens; seen[layer] tokens already cached
+ * (all sequences of the batch are at the same position).  Writes scratch->logits and next_ids. */
+int fq_llama_decode_step(const fq_llama_model* model, const fq_int4_cache* cache, const fq_decode_params* params,
+                         const int* seen, const void* x, int B, const fq_llama_scratch* scratch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -130,7 +130,7 @@ def test_decode_steps_match_cpu_restatement():
     ids = torch.tensor([5, 300], dtype=torch.int32)
     worst = 0.0
     for t in range(36):                                   # crosses two page boundaries
-        nxt = dec.decode_step(ids.cuda())
+        nxt = dec.decode_step(ids.cuda()) if t % 3 else dec.decode_step_per_op(ids.cuda())   # one-call step and per-operator route
         got = dec.logits.float().cpu()
         want = ref.step(ids).float()
         tol = 3e-2 * want.abs().max().item() + 1e-2
