@@ -46,26 +46,6 @@ __device__ __forceinline__ uint32_t pack8(const float (&q)[8]) {
     return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
-// eight 16-bit elements held as a raw 16-byte load -> fp32
-template <typename T>
-__device__ __forceinline__ void unpack8(const uint4& u, float (&v)[8]);
-template <>
-__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& u, float (&v)[8]) {
-    v[0] = bf16_lo(u.x); v[1] = bf16_hi(u.x); v[2] = bf16_lo(u.y); v[3] = bf16_hi(u.y);
-    v[4] = bf16_lo(u.z); v[5] = bf16_hi(u.z); v[6] = bf16_lo(u.w); v[7] = bf16_hi(u.w);
-}
-template <>
-__device__ __forceinline__ void unpack8<__half>(const uint4& u, float (&v)[8]) {
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-        v[2 * i] = f.x; v[2 * i + 1] = f.y;
-    }
-}
-template <>
-__device__ __forceinline__ void unpack8<float>(const uint4&, float (&)[8]) {}   // never used: fp32 takes the two-pass route
-
 template <typename T>
 __device__ __forceinline__ const T* stream_row(const T* head, const T* nw, const QuantParams& p,
                                                int b, int h, int t) {
@@ -91,113 +71,8 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
     if (page_idx < p.n_pages) {
         const int t0 = page_idx * p.page;
         const int n_tok = min(p.page, p.n_quant - t0);
-        constexpr int RI = 8;            // iterations whose raw loads fit in registers
-        const bool in_regs = sizeof(T) == 2 && (p.page + TPI - 1) / TPI <= RI;
-        // ---------------- pages of 16-bit inputs that fit in registers ----------------
-        // All loads of the page are issued before anything is computed and the K page is read
-        // once: min/max and the codes both come from the raw registers.
-        if (in_regs) {
-            if (p.K_scale != nullptr) {
-                uint4 raw[RI];
-#pragma unroll
-                for (int it = 0; it < RI; ++it) {
-                    const int tt = ti + it * TPI;
-                    raw[it] = tt < n_tok ? *reinterpret_cast<const uint4*>(stream_row<T>(Kh, Kn, p, b, h, t0 + tt) + 8 * c) : make_uint4(0, 0, 0, 0);
-                }
-                float mn[8], mx[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { mn[i] = INFINITY; mx[i] = -INFINITY; }
-#pragma unroll
-                for (int it = 0; it < RI; ++it) {
-                    if (ti + it * TPI < n_tok) {
-                        float v[8];
-                        unpack8<T>(raw[it], v);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) { mn[i] = fminf(mn[i], v[i]); mx[i] = fmaxf(mx[i], v[i]); }
-                    }
-                }
-                for (int off = LPT; off < 32; off <<= 1) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        mn[i] = fminf(mn[i], __shfl_xor_sync(0xffffffffu, mn[i], off));
-                        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], off));
-                    }
-                }
-                float sc[8], rsc[8];
-                const float eps = Dt<T>::rn(1e-6f);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float diff = Dt<T>::rn(__fsub_rn(mx[i], mn[i]));
-                    sc[i] = fmaxf(Dt<T>::rn(__fdiv_rn(diff, 15.0f)), eps);
-                    rsc[i] = __frcp_rn(sc[i]);
-                }
-                if (ti == 0) {
-                    uint32_t s4[4], m4[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        s4[i] = f32_to_bf16_bits(sc[2 * i]) | ((uint32_t)f32_to_bf16_bits(sc[2 * i + 1]) << 16);
-                        m4[i] = f32_to_bf16_bits(mn[2 * i]) | ((uint32_t)f32_to_bf16_bits(mn[2 * i + 1]) << 16);
-                    }
-                    const int64_t mo = b * p.km_sb + h * p.km_sh + (int64_t)page_idx * p.km_sp + 8 * c;
-                    *reinterpret_cast<uint4*>(p.K_scale + mo) = make_uint4(s4[0], s4[1], s4[2], s4[3]);
-                    *reinterpret_cast<uint4*>(p.K_mn + mo) = make_uint4(m4[0], m4[1], m4[2], m4[3]);
-                }
-                if (p.K_packed != nullptr) {
-#pragma unroll
-                    for (int it = 0; it < RI; ++it) {
-                        const int tt = ti + it * TPI;
-                        if (tt < n_tok) {
-                            float v[8], q[8];
-                            unpack8<T>(raw[it], v);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) q[i] = code4f(v[i], mn[i], sc[i], rsc[i]);
-                            uint8_t* row = p.K_packed + b * p.pk_sb + h * p.pk_sh + (int64_t)(t0 + tt) * p.pk_ss;
-                            *reinterpret_cast<uint32_t*>(row + 4 * c) = pack8(q);
-                        }
-                    }
-                }
-            }
-            if (p.V_packed != nullptr) {
-                uint4 raw[RI];
-#pragma unroll
-                for (int it = 0; it < RI; ++it) {
-                    const int tt = ti + it * TPI;
-                    raw[it] = tt < n_tok ? *reinterpret_cast<const uint4*>(stream_row<T>(Vh, Vn, p, b, h, t0 + tt) + 8 * c) : make_uint4(0, 0, 0, 0);
-                }
-#pragma unroll
-                for (int it = 0; it < RI; ++it) {
-                    const int tt = ti + it * TPI;
-                    if (it * TPI < n_tok) {                       // warp-uniform: the shuffles need every lane
-                        const bool live = tt < n_tok;
-                        float v[8];
-                        unpack8<T>(raw[it], v);
-                        float lo = v[0], hi = v[0];
-#pragma unroll
-                        for (int i = 1; i < 8; ++i) { lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
-                        for (int off = 1; off < LPT; off <<= 1) {
-                            lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-                            hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-                        }
-                        if (live) {
-                            const float sc = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 15.0f), 1e-6f);
-                            const float rsc = __frcp_rn(sc);
-                            float q[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) q[i] = code4f(v[i], lo, sc, rsc);
-                            uint8_t* row = p.V_packed + b * p.pk_sb + h * p.pk_sh + (int64_t)(t0 + tt) * p.pk_ss;
-                            *reinterpret_cast<uint32_t*>(row + 4 * c) = pack8(q);
-                            if (c == 0) {
-                                const int64_t mo = b * p.vm_sb + h * p.vm_sh + (int64_t)(t0 + tt) * p.vm_ss;
-                                p.V_scale[mo] = f32_to_bf16_bits(sc);
-                                p.V_mn[mo] = f32_to_bf16_bits(lo);
-                            }
-                        }
-                    }
-                }
-            }
-        }
         // ---------------- K: per page, per channel ----------------
-        if (!in_regs && p.K_scale != nullptr) {      // K_packed may be NULL: metadata only
+        if (p.K_scale != nullptr) {      // K_packed may be NULL: metadata only
             float mn[8], mx[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) { mn[i] = INFINITY; mx[i] = -INFINITY; }
@@ -246,7 +121,7 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
             }
         }
         // ---------------- V: per token ----------------
-        if (!in_regs && p.V_packed != nullptr) {
+        if (p.V_packed != nullptr) {
             for (int tt = ti; tt < n_tok + ti; tt += TPI) {   // uniform trip count for the shuffles
                 const bool live = tt < n_tok;
                 float v[8];
