@@ -648,6 +648,75 @@ def run_llama(args):
         "device_status": _lib.lib().fq_device_status()}))
 
 
+# --------------------------------------------------------------------------- secondary workload: context split
+
+def run_ctxsplit(args):
+    """One very long sequence split by page range over the ranks (torchrun, N >= 2): per decode step
+    local scores -> all-gather of top-k candidates -> global top-k -> local sparse attention ->
+    all-gather of (O, lse) -> LSE merge.  Reports the step time (max over ranks, CUDA events) and the
+    share spent in the two exchanges."""
+    import torch
+    import torch.distributed as dist
+    from flashquest_b200 import _lib
+    from flashquest_b200.eager import context_split as cs
+    from flashquest_b200.kernel.kv_quant import quantize_k_int4, quantize_v_int4
+    _lib.lib()
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world < 2:
+        if rank == 0:
+            print(json.dumps({"workload": "ctxsplit", "unavailable": "needs torchrun with at least 2 ranks"}))
+        return
+    dist.init_process_group("nccl", device_id=dev)
+    Hq, Hkv, D, page = CFG["Hq"], CFG["Hkv"], CFG["D"], CFG["page"]
+    S = args.ctx or 524288                     # the whole sequence
+    P = S // page
+    lo, hi = cs.page_range(rank, world, P)
+    g = torch.Generator(device=dev).manual_seed(900 + rank)
+    n_tok = (hi - lo) * page
+    K = torch.randn(1, Hkv, n_tok, D, device=dev, generator=g)
+    K[..., [3, 17, 64, 100]] *= 8.0
+    V = torch.randn(1, Hkv, n_tok, D, device=dev, generator=g)
+    kv = quantize_k_int4(K.half(), page) + quantize_v_int4(V.half())
+    del K, V
+    q = torch.randn(1, Hq, 1, D, device=dev, generator=torch.Generator(device=dev).manual_seed(5)).half()   # same on every rank
+    kw = dict(P_global=P, page_size=page, retention=CFG["retention"], num_sinks=CFG["sinks"], window_pages=CFG["window"])
+
+    def step(timings=None):
+        return cs.decode_context_split_int4(q, kv[0], kv[1], kv[2], kv[3], kv[4], kv[5], timings=timings, **kw)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    tm = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(tm)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    seg = lambda a, b: sum(x.elapsed_time(y) for x, y in zip(tm[a], tm[b])) / args.steps
+    parts = torch.tensor([ms, seg("start", "scored"), seg("scored", "selected"), seg("selected", "attended"),
+                          seg("attended", "merged")], device=dev)
+    dist.all_reduce(parts, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms, t_sc, t_sel, t_att, t_mrg = [float(x) for x in parts]
+        print(json.dumps({
+            "metric": "context-split sparse INT4 decode, one layer-step of one sequence", "workload": "ctxsplit", "n_gpus": world,
+            "config": {"context": S, "pages": P, "pages_per_rank": hi - lo, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D,
+                       "page_size": page, "retention": CFG["retention"]},
+            "ms_per_layer_step": ms, "steps": args.steps,
+            "phases_ms_max_over_ranks": {"local_scores": t_sc, "global_topk_incl_candidate_allgather": t_sel,
+                                         "compact_and_local_attention": t_att, "o_lse_allgather_and_merge": t_mrg},
+            "device_status": _lib.lib().fq_device_status()}))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -658,7 +727,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (small captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per GPU (profiles of batched shapes)")
     ap.add_argument("--n-split", type=int, default=0, help="override the split-K factor of the attention kernel")
-    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo", "llama"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo", "llama", "ctxsplit"],
                     help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
     ap.add_argument("--no-batched", action="store_true", help="skip the batched-attention leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -671,6 +740,8 @@ def main():
         run_turbo(args)
     elif args.workload == "llama":
         run_llama(args)
+    elif args.workload == "ctxsplit":
+        run_ctxsplit(args)
     else:
         run_ours(args)
 

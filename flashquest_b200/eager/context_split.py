@@ -50,23 +50,31 @@ class ContextSplitOps:
     index; merge(O_parts (n,B,H,1,D), lse_parts (n,B,H,1)) -> (O, lse)."""
     top_k_mask: Callable
     merge: Callable
+    compact: Optional[Callable] = None     # compact(mask (B,H,1,P) bool, bucket) -> (B,H,1,bucket) int32 descending ids, -1 padded
 
 
 def cuda_ops() -> ContextSplitOps:
-    from .selection import select_pages_vectorized
+    from .selection import build_compact_selection, select_pages_vectorized
     from .tail_merge import merge_attentions
 
     def top_k_mask(scores, k):
         return select_pages_vectorized(scores, 1.0, 0, 0, k_max_static=k)
 
-    return ContextSplitOps(top_k_mask=top_k_mask, merge=merge_attentions)
+    return ContextSplitOps(top_k_mask=top_k_mask, merge=merge_attentions, compact=build_compact_selection)
 
 
 def _all_gather(t: torch.Tensor, group) -> torch.Tensor:
+    """(world, *t.shape): one collective into one preallocated tensor where the backend has it."""
     world = dist.get_world_size(group)
-    out = [torch.empty_like(t) for _ in range(world)]
-    dist.all_gather(out, t.contiguous(), group=group)
-    return torch.stack(out)
+    t = t.contiguous()
+    out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+    try:
+        dist.all_gather_into_tensor(out, t, group=group)
+    except (RuntimeError, NotImplementedError):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t, group=group)
+        out = torch.stack(parts)
+    return out
 
 
 def select_pages_context_split(scores_local: torch.Tensor, *, P_global: int, retention: float, num_sinks: int,
@@ -92,10 +100,14 @@ def select_pages_context_split(scores_local: torch.Tensor, *, P_global: int, ret
         cand = torch.full((B, H, 2, k_c), float("-inf"), dtype=torch.float32, device=dev)
         ids = torch.full((B, H, k_c), -1, dtype=torch.int32, device=dev)
         if P_local > 0:
-            local_mask = ops.top_k_mask(scores_local, min(k_c, P_local))[:, :, 0]            # (B,H,P_local)
             n_c = min(k_c, P_local)
-            # ascending local ids of the candidates: stable sort of "not selected" keeps page order
-            order = torch.sort((~local_mask).to(torch.uint8), dim=-1, stable=True).indices[..., :n_c]
+            local_mask4 = ops.top_k_mask(scores_local, n_c)                                   # (B,H,1,P_local), exactly n_c set
+            if ops.compact is not None:
+                # the compact list is descending: reversed it is the ascending ids of the candidates
+                order = ops.compact(local_mask4, n_c)[:, :, 0].flip(-1).long()
+            else:
+                # stable sort of "not selected" keeps page order
+                order = torch.sort((~local_mask4[:, :, 0]).to(torch.uint8), dim=-1, stable=True).indices[..., :n_c]
             cand[:, :, 0, :n_c] = torch.gather(scores_local[:, :, 0], -1, order)
             ids[:, :, :n_c] = (order + lo).to(torch.int32)
         cand[:, :, 1] = ids.view(torch.float32)                    # page ids travel bit-cast in the same message

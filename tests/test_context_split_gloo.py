@@ -20,7 +20,7 @@ def _free_port():
     return port
 
 
-def _ops():
+def _ops(use_compact=False):
     from flashquest_b200.eager.context_split import ContextSplitOps
 
     def top_k_mask(scores, k):
@@ -29,7 +29,8 @@ def _ops():
     def merge(O_parts, lse_parts):
         return oracle.lse_merge(O_parts, lse_parts)
 
-    return ContextSplitOps(top_k_mask=top_k_mask, merge=merge)
+    return ContextSplitOps(top_k_mask=top_k_mask, merge=merge,
+                           compact=oracle.build_compact_selection if use_compact else None)
 
 
 def _worker(rank, world, port, case, out_q):
@@ -51,7 +52,7 @@ def _worker(rank, world, port, case, out_q):
             scores = (scores * 2).round() / 2                                # many equal scores
         ref_mask = oracle.select_pages_vectorized(scores, retention, sinks, window)
         lo, hi = cs.page_range(rank, world, P)
-        ops = _ops()
+        ops = _ops(use_compact=(world == 3))      # 3 ranks: candidate ids from the compact list; 2 ranks: from the sort
         mask = cs.select_pages_context_split(scores[..., lo:hi].contiguous(), P_global=P, retention=retention,
                                              num_sinks=sinks, window_pages=window, ops=ops)
         ok_mask = torch.equal(mask, ref_mask[..., lo:hi])
