@@ -221,14 +221,6 @@ template <typename T>
 __device__ __forceinline__ float ld_as_f32(const void* p, int64_t i) { return Dt<T>::to_f32(static_cast<const T*>(p)[i]); }
 
 // ---------------------------------------------------------------- the kernel
-template <int N, typename F>
-__device__ __forceinline__ void static_for(F&& f) {
-    if constexpr (N > 0) {
-        static_for<N - 1>(f);
-        f(std::integral_constant<int, N - 1>{});
-    }
-}
-
 // What a quarter warp knows about a unit besides its payload.
 template <int DPL, int TPL>
 struct UnitCtx {
@@ -243,10 +235,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     constexpr int DPL = D / 8;        // channels per lane
     constexpr int WPL = DPL / 8;      // 32-bit words per lane per token
     constexpr int TPL = TOK / 8;      // tokens per lane after the reduction
-#ifndef FQ_ATT_KT
-#define FQ_ATT_KT 1
-#endif
-    constexpr int KT = FQ_ATT_KT;     // tokens whose K dot products are interleaved
     constexpr int NSTATE = ATT_WARPS * 4 + ATT_WARPS;   // quarter-warp states + per-warp tail states
     constexpr int NBARS = 2 * ATT_WARPS * ATT_STAGES;
 
@@ -372,18 +360,9 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
             const uint16_t* kmr = Km + (int64_t)c.page_id * p.km_sp + DPL * l;
 #pragma unroll
             for (int j = 0; j < DPL / 8; ++j) {
-#ifdef FQ_EXP_NOMETA
-                c.ks[j] = make_uint4(0x3c003c00u + c.page_id, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u);
-                c.km[j] = make_uint4(0x3c003c00u, 0x3c003c00u + c.tok0, 0x3c003c00u, 0x3c003c00u);
-#else
                 c.ks[j] = ldg16(ksr + 8 * j);
                 c.km[j] = ldg16(kmr + 8 * j);
-#endif
             }
-#ifdef FQ_EXP_NOMETA
-            c.vs_raw = 0x3c003c00u + c.tok0; c.vm_raw = 0x3c003c00u;
-            return;
-#endif
             if (c.n_tok == TOK && TPL == 2) {
                 c.vs_raw = __ldg(reinterpret_cast<const uint32_t*>(Vs + c.tok0 + 2 * l));
                 c.vm_raw = __ldg(reinterpret_cast<const uint32_t*>(Vm + c.tok0 + 2 * l));
@@ -442,29 +421,21 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
             prefetch();
 
             float sdot[TOK];
-            // KT tokens at a time, one accumulator pair each: KT independent fma chains
+            // one token at a time (interleaving several tokens by hand measured slower: register pressure)
 #pragma unroll
-            for (int t0 = 0; t0 < TOK; t0 += KT) {
-                uint32_t w[KT][WPL];
-#pragma unroll
-                for (int tt = 0; tt < KT; ++tt) ld_words<WPL>(u + L::K_OFF + (t0 + tt) * L::ROW + 4 * WPL * l, w[tt]);
-                float2 a[KT];
-#pragma unroll
-                for (int tt = 0; tt < KT; ++tt) a[tt] = make_float2(0.f, 0.f);
+            for (int t = 0; t < TOK; ++t) {
+                uint32_t w[WPL];
+                ld_words<WPL>(u + L::K_OFF + t * L::ROW + 4 * WPL * l, w);
+                float2 a = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int wd = 0; wd < WPL; ++wd) {
-                    float f[KT][8];
+                    float f[8];
+                    nib8(w[wd], f);
 #pragma unroll
-                    for (int tt = 0; tt < KT; ++tt) nib8(w[tt][wd], f[tt]);
-#pragma unroll
-                    for (int e = 0; e < 8; e += 2) {
-                        const float2 q2 = make_float2(qs[8 * wd + e], qs[8 * wd + e + 1]);
-#pragma unroll
-                        for (int tt = 0; tt < KT; ++tt) a[tt] = __ffma2_rn(make_float2(f[tt][e], f[tt][e + 1]), q2, a[tt]);
-                    }
+                    for (int e = 0; e < 8; e += 2)
+                        a = __ffma2_rn(make_float2(f[e], f[e + 1]), make_float2(qs[8 * wd + e], qs[8 * wd + e + 1]), a);
                 }
-#pragma unroll
-                for (int tt = 0; tt < KT; ++tt) sdot[t0 + tt] = a[tt].x + a[tt].y;
+                sdot[t] = a.x + a.y;
             }
             qw_transpose_reduce<TOK>(sdot, l, qmask);
 
