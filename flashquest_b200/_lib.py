@@ -108,6 +108,8 @@ _PROTOTYPES["fq_swiglu"] = (I, [P, P, L, P, P])
 _PROTOTYPES["fq_gemv_f16"] = (I, [P, P, I, I, I, P, P])
 _PROTOTYPES["fq_argmax_f16"] = (I, [P, L, I, P, P])
 
+_PROTOTYPES["fq_decode_step_int4_dev"] = _PROTOTYPES["fq_decode_step_int4"]
+
 # entry points added by later sources register themselves here (name -> (restype, argtypes))
 EXTRA_PROTOTYPES: dict = {}
 

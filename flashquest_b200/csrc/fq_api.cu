@@ -32,6 +32,11 @@ bool pdl_enabled(int kind) {
     return (mask & kind) != 0;
 }
 
+DynPos& dyn_pos() {
+    static thread_local DynPos d;
+    return d;
+}
+
 __device__ int g_fq_status = 0;
 
 int* device_status_ptr() {

@@ -72,6 +72,7 @@ struct AttnParams {
     void* O; int64_t o_sb, o_sh;
     float* lse;
     int* tickets; float* partials; int n_split;
+    const int* pos; int pos_new;      // non-null: S_kv, P and tail_len are derived from *pos on the device (see DynPos)
     int* status;
 };
 
@@ -229,7 +230,9 @@ struct UnitCtx {
     uint32_t vs_raw, vm_raw;              // V scale / min of this lane's TPL tokens, bf16 bits (token i in half i)
 };
 
-template <typename QT, int D, int TOK>
+// DYN: the sequence length is read from *p.pos on the device (graph-capturable step); a separate
+// instantiation so that the ordinary launches keep their register budget.
+template <typename QT, int D, int TOK, bool DYN>
 __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_int4_kernel(AttnParams p) {
     using L = UnitLayout<D, TOK>;
     constexpr int DPL = D / 8;        // channels per lane
@@ -277,6 +280,12 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     __syncthreads();
     pdl_wait();        // the page list (and, in the fused step, the freshly packed page) come from the previous kernels
     pdl_trigger();
+    // tokens in completed pages; read on the device when the launch must not depend on the sequence length
+    int dyn_S = p.S_kv;
+    if constexpr (DYN) {
+        const int now = *p.pos + p.pos_new;
+        dyn_S = now - now % p.page;
+    }
 
     const uint8_t* Kp = p.K_packed + b * p.kp_sb + hkv * p.kp_sh;
     const uint8_t* Vp = p.V_packed + b * p.vp_sb + hkv * p.vp_sh;
@@ -292,9 +301,9 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         if (u < n_units) {
             const int g = u * p.n_split + split;
             const int pg = __ldg(list + (g >> cpp_log2));
-            if (pg >= 0 && pg < p.P) {
+            if (pg >= 0 && pg < p.P && pg * p.page < dyn_S) {
                 tok0 = pg * p.page + (g & ((1 << cpp_log2) - 1)) * TOK;
-                n_tok = min(TOK, p.S_kv - tok0);
+                n_tok = min(TOK, dyn_S - tok0);
                 if (n_tok > 0) page_id = pg; else n_tok = 0;
             }
         }
@@ -558,12 +567,13 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     float tm = -INFINITY, tl = 0.f, tacc[TD];
 #pragma unroll
     for (int j = 0; j < TD; ++j) tacc[j] = 0.f;
-    if (split == 0 && p.tail_len > 0 && !is_producer) {
+    const int dyn_tail = DYN ? (*p.pos + p.pos_new) % p.page : p.tail_len;
+    if (split == 0 && dyn_tail > 0 && !is_producer) {
         float qt[TD];
         const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + TD * lane;
 #pragma unroll
         for (int j = 0; j < TD; ++j) qt[j] = Dt<QT>::to_f32(qp[j]) * (p.sm_scale * LOG2E);
-        for (int t = warp; t < p.tail_len; t += ATT_WARPS) {
+        for (int t = warp; t < dyn_tail; t += ATT_WARPS) {
             const int64_t ro = b * p.tl_sb + hkv * p.tl_sh + (int64_t)t * p.tl_ss + TD * lane;
             float kv[TD], vv[TD];
 #pragma unroll
@@ -714,12 +724,12 @@ static constexpr size_t attn_smem_bytes() {
     return front + 2 * ATT_WARPS * ATT_STAGES * 8 + (size_t)ATT_WARPS * 4 * TOK * 4 + 2 * NSTATE * 4;
 }
 
-template <typename QT, int D, int TOK>
-static int launch_attn(const AttnParams& p, cudaStream_t st) {
+template <typename QT, int D, int TOK, bool DYN>
+static int launch_attn_impl(const AttnParams& p, cudaStream_t st) {
     constexpr size_t smem = attn_smem_bytes<D, TOK>();
     static_assert((size_t)ATT_STAGES * ATT_WARPS * 4 * UnitLayout<D, TOK>::STRIDE >=
                   (size_t)(ATT_WARPS * 5) * D * 4, "merge area must fit in the staging area");
-    auto kern = sparse_decode_int4_kernel<QT, D, TOK>;
+    auto kern = sparse_decode_int4_kernel<QT, D, TOK, DYN>;
     constexpr int MAX_DEV = 64;
     static bool prepared[MAX_DEV] = {};
     int dev = 0;
@@ -733,6 +743,11 @@ static int launch_attn(const AttnParams& p, cudaStream_t st) {
     cudaError_t e = launch_k(PDL_ATTN, kern, grid, dim3(ATT_THREADS), smem, st, p);
     if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "fq_sparse_decode_int4: launch failed: %s", cudaGetErrorString(e));
     return FQ_OK;
+}
+
+template <typename QT, int D, int TOK>
+static int launch_attn(const AttnParams& p, cudaStream_t st) {
+    return p.pos ? launch_attn_impl<QT, D, TOK, true>(p, st) : launch_attn_impl<QT, D, TOK, false>(p, st);
 }
 
 }  // namespace fq
@@ -830,6 +845,7 @@ extern "C" int fq_sparse_decode_int4(
     if (n_split > p.bucket) n_split = p.bucket > 0 ? p.bucket : 1;
     p.n_split = n_split;
     p.tickets = nullptr; p.partials = nullptr;
+    p.pos = dyn_pos().pos; p.pos_new = dyn_pos().n_new;
     p.status = device_status_ptr();
     if (p.status == nullptr) return FQ_ERR_CUDA;
     if (n_split > 1) {

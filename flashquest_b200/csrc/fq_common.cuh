@@ -54,6 +54,15 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
 
+// ---- token position read on the device ----
+// The graph-capturable decode step (fq_decode_step_int4_dev) cannot bake the sequence length into
+// its launches: it sets this thread-local record around its calls of the ordinary entry points,
+// which then hand `pos` to their kernels; a kernel that gets a non-null `pos` derives page
+// count, tail length and append offsets from *pos (tokens cached before this step) instead of
+// from its host-side arguments, which in that mode only size the grid (maximum values).
+struct DynPos { const int* pos = nullptr; int n_new = 0; int page = 1; int max_tokens = 0; };
+DynPos& dyn_pos();
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // Device-side status word of the current device: kernels that wait (mbarrier) record a

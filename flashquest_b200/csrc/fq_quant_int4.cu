@@ -23,6 +23,8 @@ struct QuantParams {
     int64_t vm_sb, vm_sh, vm_ss;
     void *stage_K, *stage_V;
     int64_t st_sb, st_sh, st_ss;
+    const int* pos;      // non-null: tokens already cached, read on the device (see DynPos); outputs then point at token 0
+    int max_tokens;      // capacity of the cache rows (device-side guard in that mode)
 };
 
 // Code of one element: rint((x - mn) / sc) clamped to 0..15, where the quotient is the IEEE
@@ -54,7 +56,8 @@ __device__ __forceinline__ const T* stream_row(const T* head, const T* nw, const
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
+__global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams pin) {
+    QuantParams p = pin;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = blockIdx.z, h = blockIdx.y;
     const int page_idx = blockIdx.x * 4 + warp;
@@ -67,6 +70,20 @@ __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams p) {
     const T* Vn = static_cast<const T*>(p.V_new);
     pdl_wait();        // inputs and the staging rows may come from the previous kernel
     pdl_trigger();
+    if (p.pos) {
+        // append of n_new tokens behind *pos cached ones: the staged head is the partial page
+        const int seen = *p.pos;
+        if (seen < 0 || seen + p.n_new > p.max_tokens) return;      // full: nothing is written (the host checks its own count)
+        const int partial = seen % p.page;
+        const int tok_start = seen - partial, pg_start = tok_start / p.page;
+        p.n_head = partial;
+        p.n_quant = ((partial + p.n_new) / p.page) * p.page;
+        p.n_pages = p.n_quant / p.page;
+        if (p.K_packed) p.K_packed += (int64_t)tok_start * p.pk_ss;
+        if (p.V_packed) p.V_packed += (int64_t)tok_start * p.pk_ss;
+        if (p.K_scale) { p.K_scale += (int64_t)pg_start * p.km_sp; p.K_mn += (int64_t)pg_start * p.km_sp; }
+        if (p.V_scale) { p.V_scale += (int64_t)tok_start * p.vm_ss; p.V_mn += (int64_t)tok_start * p.vm_ss; }
+    }
 
     if (page_idx < p.n_pages) {
         const int t0 = page_idx * p.page;
@@ -292,7 +309,8 @@ extern "C" int fq_quantize_kv_int4(
     p.V_scale = static_cast<uint16_t*>(V_scale); p.V_mn = static_cast<uint16_t*>(V_mn);
     p.vm_sb = vm_sb; p.vm_sh = vm_sh; p.vm_ss = vm_ss;
     p.stage_K = stage_K; p.stage_V = stage_V; p.st_sb = st_sb; p.st_sh = st_sh; p.st_ss = st_ss;
-    if (n_quant == 0 && (n_head + n_new == 0 || (!stage_K && !stage_V))) return FQ_OK;
+    p.pos = dyn_pos().pos; p.max_tokens = dyn_pos().pos ? dyn_pos().max_tokens : 0x7fffffff;
+    if (p.pos == nullptr && n_quant == 0 && (n_head + n_new == 0 || (!stage_K && !stage_V))) return FQ_OK;
 
     dim3 grid((unsigned)max(1, (p.n_pages + 3) / 4), (unsigned)H, (unsigned)B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

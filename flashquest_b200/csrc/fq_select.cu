@@ -63,7 +63,7 @@ __global__ void select_pages_kernel(
     const float* __restrict__ retention_per_head, float retention, int k_max, int sinks, int window,
     uint8_t* __restrict__ mask, int64_t mk_sb, int64_t mk_sh,
     int32_t* __restrict__ compact, int64_t cp_sb, int64_t cp_sh, int bucket,
-    int32_t* __restrict__ count) {
+    int32_t* __restrict__ count, const int* __restrict__ pos, int pos_new, int pos_page) {
     __shared__ SelShared sh;
     extern __shared__ unsigned s_keys[];                        // [P] keys (SMEM_KEYS only)
     const int b = blockIdx.y, h = blockIdx.x;
@@ -73,6 +73,10 @@ __global__ void select_pages_kernel(
     auto key_at = [&](int i) -> unsigned { return SMEM_KEYS ? s_keys[i] : score_key(row[i]); };
     pdl_wait();        // the scores come from the previous kernel
     pdl_trigger();
+    if (pos) {         // row length read on the device: completed pages after this step's append
+        P = min(P, (*pos + pos_new) / pos_page);
+        k_max = min(k_max, P);
+    }
 
     // ---- load the row once; block min / max of the keys ----
     unsigned kmin = 0xffffffffu, kmax = 0u;
@@ -318,11 +322,11 @@ extern "C" int fq_select_pages(
         }
         launch_k(PDL_SELECT, select_pages_kernel<true>, grid, dim3(select_threads(P)), smem, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
-            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count);
+            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dyn_pos().pos, dyn_pos().n_new, dyn_pos().page);
     } else {
         launch_k(PDL_SELECT, select_pages_kernel<false>, grid, dim3(select_threads(P)), 0, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
-            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count);
+            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dyn_pos().pos, dyn_pos().n_new, dyn_pos().page);
     }
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;

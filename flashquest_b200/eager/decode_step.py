@@ -134,6 +134,56 @@ class QuestDecodeInt4:
         self.launches += 4 * Ln
         return self.O.unsqueeze(3), self.lse.unsqueeze(3)
 
+    def capture_step_graph(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor, before=None, after=None):
+        """CUDA graph of step_all() for the STATIC input buffers k_new, v_new (L,B,H_kv,n,D) and q
+        (L,B,H_q,1,D): refill the buffers, call the returned `replay()`, read self.O / self.lse.
+        The launches read the sequence length from a device array (fq_decode_step_int4_dev), so one
+        capture serves every later token.  `before` / `after` (callables) are captured in the same graph
+        around the step, e.g. the copies from and to pinned host buffers.  replay() keeps the cache's
+        host-side counters in step;
+        do not mix it with step()/step_all()/update_quantized() without capturing again."""
+        c = self.cache
+        Ln = c.num_layers
+        n_new = k_new.shape[3]
+        if not (1 <= n_new < self.page):
+            raise ValueError(f"n_new={n_new} must be in [1, page_size)")
+        if k_new.dtype != c.dtype or v_new.dtype != c.dtype or k_new.stride(4) != 1 or v_new.stride() != k_new.stride():
+            raise ValueError("k_new / v_new must be dense tensors of the cache's dtype with equal strides")
+        q4 = q.view(Ln, self.B, self.Hq, self.D)
+        pos = torch.tensor(c._seen_tokens[:Ln], dtype=torch.int32, device=self.device)
+        self.attend(q[0], 0)                                       # one ordinary launch: lazy kernel attributes are set outside the capture
+        torch.cuda.synchronize(self.device)
+
+        def launch():
+            check(lib().fq_decode_step_int4_dev(
+                ctypes.byref(self._cdesc), Ln, ptr(pos),
+                ptr(k_new), ptr(v_new), k_new.stride(0), k_new.stride(1), k_new.stride(2), k_new.stride(3), n_new,
+                ptr(q4), dtype_code(q4), q4.stride(0), q4.stride(1), q4.stride(2), ctypes.byref(self._prm), 0,
+                ptr(self.scores), self.scores.stride(0), ptr(self.compact), self.compact.stride(0),
+                ptr(self.O), self.O.stride(0), ptr(self.lse), self.lse.stride(0),
+                ptr(self.workspace), self.workspace.stride(0), self.workspace.shape[1], stream_ptr(self.device)))
+
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            if before is not None:
+                before()
+            launch()
+            if after is not None:
+                after()
+
+        def replay():
+            for li in range(Ln):
+                if c._seen_tokens[li] + n_new > c.max_seq_len:
+                    raise RuntimeError(f"PersistentInt4KVCache: seen+new={c._seen_tokens[li] + n_new} exceeds max_seq_len={c.max_seq_len}")
+            graph.replay()
+            for li in range(Ln):
+                c._seen_tokens[li] += n_new
+            self.launches += 4 * Ln + 1
+            return self.O.unsqueeze(3), self.lse.unsqueeze(3)
+
+        replay.graph, replay.pos = graph, pos
+        return replay
+
     def attend(self, q: torch.Tensor, layer_idx: int):
         """q (B,H_q,1,D) or (B,H_q,D), the cache's dtype family (fp16/bf16).  Returns views
         (O (B,H_q,1,D), lse (B,H_q,1)) of preallocated per-layer buffers."""

@@ -349,6 +349,20 @@ int fq_decode_step_int4(
     float* scores, int64_t sc_sl, int32_t* compact, int64_t cp_sl, void* O, int64_t o_sl, float* lse, int64_t lse_sl,
     void* workspace, size_t ws_sl, size_t workspace_bytes, void* stream);
 
+/* fq_decode_step_int4 whose launches do not depend on the sequence length, so that the step can be
+ * captured once in a CUDA graph and replayed for every new token: pos (DEVICE array, one int per
+ * layer) holds the tokens already cached; every kernel reads it on the device, and the last
+ * launch adds n_new to each entry.  1 <= n_new < page.  scores must be (B,Hq,P_max) per layer with
+ * P_max = max_seq_len / page.  The caller keeps its own count and must not run past max_seq_len
+ * (on the device a full layer silently appends nothing). */
+int fq_decode_step_int4_dev(
+    const fq_int4_cache* cache, int n_layers, int* pos,
+    const void* K_new, const void* V_new, int64_t nw_sl, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    const void* Q, int q_dtype, int64_t q_sl, int64_t q_sb, int64_t q_sh,
+    const fq_decode_params* params, size_t params_stride,
+    float* scores, int64_t sc_sl, int32_t* compact, int64_t cp_sl, void* O, int64_t o_sl, float* lse, int64_t lse_sl,
+    void* workspace, size_t ws_sl, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * The operators around the sparse-decode path in a Llama-shaped decode step.  The reference
  * inherits them from the Hugging Face modules its patched forward wraps
