@@ -84,6 +84,7 @@ class LlamaScratchDesc(ctypes.Structure):
 
 _PROTOTYPES["fq_llama_decode_step"] = (I, [ctypes.POINTER(LlamaModelDesc), ctypes.POINTER(Int4CacheDesc),
                                           ctypes.POINTER(DecodeParams), P, P, I, ctypes.POINTER(LlamaScratchDesc), P])
+_PROTOTYPES["fq_llama_decode_step_dev"] = _PROTOTYPES["fq_llama_decode_step"]
 _PROTOTYPES["fq_awq_gemv_workspace_bytes"] = (Z, [I, I, I])
 _PROTOTYPES["fq_awq_gemv_default_splits"] = (I, [I, I, I])
 _PROTOTYPES["fq_awq_gemv"] = (I, [P, I, I, I, I, P, P, P, P, P, P, I, P, Z, I, P])

@@ -63,6 +63,14 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 struct DynPos { const int* pos = nullptr; int n_new = 0; int page = 1; int max_tokens = 0; };
 DynPos& dyn_pos();
 
+// One layer of the graph-capturable step (append + score + select + attend with the sequence
+// length read from *pos) and the closing increment of the positions; defined in fq_decode_layer.cu.
+int decode_layer_int4_dyn(const fq_int4_cache* c, int layer, const int* pos, const void* K_new, const void* V_new,
+                          int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new, const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+                          const fq_decode_params* prm, float* scores, int32_t* compact, void* O, float* lse,
+                          void* workspace, size_t workspace_bytes, void* stream);
+int advance_positions(int* pos, int n, int n_new, int max_tokens, void* stream);
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // Device-side status word of the current device: kernels that wait (mbarrier) record a

@@ -106,6 +106,55 @@ __global__ void advance_pos_kernel(int* pos, int n, int n_new, int max_tokens) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n && pos[i] + n_new <= max_tokens) pos[i] += n_new;
 }
+
+int advance_positions(int* pos, int n, int n_new, int max_tokens, void* stream) {
+    launch_k(PDL_QUANT, advance_pos_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, static_cast<cudaStream_t>(stream),
+             pos, n, n_new, max_tokens);
+    FQ_CHECK_LAUNCH("advance_positions");
+    return FQ_OK;
+}
+
+int decode_layer_int4_dyn(const fq_int4_cache* c, int l, const int* pos, const void* Kn, const void* Vn,
+                          int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new, const void* Ql, int q_dtype, int64_t q_sb, int64_t q_sh,
+                          const fq_decode_params* pl, float* sc, int32_t* cp, void* O, float* lse,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+    const int page = c->page, D = c->D, B = c->B, Hkv = c->Hkv, Hq = pl->Hq;
+    const int P_max = c->max_seq_len / page;
+    const size_t kv_esz = 2;
+    struct Guard {            // the ordinary entry points read the record while it is set
+        ~Guard() { dyn_pos() = DynPos{}; }
+    } guard;
+    dyn_pos() = DynPos{pos, n_new, page, c->max_seq_len};
+    uint8_t* Kp = c->K_packed + l * c->pk_sl;
+    uint8_t* Vp = c->V_packed + l * c->pk_sl;
+    uint16_t* Ks = static_cast<uint16_t*>(c->K_scale) + l * c->km_sl;
+    uint16_t* Km = static_cast<uint16_t*>(c->K_mn) + l * c->km_sl;
+    uint16_t* Vs = static_cast<uint16_t*>(c->V_scale) + l * c->vm_sl;
+    uint16_t* Vm = static_cast<uint16_t*>(c->V_mn) + l * c->vm_sl;
+    char* Kt = static_cast<char*>(c->K_partial) + l * c->pt_sl * kv_esz;
+    char* Vt = static_cast<char*>(c->V_partial) + l * c->pt_sl * kv_esz;
+    // host-side sizes are the maxima (they size grids and pass validation); the kernels read *pos
+    int rc = fq_quantize_kv_int4(Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, page - n_new, Kn, Vn, nw_sb, nw_sh, nw_ss, n_new,
+                                 c->kv_dtype, B, Hkv, D, page, page,
+                                 Kp, Vp, c->pk_sb, c->pk_sh, c->pk_ss, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
+                                 Vs, Vm, c->vm_sb, c->vm_sh, 1, Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, stream);
+    if (rc != FQ_OK) return rc;
+    rc = fq_page_scores_int4(Ql, q_dtype, q_sb, q_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp, B, Hq, Hkv, P_max, D,
+                             sc, (int64_t)Hq * P_max, P_max, stream);
+    if (rc != FQ_OK) return rc;
+    rc = fq_select_pages(sc, (int64_t)Hq * P_max, P_max, B, Hq, P_max, pl->retention_per_head, pl->retention,
+                         pl->k_max_static < P_max ? pl->k_max_static : P_max, pl->sinks, pl->window, nullptr, 0, 0,
+                         cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket, nullptr, stream);
+    if (rc != FQ_OK) return rc;
+    const int n_split = pl->n_split > 0 ? pl->n_split : fq_sparse_decode_default_splits(B, Hq, pl->bucket, page);
+    return fq_sparse_decode_int4(
+        Ql, q_dtype, q_sb, q_sh, Kp, c->pk_sb, c->pk_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
+        Vp, c->pk_sb, c->pk_sh, Vs, Vm, c->vm_sb, c->vm_sh,
+        cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket,
+        Kt, Vt, c->kv_dtype, c->pt_sb, c->pt_sh, c->pt_ss, page - 1,
+        B, Hq, Hkv, P_max * page, P_max, D, page, pl->sm_scale,
+        O, (int64_t)Hq * D, D, lse, workspace, workspace_bytes, n_split, stream);
+}
 }  // namespace fq
 
 extern "C" int fq_decode_step_int4_dev(
@@ -123,58 +172,18 @@ extern "C" int fq_decode_step_int4_dev(
     FQ_CHECK_ARG(n_layers <= 1 || ws_sl >= workspace_bytes, FQ_ERR_WORKSPACE,
                  "%s: the per-layer workspaces overlap (stride %zu B < %zu B)", fn, ws_sl, workspace_bytes);
     FQ_CHECK_ARG(c->kv_dtype == FQ_F16 || c->kv_dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: cache dtype code %d", fn, c->kv_dtype);
-    const int page = c->page, D = c->D, B = c->B, Hkv = c->Hkv;
-    const int P_max = c->max_seq_len / page;
-    FQ_CHECK_ARG(P_max >= 1, FQ_ERR_ARG, "%s: the cache holds less than one page", fn);
+    FQ_CHECK_ARG(c->max_seq_len / c->page >= 1, FQ_ERR_ARG, "%s: the cache holds less than one page", fn);
     const size_t kv_esz = 2, q_esz = q_dtype == FQ_F32 ? 4 : 2;
-    struct Guard {            // the ordinary entry points read the record while it is set
-        ~Guard() { dyn_pos() = DynPos{}; }
-    } guard;
-    int rc = FQ_OK;
-    for (int l = 0; l < n_layers && rc == FQ_OK; ++l) {
+    for (int l = 0; l < n_layers; ++l) {
         const fq_decode_params* pl = reinterpret_cast<const fq_decode_params*>(reinterpret_cast<const char*>(prm) + (size_t)l * prm_stride);
-        const int Hq = pl->Hq;
-        dyn_pos() = DynPos{pos + l, n_new, page, c->max_seq_len};
-        uint8_t* Kp = c->K_packed + l * c->pk_sl;
-        uint8_t* Vp = c->V_packed + l * c->pk_sl;
-        uint16_t* Ks = static_cast<uint16_t*>(c->K_scale) + l * c->km_sl;
-        uint16_t* Km = static_cast<uint16_t*>(c->K_mn) + l * c->km_sl;
-        uint16_t* Vs = static_cast<uint16_t*>(c->V_scale) + l * c->vm_sl;
-        uint16_t* Vm = static_cast<uint16_t*>(c->V_mn) + l * c->vm_sl;
-        char* Kt = static_cast<char*>(c->K_partial) + l * c->pt_sl * kv_esz;
-        char* Vt = static_cast<char*>(c->V_partial) + l * c->pt_sl * kv_esz;
-        const char* Kn = static_cast<const char*>(K_new) + (size_t)l * nw_sl * kv_esz;
-        const char* Vn = static_cast<const char*>(V_new) + (size_t)l * nw_sl * kv_esz;
-        const char* Ql = static_cast<const char*>(Q) + (size_t)l * q_sl * q_esz;
-        float* sc = scores + l * sc_sl;
-        int32_t* cp = compact + l * cp_sl;
-        // host-side sizes are the maxima (they size grids and pass validation); the kernels read *pos
-        rc = fq_quantize_kv_int4(Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, page - n_new, Kn, Vn, nw_sb, nw_sh, nw_ss, n_new,
-                                 c->kv_dtype, B, Hkv, D, page, page,
-                                 Kp, Vp, c->pk_sb, c->pk_sh, c->pk_ss, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
-                                 Vs, Vm, c->vm_sb, c->vm_sh, 1, Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, stream);
-        if (rc != FQ_OK) break;
-        rc = fq_page_scores_int4(Ql, q_dtype, q_sb, q_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp, B, Hq, Hkv, P_max, D,
-                                 sc, (int64_t)Hq * P_max, P_max, stream);
-        if (rc != FQ_OK) break;
-        rc = fq_select_pages(sc, (int64_t)Hq * P_max, P_max, B, Hq, P_max, pl->retention_per_head, pl->retention,
-                             pl->k_max_static < P_max ? pl->k_max_static : P_max, pl->sinks, pl->window, nullptr, 0, 0,
-                             cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket, nullptr, stream);
-        if (rc != FQ_OK) break;
-        const int n_split = pl->n_split > 0 ? pl->n_split : fq_sparse_decode_default_splits(B, Hq, pl->bucket, page);
-        rc = fq_sparse_decode_int4(
-            Ql, q_dtype, q_sb, q_sh, Kp, c->pk_sb, c->pk_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
-            Vp, c->pk_sb, c->pk_sh, Vs, Vm, c->vm_sb, c->vm_sh,
-            cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket,
-            Kt, Vt, c->kv_dtype, c->pt_sb, c->pt_sh, c->pt_ss, page - 1,
-            B, Hq, Hkv, P_max * page, P_max, D, page, pl->sm_scale,
-            static_cast<char*>(O) + (size_t)l * o_sl * q_esz, (int64_t)Hq * D, D, lse ? lse + l * lse_sl : nullptr,
-            workspace ? static_cast<char*>(workspace) + (size_t)l * ws_sl : nullptr, workspace_bytes, n_split, stream);
+        const int rc = decode_layer_int4_dyn(
+            c, l, pos + l, static_cast<const char*>(K_new) + (size_t)l * nw_sl * kv_esz,
+            static_cast<const char*>(V_new) + (size_t)l * nw_sl * kv_esz, nw_sb, nw_sh, nw_ss, n_new,
+            static_cast<const char*>(Q) + (size_t)l * q_sl * q_esz, q_dtype, q_sb, q_sh, pl,
+            scores + l * sc_sl, compact + l * cp_sl, static_cast<char*>(O) + (size_t)l * o_sl * q_esz,
+            lse ? lse + l * lse_sl : nullptr,
+            workspace ? static_cast<char*>(workspace) + (size_t)l * ws_sl : nullptr, workspace_bytes, stream);
+        if (rc != FQ_OK) return rc;
     }
-    dyn_pos() = DynPos{};
-    if (rc != FQ_OK) return rc;
-    launch_k(PDL_QUANT, advance_pos_kernel, dim3((unsigned)((n_layers + 127) / 128)), dim3(128), 0, static_cast<cudaStream_t>(stream),
-             pos, n_layers, n_new, c->max_seq_len);
-    FQ_CHECK_LAUNCH(fn);
-    return FQ_OK;
+    return advance_positions(pos, n_layers, n_new, c->max_seq_len, stream);
 }

@@ -56,10 +56,11 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(
 // with cos/sin computed in fp32 from pos * theta^(-2i/D) and rounded to fp16, products and sum in fp16.
 __global__ void __launch_bounds__(128) rope_kernel(__half* __restrict__ q, int64_t q_sb, int64_t q_sh, int Hq,
                                                    __half* __restrict__ k, int64_t k_sb, int64_t k_sh, int Hkv,
-                                                   int D, int pos, float theta) {
+                                                   int D, int pos, float theta, const int* __restrict__ pos_dev) {
     const int head = blockIdx.x, b = blockIdx.y;
     pdl_wait();
     pdl_trigger();
+    if (pos_dev) pos = *pos_dev;      // position read on the device (graph-capturable step)
     __half* x = head < Hq ? q + b * q_sb + head * q_sh : k + b * k_sb + (head - Hq) * k_sh;
     const int half = D / 2;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -196,7 +197,7 @@ extern "C" int fq_rope(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int
     FQ_CHECK_ARG(B <= 65535, FQ_ERR_ARG, "%s: batch %d too large", fn, B);
     launch_k(PDL_GEMV, rope_kernel, dim3((unsigned)(Hq + Hkv), (unsigned)B), dim3(D / 2 < 128 ? (D / 2 + 31) / 32 * 32 : 128), 0,
              static_cast<cudaStream_t>(stream), static_cast<__half*>(q), q_sb, q_sh, Hq, static_cast<__half*>(k), k_sb, k_sh, Hkv,
-             D, pos, theta);
+             D, pos, theta, dyn_pos().pos);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
@@ -255,11 +256,12 @@ extern "C" int fq_argmax_f16(const void* x, int64_t rows, int N, int32_t* out, v
     return FQ_OK;
 }
 
-extern "C" int fq_llama_decode_step(const fq_llama_model* m, const fq_int4_cache* cache, const fq_decode_params* prm,
-                                    const int* seen, const void* x, int B, const fq_llama_scratch* s, void* stream) {
+// seen: host positions (stream step) or nullptr with pos_dev: device positions (graph-capturable step)
+static int llama_step_impl(const fq_llama_model* m, const fq_int4_cache* cache, const fq_decode_params* prm,
+                           const int* seen, int* pos_dev, const void* x, int B, const fq_llama_scratch* s, void* stream) {
     using namespace fq;
-    const char* fn = "fq_llama_decode_step";
-    FQ_CHECK_ARG(m && cache && prm && seen && x && s && m->layers, FQ_ERR_ARG, "%s: null argument", fn);
+    const char* fn = pos_dev ? "fq_llama_decode_step_dev" : "fq_llama_decode_step";
+    FQ_CHECK_ARG(m && cache && prm && (seen || pos_dev) && x && s && m->layers, FQ_ERR_ARG, "%s: null argument", fn);
     FQ_CHECK_ARG(B >= 1 && B <= 8 && B == cache->B, FQ_ERR_ARG, "%s: batch %d (cache %d); 1..8 sequences are built", fn, B, cache->B);
     FQ_CHECK_ARG(m->n_layers >= 1 && m->n_layers <= cache->L && m->kv_heads == cache->Hkv && m->head_dim == cache->D &&
                  m->q_heads == prm->Hq, FQ_ERR_ARG, "%s: model and cache shapes differ", fn);
@@ -300,11 +302,21 @@ extern "C" int fq_llama_decode_step(const fq_llama_model* m, const fq_int4_cache
                              s->gemv_ws[0], s->gemv_ws_bytes[0], ks_qkv, stream);
             if (rc != FQ_OK) return rc;
         }
-        if ((rc = fq_rope(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, seen[l], m->rope_theta, stream)) != FQ_OK) return rc;
         void* Ol = static_cast<char*>(s->O) + (size_t)l * s->o_sl * 2;
-        rc = fq_decode_layer_int4(cache, l, seen[l], s->k, s->v, nkv, D, D, 1, s->q, FQ_F16, nq, D, prm,
-                                  s->scores + l * s->sc_sl, s->compact + l * s->cp_sl, Ol, nullptr,
-                                  static_cast<char*>(s->attn_ws) + (size_t)l * s->attn_ws_sl, s->attn_ws_bytes, stream);
+        if (pos_dev) {
+            dyn_pos() = DynPos{pos_dev + l, 1, cache->page, cache->max_seq_len};
+            rc = fq_rope(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, 0, m->rope_theta, stream);
+            dyn_pos() = DynPos{};
+            if (rc != FQ_OK) return rc;
+            rc = decode_layer_int4_dyn(cache, l, pos_dev + l, s->k, s->v, nkv, D, D, 1, s->q, FQ_F16, nq, D, prm,
+                                       s->scores + l * s->sc_sl, s->compact + l * s->cp_sl, Ol, nullptr,
+                                       static_cast<char*>(s->attn_ws) + (size_t)l * s->attn_ws_sl, s->attn_ws_bytes, stream);
+        } else {
+            if ((rc = fq_rope(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, seen[l], m->rope_theta, stream)) != FQ_OK) return rc;
+            rc = fq_decode_layer_int4(cache, l, seen[l], s->k, s->v, nkv, D, D, 1, s->q, FQ_F16, nq, D, prm,
+                                      s->scores + l * s->sc_sl, s->compact + l * s->cp_sl, Ol, nullptr,
+                                      static_cast<char*>(s->attn_ws) + (size_t)l * s->attn_ws_sl, s->attn_ws_bytes, stream);
+        }
         if (rc != FQ_OK) return rc;
         {
             const int32_t* qw[1] = {L.o.qweight}; const void* sc[1] = {L.o.scales}; const int32_t* qz[1] = {L.o.qzeros};
@@ -335,5 +347,16 @@ extern "C" int fq_llama_decode_step(const fq_llama_model* m, const fq_int4_cache
     }
     if ((rc = add_norm(m->final_norm)) != FQ_OK) return rc;
     if ((rc = fq_gemv_f16(s->normed, m->lm_head, B, H, m->vocab, s->logits, stream)) != FQ_OK) return rc;
-    return fq_argmax_f16(s->logits, B, m->vocab, s->next_ids, stream);
+    if ((rc = fq_argmax_f16(s->logits, B, m->vocab, s->next_ids, stream)) != FQ_OK) return rc;
+    return pos_dev ? advance_positions(pos_dev, m->n_layers, 1, cache->max_seq_len, stream) : FQ_OK;
+}
+
+extern "C" int fq_llama_decode_step(const fq_llama_model* m, const fq_int4_cache* cache, const fq_decode_params* prm,
+                                    const int* seen, const void* x, int B, const fq_llama_scratch* s, void* stream) {
+    return llama_step_impl(m, cache, prm, seen, nullptr, x, B, s, stream);
+}
+
+extern "C" int fq_llama_decode_step_dev(const fq_llama_model* m, const fq_int4_cache* cache, const fq_decode_params* prm,
+                                        int* pos, const void* x, int B, const fq_llama_scratch* s, void* stream) {
+    return llama_step_impl(m, cache, prm, nullptr, pos, x, B, s, stream);
 }

@@ -179,6 +179,42 @@ class LlamaInt4Decoder:
                             self.B, c.head_dim, int(pos), c.rope_theta, stream_ptr(self.dev)))
         self.launches += 1
 
+    def capture_decode_graph(self, token_ids: torch.Tensor):
+        """CUDA graph of one greedy step that feeds itself: embedding gather of the ids buffer, the
+        whole step with the positions read on the device (fq_llama_decode_step_dev), and the copy
+        of the chosen ids back into the buffer.  Returns `replay`; each call decodes one more token
+        per sequence with no host work besides the launch (`replay.ids` holds the latest ids,
+        self.logits the latest logits).  Do not mix with decode_step() without capturing again."""
+        c, n_l = self.cache, self.cfg.layers
+        ids = token_ids.to(device=self.dev, dtype=torch.int32).clone()
+        pos = torch.tensor(c._seen_tokens[:n_l], dtype=torch.int32, device=self.dev)
+        # stateless warm-up launches: lazily set kernel attributes stay outside the capture
+        cfg = self.cfg
+        self.attn.attend(torch.zeros(self.B, cfg.q_heads, 1, cfg.head_dim, dtype=torch.float16, device=self.dev), 0)
+        lw = self.w.layers[0]
+        awq_gemv_fused(self.normed.view(self.B, 1, -1), (lw.q_proj, lw.k_proj, lw.v_proj))
+        awq_gemv_fused(self.act.view(self.B, 1, -1), (lw.down_proj,))
+        torch.cuda.synchronize(self.dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            x = self.w.embed[ids.long()]
+            check(lib().fq_llama_decode_step_dev(ctypes.byref(self._model), ctypes.byref(self.attn._cdesc),
+                                                 ctypes.byref(self.attn._prm), ptr(pos), ptr(x), self.B,
+                                                 ctypes.byref(self._scratch), stream_ptr(self.dev)))
+            ids.copy_(self.next_ids)
+
+        def replay():
+            if c._seen_tokens[0] + 1 > c.max_seq_len:
+                raise RuntimeError(f"PersistentInt4KVCache: seen+new={c._seen_tokens[0] + 1} exceeds max_seq_len={c.max_seq_len}")
+            graph.replay()
+            for li in range(n_l):
+                c._seen_tokens[li] += 1
+            self.launches += 12 * n_l + 4
+            return ids
+
+        replay.graph, replay.ids, replay.pos = graph, ids, pos
+        return replay
+
     def decode_step_per_op(self, token_ids: torch.Tensor) -> torch.Tensor:
         """The same step issued operator by operator from Python (one foreign call per kernel group)."""
         c, w, B = self.cfg, self.w, self.B

@@ -426,6 +426,11 @@ typedef struct fq_llama_scratch {
  * (all sequences of the batch are at the same position).  Writes scratch->logits and next_ids. */
 int fq_llama_decode_step(const fq_llama_model* model, const fq_int4_cache* cache, const fq_decode_params* params,
                          const int* seen, const void* x, int B, const fq_llama_scratch* scratch, void* stream);
+/* The same step with the positions in a DEVICE array (one int per layer, advanced by the last
+ * launch): no launch depends on the sequence length, so the step can be captured in a CUDA graph
+ * once and replayed per token (see fq_decode_step_int4_dev). */
+int fq_llama_decode_step_dev(const fq_llama_model* model, const fq_int4_cache* cache, const fq_decode_params* params,
+                             int* pos, const void* x, int B, const fq_llama_scratch* scratch, void* stream);
 
 #ifdef __cplusplus
 }

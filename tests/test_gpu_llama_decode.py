@@ -143,3 +143,27 @@ def test_decode_steps_match_cpu_restatement():
                 assert nxt[b].item() == int(want[b].argmax())
         ids = want.argmax(-1).to(torch.int32)             # both sides continue from the reference's choice
     assert dec.cache.get_seq_length(0) == 36
+
+
+def test_graph_replayed_decode_equals_stream_decode():
+    """One captured graph replayed per token (positions on the device, ids fed back on the device)
+    produces the same logits and tokens as decode_step(), bit for bit, across a page boundary."""
+    from flashquest_b200.eager.llama_decode import LlamaConfig, LlamaInt4Decoder, random_llama_weights
+    cfg = LlamaConfig(hidden=256, layers=2, q_heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=512)
+    w = random_llama_weights(cfg, "cuda", seed=2)
+    mk = lambda: LlamaInt4Decoder(cfg, w, batch_size=2, max_seq_len=64, page_size=16, retention=0.5, num_sinks=1, window_pages=1)
+    a, b = mk(), mk()
+    ids0 = torch.tensor([7, 123], dtype=torch.int32, device="cuda")
+    for d in (a, b):                                   # a few ordinary steps first: the capture starts mid-page
+        ids = ids0
+        for _ in range(5):
+            ids = d.decode_step(ids).clone()
+    replay = a.capture_decode_graph(ids)
+    ids_b = ids
+    for t in range(20):
+        ids_a = replay().clone()
+        la = a.logits.clone()
+        ids_b = b.decode_step(ids_b).clone()
+        assert torch.equal(la, b.logits), t
+        assert torch.equal(ids_a, ids_b), t
+    assert a.cache.get_seq_length(0) == b.cache.get_seq_length(0) == 25
