@@ -68,8 +68,10 @@ DynPos& dyn_pos();
 int decode_layer_int4_dyn(const fq_int4_cache* c, int layer, const int* pos, const void* K_new, const void* V_new,
                           int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new, const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
                           const fq_decode_params* prm, float* scores, int32_t* compact, void* O, float* lse,
-                          void* workspace, size_t workspace_bytes, void* stream);
+                          void* workspace, size_t workspace_bytes, void* stream, bool append = true);
 int advance_positions(int* pos, int n, int n_new, int max_tokens, void* stream);
+int quant_append_layers_dyn(const fq_int4_cache* c, int n_layers, const int* pos, const void* K_new, const void* V_new,
+                            int64_t nw_sl, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new, void* stream);
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

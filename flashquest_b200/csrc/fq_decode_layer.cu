@@ -117,7 +117,7 @@ int advance_positions(int* pos, int n, int n_new, int max_tokens, void* stream) 
 int decode_layer_int4_dyn(const fq_int4_cache* c, int l, const int* pos, const void* Kn, const void* Vn,
                           int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new, const void* Ql, int q_dtype, int64_t q_sb, int64_t q_sh,
                           const fq_decode_params* pl, float* sc, int32_t* cp, void* O, float* lse,
-                          void* workspace, size_t workspace_bytes, void* stream) {
+                          void* workspace, size_t workspace_bytes, void* stream, bool append) {
     const int page = c->page, D = c->D, B = c->B, Hkv = c->Hkv, Hq = pl->Hq;
     const int P_max = c->max_seq_len / page;
     const size_t kv_esz = 2;
@@ -134,7 +134,9 @@ int decode_layer_int4_dyn(const fq_int4_cache* c, int l, const int* pos, const v
     char* Kt = static_cast<char*>(c->K_partial) + l * c->pt_sl * kv_esz;
     char* Vt = static_cast<char*>(c->V_partial) + l * c->pt_sl * kv_esz;
     // host-side sizes are the maxima (they size grids and pass validation); the kernels read *pos
-    int rc = fq_quantize_kv_int4(Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, page - n_new, Kn, Vn, nw_sb, nw_sh, nw_ss, n_new,
+    int rc = FQ_OK;
+    if (append)
+        rc = fq_quantize_kv_int4(Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, page - n_new, Kn, Vn, nw_sb, nw_sh, nw_ss, n_new,
                                  c->kv_dtype, B, Hkv, D, page, page,
                                  Kp, Vp, c->pk_sb, c->pk_sh, c->pk_ss, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
                                  Vs, Vm, c->vm_sb, c->vm_sh, 1, Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, stream);
@@ -174,6 +176,11 @@ extern "C" int fq_decode_step_int4_dev(
     FQ_CHECK_ARG(c->kv_dtype == FQ_F16 || c->kv_dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: cache dtype code %d", fn, c->kv_dtype);
     FQ_CHECK_ARG(c->max_seq_len / c->page >= 1, FQ_ERR_ARG, "%s: the cache holds less than one page", fn);
     const size_t kv_esz = 2, q_esz = q_dtype == FQ_F32 ? 4 : 2;
+    // every layer's new tokens are known up front: one launch appends to all layers
+    {
+        const int rc = quant_append_layers_dyn(c, n_layers, pos, K_new, V_new, nw_sl, nw_sb, nw_sh, nw_ss, n_new, stream);
+        if (rc != FQ_OK) return rc;
+    }
     for (int l = 0; l < n_layers; ++l) {
         const fq_decode_params* pl = reinterpret_cast<const fq_decode_params*>(reinterpret_cast<const char*>(prm) + (size_t)l * prm_stride);
         const int rc = decode_layer_int4_dyn(
@@ -182,7 +189,7 @@ extern "C" int fq_decode_step_int4_dev(
             static_cast<const char*>(Q) + (size_t)l * q_sl * q_esz, q_dtype, q_sb, q_sh, pl,
             scores + l * sc_sl, compact + l * cp_sl, static_cast<char*>(O) + (size_t)l * o_sl * q_esz,
             lse ? lse + l * lse_sl : nullptr,
-            workspace ? static_cast<char*>(workspace) + (size_t)l * ws_sl : nullptr, workspace_bytes, stream);
+            workspace ? static_cast<char*>(workspace) + (size_t)l * ws_sl : nullptr, workspace_bytes, stream, false);
         if (rc != FQ_OK) return rc;
     }
     return advance_positions(pos, n_layers, n_new, c->max_seq_len, stream);

@@ -24,6 +24,8 @@ struct QuantParams {
     void *stage_K, *stage_V;
     int64_t st_sb, st_sh, st_ss;
     const int* pos;      // non-null: tokens already cached, read on the device (see DynPos); outputs then point at token 0
+    int n_layers;        // > 1 (only with pos): grid.z = n_layers * B, pos[layer], every tensor offset by its layer stride
+    int64_t hd_sl, nw_sl, pk_sl, km_sl, vm_sl, st_sl;
     int max_tokens;      // capacity of the cache rows (device-side guard in that mode)
 };
 
@@ -59,7 +61,19 @@ template <typename T>
 __global__ void __launch_bounds__(128) quant_int4_kernel(QuantParams pin) {
     QuantParams p = pin;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int b = blockIdx.z, h = blockIdx.y;
+    int b = blockIdx.z;
+    const int h = blockIdx.y;
+    if (p.n_layers > 1) {              // one launch appends to every layer
+        const int layer = b / p.B;
+        b -= layer * p.B;
+        p.pos += layer;
+        p.K_head = static_cast<const T*>(p.K_head) + layer * p.hd_sl; p.V_head = static_cast<const T*>(p.V_head) + layer * p.hd_sl;
+        p.K_new = static_cast<const T*>(p.K_new) + layer * p.nw_sl;   p.V_new = static_cast<const T*>(p.V_new) + layer * p.nw_sl;
+        p.K_packed += layer * p.pk_sl; p.V_packed += layer * p.pk_sl;
+        p.K_scale += layer * p.km_sl;  p.K_mn += layer * p.km_sl;
+        p.V_scale += layer * p.vm_sl;  p.V_mn += layer * p.vm_sl;
+        p.stage_K = static_cast<T*>(p.stage_K) + layer * p.st_sl;     p.stage_V = static_cast<T*>(p.stage_V) + layer * p.st_sl;
+    }
     const int page_idx = blockIdx.x * 4 + warp;
     const int LPT = p.D >> 3;          // lanes per token
     const int TPI = 32 / LPT;          // tokens per warp iteration
@@ -310,6 +324,7 @@ extern "C" int fq_quantize_kv_int4(
     p.vm_sb = vm_sb; p.vm_sh = vm_sh; p.vm_ss = vm_ss;
     p.stage_K = stage_K; p.stage_V = stage_V; p.st_sb = st_sb; p.st_sh = st_sh; p.st_ss = st_ss;
     p.pos = dyn_pos().pos; p.max_tokens = dyn_pos().pos ? dyn_pos().max_tokens : 0x7fffffff;
+    p.n_layers = 1; p.hd_sl = p.nw_sl = p.pk_sl = p.km_sl = p.vm_sl = p.st_sl = 0;
     if (p.pos == nullptr && n_quant == 0 && (n_head + n_new == 0 || (!stage_K && !stage_V))) return FQ_OK;
 
     dim3 grid((unsigned)max(1, (p.n_pages + 3) / 4), (unsigned)H, (unsigned)B);
@@ -320,6 +335,36 @@ extern "C" int fq_quantize_kv_int4(
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
+
+namespace fq {
+// Append n_new tokens (1 <= n_new < page) to layers [0, n_layers) in ONE launch, positions read from pos[layer].
+int quant_append_layers_dyn(const fq_int4_cache* c, int n_layers, const int* pos, const void* K_new, const void* V_new,
+                            int64_t nw_sl, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new, void* stream) {
+    const char* fn = "fq_decode_step_int4_dev";
+    FQ_CHECK_ARG(aligned(K_new, 16) && aligned(V_new, 16) && nw_sl % 8 == 0 && nw_sb % 8 == 0 && nw_sh % 8 == 0 && nw_ss % 8 == 0,
+                 FQ_ERR_ALIGN, "%s: new K/V rows must be 16-byte aligned", fn);
+    QuantParams p;
+    p.K_head = c->K_partial; p.V_head = c->V_partial; p.K_new = K_new; p.V_new = V_new;
+    p.hd_sb = c->pt_sb; p.hd_sh = c->pt_sh; p.hd_ss = c->pt_ss; p.nw_sb = nw_sb; p.nw_sh = nw_sh; p.nw_ss = nw_ss;
+    p.n_head = 0; p.n_new = n_new;
+    p.B = c->B; p.H = c->Hkv; p.D = c->D; p.page = c->page; p.n_quant = 0; p.n_pages = 1;
+    p.K_packed = c->K_packed; p.V_packed = c->V_packed; p.pk_sb = c->pk_sb; p.pk_sh = c->pk_sh; p.pk_ss = c->pk_ss;
+    p.K_scale = static_cast<uint16_t*>(c->K_scale); p.K_mn = static_cast<uint16_t*>(c->K_mn);
+    p.km_sb = c->km_sb; p.km_sh = c->km_sh; p.km_sp = c->km_sp;
+    p.V_scale = static_cast<uint16_t*>(c->V_scale); p.V_mn = static_cast<uint16_t*>(c->V_mn);
+    p.vm_sb = c->vm_sb; p.vm_sh = c->vm_sh; p.vm_ss = 1;
+    p.stage_K = c->K_partial; p.stage_V = c->V_partial; p.st_sb = c->pt_sb; p.st_sh = c->pt_sh; p.st_ss = c->pt_ss;
+    p.pos = pos; p.max_tokens = c->max_seq_len;
+    p.n_layers = n_layers; p.hd_sl = c->pt_sl; p.nw_sl = nw_sl; p.pk_sl = c->pk_sl; p.km_sl = c->km_sl; p.vm_sl = c->vm_sl; p.st_sl = c->pt_sl;
+    FQ_CHECK_ARG((int64_t)c->B * n_layers <= 65535, FQ_ERR_ARG, "%s: batch x layers = %lld too large for one launch", fn, (long long)c->B * n_layers);
+    dim3 grid(1u, (unsigned)c->Hkv, (unsigned)(c->B * n_layers));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (c->kv_dtype == FQ_F16) launch_k(PDL_QUANT, quant_int4_kernel<__half>, grid, dim3(128), 0, st, p);
+    else launch_k(PDL_QUANT, quant_int4_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, p);
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+}  // namespace fq
 
 extern "C" int fq_dequantize_int4(
     const uint8_t* packed, int64_t pk_sb, int64_t pk_sh, int64_t pk_ss,

@@ -178,7 +178,7 @@ class QuestDecodeInt4:
             graph.replay()
             for li in range(Ln):
                 c._seen_tokens[li] += n_new
-            self.launches += 4 * Ln + 1
+            self.launches += 3 * Ln + 2          # one append for all layers, 3 per layer, the position update
             return self.O.unsqueeze(3), self.lse.unsqueeze(3)
 
         replay.graph, replay.pos = graph, pos
