@@ -39,6 +39,22 @@ __device__ __forceinline__ float tq_ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// shared-memory loads through 32-bit shared-window addresses (one integer add per address)
+__device__ __forceinline__ float2 tq_lds_f2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t tq_lds_u8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t tq_lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void tq_cp16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
@@ -100,7 +116,7 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
     __syncthreads();
     pdl_wait();        // the rotated Q and the page list come from the kernels before this one
     pdl_trigger();
-    const unsigned char* lutl = reinterpret_cast<const unsigned char*>(s_lut) + lane * 8;
+    const uint32_t lut_addr = (uint32_t)__cvta_generic_to_shared(s_lut) + lane * 8;      // this lane's column of the table
 
     float2 q2[4];      // this lane's 8 channels of q * sm_scale * log2(e)
     {
@@ -178,8 +194,7 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
     };
     // codebook pair of channels (2j, 2j+1) of this lane: M = msb byte << 12, Lw = lsb halfword << 8
     auto pair_at = [&](uint32_t M, uint32_t Lw, int j) -> float2 {
-        const uint32_t off = ((M >> (2 * j)) & 0x3000u) | ((Lw >> (4 * j)) & 0x0f00u);
-        return *reinterpret_cast<const float2*>(lutl + off);
+        return tq_lds_f2(lut_addr + ((M >> (2 * j)) & 0x3000u) + ((Lw >> (4 * j)) & 0x0f00u));
     };
 
     float m_run = -INFINITY, l_run = 0.f;
@@ -209,14 +224,14 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncwarp();
         if (cur_n > 0) {                                   // warp-uniform
-            const unsigned char* buf = s_stage[warp][it & 1];
+            const uint32_t buf = (uint32_t)__cvta_generic_to_shared(s_stage[warp][it & 1]);
             // ---------------- K ----------------
             float dots[TPL];
 #pragma unroll
             for (int k = 0; k < TPL; ++k) {
                 const int t = NTP * k + tp;
-                const uint32_t M = (uint32_t)buf[KM_OFF + t * MROW + c] << 12;
-                const uint32_t Lw = (uint32_t)*reinterpret_cast<const uint16_t*>(buf + KL_OFF + t * LROW + 2 * c) << 8;
+                const uint32_t M = tq_lds_u8(buf + KM_OFF + t * MROW + c) << 12;
+                const uint32_t Lw = tq_lds_u16(buf + KL_OFF + t * LROW + 2 * c) << 8;
                 float2 a = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) a = __ffma2_rn(pair_at(M, Lw, j), q2[j], a);
@@ -246,8 +261,8 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
                 const int t = NTP * k + tp;
                 const float pv = __shfl_sync(0xffffffffu, pv_mine, tp * LPT + 2 * k);
                 const float2 pv2 = make_float2(pv, pv);
-                const uint32_t M = (uint32_t)buf[VM_OFF + t * MROW + c] << 12;
-                const uint32_t Lw = (uint32_t)*reinterpret_cast<const uint16_t*>(buf + VL_OFF + t * LROW + 2 * c) << 8;
+                const uint32_t M = tq_lds_u8(buf + VM_OFF + t * MROW + c) << 12;
+                const uint32_t Lw = tq_lds_u16(buf + VL_OFF + t * LROW + 2 * c) << 8;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[j] = __ffma2_rn(pair_at(M, Lw, j), pv2, acc[j]);
             }
