@@ -156,13 +156,13 @@ def test_step_all_equals_per_layer_steps():
         assert torch.equal(Oa, Oe) and torch.equal(la, le)
 
 
-@pytest.mark.parametrize("start", [(0, 0), (95, 300)])
-def test_graph_replayed_steps_equal_stream_steps(start):
+@pytest.mark.parametrize("start,n_new", [((0, 0), 1), ((95, 300), 1), ((7, 130), 5)])
+def test_graph_replayed_steps_equal_stream_steps(start, n_new):
     """fq_decode_step_int4_dev (sequence length read on the device, one captured graph replayed
     for every token) == fq_decode_step_int4 bit for bit, from an empty cache and across page boundaries."""
     from flashquest_b200.cache.persistent_int4 import PersistentInt4KVCache
     from flashquest_b200.eager.decode_step import QuestDecodeInt4
-    B, Hq, Hkv, D, page, Ln, steps = 2, 6, 2, 128, 16, 2, 40
+    B, Hq, Hkv, D, page, Ln, steps = 2, 6, 2, 128, 16, 2, 40 if n_new == 1 else 12
     outs = []
     for mode in ("graph", "stream"):
         cache = PersistentInt4KVCache(batch_size=B, num_layers=Ln, num_kv_heads=Hkv, head_dim=D, max_seq_len=512,
@@ -172,22 +172,22 @@ def test_graph_replayed_steps_equal_stream_steps(start):
             if s0:
                 cache.update_quantized(make_kv(60 + li, (B, Hkv, s0, D), torch.float16).cuda(),
                                        make_kv(70 + li, (B, Hkv, s0, D), torch.float16, outliers=()).cuda(), li)
-        kb = torch.empty(Ln, B, Hkv, 1, D, dtype=torch.float16, device="cuda")
+        kb = torch.empty(Ln, B, Hkv, n_new, D, dtype=torch.float16, device="cuda")
         vb, qb = torch.empty_like(kb), torch.empty(Ln, B, Hq, 1, D, dtype=torch.float16, device="cuda")
         replay = step.capture_step_graph(kb, vb, qb) if mode == "graph" else None
         res = []
         for t in range(steps):
-            kb.copy_(make_kv(800 + t, (Ln, B, Hkv, 1, D), torch.float16))
-            vb.copy_(make_kv(900 + t, (Ln, B, Hkv, 1, D), torch.float16, outliers=()))
+            kb.copy_(make_kv(800 + t, (Ln, B, Hkv, n_new, D), torch.float16))
+            vb.copy_(make_kv(900 + t, (Ln, B, Hkv, n_new, D), torch.float16, outliers=()))
             qb.copy_(make_q(1000 + t, (Ln, B, Hq, 1, D), torch.float16))
             O, lse = replay() if mode == "graph" else step.step_all(kb, vb, qb)
             res.append((O.clone(), lse.clone()))
-        assert [cache.get_seq_length(li) for li in range(Ln)] == [s + steps for s in start]
+        assert [cache.get_seq_length(li) for li in range(Ln)] == [s + steps * n_new for s in start]
         outs.append((res, [t.clone() for t in (cache.K_packed, cache.V_packed, cache.K_scale, cache.K_mn, cache.V_scale, cache.V_mn)]))
     (ra, ca), (rb, cb) = outs
     for t, ((Oa, la), (Ob, lb)) in enumerate(zip(ra, rb)):
         assert torch.equal(Oa, Ob) and torch.equal(la, lb), t
-    n_tok = [s + steps for s in start]
+    n_tok = [s + steps * n_new for s in start]
     for li in range(Ln):                     # cache contents of the filled part
         nq = n_tok[li] - n_tok[li] % page
         assert torch.equal(ca[0][li][:, :, :nq], cb[0][li][:, :, :nq]) and torch.equal(ca[1][li][:, :, :nq], cb[1][li][:, :, :nq])
