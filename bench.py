@@ -247,7 +247,7 @@ def run_ours(args):
     with torch.cuda.stream(side):
         one_step()
     torch.cuda.current_stream().wait_stream(side)
-    with torch.cuda.graph(graph):
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
         one_step()
     for _ in range(max(args.warmup, 3)):
         graph.replay()
@@ -299,7 +299,7 @@ def run_ours(args):
                 ptr(O), O.stride(0), O.stride(1), ptr(step.lse[li]), ptr(step.workspace[li]), step.workspace.shape[1],
                 step.n_split, stream_ptr(dev)))
     g2 = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g2):
+    with torch.cuda.graph(g2, capture_error_mode="thread_local"):
         attn_only()
     for _ in range(3):
         g2.replay()
@@ -505,7 +505,7 @@ def run_awq(args):
                 awq_gemv_fused(x, pj)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 for pj in projs:
                     awq_gemv_fused(x, pj)
             for _ in range(max(args.warmup, 3)):

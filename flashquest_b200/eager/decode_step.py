@@ -164,7 +164,7 @@ class QuestDecodeInt4:
                 ptr(self.workspace), self.workspace.stride(0), self.workspace.shape[1], stream_ptr(self.device)))
 
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             if before is not None:
                 before()
             launch()

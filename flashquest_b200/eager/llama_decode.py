@@ -196,7 +196,7 @@ class LlamaInt4Decoder:
         awq_gemv_fused(self.act.view(self.B, 1, -1), (lw.down_proj,))
         torch.cuda.synchronize(self.dev)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             x = self.w.embed[ids.long()]
             check(lib().fq_llama_decode_step_dev(ctypes.byref(self._model), ctypes.byref(self.attn._cdesc),
                                                  ctypes.byref(self.attn._prm), ptr(pos), ptr(x), self.B,
