@@ -20,7 +20,6 @@ on CPU ranks with the `gloo` backend.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Callable, Optional
 

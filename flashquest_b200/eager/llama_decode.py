@@ -17,9 +17,9 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional
 
-import torch
-
 import ctypes
+
+import torch
 
 from .._lib import (AwqLinearDesc, LlamaLayerDesc, LlamaModelDesc, LlamaScratchDesc, check, lib, ptr, stream_ptr)
 from ..cache.persistent_int4 import PersistentInt4KVCache
