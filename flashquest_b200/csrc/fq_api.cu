@@ -24,39 +24,31 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-bool pdl_enabled(int kind) {
-    static const int mask = [] {
-        const char* e = getenv("FQ_PDL");
-        return e ? atoi(e) : (PDL_SCORES | PDL_ATTN | PDL_QUANT | PDL_GEMV);
-    }();
-    return (mask & kind) != 0;
-}
-
-DynPos& dyn_pos() {
-    static thread_local DynPos d;
-    return d;
-}
-
 __device__ int g_fq_status = 0;
 
+// The address is looked up once per device and remembered (relaxed atomics: concurrent host
+// threads may race to store the same value).  It goes stale if the host process calls
+// cudaDeviceReset(); reload the library in that case.
 int* device_status_ptr() {
     constexpr int MAX_DEV = 64;
-    static int* ptrs[MAX_DEV] = {nullptr};
+    static std::atomic<int*> ptrs[MAX_DEV];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) {
         set_error("device_status_ptr: cannot identify the current device");
         return nullptr;
     }
-    if (ptrs[dev] == nullptr) {
+    int* ptr = ptrs[dev].load(std::memory_order_relaxed);
+    if (ptr == nullptr) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_fq_status);
         if (e != cudaSuccess) {
             set_error("device_status_ptr: %s", cudaGetErrorString(e));
             return nullptr;
         }
-        ptrs[dev] = static_cast<int*>(p);
+        ptr = static_cast<int*>(p);
+        ptrs[dev].store(ptr, std::memory_order_relaxed);
     }
-    return ptrs[dev];
+    return ptr;
 }
 
 }  // namespace fq

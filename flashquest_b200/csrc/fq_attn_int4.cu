@@ -34,27 +34,14 @@
 // Split-K: each CTA writes (m, l, acc[D]) to the workspace and takes a ticket; the CTA that
 // draws the last ticket of its row merges the partials in split order and writes O / LSE.
 // No CTA ever waits for another one.
-#include <type_traits>
-
-#include <cstdlib>
-
 #include "fq_common.cuh"
 
 namespace fq {
 
-#ifndef FQ_ATT_WARPS
-#define FQ_ATT_WARPS 4      // consumer warps per CTA (one more warp issues the copies)
-#endif
-#ifndef FQ_ATT_STAGES
-#define FQ_ATT_STAGES 2
-#endif
-#ifndef FQ_ATT_CTAS_PER_SM
-#define FQ_ATT_CTAS_PER_SM 3
-#endif
-constexpr int ATT_WARPS = FQ_ATT_WARPS;
+constexpr int ATT_WARPS = 4;                        // consumer warps per CTA (one more warp issues the copies)
 constexpr int ATT_THREADS = (ATT_WARPS + 1) * 32;   // consumers + the producer warp
-constexpr int ATT_STAGES = FQ_ATT_STAGES;
-constexpr int ATT_CTAS_PER_SM = FQ_ATT_CTAS_PER_SM;
+constexpr int ATT_STAGES = 2;
+constexpr int ATT_CTAS_PER_SM = 3;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr unsigned WAIT_SPIN_LIMIT = 1u << 24;   // bounded wait on a stage; then give up
@@ -109,24 +96,6 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-#ifdef FQ_ATT_TRACE
-// Debug build only: per-CTA phase timestamps (globaltimer, ns) for timeline analysis.
-__device__ unsigned long long g_trace[4096 * 8];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define FQ_TRACE(slot)                                                                        \
-    do {                                                                                      \
-        if (threadIdx.x == 0) {                                                               \
-            const int cta__ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); \
-            if (cta__ < 4096) g_trace[cta__ * 8 + (slot)] = gtime();                          \
-        }                                                                                     \
-    } while (0)
-#else
-#define FQ_TRACE(slot) do {} while (0)
-#endif
 
 // ---------------------------------------------------------------- unit layout in shared memory
 template <int D, int TOK>
@@ -258,7 +227,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, qw = lane >> 3, l = lane & 7;
     const unsigned qmask = 0xffu << (8 * qw);
     const bool is_producer = warp == ATT_WARPS;
-    FQ_TRACE(0);
 
     // ---- units of the compact list owned by this CTA ----
     // Units are dealt round-robin to the splits (unit g belongs to split g % n_split), so a
@@ -388,7 +356,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         };
         ctx_cur.page_id = -1; ctx_nxt.page_id = -1;
         if (n_iter > 0) load_ctx(ctx_cur, 0);
-        FQ_TRACE(1);
 
         // ---- q slice of this lane, pre-multiplied by sm_scale*log2(e) and the nibble scale ----
         float qn[DPL];    // q*sm_scale*log2e times the nibble pre-scale (a power of two)
@@ -404,7 +371,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
             }
         }
         float* pvb = pv_bcast + (warp * 4 + qw) * TOK;
-        FQ_TRACE(2);
 
         // One unit: K dot products, softmax update, V accumulation (see the header comment).
         auto compute_unit = [&](const unsigned char* u, const UnitCtx<DPL, TPL>& c, auto&& prefetch) {
@@ -513,7 +479,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
                 if (++spins > WAIT_SPIN_LIMIT) { gave_up = true; break; }
             }
             if (__any_sync(0xffffffffu, gave_up)) { timed_out = true; break; }
-            if (it == 0) FQ_TRACE(3);
             // the next unit's metadata is requested while this unit is being worked on
             auto prefetch = [&]() {
                 if (it + 1 < n_iter) load_ctx(ctx_nxt, it + 1);
@@ -543,7 +508,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         }
     }
 
-    FQ_TRACE(4);
     // ---------------- un-scale the V accumulators of this quarter warp ----------------
     float o[DPL];
     {
@@ -637,7 +601,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         for (int i = 0; i < NSTATE; ++i) acc_d = fmaf(st_acc[i * D + tid], st_m[i], acc_d);
     }
 
-    FQ_TRACE(5);
     QT* Op = static_cast<QT*>(p.O) + b * p.o_sb + hq * p.o_sh;
     const int row = b * p.Hq + hq;
     if (p.n_split == 1) {
@@ -658,7 +621,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         __threadfence();
     }
     __syncthreads();
-    FQ_TRACE(6);
     if (s_ticket != p.n_split - 1) return;
     // The partials of this row are merged in split order with every load independent of the
     // others (a dependent chain of L2 round trips here would cost more than the attention).
@@ -711,7 +673,6 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         if (p.lse) p.lse[row] = l_all > 0.f ? (m_all + log2f(l_all)) * LN2 : -INFINITY;
         p.tickets[row] = 0;   // leave the workspace ready for the next call
     }
-    FQ_TRACE(7);
 }
 
 template <int D, int TOK>
@@ -731,13 +692,13 @@ static int launch_attn_impl(const AttnParams& p, cudaStream_t st) {
                   (size_t)(ATT_WARPS * 5) * D * 4, "merge area must fit in the staging area");
     auto kern = sparse_decode_int4_kernel<QT, D, TOK, DYN>;
     constexpr int MAX_DEV = 64;
-    static bool prepared[MAX_DEV] = {};
+    static std::atomic<bool> prepared[MAX_DEV];     // relaxed: concurrent host threads may repeat the idempotent set-up
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return fail(FQ_ERR_CUDA, "fq_sparse_decode_int4: cannot identify the current device");
-    if (!prepared[dev]) {
+    if (!prepared[dev].load(std::memory_order_relaxed)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "fq_sparse_decode_int4: cannot reserve %zu B of shared memory: %s", smem, cudaGetErrorString(e));
-        prepared[dev] = true;
+        prepared[dev].store(true, std::memory_order_relaxed);
     }
     dim3 grid((unsigned)p.n_split, (unsigned)p.Hq, (unsigned)p.B);
     cudaError_t e = launch_k(PDL_ATTN, kern, grid, dim3(ATT_THREADS), smem, st, p);
@@ -752,11 +713,6 @@ static int launch_attn(const AttnParams& p, cudaStream_t st) {
 
 }  // namespace fq
 
-#ifdef FQ_ATT_TRACE
-extern "C" int fq_debug_read_trace(unsigned long long* dst, int n) {
-    return (int)cudaMemcpyFromSymbol(dst, fq::g_trace, sizeof(unsigned long long) * n);
-}
-#endif
 
 extern "C" size_t fq_sparse_decode_workspace_bytes(int B, int Hq, int D, int n_split) {
     if (B <= 0 || Hq <= 0 || D <= 0 || n_split <= 1) return 0;
@@ -782,7 +738,8 @@ extern "C" int fq_sparse_decode_default_splits(int B, int Hq, int bucket, int pa
     return (int)n_split;
 }
 
-extern "C" int fq_sparse_decode_int4(
+namespace fq {
+int sparse_decode_int4_launch(
     const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
     const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
     const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
@@ -793,8 +750,7 @@ extern "C" int fq_sparse_decode_int4(
     int tail_len,
     int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
     void* O, int64_t o_sb, int64_t o_sh, float* lse,
-    void* workspace, size_t workspace_bytes, int n_split, void* stream) {
-    using namespace fq;
+    void* workspace, size_t workspace_bytes, int n_split, void* stream, const DynPos& dp) {
     const char* fn = "fq_sparse_decode_int4";
     FQ_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && S_kv >= 0 && P >= 0 && bucket >= 0 && tail_len >= 0, FQ_ERR_ARG, "%s: bad sizes", fn);
     FQ_CHECK_ARG(B <= 65535 && Hq <= 65535, FQ_ERR_ARG, "%s: B and H_q must be <= 65535", fn);
@@ -845,7 +801,7 @@ extern "C" int fq_sparse_decode_int4(
     if (n_split > p.bucket) n_split = p.bucket > 0 ? p.bucket : 1;
     p.n_split = n_split;
     p.tickets = nullptr; p.partials = nullptr;
-    p.pos = dyn_pos().pos; p.pos_new = dyn_pos().n_new;
+    p.pos = dp.pos; p.pos_new = dp.n_new;
     p.status = device_status_ptr();
     if (p.status == nullptr) return FQ_ERR_CUDA;
     if (n_split > 1) {
@@ -868,6 +824,27 @@ extern "C" int fq_sparse_decode_int4(
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
+}  // namespace fq
+
+extern "C" int fq_sparse_decode_int4(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss,
+    int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, float* lse,
+    void* workspace, size_t workspace_bytes, int n_split, void* stream) {
+    return fq::sparse_decode_int4_launch(
+        Q, q_dtype, q_sb, q_sh, K_packed, kp_sb, kp_sh, K_scale, K_mn, km_sb, km_sh, km_sp,
+        V_packed, vp_sb, vp_sh, V_scale, V_mn, vm_sb, vm_sh, compact, cp_sb, cp_sh, bucket,
+        K_tail, V_tail, tail_dtype, tl_sb, tl_sh, tl_ss, tail_len,
+        B, Hq, Hkv, S_kv, P, D, page, sm_scale, O, o_sb, o_sh, lse,
+        workspace, workspace_bytes, n_split, stream, fq::DynPos{});
+}
 
 namespace fq {
 
@@ -885,26 +862,28 @@ static __device__ __align__(256) unsigned char g_static_scratch[FQ_STATIC_SCRATC
 
 // Device address of g_static_scratch on the current device.  In host code the array's name
 // is only a handle for the runtime, not a device pointer, so the address is looked up once
-// per device (with that device current) and remembered.
+// per device (with that device current) and remembered (relaxed atomics: concurrent host threads
+// may race to store the same value).  After a cudaDeviceReset() in the host process the
+// remembered address is stale: reload the library in that case.
 static void* static_scratch_ptr() {
     constexpr int MAX_DEV = 64;
-    static void* ptrs[MAX_DEV] = {nullptr};
+    static std::atomic<void*> ptrs[MAX_DEV];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= MAX_DEV) {
         set_error("fq_sparse_decode_int4_static: cannot identify the current device");
         return nullptr;
     }
-    if (ptrs[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = ptrs[dev].load(std::memory_order_relaxed);
+    if (ptr == nullptr) {
         e = cudaGetSymbolAddress(&ptr, g_static_scratch);
         if (e != cudaSuccess || ptr == nullptr) {
             set_error("fq_sparse_decode_int4_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
             return nullptr;
         }
-        ptrs[dev] = ptr;
+        ptrs[dev].store(ptr, std::memory_order_relaxed);
     }
-    return ptrs[dev];
+    return ptr;
 }
 
 }  // namespace fq

@@ -5,6 +5,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <type_traits>
+
 #include "../../include/flashquest_b200.h"
 
 namespace fq {
@@ -32,11 +35,10 @@ int fail(int code, const char* fmt, ...);
 // previous kernel) and block in pdl_wait() until the previous kernel has completed and its
 // writes are visible.  pdl_trigger() comes right after the wait in every kernel, so at most
 // two kernels of a chain overlap and whatever a kernel reads before its wait must have been
-// written at least two kernels earlier.  FQ_PDL=<bit mask of PDL_*> in the environment selects which kernels get the attribute (0 = none);
-// by default all but the selection kernel, which measured 3 us slower per launch when it was
-// made resident early beside the scoring kernel.
-bool pdl_enabled(int kind);
+// written at least two kernels earlier.  All kernels get the attribute but the selection kernel,
+// which measured 3 us slower per launch when it was made resident early beside the scoring kernel.
 enum { PDL_SCORES = 1, PDL_SELECT = 2, PDL_ATTN = 4, PDL_QUANT = 8, PDL_GEMV = 16 };
+constexpr bool pdl_enabled(int kind) { return kind != PDL_SELECT; }
 
 template <typename... KP, typename... A>
 inline cudaError_t launch_k(int kind, void (*kernel)(KP...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
@@ -56,12 +58,41 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 // ---- token position read on the device ----
 // The graph-capturable decode step (fq_decode_step_int4_dev) cannot bake the sequence length into
-// its launches: it sets this thread-local record around its calls of the ordinary entry points,
-// which then hand `pos` to their kernels; a kernel that gets a non-null `pos` derives page
-// count, tail length and append offsets from *pos (tokens cached before this step) instead of
-// from its host-side arguments, which in that mode only size the grid (maximum values).
+// its launches.  It hands this record to the launch functions below; a kernel that gets a non-null
+// `pos` derives page count, tail length and append offsets from *pos (tokens cached before this
+// step) instead of from its host-side arguments, which in that mode only size the grid (maximum
+// values).  The public entry points pass an empty record.
 struct DynPos { const int* pos = nullptr; int n_new = 0; int page = 1; int max_tokens = 0; };
-DynPos& dyn_pos();
+
+// Launch functions behind the public entry points of the same names, with the position record explicit.
+int quantize_kv_int4_launch(
+    const void* K_head, const void* V_head, int64_t hd_sb, int64_t hd_sh, int64_t hd_ss, int n_head,
+    const void* K_new, const void* V_new, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    int dtype, int B, int H, int D, int page, int n_quant,
+    uint8_t* K_packed, uint8_t* V_packed, int64_t pk_sb, int64_t pk_sh, int64_t pk_ss,
+    void* K_scale, void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    void* V_scale, void* V_mn, int64_t vm_sb, int64_t vm_sh, int64_t vm_ss,
+    void* stage_K, void* stage_V, int64_t st_sb, int64_t st_sh, int64_t st_ss, void* stream, const DynPos& dp);
+int page_scores_int4_launch(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int B, int Hq, int Hkv, int P, int D, float* scores, int64_t sc_sb, int64_t sc_sh, void* stream, const DynPos& dp);
+int select_pages_launch(
+    const float* scores, int64_t sc_sb, int64_t sc_sh, int B, int H, int P,
+    const float* retention_per_head, float retention, int k_max, int sinks, int window,
+    uint8_t* mask, int64_t mk_sb, int64_t mk_sh, int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    int32_t* count, void* stream, const DynPos& dp);
+int sparse_decode_int4_launch(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, float* lse,
+    void* workspace, size_t workspace_bytes, int n_split, void* stream, const DynPos& dp);
 
 // One layer of the graph-capturable step (append + score + select + attend with the sequence
 // length read from *pos) and the closing increment of the positions; defined in fq_decode_layer.cu.
@@ -72,6 +103,8 @@ int decode_layer_int4_dyn(const fq_int4_cache* c, int layer, const int* pos, con
 int advance_positions(int* pos, int n, int n_new, int max_tokens, void* stream);
 int quant_append_layers_dyn(const fq_int4_cache* c, int n_layers, const int* pos, const void* K_new, const void* V_new,
                             int64_t nw_sl, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new, void* stream);
+int rope_launch(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv, int B, int D, int pos,
+                float theta, void* stream, const int* pos_dev);
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

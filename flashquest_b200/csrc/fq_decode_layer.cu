@@ -121,10 +121,7 @@ int decode_layer_int4_dyn(const fq_int4_cache* c, int l, const int* pos, const v
     const int page = c->page, D = c->D, B = c->B, Hkv = c->Hkv, Hq = pl->Hq;
     const int P_max = c->max_seq_len / page;
     const size_t kv_esz = 2;
-    struct Guard {            // the ordinary entry points read the record while it is set
-        ~Guard() { dyn_pos() = DynPos{}; }
-    } guard;
-    dyn_pos() = DynPos{pos, n_new, page, c->max_seq_len};
+    const DynPos dp{pos, n_new, page, c->max_seq_len};
     uint8_t* Kp = c->K_packed + l * c->pk_sl;
     uint8_t* Vp = c->V_packed + l * c->pk_sl;
     uint16_t* Ks = static_cast<uint16_t*>(c->K_scale) + l * c->km_sl;
@@ -136,26 +133,26 @@ int decode_layer_int4_dyn(const fq_int4_cache* c, int l, const int* pos, const v
     // host-side sizes are the maxima (they size grids and pass validation); the kernels read *pos
     int rc = FQ_OK;
     if (append)
-        rc = fq_quantize_kv_int4(Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, page - n_new, Kn, Vn, nw_sb, nw_sh, nw_ss, n_new,
-                                 c->kv_dtype, B, Hkv, D, page, page,
-                                 Kp, Vp, c->pk_sb, c->pk_sh, c->pk_ss, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
-                                 Vs, Vm, c->vm_sb, c->vm_sh, 1, Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, stream);
+        rc = quantize_kv_int4_launch(Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, page - n_new, Kn, Vn, nw_sb, nw_sh, nw_ss, n_new,
+                                     c->kv_dtype, B, Hkv, D, page, page,
+                                     Kp, Vp, c->pk_sb, c->pk_sh, c->pk_ss, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
+                                     Vs, Vm, c->vm_sb, c->vm_sh, 1, Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, stream, dp);
     if (rc != FQ_OK) return rc;
-    rc = fq_page_scores_int4(Ql, q_dtype, q_sb, q_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp, B, Hq, Hkv, P_max, D,
-                             sc, (int64_t)Hq * P_max, P_max, stream);
+    rc = page_scores_int4_launch(Ql, q_dtype, q_sb, q_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp, B, Hq, Hkv, P_max, D,
+                                 sc, (int64_t)Hq * P_max, P_max, stream, dp);
     if (rc != FQ_OK) return rc;
-    rc = fq_select_pages(sc, (int64_t)Hq * P_max, P_max, B, Hq, P_max, pl->retention_per_head, pl->retention,
-                         pl->k_max_static < P_max ? pl->k_max_static : P_max, pl->sinks, pl->window, nullptr, 0, 0,
-                         cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket, nullptr, stream);
+    rc = select_pages_launch(sc, (int64_t)Hq * P_max, P_max, B, Hq, P_max, pl->retention_per_head, pl->retention,
+                             pl->k_max_static < P_max ? pl->k_max_static : P_max, pl->sinks, pl->window, nullptr, 0, 0,
+                             cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket, nullptr, stream, dp);
     if (rc != FQ_OK) return rc;
     const int n_split = pl->n_split > 0 ? pl->n_split : fq_sparse_decode_default_splits(B, Hq, pl->bucket, page);
-    return fq_sparse_decode_int4(
+    return sparse_decode_int4_launch(
         Ql, q_dtype, q_sb, q_sh, Kp, c->pk_sb, c->pk_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp,
         Vp, c->pk_sb, c->pk_sh, Vs, Vm, c->vm_sb, c->vm_sh,
         cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket,
         Kt, Vt, c->kv_dtype, c->pt_sb, c->pt_sh, c->pt_ss, page - 1,
         B, Hq, Hkv, P_max * page, P_max, D, page, pl->sm_scale,
-        O, (int64_t)Hq * D, D, lse, workspace, workspace_bytes, n_split, stream);
+        O, (int64_t)Hq * D, D, lse, workspace, workspace_bytes, n_split, stream, dp);
 }
 }  // namespace fq
 

@@ -189,17 +189,23 @@ extern "C" int fq_add_rmsnorm(const void* a, const void* b, const void* weight, 
     return FQ_OK;
 }
 
-extern "C" int fq_rope(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv,
-                       int B, int D, int pos, float theta, void* stream) {
-    using namespace fq;
+namespace fq {
+int rope_launch(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv,
+                int B, int D, int pos, float theta, void* stream, const int* pos_dev) {
     const char* fn = "fq_rope";
     FQ_CHECK_ARG(q && k && B > 0 && Hq > 0 && Hkv > 0 && D > 0 && D % 2 == 0 && pos >= 0 && theta > 0.f, FQ_ERR_ARG, "%s: bad arguments", fn);
     FQ_CHECK_ARG(B <= 65535, FQ_ERR_ARG, "%s: batch %d too large", fn, B);
     launch_k(PDL_GEMV, rope_kernel, dim3((unsigned)(Hq + Hkv), (unsigned)B), dim3(D / 2 < 128 ? (D / 2 + 31) / 32 * 32 : 128), 0,
              static_cast<cudaStream_t>(stream), static_cast<__half*>(q), q_sb, q_sh, Hq, static_cast<__half*>(k), k_sb, k_sh, Hkv,
-             D, pos, theta, dyn_pos().pos);
+             D, pos, theta, pos_dev);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
+}
+}  // namespace fq
+
+extern "C" int fq_rope(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv,
+                       int B, int D, int pos, float theta, void* stream) {
+    return fq::rope_launch(q, q_sb, q_sh, Hq, k, k_sb, k_sh, Hkv, B, D, pos, theta, stream, nullptr);
 }
 
 extern "C" int fq_swiglu(const void* gate, const void* up, int64_t n, void* out, void* stream) {
@@ -304,9 +310,7 @@ static int llama_step_impl(const fq_llama_model* m, const fq_int4_cache* cache, 
         }
         void* Ol = static_cast<char*>(s->O) + (size_t)l * s->o_sl * 2;
         if (pos_dev) {
-            dyn_pos() = DynPos{pos_dev + l, 1, cache->page, cache->max_seq_len};
-            rc = fq_rope(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, 0, m->rope_theta, stream);
-            dyn_pos() = DynPos{};
+            rc = rope_launch(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, 0, m->rope_theta, stream, pos_dev + l);
             if (rc != FQ_OK) return rc;
             rc = decode_layer_int4_dyn(cache, l, pos_dev + l, s->k, s->v, nkv, D, D, 1, s->q, FQ_F16, nq, D, prm,
                                        s->scores + l * s->sc_sl, s->compact + l * s->cp_sl, Ol, nullptr,

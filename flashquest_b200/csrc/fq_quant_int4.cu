@@ -272,7 +272,8 @@ __global__ void __launch_bounds__(256) dequant_int4_kernel(
 
 }  // namespace fq
 
-extern "C" int fq_quantize_kv_int4(
+namespace fq {
+int quantize_kv_int4_launch(
     const void* K_head, const void* V_head, int64_t hd_sb, int64_t hd_sh, int64_t hd_ss, int n_head,
     const void* K_new, const void* V_new, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
     int dtype, int B, int H, int D, int page, int n_quant,
@@ -280,7 +281,7 @@ extern "C" int fq_quantize_kv_int4(
     void* K_scale, void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
     void* V_scale, void* V_mn, int64_t vm_sb, int64_t vm_sh, int64_t vm_ss,
     void* stage_K, void* stage_V, int64_t st_sb, int64_t st_sh, int64_t st_ss,
-    void* stream) {
+    void* stream, const DynPos& dp) {
     using namespace fq;
     const char* fn = "fq_quantize_kv_int4";
     FQ_CHECK_ARG(B > 0 && H > 0 && page > 0 && n_head >= 0 && n_new >= 0 && n_quant >= 0, FQ_ERR_ARG,
@@ -323,7 +324,7 @@ extern "C" int fq_quantize_kv_int4(
     p.V_scale = static_cast<uint16_t*>(V_scale); p.V_mn = static_cast<uint16_t*>(V_mn);
     p.vm_sb = vm_sb; p.vm_sh = vm_sh; p.vm_ss = vm_ss;
     p.stage_K = stage_K; p.stage_V = stage_V; p.st_sb = st_sb; p.st_sh = st_sh; p.st_ss = st_ss;
-    p.pos = dyn_pos().pos; p.max_tokens = dyn_pos().pos ? dyn_pos().max_tokens : 0x7fffffff;
+    p.pos = dp.pos; p.max_tokens = dp.pos ? dp.max_tokens : 0x7fffffff;
     p.n_layers = 1; p.hd_sl = p.nw_sl = p.pk_sl = p.km_sl = p.vm_sl = p.st_sl = 0;
     if (p.pos == nullptr && n_quant == 0 && (n_head + n_new == 0 || (!stage_K && !stage_V))) return FQ_OK;
 
@@ -334,6 +335,23 @@ extern "C" int fq_quantize_kv_int4(
     else launch_k(PDL_QUANT, quant_int4_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, p);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
+}
+
+}  // namespace fq
+
+extern "C" int fq_quantize_kv_int4(
+    const void* K_head, const void* V_head, int64_t hd_sb, int64_t hd_sh, int64_t hd_ss, int n_head,
+    const void* K_new, const void* V_new, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    int dtype, int B, int H, int D, int page, int n_quant,
+    uint8_t* K_packed, uint8_t* V_packed, int64_t pk_sb, int64_t pk_sh, int64_t pk_ss,
+    void* K_scale, void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    void* V_scale, void* V_mn, int64_t vm_sb, int64_t vm_sh, int64_t vm_ss,
+    void* stage_K, void* stage_V, int64_t st_sb, int64_t st_sh, int64_t st_ss,
+    void* stream) {
+    return fq::quantize_kv_int4_launch(K_head, V_head, hd_sb, hd_sh, hd_ss, n_head, K_new, V_new, nw_sb, nw_sh, nw_ss, n_new,
+                                       dtype, B, H, D, page, n_quant, K_packed, V_packed, pk_sb, pk_sh, pk_ss,
+                                       K_scale, K_mn, km_sb, km_sh, km_sp, V_scale, V_mn, vm_sb, vm_sh, vm_ss,
+                                       stage_K, stage_V, st_sb, st_sh, st_ss, stream, fq::DynPos{});
 }
 
 namespace fq {

@@ -21,9 +21,11 @@ constexpr int SEL_MAX_WARPS = 32;
 constexpr int SEL_BINS = 2048;
 constexpr int SEL_CAND_MAX = 128;
 
-// larger float -> larger key; -0 folds onto +0; NaN with a clear sign bit sorts above +inf.
+// larger float -> larger key; -0 folds onto +0; every NaN (either sign) takes the largest key,
+// which is how torch.topk orders NaNs.
 __device__ __forceinline__ uint32_t score_key(float f) {
     uint32_t u = __float_as_uint(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return 0xffffffffu;
     if (u == 0x80000000u) u = 0u;
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
@@ -295,15 +297,12 @@ __global__ void build_compact_kernel(const uint8_t* __restrict__ mask, int64_t m
 static int select_threads(int P) { return P <= 512 ? 128 : (P <= 1024 ? 256 : (P <= 4096 ? 512 : 1024)); }
 constexpr int SEL_SMEM_MAX_P = 49152;   // 192 KB of keys
 
-}  // namespace fq
-
-extern "C" int fq_select_pages(
+int select_pages_launch(
     const float* scores, int64_t sc_sb, int64_t sc_sh, int B, int H, int P,
     const float* retention_per_head, float retention, int k_max, int sinks, int window,
     uint8_t* mask, int64_t mk_sb, int64_t mk_sh,
     int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
-    int32_t* count, void* stream) {
-    using namespace fq;
+    int32_t* count, void* stream, const DynPos& dp) {
     const char* fn = "fq_select_pages";
     FQ_CHECK_ARG(B > 0 && H > 0 && P >= 0, FQ_ERR_ARG, "%s: bad sizes B=%d H=%d P=%d", fn, B, H, P);
     FQ_CHECK_ARG(retention_per_head || (retention >= 0.f && retention <= 1.f), FQ_ERR_ARG,
@@ -322,14 +321,26 @@ extern "C" int fq_select_pages(
         }
         launch_k(PDL_SELECT, select_pages_kernel<true>, grid, dim3(select_threads(P)), smem, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
-            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dyn_pos().pos, dyn_pos().n_new, dyn_pos().page);
+            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dp.pos, dp.n_new, dp.page);
     } else {
         launch_k(PDL_SELECT, select_pages_kernel<false>, grid, dim3(select_threads(P)), 0, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
-            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dyn_pos().pos, dyn_pos().n_new, dyn_pos().page);
+            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dp.pos, dp.n_new, dp.page);
     }
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
+}
+
+}  // namespace fq
+
+extern "C" int fq_select_pages(
+    const float* scores, int64_t sc_sb, int64_t sc_sh, int B, int H, int P,
+    const float* retention_per_head, float retention, int k_max, int sinks, int window,
+    uint8_t* mask, int64_t mk_sb, int64_t mk_sh,
+    int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    int32_t* count, void* stream) {
+    return fq::select_pages_launch(scores, sc_sb, sc_sh, B, H, P, retention_per_head, retention, k_max, sinks, window,
+                                   mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, stream, fq::DynPos{});
 }
 
 extern "C" int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,

@@ -215,8 +215,10 @@ class LlamaInt4Decoder:
         replay.graph, replay.ids, replay.pos = graph, ids, pos
         return replay
 
-    def decode_step_per_op(self, token_ids: torch.Tensor) -> torch.Tensor:
-        """The same step issued operator by operator from Python (one foreign call per kernel group)."""
+    def decode_step_per_op(self, token_ids: torch.Tensor, trace: Optional[list] = None) -> torch.Tensor:
+        """The same step issued operator by operator from Python (one foreign call per kernel group).
+        `trace`, if given, receives a copy of the residual stream after every addition (2 per layer + 1):
+        the hidden states a per-block comparison needs."""
         c, w, B = self.cfg, self.w, self.B
         L = lib()
         st = stream_ptr(self.dev)
@@ -233,6 +235,8 @@ class LlamaInt4Decoder:
             out = self.resid[flip]
             flip ^= 1
             self._add_rmsnorm(x, delta, weight, out, self.normed)
+            if trace is not None:
+                trace.append(out.clone())
             return out
 
         delta = None                                             # output of the previous block, not yet added

@@ -30,6 +30,13 @@ def _workspace(device, nbytes: int, rows: int):
     return ws
 
 
+def reset_workspaces():
+    """Zeroes every cached scratch buffer.  To be called after fq_device_status() has reported a
+    timed-out wait: a kernel that gave up leaves its ticket words non-zero."""
+    for ws, _ in _workspaces.values():
+        ws.zero_()
+
+
 def _vmeta(t: torch.Tensor, B, H, S):
     """V_scale / V_mn as (B,H,S) with unit token stride and 16-byte aligned (b,h) rows; the
     reference passes (B,H,S,1) from the caches and (B,H,S) from some tests."""

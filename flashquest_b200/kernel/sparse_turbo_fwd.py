@@ -22,18 +22,17 @@ def _scale3(t, B, H, S):
     return t if S <= 1 or t.stride(2) == 1 else t.contiguous()
 
 
-def flash_attn_sparse_turbo_fwd(Q, K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_scale_turbo, *,
+def sparse_decode_turbo_rotated(Q_rot, K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_scale_turbo, *,
                                 selection_mask, page_size: int = 64, sm_scale=None, return_lse: bool = True,
                                 n_split=None):
-    """Decode-only fused TurboQuant sparse forward (K3-V3), kernel/sparse_turbo_fwd.py:254.
-
-    Q (B,H_q,1,D) bf16 (fp16 accepted) in the RAW basis: it is rotated with the WHT before the
-    kernel and the output is rotated back after it, as the reference wrapper does.
-    Returns (O (B,H_q,1,D) Q.dtype, lse (B,H_q,1) fp32 or None), both in the raw basis."""
-    assert Q.is_cuda and Q.dtype in (torch.bfloat16, torch.float16)
+    """The kernel of flash_attn_sparse_turbo_fwd alone, in the ROTATED basis: Q_rot (B,H_q,1,D) is
+    taken as it is (no WHT before), O_rot comes back un-rotated-back (no WHT after).  This is the part
+    of kernel/sparse_turbo_fwd.py:92-251 that runs on the GPU in the reference; parity of the
+    arithmetic is checked here, the two bf16 rotations are checked by the WHT tests."""
+    assert Q_rot.is_cuda and Q_rot.dtype in (torch.bfloat16, torch.float16)
     assert K_msb.dtype == torch.uint8 and K_lsb.dtype == torch.uint8
     assert V_msb.dtype == torch.uint8 and V_lsb.dtype == torch.uint8
-    B, H_q, S_q, D = Q.shape
+    B, H_q, S_q, D = Q_rot.shape
     if S_q != 1:
         raise NotImplementedError(f"flash_attn_sparse_turbo_fwd: decode-only (S_q={S_q})")
     if D not in _SUPPORTED_HEAD_DIMS:
@@ -47,9 +46,11 @@ def flash_attn_sparse_turbo_fwd(Q, K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_
     require_cuda(K_msb, K_lsb, V_msb, V_lsb, K_scale_turbo, V_scale_turbo, selection_mask)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    dev = Q.device
-    Q_rot = wht_along_head_dim(Q).reshape(B, H_q, D)
-    O_rot = torch.empty(B, H_q, D, dtype=Q.dtype, device=dev)
+    dev = Q_rot.device
+    Q_rot = Q_rot.reshape(B, H_q, D)
+    if Q_rot.stride(-1) != 1 or Q_rot.stride(0) % 8 or Q_rot.stride(1) % 8 or Q_rot.data_ptr() % 16:
+        Q_rot = Q_rot.contiguous()
+    O_rot = torch.empty(B, H_q, D, dtype=Q_rot.dtype, device=dev)
     L = torch.empty(B, H_q, dtype=torch.float32, device=dev) if return_lse else None
     compact = build_compact_selection(selection_mask, max(num_pages, 1)).squeeze(2)
     bucket = compact.shape[-1]
@@ -70,5 +71,24 @@ def flash_attn_sparse_turbo_fwd(Q, K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_
             B, H_q, H_kv, S_kv, num_pages, D, int(page_size), float(sm_scale),
             ptr(O_rot), O_rot.stride(0), O_rot.stride(1), ptr(L),
             ptr(ws), ws.numel() if ws is not None else 0, int(n_split), stream_ptr(dev)))
-    O = wht_along_head_dim(O_rot).unsqueeze(2)
-    return O, (L.unsqueeze(2) if L is not None else None)
+    return O_rot.unsqueeze(2), (L.unsqueeze(2) if L is not None else None)
+
+
+def flash_attn_sparse_turbo_fwd(Q, K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_scale_turbo, *,
+                                selection_mask, page_size: int = 64, sm_scale=None, return_lse: bool = True,
+                                n_split=None):
+    """Decode-only fused TurboQuant sparse forward (K3-V3), kernel/sparse_turbo_fwd.py:254.
+
+    Q (B,H_q,1,D) bf16 (fp16 accepted) in the RAW basis: it is rotated with the WHT before the
+    kernel and the output is rotated back after it, as the reference wrapper does
+    (kernel/sparse_turbo_fwd.py:305,343-344).
+    Returns (O (B,H_q,1,D) Q.dtype, lse (B,H_q,1) fp32 or None), both in the raw basis."""
+    assert Q.is_cuda and Q.dtype in (torch.bfloat16, torch.float16)
+    if Q.dim() == 4 and Q.shape[2] != 1:
+        raise NotImplementedError(f"flash_attn_sparse_turbo_fwd: decode-only (S_q={Q.shape[2]})")
+    if Q.shape[-1] not in _SUPPORTED_HEAD_DIMS:
+        raise NotImplementedError(f"head_dim={Q.shape[-1]} not in {_SUPPORTED_HEAD_DIMS}")
+    O_rot, L = sparse_decode_turbo_rotated(wht_along_head_dim(Q), K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_scale_turbo,
+                                           selection_mask=selection_mask, page_size=page_size, sm_scale=sm_scale,
+                                           return_lse=return_lse, n_split=n_split)
+    return wht_along_head_dim(O_rot), L

@@ -26,7 +26,7 @@ __all__ = [
     "k_page_meta_int4", "wht_along_head_dim", "quantize_k_turbo", "quantize_v_turbo",
     "dequantize_k_turbo", "dequantize_v_turbo", "turbo_codebook", "page_scores_int4_fast",
     "k_per_head", "select_pages_vectorized", "build_compact_selection", "sparse_attn_int4",
-    "sparse_attn_turbo", "lse_merge", "awq_gemv", "awq_pack", "set_num_threads",
+    "sparse_attn_turbo", "sparse_attn_turbo_rotated", "lse_merge", "awq_gemv", "awq_pack", "set_num_threads",
 ]
 
 
@@ -300,26 +300,37 @@ def sparse_attn_int4(Q, K_packed, K_scale, K_mn, V_packed, V_scale, V_mn, *, sel
     return O, lse
 
 
-def sparse_attn_turbo(Q, K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_scale_turbo, *,
-                      selection_mask, page_size=64, sm_scale=None):
-    """kernel/sparse_turbo_fwd.py:254 semantics with fp32 rotations and fp64 accumulation:
-    Q is rotated (WHT in fp32), attention runs in the rotated basis, O is rotated back in
-    fp32.  Returns (O fp32 (B,H_q,1,D) raw basis, lse (B,H_q,1))."""
-    B, H_q, S_q, D = Q.shape
+def sparse_attn_turbo_rotated(Q_rot, K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_scale_turbo, *,
+                              selection_mask, page_size=64, sm_scale=None):
+    """The kernel part of kernel/sparse_turbo_fwd.py:92-251 in fp64 accumulation: Q_rot (fp32, fp16 or
+    bf16) is already in the rotated basis and O comes back in the rotated basis (fp32), so that a
+    GPU kernel can be compared on exactly the same operands, without the two rotations.
+    Returns (O_rot fp32 (B,H_q,1,D), lse (B,H_q,1))."""
+    B, H_q, S_q, D = Q_rot.shape
     if S_q != 1:
         raise NotImplementedError(f"decode-only (S_q={S_q})")
     H_kv, S_kv = K_msb.shape[1], K_msb.shape[2]
     P = selection_mask.shape[-1]
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    Q_rot = wht_along_head_dim(Q.float())
+    Q_rot = _c(Q_rot)
     m8 = _c(selection_mask.reshape(B, H_q, P).to(torch.uint8))
     O_rot = torch.empty(B, H_q, 1, D, dtype=torch.float32)
     lse = torch.empty(B, H_q, 1, dtype=torch.float32)
     _load().orc_sparse_attn_turbo(
-        _p(Q_rot), 0, _p(_c(K_msb)), _p(_c(K_lsb)), _p(_c(K_scale_turbo)),
+        _p(Q_rot), _dt(Q_rot), _p(_c(K_msb)), _p(_c(K_lsb)), _p(_c(K_scale_turbo)),
         _p(_c(V_msb)), _p(_c(V_lsb)), _p(_c(V_scale_turbo)), _p(m8),
         B, H_q, H_kv, S_kv, P, D, int(page_size), ctypes.c_float(sm_scale), _p(O_rot), _p(lse))
+    return O_rot, lse
+
+
+def sparse_attn_turbo(Q, K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb, V_scale_turbo, *,
+                      selection_mask, page_size=64, sm_scale=None):
+    """kernel/sparse_turbo_fwd.py:254 semantics with fp32 rotations and fp64 accumulation:
+    Q is rotated (WHT in fp32), attention runs in the rotated basis, O is rotated back in
+    fp32.  Returns (O fp32 (B,H_q,1,D) raw basis, lse (B,H_q,1))."""
+    O_rot, lse = sparse_attn_turbo_rotated(wht_along_head_dim(Q.float()), K_msb, K_lsb, K_scale_turbo, V_msb, V_lsb,
+                                           V_scale_turbo, selection_mask=selection_mask, page_size=page_size, sm_scale=sm_scale)
     return wht_along_head_dim(O_rot), lse
 
 

@@ -198,6 +198,43 @@ def test_full_size_invariances(att):
     assert att.status() == 0
 
 
+@pytest.mark.parametrize("S,k_max", [(131072, 1024), (524288, 4096)])
+def test_config4_shapes(att, S, k_max):
+    """BASELINE config 4's two shapes (retention 0.125, page 16, 24/8 heads): 128k context
+    (8192 pages, bucket 1026) and 512k context (32 768 pages, bucket 4098).  Whole chain on the GPU
+    for one sequence; scores, page set, compact list and attention of one GQA group against the
+    oracle on the same packed bytes."""
+    from flashquest_b200.eager.criticality import page_scores_int4_fast
+    from flashquest_b200.eager.selection import select_pages_compact
+    from flashquest_b200.kernel.kv_quant import quantize_k_int4, quantize_v_int4
+    B, Hq, Hkv, D, page = 1, 24, 8, 128, 16
+    P, bucket = S // page, k_max + 2
+    g = torch.Generator(device="cuda").manual_seed(S % 1000 + 11)
+    K = torch.randn(B, Hkv, S, D, device="cuda", generator=g)
+    K[..., [3, 17, 64, 100]] *= 8
+    K, V = K.half(), torch.randn(B, Hkv, S, D, device="cuda", generator=g).half()
+    Q = torch.randn(B, Hq, 1, D, device="cuda", generator=g).half()
+    kv = quantize_k_int4(K, page) + quantize_v_int4(V)
+    del K, V
+    scores = page_scores_int4_fast(Q, kv[1], kv[2])
+    comp, mask = select_pages_compact(scores, 0.125, 1, 1, k_max_static=k_max, BUCKET_MAX=bucket, return_mask=True)
+    assert comp.shape[-1] == bucket and int(mask.sum(-1).min()) >= k_max and int(mask.sum(-1).max()) <= bucket
+    O, lse = att.compact(Q, *kv, selected_page_ids=comp, page_size=page)
+    for n_split in (1, 9):
+        O2, lse2 = att.compact(Q, *kv, selected_page_ids=comp, page_size=page, n_split=n_split)
+        assert (O2.float() - O.float()).abs().max() <= 1e-3 and (lse2 - lse).abs().max() <= 1e-4
+    hkv, heads = 5, slice(15, 18)
+    cpu = [t[:, hkv:hkv + 1].cpu() for t in kv]
+    s_ref = oracle.page_scores_int4_fast(Q.cpu()[:, heads], cpu[1], cpu[2])
+    assert torch.equal(scores.cpu()[:, heads], s_ref)
+    m_ref = oracle.select_pages_vectorized(s_ref, 0.125, 1, 1, k_max_static=k_max)
+    assert torch.equal(mask.cpu()[:, heads], m_ref)
+    assert torch.equal(comp.cpu()[:, heads], oracle.build_compact_selection(m_ref, bucket))
+    Ow, lw = oracle.sparse_attn_int4(Q.cpu()[:, heads], *cpu, selection_mask=m_ref, page_size=page)
+    _close(O[:, heads], lse[:, heads], Ow, lw, torch.float16)
+    assert att.status() == 0
+
+
 def test_many_ctas_with_refills_and_empty_trailing_units(att):
     """A grid larger than the GPU, several pipeline refills per CTA and last iterations whose
     units are partly empty (regression: an empty unit must not let a copy-issuing lane fall two

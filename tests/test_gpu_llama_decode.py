@@ -39,7 +39,11 @@ class _Ref:
         self.K = [None] * cfg.layers
         self.V = [None] * cfg.layers
 
-    def step(self, ids):
+    def step(self, ids, trace=None, views_fn=None, kv_err=None):
+        """views_fn(layer) -> the GPU cache's views AFTER the GPU ran the same step: the attention then
+        reads the GPU's packed bytes and staged tokens (teacher-forced cache), so that a last-bit
+        difference in k or v cannot move a 4-bit code and with it every later result; the k / v this
+        restatement computes itself are compared with the GPU's staged ones into kv_err instead."""
         c, w = self.cfg, self.w
         B = ids.shape[0]
         pos = 0 if self.K[0] is None else self.K[0].shape[2]
@@ -48,6 +52,8 @@ class _Ref:
         for li, lw in enumerate(w.layers):
             if delta is not None:
                 x = x + delta
+                if trace is not None:
+                    trace.append(x)
             n = _rms(x, lw.input_norm.cpu(), c.rms_eps)
             q = _awq(n, lw.q_proj).view(B, c.q_heads, c.head_dim)
             k = _awq(n, lw.k_proj).view(B, c.kv_heads, c.head_dim)
@@ -57,8 +63,19 @@ class _Ref:
             self.V[li] = v.unsqueeze(2) if self.V[li] is None else torch.cat([self.V[li], v.unsqueeze(2)], 2)
             seen = self.K[li].shape[2]
             nq = seen - seen % self.page
-            Kc, Vc = self.K[li][:, :, :nq], self.V[li][:, :, :nq]
-            kv = oracle.quantize_k_int4(Kc, self.page) + oracle.quantize_v_int4(Vc)
+            K_tail, V_tail = self.K[li][:, :, nq:], self.V[li][:, :, nq:]
+            if views_fn is None:
+                Kc, Vc = self.K[li][:, :, :nq], self.V[li][:, :, :nq]
+                kv = oracle.quantize_k_int4(Kc, self.page) + oracle.quantize_v_int4(Vc)
+            else:
+                vw = views_fn(li)
+                assert vw["seq_len"] == seen and vw["completed_len"] == nq
+                kv = tuple(vw[n].cpu() for n in ("K_packed", "K_scale", "K_mn", "V_packed", "V_scale", "V_mn"))
+                gk, gv = vw["K_partial"].cpu(), vw["V_partial"].cpu()
+                if seen > nq and kv_err is not None:      # the newest token is still staged unquantised: compare it
+                    for mine, theirs in ((k, gk[:, :, -1]), (v, gv[:, :, -1])):
+                        kv_err.append(float((mine.float() - theirs.float()).abs().max() / (2e-3 * mine.float().abs().max() + 1e-3)))
+                K_tail, V_tail = gk, gv
             r, s, wn, kms = self.sel
             if nq > 0:
                 sc = oracle.page_scores_int4_fast(q.unsqueeze(2), kv[1], kv[2])
@@ -66,14 +83,18 @@ class _Ref:
             else:
                 mask = torch.zeros(B, c.q_heads, 1, 0, dtype=torch.bool)
             O, _ = oracle.sparse_attn_int4(q.unsqueeze(2), *kv, selection_mask=mask, page_size=self.page,
-                                           K_partial=self.K[li][:, :, nq:], V_partial=self.V[li][:, :, nq:])
+                                           K_partial=K_tail, V_partial=V_tail)
             attn = _awq(O.half().reshape(B, -1), lw.o_proj)
             x = x + attn
+            if trace is not None:
+                trace.append(x)
             n = _rms(x, lw.post_norm.cpu(), c.rms_eps)
             gate, up = _awq(n, lw.gate_proj), _awq(n, lw.up_proj)
             act = torch.nn.functional.silu(gate.float()).half() * up
             delta = _awq(act, lw.down_proj)
         x = x + delta
+        if trace is not None:
+            trace.append(x)
         n = _rms(x, w.final_norm.cpu(), c.rms_eps)
         return (n.float() @ w.lm_head.cpu().float().T).half()
 
@@ -143,6 +164,52 @@ def test_decode_steps_match_cpu_restatement():
                 assert nxt[b].item() == int(want[b].argmax())
         ids = want.argmax(-1).to(torch.int32)             # both sides continue from the reference's choice
     assert dec.cache.get_seq_length(0) == 36
+
+
+@pytest.mark.parametrize("layers", [1, 2])
+def test_decode_steps_at_config3_widths(layers):
+    """One and two layers at BASELINE config 3's widths (hidden 3072, 24/8 heads x 128, FFN 8192,
+    vocab 128 256), teacher-forced token ids AND cache contents, from an empty cache across a page
+    boundary: the residual stream after every block and the logits against the CPU restatement.
+
+    Bound: 2e-3 * max|reference| + one fp16 ulp of the value.  The restatement attends over the GPU
+    cache's own bytes (a 4-bit code is a discontinuous function of k: one fp16 ulp in k can move a
+    code by one step, which is 1/15 of the page's range; with free-running caches the logits drift
+    to 6e-3 * max within one page) and its own k / v are compared with the staged ones at the same
+    bound.  Every page is kept (retention 1) so that a last-bit difference in q cannot change the
+    page set, which is checked exactly elsewhere."""
+    from flashquest_b200.eager.llama_decode import LlamaConfig, LlamaInt4Decoder, random_llama_weights
+    cfg = LlamaConfig(layers=layers)
+    w = random_llama_weights(cfg, "cuda", seed=4, scale_down=0.25)
+    page, B = 16, 1
+    dec = LlamaInt4Decoder(cfg, w, batch_size=B, max_seq_len=64, page_size=page, retention=1.0, num_sinks=1, window_pages=1)
+    ref = _Ref(cfg, w, page, 1.0, 1, 1, dec.attn.k_max_static)
+    ids = torch.tensor([4711], dtype=torch.int32)
+    worst_h = worst_l = 0.0
+    kv_err = []
+    for t in range(19):
+        tr_g, tr_r = [], []
+        if t % 2:
+            dec.decode_step(ids.cuda())
+        else:
+            dec.decode_step_per_op(ids.cuda(), trace=tr_g)
+        got = dec.logits.float().cpu()
+        want = ref.step(ids, trace=tr_r, views_fn=dec.cache.get_views, kv_err=kv_err).float()
+        for hg, hr in zip(tr_g, tr_r):
+            hr = hr.float()
+            tol = 2e-3 * hr.abs().max() + 2 ** -11 * hr.abs()
+            err = (hg.float().cpu() - hr).abs()
+            worst_h = max(worst_h, float((err / tol).max()))
+            assert (err <= tol).all(), (t, float(err.max()), float(hr.abs().max()))
+        assert len(tr_g) == (len(tr_r) if tr_g else 0)
+        tol = 2e-3 * want.abs().max() + 2 ** -11 * want.abs()
+        err = (got - want).abs()
+        worst_l = max(worst_l, float((err / tol).max()))
+        assert (err <= tol).all(), (t, float(err.max()), float(want.abs().max()))
+        ids = want.argmax(-1).to(torch.int32)
+    assert kv_err and max(kv_err) <= 1.0, max(kv_err)
+    print(f"config-3 widths, {layers} layer(s): worst hidden error {worst_h:.2f} of the bound, logits {worst_l:.2f}, "
+          f"k/v {max(kv_err):.2f}")
 
 
 def test_graph_replayed_decode_equals_stream_decode():

@@ -115,6 +115,82 @@ def test_turbo_attention(golden, T, B, Hq, Hkv, S, D, page):
     assert (O0 == 0).all() and torch.isinf(l0).all()
 
 
+def _close_rot(O, lse, Ow, lw, dtype):
+    """North-star bound: max-abs 2e-3 on O plus one ulp of the output dtype, 1e-3 on the LSE."""
+    ulp = 2 ** -8 if dtype == torch.bfloat16 else 2 ** -11
+    err = (O.float().cpu() - Ow).abs()
+    assert (err <= 2e-3 + ulp * Ow.abs()).all(), float(err.max())
+    fin = torch.isfinite(lw)
+    assert torch.equal(torch.isfinite(lse.cpu()), fin)
+    assert ((lse.cpu() - lw)[fin].abs() <= 1e-3).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,page", [(1, 6, 2, 128, 128, 16), (2, 8, 4, 512, 128, 16), (1, 4, 2, 256, 64, 32),
+                                               (1, 24, 8, 4096, 128, 16)])
+def test_turbo_attention_rotated_basis(T, dtype, B, Hq, Hkv, S, D, page):
+    """The kernel against the oracle on the SAME rotated query (fp16 and bf16): no rotation on either
+    side, so the bound is the north-star one, not the bf16-rotation slack of the wrapper test."""
+    from flashquest_b200.kernel.sparse_turbo_fwd import sparse_decode_turbo_rotated
+    K = make_kv(71, (B, Hkv, S, D), torch.bfloat16)
+    V = make_kv(72, (B, Hkv, S, D), torch.bfloat16, outliers=())
+    Q_rot = oracle.wht_along_head_dim(make_q(73, (B, Hq, 1, D), dtype))          # rounded to dtype: both sides see these bits
+    Km, Kl, Kst, Ksr, Kmr = oracle.quantize_k_turbo(K, page)
+    Vm, Vl, Vst = oracle.quantize_v_turbo(V)
+    mask = oracle.select_pages_vectorized(oracle.page_scores_int4_fast(make_q(73, (B, Hq, 1, D), dtype), Ksr, Kmr), 0.3, 1, 1)
+    Ow, lw = oracle.sparse_attn_turbo_rotated(Q_rot, Km, Kl, Kst, Vm, Vl, Vst, selection_mask=mask, page_size=page)
+    dev = [t.cuda() for t in (Km, Kl, Kst, Vm, Vl, Vst)]
+    for n_split in (1, 3, None):
+        O, lse = sparse_decode_turbo_rotated(Q_rot.cuda(), *dev, selection_mask=mask.cuda(), page_size=page, n_split=n_split)
+        assert O.shape == (B, Hq, 1, D) and O.dtype == dtype and lse.shape == (B, Hq, 1)
+        _close_rot(O, lse, Ow, lw, dtype)
+
+
+def _student_t_kv(seed, shape, dtype, df=3, dims=(3, 17, 29, 41, 64, 77, 100, 119)):
+    """BASELINE config 2's distribution: N(0,1) with Student-t (df 3) values on 8 of the 128 channels."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    x[..., list(dims)] = rng.standard_t(df, size=shape[:-1] + (len(dims),)).astype(np.float32)
+    return torch.from_numpy(x).to(dtype)
+
+
+def test_turbo_config2_shape(T):
+    """BASELINE config 2 as stated: batch 16, 8 KV heads x 128, context 32k, page 16, retention 0.25,
+    heavy-tailed outlier channels.  Pack-on-append over the whole batch on the GPU; planes and scales
+    bit-exact against the oracle on one sequence; attention (rotated basis) against the oracle on one
+    sequence and one GQA group at the north-star bound."""
+    from flashquest_b200.eager.criticality import page_scores_int4_fast
+    from flashquest_b200.eager.selection import select_pages_vectorized
+    from flashquest_b200.kernel.sparse_turbo_fwd import sparse_decode_turbo_rotated
+    B, Hq, Hkv, S, D, page = 16, 24, 8, 32768, 128, 16
+    b_chk = 5
+    parts = []
+    for b in range(B):
+        K = _student_t_kv(500 + 2 * b, (1, Hkv, S, D), torch.bfloat16)
+        V = _student_t_kv(501 + 2 * b, (1, Hkv, S, D), torch.bfloat16)
+        got = T.kvq.quantize_k_turbo(K.cuda(), page) + T.kvq.quantize_v_turbo(V.cuda())
+        if b == b_chk:
+            want = oracle.quantize_k_turbo(K, page) + oracle.quantize_v_turbo(V)
+            for g, w, key in zip(got, want, ("Kmsb", "Klsb", "Kst", "Ksr", "Kmr", "Vmsb", "Vlsb", "Vst")):
+                assert bit_equal(g.cpu(), w), key
+            want_chk = want
+        parts.append(got)
+    Km, Kl, Kst, Ksr, Kmr, Vm, Vl, Vst = (torch.cat([p[i] for p in parts]) for i in range(8))
+    del parts
+    Q = make_q(77, (B, Hq, 1, D), torch.bfloat16)
+    Q_rot = oracle.wht_along_head_dim(Q)
+    mask = select_pages_vectorized(page_scores_int4_fast(Q.cuda(), Ksr, Kmr), 0.25, 1, 1)
+    O, lse = sparse_decode_turbo_rotated(Q_rot.cuda(), Km, Kl, Kst, Vm, Vl, Vst, selection_mask=mask, page_size=page)
+    hs = slice(6, 9)                                  # the query heads of KV head 2
+    wk = [t[:, 2:3] for t in want_chk]
+    m_ref = oracle.select_pages_vectorized(oracle.page_scores_int4_fast(Q[b_chk:b_chk + 1, hs], wk[3], wk[4]), 0.25, 1, 1)
+    assert torch.equal(mask[b_chk:b_chk + 1, hs].cpu(), m_ref)
+    Ow, lw = oracle.sparse_attn_turbo_rotated(Q_rot[b_chk:b_chk + 1, hs], wk[0], wk[1], wk[2], wk[5], wk[6], wk[7],
+                                              selection_mask=m_ref, page_size=page)
+    _close_rot(O[b_chk:b_chk + 1, hs], lse[b_chk:b_chk + 1, hs], Ow, lw, torch.bfloat16)
+
+
 def test_tail_attention_and_merge(golden, T):
     for case in golden.meta["chain"]:
         n = case["name"]

@@ -6,8 +6,8 @@ cudaMalloc/cudaFree because they stall the device, a plugin that is handed nothi
 inputs and outputs.  For them the split-K scratch sits in a fixed 4 MiB array inside the
 library.  This test drives that entry point straight through ctypes and checks that it
 returns what fq_sparse_decode_int4 returns with a caller-provided workspace, twice in a row
-(the second call finds the array dirty from the first), and that a request larger than the
-array is refused.  Collected last on purpose (file name), and independent of the other tests.
+(the second call finds the array dirty from the first), that one of the shapes also agrees
+with the CPU oracle, and that a request larger than the array is refused.  Collected last on purpose (file name), and independent of the other tests.
 """
 import ctypes
 import math
@@ -77,6 +77,16 @@ def test_static_scratch_entry_matches_workspace_entry():
             assert (O.float() - O_ref.float()).abs().max().item() <= O_TOL, (i, rep)
             assert (lse - lse_ref).abs().max().item() <= LSE_TOL, (i, rep)
         assert lib.fq_device_status() == 0
+        if i == 0:
+            # and against the CPU oracle, so that the check does not rest on the other entry point alone
+            import oracle
+            Q, Kp, Ks, Km, Vp, Vs, Vm, comp, tail = (x.cpu() for x in t)
+            Ow, lw = oracle.sparse_attn_int4(Q.unsqueeze(2), Kp, Ks, Km, Vp, Vs.unsqueeze(-1), Vm.unsqueeze(-1),
+                                             selected_page_ids=comp.unsqueeze(2), page_size=page,
+                                             K_partial=tail[0], V_partial=tail[1])
+            err = (O.float().cpu() - Ow.squeeze(2)).abs()
+            assert (err <= O_TOL + 2 ** -11 * Ow.squeeze(2).abs()).all(), float(err.max())
+            assert (lse.cpu() - lw.squeeze(2)).abs().max().item() <= LSE_TOL
     # default split count (n_split <= 0) also works
     rc, O, lse = _call(lib, True, t, B, Hq, Hkv, S, D, page, 0)
     assert rc == 0 and (O.float() - O_ref.float()).abs().max().item() <= O_TOL
