@@ -55,6 +55,16 @@ class DecodeParams(ctypes.Structure):
                 ("window", I), ("bucket", I), ("sm_scale", F), ("n_split", I)]
 
 
+class TurboCacheDesc(ctypes.Structure):
+    """struct fq_turbo_cache (include/flashquest_b200.h)."""
+    _fields_ = [("K_msb", P), ("K_lsb", P), ("V_msb", P), ("V_lsb", P),
+                ("ms_sl", L), ("ms_sb", L), ("ms_sh", L), ("ms_ss", L), ("ls_sl", L), ("ls_sb", L), ("ls_sh", L), ("ls_ss", L),
+                ("K_scale_turbo", P), ("V_scale_turbo", P), ("st_sl", L), ("st_sb", L), ("st_sh", L),
+                ("K_scale_raw", P), ("K_mn_raw", P), ("km_sl", L), ("km_sb", L), ("km_sh", L), ("km_sp", L),
+                ("K_partial", P), ("V_partial", P), ("pt_sl", L), ("pt_sb", L), ("pt_sh", L), ("pt_ss", L),
+                ("kv_dtype", I), ("L", I), ("B", I), ("Hkv", I), ("D", I), ("page", I), ("max_seq_len", I)]
+
+
 class AwqLinearDesc(ctypes.Structure):
     """struct fq_awq_linear."""
     _fields_ = [("qweight", P), ("scales", P), ("qzeros", P), ("bias", P), ("K", I), ("N", I)]
@@ -110,6 +120,10 @@ _PROTOTYPES["fq_gemv_f16"] = (I, [P, P, I, I, I, P, P])
 _PROTOTYPES["fq_argmax_f16"] = (I, [P, L, I, P, P])
 
 _PROTOTYPES["fq_decode_step_int4_dev"] = _PROTOTYPES["fq_decode_step_int4"]
+_PROTOTYPES["fq_decode_layer_turbo_scratch_bytes"] = (Z, [I, I, I])
+_PROTOTYPES["fq_decode_layer_turbo"] = (I, [ctypes.POINTER(TurboCacheDesc), I, I, P, P, L, L, L, I, P, I, L, L,
+                                           ctypes.POINTER(DecodeParams), P, P, P, Z, P, P, P, Z, P])
+_PROTOTYPES["fq_prefill_attention"] = (I, [P, L, L, L, P, L, L, L, P, L, L, L, I, I, I, I, I, I, I, F, P, L, L, L, P])
 
 # entry points added by later sources register themselves here (name -> (restype, argtypes))
 EXTRA_PROTOTYPES: dict = {}

@@ -9,11 +9,12 @@ constructor argument (default bf16 as in the reference).
 from __future__ import annotations
 
 import torch
+from transformers.cache_utils import Cache
 
 from ..kernel.kv_quant import quantize_kv_int4_into
 
 
-class PersistentInt4KVCache:
+class PersistentInt4KVCache(Cache):
     kv_bits = 4
 
     def __init__(self, *, batch_size: int, num_layers: int, num_kv_heads: int, head_dim: int,

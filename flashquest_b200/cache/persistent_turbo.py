@@ -4,11 +4,12 @@ and error behaviour; the append is three launches and allocates nothing)."""
 from __future__ import annotations
 
 import torch
+from transformers.cache_utils import Cache
 
 from ..kernel.kv_quant import quantize_kv_int4_into, quantize_turbo_into
 
 
-class PersistentTurboKVCache:
+class PersistentTurboKVCache(Cache):
     kv_bits = 3
 
     def __init__(self, *, batch_size: int, num_layers: int, num_kv_heads: int, head_dim: int,

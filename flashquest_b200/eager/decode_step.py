@@ -14,7 +14,7 @@ import math
 
 import torch
 
-from .._lib import DecodeParams, Int4CacheDesc, check, dtype_code, lib, ptr, stream_ptr
+from .._lib import DecodeParams, Int4CacheDesc, TurboCacheDesc, check, dtype_code, lib, ptr, stream_ptr
 
 
 class QuestDecodeInt4:
@@ -75,10 +75,22 @@ class QuestDecodeInt4:
             self.Hq, self.retention_per_q.data_ptr() if self.retention_per_q is not None else None, self.retention,
             self.k_max_static, self.num_sinks, self.window_pages, self.bucket, self.sm_scale, self.n_split)
 
-    def step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor, layer_idx: int):
+    def params_for(self, head_pattern_layer: torch.Tensor):
+        """fq_decode_params of one layer whose retrieval / streaming KV heads are given by
+        head_pattern_layer (H_kv,) bool: retrieval heads keep `retention`, streaming heads 0
+        (eager/llama_persistent_patch.py:214-219).  Returns (struct, tensor kept alive by the caller)."""
+        n_rep = self.Hq // self.Hkv
+        pat = head_pattern_layer.to(self.device).bool().repeat_interleave(n_rep)
+        r = torch.where(pat, torch.full((self.Hq,), self.retention, device=self.device),
+                        torch.zeros(self.Hq, device=self.device)).float().contiguous()
+        return DecodeParams(self.Hq, r.data_ptr(), self.retention, self.k_max_static, self.num_sinks, self.window_pages,
+                            self.bucket, self.sm_scale, self.n_split), r
+
+    def step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor, layer_idx: int, prm=None):
         """Append k_new, v_new (B,H_kv,n,D) to the layer and attend with q (B,H_q,1,D) in ONE
         foreign call (fq_decode_layer_int4): what cache.update_quantized followed by attend()
-        does, without the per-call slicing.  Tensors must have the cache's dtype."""
+        does, without the per-call slicing.  Tensors must have the cache's dtype.  `prm`: a
+        per-layer fq_decode_params (params_for) instead of the engine's own."""
         c = self.cache
         if layer_idx < 0 or layer_idx >= c.num_layers:
             raise IndexError(f"layer_idx {layer_idx} out of range [0, {c.num_layers})")
@@ -95,7 +107,7 @@ class QuestDecodeInt4:
         check(lib().fq_decode_layer_int4(
             ctypes.byref(self._cdesc), layer_idx, seen,
             ptr(k_new), ptr(v_new), k_new.stride(0), k_new.stride(1), k_new.stride(2), n_new,
-            ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1), ctypes.byref(self._prm),
+            ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1), ctypes.byref(prm if prm is not None else self._prm),
             ptr(self.scores[layer_idx]), ptr(self.compact[layer_idx]), ptr(O), ptr(lse),
             ptr(self.workspace[layer_idx]), self.workspace.shape[1], stream_ptr(self.device)))
         c._seen_tokens[layer_idx] = seen + n_new
@@ -226,4 +238,80 @@ class QuestDecodeInt4:
             ptr(O), O.stride(0), O.stride(1), ptr(lse),
             ptr(self.workspace[li]), self.workspace.shape[1], self.n_split, st))
         self.launches += 1
+        return O.unsqueeze(2), lse.unsqueeze(2)
+
+
+class QuestDecodeTurbo:
+    """Decode-branch dispatcher for the persistent TurboQuant (K3-V3) cache: the kv_bits == 3 route of
+    make_quest_persistent_forward (flashquest/eager/llama_persistent_patch.py:93-115,202-245) as ONE
+    foreign call per layer (fq_decode_layer_turbo): append, page scores from the raw page metadata,
+    top-k + compact index, rotation of Q, sparse attention in the rotated basis, rotation of O, tail
+    attention and LSE merge.  All buffers are preallocated."""
+
+    def __init__(self, cache, *, num_q_heads: int, retention: float = 0.20, num_sinks: int = 4, window_pages: int = 2,
+                 q_dtype=torch.bfloat16, n_split: int | None = None):
+        if getattr(cache, "kv_bits", None) != 3:
+            raise NotImplementedError(f"QuestDecodeTurbo only supports kv_bits=3; got {getattr(cache, 'kv_bits', None)}")
+        if not (0.0 <= float(retention) <= 1.0):
+            raise ValueError(f"scalar retention must be in [0, 1]; got {retention}")
+        self.cache = cache
+        self.Hq, self.Hkv = num_q_heads, cache.num_kv_heads
+        if self.Hq % self.Hkv != 0:
+            raise ValueError(f"H_q={self.Hq} must be divisible by H_kv={self.Hkv}")
+        self.D, self.page, self.B = cache.head_dim, cache.page_size, cache.batch_size
+        if self.page % 16 != 0:
+            raise NotImplementedError(f"the TurboQuant attention kernel needs page_size a multiple of 16; got {self.page}")
+        self.retention, self.num_sinks, self.window_pages = float(retention), int(num_sinks), int(window_pages)
+        P_max = cache.max_seq_len // self.page
+        self.k_max_static = math.ceil(self.retention * P_max)
+        self.bucket = max(1, self.k_max_static + self.num_sinks + self.window_pages)
+        dev = cache.K_msb.device
+        self.device, self.q_dtype = dev, q_dtype
+        self.sm_scale = 1.0 / math.sqrt(self.D)
+        self.scores = torch.empty(self.B, self.Hq, max(P_max, 1), dtype=torch.float32, device=dev)
+        self.compact = torch.empty(self.B, self.Hq, self.bucket, dtype=torch.int32, device=dev)
+        self.O = torch.empty(cache.num_layers, self.B, self.Hq, self.D, dtype=q_dtype, device=dev)
+        self.lse = torch.empty(cache.num_layers, self.B, self.Hq, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            self.n_split = n_split or max(1, min(lib().fq_sparse_decode_default_splits(self.B, self.Hq, self.bucket, self.page), 64))
+            self.scratch = torch.empty(lib().fq_decode_layer_turbo_scratch_bytes(self.B, self.Hq, self.D), dtype=torch.uint8, device=dev)
+            self.workspace = torch.zeros(max(lib().fq_sparse_decode_workspace_bytes(self.B, self.Hq, self.D, self.n_split), 256),
+                                         dtype=torch.uint8, device=dev)
+        c = cache
+        self._cdesc = TurboCacheDesc(
+            c.K_msb.data_ptr(), c.K_lsb.data_ptr(), c.V_msb.data_ptr(), c.V_lsb.data_ptr(),
+            *c.K_msb.stride()[:4], *c.K_lsb.stride()[:4],
+            c.K_scale_turbo.data_ptr(), c.V_scale_turbo.data_ptr(), *c.K_scale_turbo.stride()[:3],
+            c.K_scale_raw.data_ptr(), c.K_mn_raw.data_ptr(), *c.K_scale_raw.stride()[:4],
+            c.K_partial.data_ptr(), c.V_partial.data_ptr(), *c.K_partial.stride()[:4],
+            dtype_code(c.K_partial), c.num_layers, self.B, self.Hkv, self.D, self.page, c.max_seq_len)
+        self._prm = DecodeParams(self.Hq, None, self.retention, self.k_max_static, self.num_sinks, self.window_pages,
+                                 self.bucket, self.sm_scale, self.n_split)
+        self.launches = 0
+
+    params_for = QuestDecodeInt4.params_for
+
+    def step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor, layer_idx: int, prm=None):
+        """Append k_new, v_new (B,H_kv,n,D) and attend with q (B,H_q,1,D) (raw basis): (O (B,H_q,1,D), lse (B,H_q,1))."""
+        c = self.cache
+        if layer_idx < 0 or layer_idx >= c.num_layers:
+            raise IndexError(f"layer_idx {layer_idx} out of range [0, {c.num_layers})")
+        seen = c._seen_tokens[layer_idx]
+        n_new = k_new.shape[2]
+        if seen + n_new > c.max_seq_len:
+            raise RuntimeError(f"PersistentTurboKVCache: seen+new={seen + n_new} exceeds max_seq_len={c.max_seq_len}")
+        if k_new.dtype != c.dtype or v_new.dtype != c.dtype:
+            k_new, v_new = k_new.to(c.dtype), v_new.to(c.dtype)
+        if k_new.stride(3) != 1 or v_new.stride() != k_new.stride():
+            k_new, v_new = k_new.contiguous(), v_new.contiguous()
+        q3 = q.reshape(self.B, self.Hq, self.D).contiguous()
+        O, lse = self.O[layer_idx], self.lse[layer_idx]
+        check(lib().fq_decode_layer_turbo(
+            ctypes.byref(self._cdesc), layer_idx, seen,
+            ptr(k_new), ptr(v_new), k_new.stride(0), k_new.stride(1), k_new.stride(2), n_new,
+            ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1), ctypes.byref(prm if prm is not None else self._prm),
+            ptr(self.scores), ptr(self.compact), ptr(self.scratch), self.scratch.numel(), ptr(O), ptr(lse),
+            ptr(self.workspace), self.workspace.numel(), stream_ptr(self.device)))
+        c._seen_tokens[layer_idx] = seen + n_new
+        self.launches += 10
         return O.unsqueeze(2), lse.unsqueeze(2)

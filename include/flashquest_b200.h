@@ -139,6 +139,25 @@ int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
                      int32_t* compact, int64_t cp_sr, int bucket, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Dense causal attention of the prefill branch (S_q > 1).
+ * Replaces the torch.nn.functional.scaled_dot_product_attention(q, K_full, V_full,
+ * is_causal=True, enable_gqa=True) call of the patched forward
+ * (eager/llama_persistent_patch.py:196-201), where K_full / V_full are the dequantised
+ * completed pages followed by the staged tail.  The causal mask is aligned at the top left,
+ * as torch aligns it when S_q != S_kv: query i attends keys 0..i.  Tensor-core kernel
+ * (mma.sync, fp32 accumulation, softmax in fp32).
+ *   Q (B,Hq,Sq,D), K,V (B,Hkv,Skv,D), O (B,Hq,Sq,D): all `dtype` (F16|BF16), element strides
+ *   *_sb,*_sh,*_ss (head_dim contiguous; pass O's strides to write a (B,Sq,Hq*D) buffer).
+ * D in {64,128}; Q/K/V rows 16-byte aligned.
+ */
+int fq_prefill_attention(
+    const void* Q, int64_t q_sb, int64_t q_sh, int64_t q_ss,
+    const void* K, int64_t k_sb, int64_t k_sh, int64_t k_ss,
+    const void* V, int64_t v_sb, int64_t v_sh, int64_t v_ss,
+    int dtype, int B, int Hq, int Hkv, int Sq, int Skv, int D, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, int64_t o_ss, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Sparse decode attention over selected packed INT4 pages (GQA, split-K, LSE merge).
  * Replaces flash_attn_sparse_int4_fwd_compact (kernel/sparse_int4_fwd_compact.py:153-244)
  * and, with a compact list built from the mask, flash_attn_sparse_int4_fwd
@@ -330,6 +349,41 @@ int fq_decode_layer_int4(
     const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
     const fq_decode_params* params,
     float* scores, int32_t* compact, void* O, float* lse,
+    void* workspace, size_t workspace_bytes, void* stream);
+
+/* One decode step of one layer on a persistent TurboQuant K3-V3 cache, in one host call: what the
+ * reference's patched forward does for cache.kv_bits == 3 (eager/llama_persistent_patch.py:93-115,
+ * 193-245): PersistentTurboKVCache.update_quantized (cache/persistent_turbo.py:83-147),
+ * page_scores_int4_fast on K_scale_raw / K_mn_raw, select_pages_vectorized +
+ * build_compact_selection, flash_attn_sparse_turbo_fwd (with the rotation of Q before and of O
+ * after the kernel, kernel/sparse_turbo_fwd.py:305,343-344), _bf16_dense_attn_with_lse over the
+ * staged tokens and _merge_two_attentions.
+ * fq_turbo_cache describes the storage of PersistentTurboKVCache (cache/persistent_turbo.py:46-66)
+ * like fq_int4_cache does for the INT4 cache; both msb planes share one set of strides, both lsb
+ * planes another, both token scales a third.  Q and O are dense (B,Hq,D) in the RAW basis;
+ * scores (B,Hq,P) and compact (B,Hq,bucket) are scratch; `scratch` holds
+ * fq_decode_layer_turbo_scratch_bytes(B,Hq,D) bytes (rotated Q and O, the two partial results);
+ * workspace / n_split as for fq_sparse_decode_turbo.  page must be a multiple of 16. */
+typedef struct fq_turbo_cache {
+    uint8_t* K_msb; uint8_t* K_lsb; uint8_t* V_msb; uint8_t* V_lsb;   /* (L,B,H,S,D/8) and (L,B,H,S,D/4) u8 */
+    int64_t ms_sl, ms_sb, ms_sh, ms_ss;            /* msb planes, bytes */
+    int64_t ls_sl, ls_sb, ls_sh, ls_ss;            /* lsb planes, bytes */
+    void* K_scale_turbo; void* V_scale_turbo;      /* (L,B,H,S) bf16, token stride 1 */
+    int64_t st_sl, st_sb, st_sh;
+    void* K_scale_raw; void* K_mn_raw;             /* (L,B,H,P,D) bf16 */
+    int64_t km_sl, km_sb, km_sh, km_sp;
+    void* K_partial; void* V_partial;              /* (L,B,H,page,D) kv_dtype */
+    int64_t pt_sl, pt_sb, pt_sh, pt_ss;
+    int kv_dtype;                                  /* FQ_F16 | FQ_BF16 */
+    int L, B, Hkv, D, page, max_seq_len;
+} fq_turbo_cache;
+size_t fq_decode_layer_turbo_scratch_bytes(int B, int Hq, int D);
+int fq_decode_layer_turbo(
+    const fq_turbo_cache* cache, int layer, int seen,
+    const void* K_new, const void* V_new, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new,
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const fq_decode_params* params,
+    float* scores, int32_t* compact, void* scratch, size_t scratch_bytes, void* O, float* lse,
     void* workspace, size_t workspace_bytes, void* stream);
 
 /* fq_decode_layer_int4 for layers [0, n_layers) in one foreign call — the layer loop of the
