@@ -123,6 +123,11 @@ _PROTOTYPES["fq_decode_step_int4_dev"] = _PROTOTYPES["fq_decode_step_int4"]
 _PROTOTYPES["fq_decode_layer_turbo_scratch_bytes"] = (Z, [I, I, I])
 _PROTOTYPES["fq_decode_layer_turbo"] = (I, [ctypes.POINTER(TurboCacheDesc), I, I, P, P, L, L, L, I, P, I, L, L,
                                            ctypes.POINTER(DecodeParams), P, P, P, Z, P, P, P, Z, P])
+_PROTOTYPES["fq_lse_merge_strided"] = (I, [P, L, P, L, I, I, L, I, P, P, P])
+_PROTOTYPES["fq_ctx_scratch_bytes"] = (Z, [I, I, I, I, I, I])
+_PROTOTYPES["fq_ctx_local_candidates"] = (I, [P, I, L, L, P, P, L, L, L, I, I, I, I, I, I, I, I, I, P, Z, P, P])
+_PROTOTYPES["fq_ctx_select_attend"] = (I, [P, I, I, I, I, I, I, I, I, P, I, L, L, P, L, L, P, P, L, L, L, P, L, L, P, P, L, L,
+                                          P, P, I, L, L, L, I, I, I, I, I, I, F, I, P, Z, P, P, P, Z, I, P])
 _PROTOTYPES["fq_prefill_attention"] = (I, [P, L, L, L, P, L, L, L, P, L, L, L, I, I, I, I, I, I, I, F, P, L, L, L, P])
 
 # entry points added by later sources register themselves here (name -> (restype, argtypes))

@@ -20,6 +20,8 @@ on CPU ranks with the `gloo` backend.
 """
 from __future__ import annotations
 
+import ctypes
+import math
 from dataclasses import dataclass
 from typing import Callable, Optional
 
@@ -111,8 +113,13 @@ def select_pages_context_split(scores_local: torch.Tensor, *, P_global: int, ret
             ids[:, :, :n_c] = (order + lo).to(torch.int32)
         cand[:, :, 1] = ids.view(torch.float32)                    # page ids travel bit-cast in the same message
         gathered = _all_gather(cand, group)                        # (G,B,H,2,k_c), rank-major = ascending page id
-        g_scores = gathered[:, :, :, 0].permute(1, 2, 0, 3).reshape(B, H, 1, world * k_c).contiguous()
+        g_scores = gathered[:, :, :, 0].permute(1, 2, 0, 3).reshape(B, H, world * k_c)
         g_ids = gathered[:, :, :, 1].contiguous().view(torch.int32).permute(1, 2, 0, 3).reshape(B, H, world * k_c)
+        # padding slots (id -1, score -inf) go behind every real candidate, keeping the ascending page order of
+        # the rest: a page whose real score is -inf must win a tie against a slot that holds no page
+        order = torch.sort((g_ids < 0).to(torch.uint8), dim=-1, stable=True).indices
+        g_scores = torch.gather(g_scores, -1, order).unsqueeze(2).contiguous()
+        g_ids = torch.gather(g_ids, -1, order)
         win = ops.top_k_mask(g_scores, min(k, world * k_c))[:, :, 0]                           # (B,H,G*k_c)
         mine = win & (g_ids >= lo) & (g_ids < hi)
         # winners of other ranks go to a spare column past the end
@@ -188,3 +195,116 @@ def decode_context_split_int4(Q, K_packed, K_scale, K_mn, V_packed, V_scale, V_m
     out = merge_context_split(O_r, lse_r, group=group)
     mark("merged")
     return out
+
+
+class ContextSplitInt4:
+    """The same decode step with everything preallocated and the device work in three foreign calls
+    (fq_ctx_local_candidates, fq_ctx_select_attend, fq_lse_merge_strided) around the two all-gathers,
+    so that a whole layer-step — collectives included — can be captured in ONE CUDA graph and
+    replayed without host work.  Scalar retention only.  One instance serves one (shape, group)."""
+
+    def __init__(self, *, batch_size: int, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, P_global: int,
+                 retention: float, num_sinks: int, window_pages: int, k_max_static: Optional[int] = None,
+                 q_dtype=torch.float16, group=None, device=None, n_split: Optional[int] = None):
+        from .._lib import lib
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.B, self.Hq, self.Hkv, self.D, self.page = batch_size, num_q_heads, num_kv_heads, head_dim, page_size
+        self.P_global, self.sinks, self.window = int(P_global), int(num_sinks), int(window_pages)
+        self.lo, self.hi = page_range(self.rank, self.world, self.P_global)
+        self.P_local = self.hi - self.lo
+        self.k = global_k(float(retention), self.P_global, k_max_static)
+        p_max = max(page_range(r, self.world, self.P_global)[1] - page_range(r, self.world, self.P_global)[0] for r in range(self.world))
+        self.k_c = max(1, min(self.k, p_max))
+        self.bucket_local = max(1, min(self.P_local, self.k + self.sinks + self.window))
+        dev = torch.device(device if device is not None else torch.cuda.current_device())
+        self.device, self.q_dtype = dev, q_dtype
+        self.sm_scale = 1.0 / math.sqrt(head_dim)
+        rows = batch_size * num_q_heads
+        L = lib()
+        with torch.cuda.device(dev):
+            self.n_split = n_split or L.fq_sparse_decode_default_splits(batch_size, num_q_heads, self.bucket_local, page_size)
+            self.scratch = torch.empty(L.fq_ctx_scratch_bytes(batch_size, num_q_heads, self.world, self.k_c, self.P_local, self.bucket_local),
+                                       dtype=torch.uint8, device=dev)
+            self.workspace = torch.zeros(max(L.fq_sparse_decode_workspace_bytes(batch_size, num_q_heads, head_dim, self.n_split), 256),
+                                         dtype=torch.uint8, device=dev)
+        self.msg = torch.empty(batch_size, num_q_heads, 2, self.k_c, dtype=torch.float32, device=dev)
+        self.gathered = torch.empty(self.world, batch_size, num_q_heads, 2, self.k_c, dtype=torch.float32, device=dev)
+        self.o_bytes = rows * head_dim * 2
+        self.msg2 = torch.empty(self.o_bytes + rows * 4, dtype=torch.uint8, device=dev)
+        self.gathered2 = torch.empty(self.world, self.msg2.numel(), dtype=torch.uint8, device=dev)
+        self.O = torch.empty(batch_size, num_q_heads, head_dim, dtype=q_dtype, device=dev)
+        self.lse = torch.empty(batch_size, num_q_heads, dtype=torch.float32, device=dev)
+
+    def step(self, q, K_packed, K_scale, K_mn, V_packed, V_scale, V_mn, K_partial=None, V_partial=None, marks=None):
+        """q (B,H_q,1,D) (same on every rank); K/V tensors: this rank's page range, laid out as for
+        flash_attn_sparse_int4_fwd_compact (contiguous; V_scale / V_mn (B,H_kv,S_local[,1])); the staged tail on
+        the last rank only.  Returns (O (B,H_q,1,D), lse (B,H_q,1)), identical on every rank.  `marks`: an
+        optional callable(name) invoked between the phases (e.g. to record CUDA events)."""
+        from .._lib import check, dtype_code, lib, ptr, stream_ptr
+        L = lib()
+        st = stream_ptr(self.device)
+        B, Hq, Hkv, D = self.B, self.Hq, self.Hkv, self.D
+        q3 = q.reshape(B, Hq, D)
+        if q3.dtype != self.q_dtype or not q3.is_contiguous():
+            q3 = q3.to(self.q_dtype).contiguous()
+        Vs = V_scale.squeeze(-1) if V_scale.dim() == 4 else V_scale
+        Vm = V_mn.squeeze(-1) if V_mn.dim() == 4 else V_mn
+        mark = marks or (lambda name: None)
+        mark("start")
+        check(L.fq_ctx_local_candidates(
+            ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1), ptr(K_scale), ptr(K_mn), *K_scale.stride()[:3],
+            B, Hq, Hkv, self.P_local, D, self.lo, self.k_c, self.world, self.bucket_local,
+            ptr(self.scratch), self.scratch.numel(), ptr(self.msg), st))
+        mark("candidates")
+        dist.all_gather_into_tensor(self.gathered, self.msg, group=self.group)
+        mark("gathered")
+        tail_len, tl, tcode, Kt, Vt = 0, (0, 0, 0), 2, None, None
+        if K_partial is not None and K_partial.shape[2] > 0:
+            Kt, Vt = K_partial, V_partial
+            if Kt.stride(3) != 1 or Kt.stride() != Vt.stride():
+                Kt, Vt = Kt.contiguous(), Vt.contiguous()
+            tail_len, tl, tcode = Kt.shape[2], Kt.stride()[:3], dtype_code(Kt)
+        lse_ptr = ctypes.c_void_p(self.msg2.data_ptr() + self.o_bytes)
+        check(L.fq_ctx_select_attend(
+            ptr(self.gathered), self.world, self.k_c, self.k, self.sinks, self.window, self.lo, self.hi, self.P_global,
+            ptr(q3), dtype_code(q3), q3.stride(0), q3.stride(1),
+            ptr(K_packed), K_packed.stride(0), K_packed.stride(1), ptr(K_scale), ptr(K_mn), *K_scale.stride()[:3],
+            ptr(V_packed), V_packed.stride(0), V_packed.stride(1), ptr(Vs), ptr(Vm), Vs.stride(0), Vs.stride(1),
+            ptr(Kt), ptr(Vt), tcode, *tl, tail_len,
+            B, Hq, Hkv, D, self.page, self.sm_scale, self.bucket_local,
+            ptr(self.scratch), self.scratch.numel(), ptr(self.msg2), lse_ptr,
+            ptr(self.workspace), self.workspace.numel(), self.n_split, st))
+        mark("attended")
+        dist.all_gather_into_tensor(self.gathered2, self.msg2, group=self.group)
+        mark("gathered2")
+        n2 = self.msg2.numel()
+        check(L.fq_lse_merge_strided(
+            ptr(self.gathered2), n2 // 2, ctypes.c_void_p(self.gathered2.data_ptr() + self.o_bytes), n2 // 4,
+            dtype_code(self.O), self.world, B * Hq, D, ptr(self.O), ptr(self.lse), st))
+        mark("merged")
+        return self.O.unsqueeze(2), self.lse.unsqueeze(2)
+
+    def local_mask(self) -> torch.Tensor:
+        """The bool mask (B,H_q,1,P_local) of the pages this rank attended in the last step (a view of the
+        scratch buffer; the layout is the one fq_ctx_scratch_bytes sums up)."""
+        pad = lambda x: (x + 255) // 256 * 256
+        rows, n, pl = self.B * self.Hq, self.world * self.k_c, max(self.P_local, 1)
+        off = pad(rows * pl * 4) + pad(rows * self.k_c * 4) + 2 * pad(rows * n * 4) + pad(rows * n)
+        return self.scratch[off: off + rows * self.P_local].view(self.B, self.Hq, 1, self.P_local).bool()
+
+    def capture(self, *args, **kwargs):
+        """CUDA graph of step(*args) for static input tensors (collectives included); returns replay()
+        -> (O, lse).  One ordinary step runs first (lazy kernel attributes, NCCL set-up)."""
+        self.step(*args, **kwargs)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            out = self.step(*args, **kwargs)
+
+        def replay():
+            graph.replay()
+            return out
+
+        replay.graph = graph
+        return replay

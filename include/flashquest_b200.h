@@ -282,6 +282,51 @@ int fq_sparse_decode_turbo(
 int fq_lse_merge(const void* O_parts, const float* lse_parts, int dtype, int n, int64_t rows, int D,
                  void* O, float* lse, void* stream);
 
+/* fq_lse_merge with strided parts: part i of row r starts at O_parts + i*o_part_stride + r*D
+ * (elements of dtype) and lse_parts + i*lse_part_stride + r (floats), e.g. messages gathered
+ * from several GPUs that each hold (O, lse) back to back. */
+int fq_lse_merge_strided(const void* O_parts, int64_t o_part_stride, const float* lse_parts, int64_t lse_part_stride,
+                         int dtype, int n, int64_t rows, int D, void* O, float* lse, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Context split: ONE long sequence whose pages are split over G GPUs by contiguous range (rank r
+ * owns pages [lo, hi) with their packed codes and metadata; Q is replicated).  Not in the
+ * reference, which is single-GPU; the result equals the single-GPU result of
+ * select_pages_vectorized (eager/selection.py:65-126) + flash_attn_sparse_int4_fwd_compact
+ * (kernel/sparse_int4_fwd_compact.py:153-244) + tail + merge over the whole sequence.  Per decode
+ * step and layer the host runs, on every rank,
+ *   fq_ctx_local_candidates -> all-gather of msg -> fq_ctx_select_attend -> all-gather of
+ *   (O, lse) -> fq_lse_merge_strided,
+ * with both all-gathers delivering into this rank's own memory (e.g. ncclAllGather); none of the
+ * kernels reads another GPU's memory.  All three calls only enqueue work on `stream` and can be
+ * captured in a CUDA graph together with the collectives.
+ *   k_global = the single-GPU k (clamp(ceil(fp32(retention)*P_global), 0, P_global), capped by
+ *   the static k_max); k_c = min(k_global, largest page count of any rank) candidate slots per
+ *   rank and head; bucket_local = min(P_local, k_global + sinks + window).
+ *   msg (B,Hq,2,k_c) fp32: scores and (bit-cast) global page ids of this rank's candidates;
+ *   gathered (G,B,Hq,2,k_c): all ranks' messages in rank order.
+ *   O_msg (B,Hq,D) q_dtype and lse_msg (B,Hq) fp32: this rank's partial result, to be gathered.
+ *   scratch: fq_ctx_scratch_bytes(B,Hq,G,k_c,P_local,bucket_local) bytes, the same buffer for
+ *   both calls; workspace / n_split as for fq_sparse_decode_int4.
+ * Scalar retention only.  K_tail / V_tail: the staged tokens, on the last rank only. */
+size_t fq_ctx_scratch_bytes(int B, int Hq, int G, int k_c, int P_local, int bucket_local);
+int fq_ctx_local_candidates(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int B, int Hq, int Hkv, int P_local, int D, int lo, int k_c, int G, int bucket_local,
+    void* scratch, size_t scratch_bytes, float* msg, void* stream);
+int fq_ctx_select_attend(
+    const float* gathered, int G, int k_c, int k_global, int sinks, int window, int lo, int hi, int P_global,
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
+    int B, int Hq, int Hkv, int D, int page, float sm_scale, int bucket_local,
+    void* scratch, size_t scratch_bytes, void* O_msg, float* lse_msg,
+    void* workspace, size_t workspace_bytes, int n_split, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * AWQ W4A16 GEMV, several projections of the same input fused in one launch.
  * Replaces fused_qkv_proj / fused_gate_up_proj (kernel/fused_proj.py:18-53), which in the

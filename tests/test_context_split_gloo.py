@@ -48,7 +48,13 @@ def _worker(rank, world, port, case, out_q):
         Kp, Ks, Km = oracle.quantize_k_int4(k, page)
         Vp, Vs, Vm = oracle.quantize_v_int4(v)
         scores = oracle.page_scores_int4_fast(q, Ks, Km)                     # (B,Hq,1,P)
-        if ties:
+        if ties == "inf":
+            # -inf and NaN scores: a page whose score is -inf must still beat an empty candidate slot of a rank
+            # that has fewer pages than slots, and a NaN ranks above everything (as in torch.topk)
+            scores = scores.clone()
+            scores[..., 3:] = float("-inf")
+            scores[..., 1] = float("nan")
+        elif ties:
             scores = (scores * 2).round() / 2                                # many equal scores
         ref_mask = oracle.select_pages_vectorized(scores, retention, sinks, window)
         lo, hi = cs.page_range(rank, world, P)
@@ -81,6 +87,7 @@ CASES = [
     (2, 4, 2, 800, 64, 16, 0.5, 4, 2, True),       # P = 50 does not divide by 3; forced pages span ranks
     (1, 2, 1, 256, 64, 16, 1.0, 0, 0, False),      # everything selected
     (1, 2, 1, 256, 64, 16, 0.0, 2, 1, True),       # only forced pages: most ranks attend nothing
+    (1, 2, 1, 112, 64, 16, 0.7, 0, 0, "inf"),      # P = 7, k = 5: more slots than pages on one rank, -inf and NaN scores
 ]
 
 

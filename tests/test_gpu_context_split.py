@@ -57,6 +57,21 @@ def _worker(rank, world, port, out_q):
         torch.cuda.synchronize()
         out_q.put((rank, bool(torch.equal(local_mask, ref_mask[..., lo:hi])),
                    (O.float() - O_ref.float()).abs().max().item(), (lse - lse_ref).abs().max().item()))
+        # the preallocated, graph-captured form of the same step
+        dec = cs.ContextSplitInt4(batch_size=B, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D, page_size=page, P_global=P,
+                                  q_dtype=torch.float16, device="cuda", **kw)
+        loc = (q, Kp[:, :, sl].contiguous(), Ks[:, :, lo:hi].contiguous(), Km[:, :, lo:hi].contiguous(),
+               Vp[:, :, sl].contiguous(), Vs[:, :, sl].contiguous(), Vm[:, :, sl].contiguous())
+        tail = dict(K_partial=kt if last else None, V_partial=vt if last else None)
+        O2, lse2 = dec.step(*loc, **tail)
+        torch.cuda.synchronize()
+        ok2 = bool(torch.equal(dec.local_mask(), ref_mask[..., lo:hi]))
+        e2 = ((O2.float() - O_ref.float()).abs().max().item(), (lse2 - lse_ref).abs().max().item())
+        replay = dec.capture(*loc, **tail)
+        for _ in range(3):
+            O3, lse3 = replay()
+        torch.cuda.synchronize()
+        out_q.put((rank + 100, ok2 and bool(torch.equal(O3, O2)) and bool(torch.equal(lse3, lse2)), e2[0], e2[1]))
     finally:
         dist.destroy_process_group()
 
@@ -73,6 +88,6 @@ def test_two_gpu_context_split_matches_single_gpu():
     for p in procs:
         p.join(300)
         assert p.exitcode == 0
-    for rank, ok, err, err_l in sorted(out_q.get(timeout=5) for _ in range(2)):
-        assert ok, f"rank {rank}: mask differs"
+    for rank, ok, err, err_l in sorted(out_q.get(timeout=5) for _ in range(4)):
+        assert ok, f"rank {rank % 100}: {'graph-captured step: page set or replay' if rank >= 100 else 'mask'} differs"
         assert err <= 2e-3 and err_l <= 1e-3, (rank, err, err_l)   # fp16 partial outputs
