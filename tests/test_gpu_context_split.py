@@ -18,11 +18,28 @@ def _free_port():
 
 
 def _worker(rank, world, port, out_q):
+    import datetime
+    import traceback
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    # a short collective timeout: a rank that fails must not leave its peer waiting for minutes
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=60))
     try:
+        _worker_body(rank, world, out_q, dist)
+    except Exception:
+        out_q.put((rank + 1000, False, traceback.format_exc(), 0.0))
+        raise
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def _worker_body(rank, world, out_q, dist):
+    if True:
         from flashquest_b200.eager import context_split as cs
         from flashquest_b200.eager.criticality import page_scores_int4_fast
         from flashquest_b200.eager.selection import build_compact_selection, select_pages_vectorized
@@ -72,8 +89,6 @@ def _worker(rank, world, port, out_q):
             O3, lse3 = replay()
         torch.cuda.synchronize()
         out_q.put((rank + 100, ok2 and bool(torch.equal(O3, O2)) and bool(torch.equal(lse3, lse2)), e2[0], e2[1]))
-    finally:
-        dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
@@ -85,9 +100,20 @@ def test_two_gpu_context_split_matches_single_gpu():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, out_q)) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(300)
-        assert p.exitcode == 0
-    for rank, ok, err, err_l in sorted(out_q.get(timeout=5) for _ in range(4)):
+    results = []
+    try:
+        for _ in range(4):
+            item = out_q.get(timeout=150)
+            assert item[0] < 1000, f"rank {item[0] - 1000} raised:\n{item[2]}"
+            results.append(item)
+        for p in procs:
+            p.join(60)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:                      # never leave a worker behind on the GPUs
+            if p.is_alive():
+                p.kill()
+                p.join(10)
+    for rank, ok, err, err_l in sorted(results):
         assert ok, f"rank {rank % 100}: {'graph-captured step: page set or replay' if rank >= 100 else 'mask'} differs"
         assert err <= 2e-3 and err_l <= 1e-3, (rank, err, err_l)   # fp16 partial outputs
