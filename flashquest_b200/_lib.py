@@ -98,6 +98,7 @@ _PROTOTYPES["fq_llama_decode_step_dev"] = _PROTOTYPES["fq_llama_decode_step"]
 _PROTOTYPES["fq_awq_gemv_workspace_bytes"] = (Z, [I, I, I])
 _PROTOTYPES["fq_awq_gemv_default_splits"] = (I, [I, I, I])
 _PROTOTYPES["fq_awq_gemv"] = (I, [P, I, I, I, I, P, P, P, P, P, P, I, P, Z, I, P])
+_PROTOTYPES["fq_awq_gemm"] = (I, [P, I, I, I, I, P, P, P, P, P, P, I, P])
 _PROTOTYPES["fq_wht"] = (I, [P, P, I, L, I, P])
 _PROTOTYPES["fq_quantize_turbo"] = (I, [P, L, L, L, I, P, L, L, L, I, I, I, I, I, I, P, L, L, L, P, L, L, L, P, L, L, L, P])
 _PROTOTYPES["fq_dequantize_turbo"] = (I, [P, L, L, L, P, L, L, L, P, L, L, L, I, I, I, I, P, L, L, L, P])

@@ -1,8 +1,9 @@
-"""Fused AWQ projections for decode — counterpart of flashquest/kernel/fused_proj.py:18-53.
+"""Fused AWQ projections — counterpart of flashquest/kernel/fused_proj.py:18-53.
 
 The reference calls the q/k/v (or gate/up) AutoAWQ modules one after the other; here the
-projections that share one input run in ONE launch of the W4A16 GEMV (`fq_awq_gemv`), reading
-each module's qweight / scales / qzeros in place.  Decode shapes only: at most 8 rows."""
+projections that share one input run in ONE launch, reading each module's qweight / scales /
+qzeros in place: the W4A16 GEMV (`fq_awq_gemv`, CUDA cores) for decode shapes of at most 8
+rows, the tensor-core dequant-GEMM (`fq_awq_gemm`, tcgen05) for prefill / batched shapes."""
 from __future__ import annotations
 
 import ctypes
@@ -80,13 +81,61 @@ def awq_gemv_fused(hidden: torch.Tensor, projs: Sequence) -> tuple[torch.Tensor,
     return tuple(o.reshape(*lead, N) for o, N in zip(outs, Ns))
 
 
+def awq_gemm_fused(hidden: torch.Tensor, projs: Sequence) -> tuple[torch.Tensor, ...]:
+    """y_i = hidden @ dequant(projs[i]) (+ bias) for up to 4 AWQ linears in one launch of the
+    tensor-core dequant-GEMM, any number of rows.  Same module attributes as awq_gemv_fused;
+    every out_features must be a multiple of 128."""
+    require_cuda(hidden)
+    if hidden.dtype != torch.float16:
+        raise NotImplementedError(f"AWQ GEMM computes in fp16 (AutoAWQ's dtype), got {hidden.dtype}")
+    K = hidden.shape[-1]
+    x = hidden.reshape(-1, K).contiguous()
+    M = x.shape[0]
+    n = len(projs)
+    group = getattr(projs[0], "group_size", 128)
+    inter = bool(getattr(projs[0], "interleaved", True))
+    outs, Ns = [], []
+    for pj in projs:
+        qw, sc, qz = pj.qweight, pj.scales, pj.qzeros
+        N = qw.shape[1] * 8
+        if qw.dtype != torch.int32 or qz.dtype != torch.int32 or sc.dtype != torch.float16:
+            raise ValueError("AWQ linear needs int32 qweight / qzeros and fp16 scales")
+        if qw.shape[0] != K or tuple(sc.shape) != (K // group, N) or tuple(qz.shape) != (K // group, N // 8):
+            raise ValueError(f"AWQ layout mismatch: qweight {tuple(qw.shape)}, scales {tuple(sc.shape)}, "
+                             f"qzeros {tuple(qz.shape)} for K={K}, group={group}")
+        if not (qw.is_contiguous() and sc.is_contiguous() and qz.is_contiguous()):
+            raise ValueError("AWQ tensors must be contiguous")
+        if getattr(pj, "group_size", group) != group or bool(getattr(pj, "interleaved", True)) != inter:
+            raise ValueError("fused projections must share group size and nibble order")
+        Ns.append(N)
+        outs.append(torch.empty(M, N, dtype=torch.float16, device=hidden.device))
+    VP = ctypes.c_void_p * n
+    biases = [getattr(pj, "bias", None) for pj in projs]
+    bias_arr = VP(*[ptr(b) if b is not None else None for b in biases]) if any(b is not None for b in biases) else None
+    with torch.cuda.device(hidden.device):
+        if M > 0:
+            check(lib().fq_awq_gemm(
+                ptr(x), M, K, group, n,
+                VP(*[ptr(pj.qweight) for pj in projs]), VP(*[ptr(pj.scales) for pj in projs]),
+                VP(*[ptr(pj.qzeros) for pj in projs]), bias_arr, (ctypes.c_int * n)(*Ns), VP(*[ptr(o) for o in outs]),
+                int(inter), stream_ptr(hidden.device)))
+    lead = hidden.shape[:-1]
+    return tuple(o.reshape(*lead, N) for o, N in zip(outs, Ns))
+
+
+def awq_linear_fused(hidden: torch.Tensor, projs: Sequence) -> tuple[torch.Tensor, ...]:
+    """The GEMV for decode shapes (at most 8 rows), the tensor-core GEMM above that."""
+    rows = hidden.numel() // hidden.shape[-1]
+    return awq_gemv_fused(hidden, projs) if rows <= 8 else awq_gemm_fused(hidden, projs)
+
+
 def fused_qkv_proj(hidden: torch.Tensor, q_proj, k_proj, v_proj) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """(Q, K, V) = hidden through the three AWQ linears, one launch."""
-    q, k, v = awq_gemv_fused(hidden, (q_proj, k_proj, v_proj))
+    q, k, v = awq_linear_fused(hidden, (q_proj, k_proj, v_proj))
     return q, k, v
 
 
 def fused_gate_up_proj(hidden: torch.Tensor, gate_proj, up_proj) -> tuple[torch.Tensor, torch.Tensor]:
     """(gate, up) = hidden through the two AWQ linears, one launch; the caller applies SwiGLU."""
-    gate, up = awq_gemv_fused(hidden, (gate_proj, up_proj))
+    gate, up = awq_linear_fused(hidden, (gate_proj, up_proj))
     return gate, up

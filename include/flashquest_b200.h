@@ -348,6 +348,21 @@ int fq_awq_gemv(
     const int32_t* const* qweight, const void* const* scales, const int32_t* const* qzeros, const void* const* bias,
     const int* N, void* const* y, int interleaved, void* workspace, size_t workspace_bytes, int k_split, void* stream);
 
+/* AWQ W4A16 dequant-GEMM for prefill / batched shapes (any M >= 1): the same computation as
+ * fq_awq_gemv — the linears kernel/fused_proj.py:36-39,51-53 and the patched forward
+ * (eager/llama_persistent_patch.py:176-178,251) run through AutoAWQ's GEMM modules — on the tensor
+ * cores (tcgen05.mma, fp32 accumulation in tensor memory, operands staged by TMA).  The codes are
+ * dequantised to fp16, (code - zero) * scale rounded once, as AutoAWQ's GEMM kernels do.  Parity
+ * unpinned, as for fq_awq_gemv.
+ *   x (M,K) fp16 dense; up to 4 projections that share x (fused QKV, gate/up): arrays of n_proj
+ *   HOST arrays of device pointers / sizes; N[i] a multiple of 128, K a multiple of the group
+ *   size (64, 128 or 256); y[i] (M,N[i]) fp16 dense; bias NULL or per projection NULL / (N[i]) fp16.
+ * Needs no workspace.  The call builds TMA descriptors on the host (no allocation, no sync). */
+int fq_awq_gemm(
+    const void* x, int M, int K, int group, int n_proj,
+    const int32_t* const* qweight, const void* const* scales, const int32_t* const* qzeros, const void* const* bias,
+    const int* N, void* const* y, int interleaved, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * One decode step of one layer on a persistent INT4 cache: append + score + select + attend.
  * Replaces, in one host call and four launches, what the reference's patched forward does

@@ -83,3 +83,52 @@ def test_rejects_bad_arguments():
         awq_gemv_fused(torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda"), (dev,))
     with pytest.raises(ValueError):
         awq_gemv_fused(torch.zeros(1, 128, dtype=torch.float16, device="cuda"), (dev,))
+
+
+def _check_gemm(y_dev, x, lin, group, interleaved):
+    """Tensor-core path: weights rounded once to fp16 (as AutoAWQ's GEMM kernels do), fp32 accumulation."""
+    qw, sc, qz, b = lin
+    ref = oracle.awq_gemv(x, qw, sc, qz, group_size=group, interleaved=interleaved)
+    if b is not None:
+        ref = ref + b.float()
+    got = y_dev.float().cpu().reshape(ref.shape)
+    tol = 2e-3 * ref.abs().max().item() + 1e-3
+    err = (got - ref).abs().max().item()
+    assert err <= tol, (err, tol)
+
+
+@pytest.mark.parametrize("M", [16, 200, 256, 1000])
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_gemm_fused_qkv(M, interleaved):
+    """The tcgen05 dequant-GEMM on the fused QKV shape of BASELINE config 3, ragged and full row tiles,
+    both nibble orders, row by row against the oracle's dequant-matmul."""
+    from flashquest_b200 import _lib
+    from flashquest_b200.kernel.fused_proj import fused_qkv_proj
+    K, group = 3072, 128
+    lins = [_make_linear(K, N, group, 40 + i, interleaved, bias=(i == 2)) for i, N in enumerate((3072, 1024, 1024))]
+    x = (torch.randn(M, K, generator=torch.Generator().manual_seed(M)) * 0.5).half()
+    outs = fused_qkv_proj(x.cuda(), *[_to_dev(l, group, interleaved) for l in lins])
+    torch.cuda.synchronize()
+    assert _lib.lib().fq_device_status() == 0
+    assert outs[0].shape == (M, 3072) and outs[2].shape == (M, 1024)
+    rows = sorted(r for r in {0, 1, 127, 128, M // 2, M - 1} if r < M)
+    for y, l in zip(outs, lins):
+        _check_gemm(y[rows], x[rows], l, group, interleaved)
+
+
+def test_gemm_gate_up_down_and_group64():
+    from flashquest_b200.kernel.fused_proj import awq_gemm_fused, fused_gate_up_proj
+    K, group, M = 3072, 128, 300
+    lins = [_make_linear(K, 8192, group, 50 + i, True) for i in range(2)]
+    x = (torch.randn(M, K, generator=torch.Generator().manual_seed(9)) * 0.5).half()
+    gate, up = fused_gate_up_proj(x.cuda(), *[_to_dev(l, group, True) for l in lins])
+    rows = [0, 255, 256, 299]
+    _check_gemm(gate[rows], x[rows], lins[0], group, True)
+    _check_gemm(up[rows], x[rows], lins[1], group, True)
+    for K, N, group in ((8192, 3072, 128), (512, 128, 64)):
+        lin = _make_linear(K, N, group, 61, True)
+        x = (torch.randn(40, K, generator=torch.Generator().manual_seed(6)) * 0.5).half()
+        (y,) = awq_gemm_fused(x.cuda(), (_to_dev(lin, group, True),))
+        _check_gemm(y, x, lin, group, True)
+    with pytest.raises(NotImplementedError):
+        awq_gemm_fused(torch.zeros(16, 256, dtype=torch.float16, device="cuda"), (_to_dev(_make_linear(256, 64, 128, 1), 128, True),))
