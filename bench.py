@@ -788,7 +788,37 @@ def run_awq(args):
             rows.append({"proj": name, "M": M, "us_per_launch": round(us, 2), "bytes": nbytes,
                          "GBs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / peak, 3)})
             del projs, g
+    # ---- the tensor-core dequant-GEMM at prefill / batched shapes ----
+    from flashquest_b200.kernel.fused_proj import awq_gemm_fused
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        tpeak, tkind = float(pk["bf16_tflops_sustained"]), "measured (cuBLAS bf16, sustained)"
+    except Exception:
+        tpeak, tkind = 1400.0, "fallback"
+    gemm_rows = []
+    for name, K, Ns in (("qkv", 3072, (3072, 1024, 1024)), ("gate_up", 3072, (8192, 8192)), ("down", 8192, (3072,))):
+        projs = [linear(K, N, 900 + i) for i, N in enumerate(Ns)]
+        for M in (512, 4096, 32768):
+            x = torch.randn(M, K, device=dev).half()
+            for _ in range(3):
+                awq_gemm_fused(x, projs)
+            torch.cuda.synchronize()
+            reps = 5 if M >= 32768 else 20
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                awq_gemm_fused(x, projs)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            flops = 2.0 * M * K * sum(Ns)
+            gemm_rows.append({"proj": name, "M": M, "us_per_launch": round(us, 1), "TFLOPs": round(flops / us / 1e6, 1),
+                              "frac_of_tensor_peak": round(flops / us / 1e6 / tpeak, 3)})
+            del x
+        del projs
     return {"metric": "AWQ W4A16 GEMV weight bytes per second", "unit": "GB/s", "workload": "awq",
+            "gemm": {"kernel": "awq_gemm_kernel (tcgen05.mma, TMEM accumulators)", "peak_TFLOPs": tpeak, "peak_kind": tkind, "rows": gemm_rows},
             "parity": "unpinned (AutoAWQ's source is not in the reference tree; the oracle restates its published GEMM packing)",
             "peak": peak, "peak_kind": peak_kind, "steps": args.steps, "rows": rows,
             "device_status": _lib.lib().fq_device_status()}
