@@ -116,6 +116,7 @@ _PROTOTYPES["fq_decode_step_int4"] = (I, [ctypes.POINTER(Int4CacheDesc), I, P, P
 
 _PROTOTYPES["fq_add_rmsnorm"] = (I, [P, P, P, F, L, I, P, P, P])
 _PROTOTYPES["fq_rope"] = (I, [P, L, L, I, P, L, L, I, I, I, I, F, P])
+_PROTOTYPES["fq_rope_tokens"] = (I, [P, L, L, I, P, L, L, I, I, I, I, F, P])
 _PROTOTYPES["fq_swiglu"] = (I, [P, P, L, P, P])
 _PROTOTYPES["fq_gemv_f16"] = (I, [P, P, I, I, I, P, P])
 _PROTOTYPES["fq_argmax_f16"] = (I, [P, L, I, P, P])

@@ -104,7 +104,7 @@ int advance_positions(int* pos, int n, int n_new, int max_tokens, void* stream);
 int quant_append_layers_dyn(const fq_int4_cache* c, int n_layers, const int* pos, const void* K_new, const void* V_new,
                             int64_t nw_sl, int64_t nw_sb, int64_t nw_sh, int64_t nw_ss, int n_new, void* stream);
 int rope_launch(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv, int B, int D, int pos,
-                float theta, void* stream, const int* pos_dev);
+                float theta, void* stream, const int* pos_dev, int pos_step);
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

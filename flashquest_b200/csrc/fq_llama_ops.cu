@@ -56,11 +56,12 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(
 // with cos/sin computed in fp32 from pos * theta^(-2i/D) and rounded to fp16, products and sum in fp16.
 __global__ void __launch_bounds__(128) rope_kernel(__half* __restrict__ q, int64_t q_sb, int64_t q_sh, int Hq,
                                                    __half* __restrict__ k, int64_t k_sb, int64_t k_sh, int Hkv,
-                                                   int D, int pos, float theta, const int* __restrict__ pos_dev) {
+                                                   int D, int pos, float theta, const int* __restrict__ pos_dev, int pos_step) {
     const int head = blockIdx.x, b = blockIdx.y;
     pdl_wait();
     pdl_trigger();
     if (pos_dev) pos = *pos_dev;      // position read on the device (graph-capturable step)
+    pos += b * pos_step;              // rows are consecutive tokens of one sequence (prefill) when pos_step = 1
     __half* x = head < Hq ? q + b * q_sb + head * q_sh : k + b * k_sb + (head - Hq) * k_sh;
     const int half = D / 2;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -191,13 +192,13 @@ extern "C" int fq_add_rmsnorm(const void* a, const void* b, const void* weight, 
 
 namespace fq {
 int rope_launch(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv,
-                int B, int D, int pos, float theta, void* stream, const int* pos_dev) {
+                int B, int D, int pos, float theta, void* stream, const int* pos_dev, int pos_step) {
     const char* fn = "fq_rope";
     FQ_CHECK_ARG(q && k && B > 0 && Hq > 0 && Hkv > 0 && D > 0 && D % 2 == 0 && pos >= 0 && theta > 0.f, FQ_ERR_ARG, "%s: bad arguments", fn);
     FQ_CHECK_ARG(B <= 65535, FQ_ERR_ARG, "%s: batch %d too large", fn, B);
     launch_k(PDL_GEMV, rope_kernel, dim3((unsigned)(Hq + Hkv), (unsigned)B), dim3(D / 2 < 128 ? (D / 2 + 31) / 32 * 32 : 128), 0,
              static_cast<cudaStream_t>(stream), static_cast<__half*>(q), q_sb, q_sh, Hq, static_cast<__half*>(k), k_sb, k_sh, Hkv,
-             D, pos, theta, pos_dev);
+             D, pos, theta, pos_dev, pos_step);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
@@ -205,7 +206,12 @@ int rope_launch(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_
 
 extern "C" int fq_rope(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv,
                        int B, int D, int pos, float theta, void* stream) {
-    return fq::rope_launch(q, q_sb, q_sh, Hq, k, k_sb, k_sh, Hkv, B, D, pos, theta, stream, nullptr);
+    return fq::rope_launch(q, q_sb, q_sh, Hq, k, k_sb, k_sh, Hkv, B, D, pos, theta, stream, nullptr, 0);
+}
+
+extern "C" int fq_rope_tokens(void* q, int64_t q_st, int64_t q_sh, int Hq, void* k, int64_t k_st, int64_t k_sh, int Hkv,
+                              int n_tokens, int D, int pos0, float theta, void* stream) {
+    return fq::rope_launch(q, q_st, q_sh, Hq, k, k_st, k_sh, Hkv, n_tokens, D, pos0, theta, stream, nullptr, 1);
 }
 
 extern "C" int fq_swiglu(const void* gate, const void* up, int64_t n, void* out, void* stream) {
@@ -310,7 +316,7 @@ static int llama_step_impl(const fq_llama_model* m, const fq_int4_cache* cache, 
         }
         void* Ol = static_cast<char*>(s->O) + (size_t)l * s->o_sl * 2;
         if (pos_dev) {
-            rc = rope_launch(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, 0, m->rope_theta, stream, pos_dev + l);
+            rc = rope_launch(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, 0, m->rope_theta, stream, pos_dev + l, 0);
             if (rc != FQ_OK) return rc;
             rc = decode_layer_int4_dyn(cache, l, pos_dev + l, s->k, s->v, nkv, D, D, 1, s->q, FQ_F16, nq, D, prm,
                                        s->scores + l * s->sc_sl, s->compact + l * s->cp_sl, Ol, nullptr,

@@ -167,6 +167,74 @@ class LlamaInt4Decoder:
         self.launches += 12 * n_l + 3
         return self.next_ids
 
+    def prefill(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """Prefill of ONE sequence (batch_size must be 1): token_ids (S,) are run through all layers at
+        once — the S_q > 1 branch of the reference's patched forward
+        (flashquest/eager/llama_persistent_patch.py:196-201) inside HF's layer loop: per layer
+        add+RMSNorm over all rows, fused AWQ q/k/v on the tensor-core dequant-GEMM, RoPE per token,
+        bulk quantise-on-append of the S tokens, dense causal attention over the dequantised
+        completed pages followed by the staged tail, AWQ o / gate / up / down GEMMs, SwiGLU; after
+        the last layer the final norm, lm_head and argmax of the LAST token only.  Returns the next
+        token id (1,) int32 (greedy); self.logits holds the last token's logits."""
+        from ..kernel.fused_proj import awq_gemm_fused, awq_linear_fused
+        from ..kernel.kv_quant import dequantize_k_int4, dequantize_v_int4
+        from ..kernel.prefill_attn import prefill_causal_attention
+        c, w = self.cfg, self.w
+        if self.B != 1:
+            raise NotImplementedError("prefill runs one sequence; batch the decode steps instead")
+        cache = self.cache
+        if cache.get_seq_length(0) != 0:
+            raise RuntimeError("prefill expects an empty cache")
+        S = int(token_ids.numel())
+        if S > cache.max_seq_len:
+            raise RuntimeError(f"PersistentInt4KVCache: seen+new={S} exceeds max_seq_len={cache.max_seq_len}")
+        L = lib()
+        st = stream_ptr(self.dev)
+        H, D, Hq, Hkv = c.hidden, c.head_dim, c.q_heads, c.kv_heads
+        lin = awq_linear_fused                                     # the GEMV below 9 rows, the tensor-core GEMM above
+        x = w.embed[token_ids.to(self.dev).long()]                # (S, H) gather: plumbing
+        normed = torch.empty_like(x)
+        delta = None
+        for li, lw in enumerate(w.layers):
+            if delta is None:
+                check(L.fq_add_rmsnorm(ptr(x), None, ptr(lw.input_norm), c.rms_eps, S, H, None, ptr(normed), st))
+            else:
+                x2 = torch.empty_like(x)
+                check(L.fq_add_rmsnorm(ptr(x), ptr(delta), ptr(lw.input_norm), c.rms_eps, S, H, ptr(x2), ptr(normed), st))
+                x = x2
+            q, k, v = lin(normed, (lw.q_proj, lw.k_proj, lw.v_proj))                 # (S, Hq*D), (S, Hkv*D) x2
+            check(L.fq_rope_tokens(ptr(q), Hq * D, D, Hq, ptr(k), Hkv * D, D, Hkv, S, D, 0, c.rope_theta, st))
+            q4 = q.view(1, S, Hq, D).transpose(1, 2)               # (1, Hq, S, D) views, token stride Hq*D
+            k4, v4 = k.view(1, S, Hkv, D).transpose(1, 2), v.view(1, S, Hkv, D).transpose(1, 2)
+            cache.update_quantized(k4, v4, li)
+            vw = cache.get_views(li)
+            if vw["completed_len"] > 0:
+                # bf16 -> fp16 is exact: the reference's bf16-rounded dequantised values, in the staging dtype
+                Kd = dequantize_k_int4(vw["K_packed"], vw["K_scale"], vw["K_mn"], cache.page_size).to(cache.dtype)
+                Vd = dequantize_v_int4(vw["V_packed"], vw["V_scale"], vw["V_mn"]).to(cache.dtype)
+                K_full, V_full = torch.cat([Kd, vw["K_partial"]], 2), torch.cat([Vd, vw["V_partial"]], 2)
+                del Kd, Vd
+            else:
+                K_full, V_full = vw["K_partial"], vw["V_partial"]
+            attn = prefill_causal_attention(q4, K_full, V_full, out_bshd=True).view(S, Hq * D)
+            del K_full, V_full, q, k, v
+            (attn_out,) = lin(attn, (lw.o_proj,))
+            x2 = torch.empty_like(x)
+            check(L.fq_add_rmsnorm(ptr(x), ptr(attn_out), ptr(lw.post_norm), c.rms_eps, S, H, ptr(x2), ptr(normed), st))
+            x = x2
+            gate, up = lin(normed, (lw.gate_proj, lw.up_proj))
+            act = torch.empty_like(gate)
+            check(L.fq_swiglu(ptr(gate), ptr(up), gate.numel(), ptr(act), st))
+            (delta,) = lin(act, (lw.down_proj,))
+            del gate, up, act, attn, attn_out
+            self.launches += 12
+        last = torch.empty(1, H, dtype=torch.float16, device=self.dev)
+        check(L.fq_add_rmsnorm(ptr(x[S - 1:]), ptr(delta[S - 1:]), ptr(w.final_norm), c.rms_eps, 1, H, ptr(last), ptr(self.normed), st))
+        check(L.fq_gemv_f16(ptr(self.normed), ptr(w.lm_head), 1, H, c.vocab, ptr(self.logits), st))
+        check(L.fq_argmax_f16(ptr(self.logits), 1, c.vocab, ptr(self.next_ids), st))
+        self.launches += 3
+        return self.next_ids
+
     # -- thin wrappers over the C ABI ------------------------------------------------------
     def _add_rmsnorm(self, a, b, weight, sum_out, y):
         check(lib().fq_add_rmsnorm(ptr(a), ptr(b), ptr(weight), self.cfg.rms_eps, a.shape[0], a.shape[1],

@@ -494,6 +494,10 @@ int fq_add_rmsnorm(const void* a, const void* b, const void* weight, float eps, 
                    void* sum_out, void* y, void* stream);
 int fq_rope(void* q, int64_t q_sb, int64_t q_sh, int Hq, void* k, int64_t k_sb, int64_t k_sh, int Hkv,
             int B, int D, int pos, float theta, void* stream);
+/* The same rotation for n_tokens consecutive tokens of ONE sequence (prefill): row t of q / k
+ * (token strides q_st / k_st, head strides q_sh / k_sh, elements) is rotated for position pos0 + t. */
+int fq_rope_tokens(void* q, int64_t q_st, int64_t q_sh, int Hq, void* k, int64_t k_st, int64_t k_sh, int Hkv,
+                   int n_tokens, int D, int pos0, float theta, void* stream);
 int fq_swiglu(const void* gate, const void* up, int64_t n, void* out, void* stream);
 int fq_gemv_f16(const void* x, const void* W, int M, int K, int N, void* y, void* stream);
 int fq_argmax_f16(const void* x, int64_t rows, int N, int32_t* out, void* stream);

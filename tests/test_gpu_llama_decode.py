@@ -212,6 +212,84 @@ def test_decode_steps_at_config3_widths(layers):
           f"k/v {max(kv_err):.2f}")
 
 
+def _ref_prefill(cfg, w, ids, page):
+    """CPU restatement of the prefill branch: all tokens at once, attention over the dequantised completed
+    pages followed by the staged tail, causal; returns (last-token logits, per-layer K, V as appended)."""
+    S = ids.numel()
+    x = w.embed.cpu()[ids.long()]
+    Ks, Vs = [], []
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2).float() / cfg.head_dim))
+
+    def rope_all(t):                       # t (S, H, D)
+        ang = torch.arange(S).float()[:, None] * inv[None, :]
+        cos = torch.cat([ang, ang], -1).cos().half()[:, None, :]
+        sin = torch.cat([ang, ang], -1).sin().half()[:, None, :]
+        D = t.shape[-1]
+        rot = torch.cat([-t[..., D // 2:], t[..., : D // 2]], dim=-1)
+        return t * cos + rot * sin
+    delta = None
+    for lw in w.layers:
+        if delta is not None:
+            x = x + delta
+        n = _rms(x, lw.input_norm.cpu(), cfg.rms_eps)
+        q = rope_all(_awq(n, lw.q_proj).view(S, cfg.q_heads, cfg.head_dim))
+        k = rope_all(_awq(n, lw.k_proj).view(S, cfg.kv_heads, cfg.head_dim))
+        v = _awq(n, lw.v_proj).view(S, cfg.kv_heads, cfg.head_dim)
+        K4, V4 = k.transpose(0, 1).unsqueeze(0).contiguous(), v.transpose(0, 1).unsqueeze(0).contiguous()
+        Ks.append(K4); Vs.append(V4)
+        nq = S - S % page
+        kq, vq = oracle.quantize_k_int4(K4[:, :, :nq], page), oracle.quantize_v_int4(V4[:, :, :nq])
+        Kf = torch.cat([oracle.dequantize_k_int4(*kq, page).half(), K4[:, :, nq:]], 2).float()
+        Vf = torch.cat([oracle.dequantize_v_int4(*vq).half(), V4[:, :, nq:]], 2).float()
+        n_rep = cfg.q_heads // cfg.kv_heads
+        sc = q.transpose(0, 1).float() @ Kf[0].repeat_interleave(n_rep, 0).transpose(-1, -2) / math.sqrt(cfg.head_dim)
+        i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
+        att = torch.softmax(sc.masked_fill(j > i, float("-inf")), -1) @ Vf[0].repeat_interleave(n_rep, 0)      # (Hq, S, D)
+        x = x + _awq(att.transpose(0, 1).reshape(S, -1).half(), lw.o_proj)
+        n = _rms(x, lw.post_norm.cpu(), cfg.rms_eps)
+        act = torch.nn.functional.silu(_awq(n, lw.gate_proj).float()).half() * _awq(n, lw.up_proj)
+        delta = _awq(act, lw.down_proj)
+    x = x + delta
+    n = _rms(x[-1:], w.final_norm.cpu(), cfg.rms_eps)
+    return (n.float() @ w.lm_head.cpu().float().T).half(), Ks, Vs
+
+
+def test_prefill_then_decode():
+    """Prefill of a 45-token prompt (tensor-core AWQ GEMM, per-token RoPE, bulk quantise-on-append, dense causal
+    attention over dequantised pages + tail) against the CPU restatement, then decode steps that continue from
+    the cache the prefill left (teacher-forced cache, tight bound)."""
+    from flashquest_b200.eager.llama_decode import LlamaConfig, LlamaInt4Decoder, random_llama_weights
+    cfg = LlamaConfig(hidden=256, layers=2, q_heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=512)
+    w = random_llama_weights(cfg, "cuda", seed=5)
+    page, S = 16, 45
+    dec = LlamaInt4Decoder(cfg, w, batch_size=1, max_seq_len=96, page_size=page, retention=1.0, num_sinks=1, window_pages=1)
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, cfg.vocab, (S,), generator=g, dtype=torch.int32)
+    nxt = dec.prefill(ids.cuda())
+    got = dec.logits.float().cpu()
+    want, Ks, Vs = _ref_prefill(cfg, w, ids, page)
+    want = want.float()
+    tol = 3e-2 * want.abs().max().item() + 1e-2          # free-running: the 4-bit codes of k / v may differ by a step
+    assert (got - want).abs().max().item() <= tol, ((got - want).abs().max().item(), tol)
+    assert dec.cache.get_seq_length(0) == S
+    # what layer 0 appended depends on the embedding, the norm, the tensor-core GEMM and the per-token RoPE only: tight
+    vw = dec.cache.get_views(0)
+    for name, ref_t in (("K_partial", Ks[0]), ("V_partial", Vs[0])):
+        err = (vw[name].float().cpu() - ref_t[:, :, 32:].float()).abs().max().item()
+        assert err <= 2e-3 * ref_t.float().abs().max().item() + 4e-3, (name, err)       # + sin/cos of fp32 angles (see the RoPE op test)
+    # decode continues from the prefilled cache
+    ref = _Ref(cfg, w, page, 1.0, 1, 1, dec.attn.k_max_static)
+    ref.K, ref.V = [k.clone() for k in Ks], [v.clone() for v in Vs]
+    ids_t = want.argmax(-1).to(torch.int32)
+    for t in range(6):
+        dec.decode_step(ids_t.cuda())
+        got = dec.logits.float().cpu()
+        want = ref.step(ids_t, views_fn=dec.cache.get_views).float()
+        tol = 2e-3 * want.abs().max() + 2 ** -11 * want.abs()
+        assert ((got - want).abs() <= tol).all(), (t, float((got - want).abs().max()))
+        ids_t = want.argmax(-1).to(torch.int32)
+
+
 def test_graph_replayed_decode_equals_stream_decode():
     """One captured graph replayed per token (positions on the device, ids fed back on the device)
     produces the same logits and tokens as decode_step(), bit for bit, across a page boundary."""
