@@ -924,8 +924,9 @@ def run_llama(args):
     w = random_llama_weights(cfg, dev, seed=3)
     dec = LlamaInt4Decoder(cfg, w, batch_size=1, max_seq_len=S + 256, page_size=16, retention=0.25, num_sinks=1, window_pages=1,
                            device=dev)
-    rng = random.Random(0)
-    prompt = torch.tensor([rng.randrange(cfg.vocab) for _ in range(S)], dtype=torch.int32, device=dev)
+    from flashquest_b200 import bench_record as br
+    prompt_ids = br.synthetic_token_ids(cfg.vocab, S, 0)
+    prompt = torch.tensor(prompt_ids, dtype=torch.int32, device=dev)
     # one short prefill first: lazily set kernel attributes and the allocator's pools stay out of the timed one
     warm = LlamaInt4Decoder(cfg, w, batch_size=1, max_seq_len=512, page_size=16, retention=0.25, num_sinks=1, window_pages=1, device=dev)
     warm.prefill(prompt[:300])
@@ -959,6 +960,39 @@ def run_llama(args):
                                (cfg.hidden, 2 * cfg.ffn), (cfg.ffn, cfg.hidden))) + cfg.vocab * cfg.hidden * 2
     lin_flops = 2.0 * S * cfg.layers * (cfg.hidden * (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim + cfg.q_heads * cfg.head_dim * cfg.hidden +
                                         3 * cfg.hidden * cfg.ffn)
+    record_path = getattr(args, "record", None)
+    if record_path:
+        # the reference's own record format: prefill + 127 decode steps per repetition on a re-used cache allocation
+        rcfg = br.run_config(S, n_decode + 1, 3, 0, model="random-init Llama-3.2-3B architecture (AWQ 4-bit, group 128)", kv_bits=4,
+                             retention=0.25, page_size=16, num_sinks=1, window_pages=1, warmup_steps=done, cache_capacity=S + 256,
+                             input_sha256=br.input_sha256(prompt_ids), generation="manual-greedy-fixed-output-count-v1",
+                             runtime={"cuda": torch.version.cuda, "devices": [str(dev)], "dtype": "torch.float16", "weight_kernel": "fq_awq_gemv / fq_awq_gemm",
+                                      "weight_storage_bytes": wbytes})
+        rec = br.new_record("flashquest_b200", "AWQ-INT4 + INT4 KV, retention=0.25", rcfg)
+        t_wall = time.time()
+        for _ in range(rcfg["reps"]):
+            dec.cache._seen_tokens = [0] * cfg.layers
+            torch.cuda.reset_peak_memory_stats()
+            torch.cuda.synchronize()
+            t0 = time.monotonic_ns()
+            nxt = dec.prefill(prompt).clone()
+            torch.cuda.synchronize()
+            t1 = time.monotonic_ns()
+            rp = dec.capture_decode_graph(nxt)
+            torch.cuda.synchronize()
+            t1b = time.monotonic_ns()
+            for _ in range(n_decode):
+                rp()
+            torch.cuda.synchronize()
+            t2 = time.monotonic_ns()
+            rec["samples"].append(br.make_sample(S, n_decode, (t1 - t0) / 1e9, (t2 - t1b) / 1e9,
+                                                 round(torch.cuda.max_memory_allocated() / 2 ** 20, 1), round(torch.cuda.max_memory_reserved() / 2 ** 20, 1)))
+            del rp
+        rec["wall_s"] = time.time() - t_wall
+        br.summarize_samples(rec)
+        rec["provenance"] = br.provenance({"torch": torch.__version__}, [{"name": torch.cuda.get_device_name(dev)}])
+        with open(record_path, "w") as f:
+            json.dump(br.export_record(rec), f, indent=1)
     return {
         "metric": "Llama-3.2-3B-shaped AWQ decode tokens/s at 32k ctx (sparse INT4 attention)", "workload": "llama",
         "value": 1e3 / ms, "unit": "tokens/s", "ms_per_token": ms, "decode_steps_timed": timed, "decode_steps_total": n_decode,
@@ -1012,6 +1046,7 @@ def main():
                     help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
     ap.add_argument("--no-batched", action="store_true", help="skip the batched-attention leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--record", default=None, help="--workload llama: also write a benchmark record in the reference's schema-3 format to this path")
     ap.add_argument("--no-extra", action="store_true", help="skip BASELINE config 4 (batch-sharded and context-split legs) and the secondary workloads")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (AWQ GEMV table, TurboQuant, Llama decode)")
     args = ap.parse_args()
