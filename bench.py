@@ -401,7 +401,7 @@ def run_ours(args):
         secondary = None
         if rank == 0 and world == 1 and not args.no_secondary:
             secondary = {}
-            for name, fn in (("awq", run_awq), ("turbo", run_turbo), ("llama", run_llama)):
+            for name, fn in (("awq", run_awq), ("turbo", run_turbo), ("prefill_attn", run_prefill_attn), ("llama", run_llama)):
                 torch.cuda.empty_cache()
                 try:
                     secondary[name] = fn(args)
@@ -900,6 +900,44 @@ def run_turbo(args):
         "peak": peak, "peak_kind": peak_kind, "device_status": _lib.lib().fq_device_status()}
 
 
+# --------------------------------------------------------------------------- secondary workload: prefill attention
+
+def run_prefill_attn(args):
+    """The dense causal attention of the prefill branch alone (fq_prefill_attention): 24 query / 8 KV heads, head_dim 128,
+    fp16, S_q = S_kv = context (default 8192), against the measured tensor peak."""
+    import torch
+    from flashquest_b200 import _lib
+    from flashquest_b200.kernel.prefill_attn import prefill_causal_attention
+    _lib.lib()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    S, Hq, Hkv, D = args.ctx or 8192, CFG["Hq"], CFG["Hkv"], CFG["D"]
+    g = torch.Generator(device=dev).manual_seed(1)
+    q = torch.randn(1, Hq, S, D, device=dev, generator=g).half()
+    k = torch.randn(1, Hkv, S, D, device=dev, generator=g).half()
+    v = torch.randn(1, Hkv, S, D, device=dev, generator=g).half()
+    for _ in range(max(args.warmup, 3)):
+        prefill_causal_attention(q, k, v)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        prefill_causal_attention(q, k, v)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    flops = 4.0 * Hq * D * S * (S + 1) / 2           # QK^T and PV over the causal half
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tpeak = float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        tpeak = 1400.0
+    return {"metric": "prefill causal attention", "workload": "prefill_attn", "kernel": "prefill_attn_kernel (mma.sync m16n8k16, fp32 accumulate)",
+            "config": {"q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "S_q": S, "S_kv": S, "dtype": "f16"},
+            "us_per_call": us, "TFLOPs": flops / us / 1e6, "frac_of_tensor_peak": flops / us / 1e6 / tpeak, "peak_TFLOPs": tpeak,
+            "device_status": _lib.lib().fq_device_status()}
+
+
 # --------------------------------------------------------------------------- secondary workload: Llama decode
 
 def run_llama(args):
@@ -1042,7 +1080,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (small captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per GPU (profiles of batched shapes)")
     ap.add_argument("--n-split", type=int, default=0, help="override the split-K factor of the attention kernel")
-    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo", "llama", "ctxsplit"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo", "llama", "ctxsplit", "prefill_attn"],
                     help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
     ap.add_argument("--no-batched", action="store_true", help="skip the batched-attention leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -1058,6 +1096,8 @@ def main():
         print(json.dumps(run_turbo(args)))
     elif args.workload == "llama":
         print(json.dumps(run_llama(args)))
+    elif args.workload == "prefill_attn":
+        print(json.dumps(run_prefill_attn(args)))
     elif args.workload == "ctxsplit":
         run_ctxsplit(args)
     else:

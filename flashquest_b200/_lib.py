@@ -130,6 +130,12 @@ _PROTOTYPES["fq_ctx_scratch_bytes"] = (Z, [I, I, I, I, I, I])
 _PROTOTYPES["fq_ctx_local_candidates"] = (I, [P, I, L, L, P, P, L, L, L, I, I, I, I, I, I, I, I, I, P, Z, P, P])
 _PROTOTYPES["fq_ctx_select_attend"] = (I, [P, I, I, I, I, I, I, I, I, P, I, L, L, P, L, L, P, P, L, L, L, P, L, L, P, P, L, L,
                                           P, P, I, L, L, L, I, I, I, I, I, I, F, I, P, Z, P, P, P, Z, I, P])
+_PROTOTYPES["fq_quantize_kv_int8"] = (I, [P, P, L, L, L, I, I, I, I, I, I, P, P, L, L, L, P, P, L, L, L, P, P, L, L, P])
+_PROTOTYPES["fq_dequantize_int8"] = (I, [P, L, L, L, P, P, L, L, L, I, I, I, I, I, I, P, L, L, L, P])
+_PROTOTYPES["fq_page_scores_int8"] = (I, [P, I, L, L, P, P, L, L, L, I, I, I, I, I, P, L, L, P])
+_PROTOTYPES["fq_sparse_decode_int8_workspace_bytes"] = (Z, [I, I, I, I])
+_PROTOTYPES["fq_sparse_decode_int8"] = (I, [P, I, L, L, P, P, L, L, L, P, P, L, L, L, P, P, L, L, P, L, L, I,
+                                           P, P, I, L, L, L, I, I, I, I, I, I, I, I, F, P, P, P, Z, I, P])
 _PROTOTYPES["fq_prefill_attention"] = (I, [P, L, L, L, P, L, L, L, P, L, L, L, I, I, I, I, I, I, I, F, P, L, L, L, P])
 
 # entry points added by later sources register themselves here (name -> (restype, argtypes))

@@ -1,0 +1,347 @@
+// INT8 KV variant of the path (KIVI-style asymmetric uint8, 255 levels): quantise / dequantise,
+// and sparse decode attention over selected uint8 pages.  Same structure as the INT4 variant with
+// one code per byte: K per page and channel (scale and min computed in the input dtype), V per
+// token in fp32.  The page scores of this variant are the INT4 scoring kernel with 255 levels.
+// This is the kv_bits == 8 route of the dispatcher; the decode loop spends its bytes on codes
+// (D bytes per token and head for each of K and V), so the kernels stay simple: a warp owns a
+// token row, a lane D/32 channels.
+#include "fq_common.cuh"
+
+namespace fq {
+
+constexpr float I8_LOG2E = 1.4426950408889634f;
+constexpr float I8_LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float i8_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// K: one warp per (b, h, page); lane owns channels lane, lane+32, ...
+template <typename T>
+__global__ void __launch_bounds__(128) quant_k_int8_kernel(const T* __restrict__ K, int64_t k_sb, int64_t k_sh, int64_t k_ss,
+                                                           int B, int H, int S, int D, int page,
+                                                           uint8_t* __restrict__ codes, int64_t c_sb, int64_t c_sh, int64_t c_ss,
+                                                           uint16_t* __restrict__ scale, uint16_t* __restrict__ mn, int64_t m_sb, int64_t m_sh, int64_t m_sp) {
+    const int lane = threadIdx.x & 31;
+    const int P = (S + page - 1) / page;
+    const int64_t w = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (w >= (int64_t)B * H * P) return;
+    const int p = (int)(w % P), h = (int)((w / P) % H), b = (int)(w / ((int64_t)P * H));
+    const int t0 = p * page, n_tok = min(page, S - t0);
+    const T* src = K + b * k_sb + h * k_sh + (int64_t)t0 * k_ss;
+    for (int d = lane; d < D; d += 32) {
+        float lo = INFINITY, hi = -INFINITY;
+        for (int t = 0; t < n_tok; ++t) {
+            const float v = Dt<T>::to_f32(src[(int64_t)t * k_ss + d]);
+            lo = fminf(lo, v); hi = fmaxf(hi, v);
+        }
+        // scale arithmetic in the input dtype: (mx - mn) rounded to T, the quotient by 255 rounded to T, clamped at T(1e-6)
+        const float diff = Dt<T>::rn(__fsub_rn(hi, lo));
+        float sc = Dt<T>::rn(__fdiv_rn(diff, 255.0f));
+        sc = fmaxf(sc, Dt<T>::rn(1e-6f));
+        const int64_t mo = b * m_sb + h * m_sh + (int64_t)p * m_sp + d;
+        scale[mo] = f32_to_bf16_bits(sc);
+        mn[mo] = f32_to_bf16_bits(lo);
+        for (int t = 0; t < n_tok; ++t) {
+            const float v = Dt<T>::to_f32(src[(int64_t)t * k_ss + d]);
+            const float c = rintf(__fdiv_rn(__fsub_rn(v, lo), sc));
+            codes[b * c_sb + h * c_sh + (int64_t)(t0 + t) * c_ss + d] = (uint8_t)fminf(fmaxf(c, 0.f), 255.f);
+        }
+    }
+}
+
+// V: one warp per token
+template <typename T>
+__global__ void __launch_bounds__(128) quant_v_int8_kernel(const T* __restrict__ V, int64_t v_sb, int64_t v_sh, int64_t v_ss,
+                                                           int B, int H, int S, int D,
+                                                           uint8_t* __restrict__ codes, int64_t c_sb, int64_t c_sh, int64_t c_ss,
+                                                           uint16_t* __restrict__ scale, uint16_t* __restrict__ mn, int64_t m_sb, int64_t m_sh) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (w >= (int64_t)B * H * S) return;
+    const int t = (int)(w % S), h = (int)((w / S) % H), b = (int)(w / ((int64_t)S * H));
+    const T* src = V + b * v_sb + h * v_sh + (int64_t)t * v_ss;
+    float lo = INFINITY, hi = -INFINITY;
+    for (int d = lane; d < D; d += 32) {
+        const float v = Dt<T>::to_f32(src[d]);
+        lo = fminf(lo, v); hi = fmaxf(hi, v);
+    }
+    lo = warp_min(lo); hi = warp_max(hi);
+    const float sc = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 255.0f), 1e-6f);
+    for (int d = lane; d < D; d += 32) {
+        const float c = rintf(__fdiv_rn(__fsub_rn(Dt<T>::to_f32(src[d]), lo), sc));
+        codes[b * c_sb + h * c_sh + (int64_t)t * c_ss + d] = (uint8_t)fminf(fmaxf(c, 0.f), 255.f);
+    }
+    if (lane == 0) {
+        scale[b * m_sb + h * m_sh + t] = f32_to_bf16_bits(sc);
+        mn[b * m_sb + h * m_sh + t] = f32_to_bf16_bits(lo);
+    }
+}
+
+__global__ void __launch_bounds__(256) dequant_int8_kernel(const uint8_t* __restrict__ codes, int64_t c_sb, int64_t c_sh, int64_t c_ss,
+                                                           const uint16_t* __restrict__ scale, const uint16_t* __restrict__ mn,
+                                                           int64_t m_sb, int64_t m_sh, int64_t m_s2, int per_page, int B, int H, int S, int D, int page,
+                                                           uint16_t* __restrict__ out, int64_t o_sb, int64_t o_sh, int64_t o_ss) {
+    const int64_t total = (int64_t)B * H * S * D;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int d = (int)(i % D);
+        int64_t r = i / D;
+        const int t = (int)(r % S);
+        r /= S;
+        const int h = (int)(r % H), b = (int)(r / H);
+        const int64_t mo = per_page ? b * m_sb + h * m_sh + (int64_t)(t / page) * m_s2 + d : b * m_sb + h * m_sh + (int64_t)t * m_s2;
+        const float v = __fadd_rn(__fmul_rn((float)codes[b * c_sb + h * c_sh + (int64_t)t * c_ss + d], bf16_lo(scale[mo])), bf16_lo(mn[mo]));
+        out[b * o_sb + h * o_sh + (int64_t)t * o_ss + d] = f32_to_bf16_bits(v);
+    }
+}
+
+struct Int8AttnParams {
+    const void* Q; int q_dtype; int64_t q_sb, q_sh;
+    const uint8_t *K, *V; int64_t kv_sb, kv_sh, kv_ss;
+    const uint16_t *K_scale, *K_mn; int64_t km_sb, km_sh, km_sp;
+    const uint16_t *V_scale, *V_mn; int64_t vm_sb, vm_sh;
+    const int32_t* compact; int64_t cp_sb, cp_sh; int bucket;
+    const void *K_tail, *V_tail; int tail_dtype; int64_t tl_sb, tl_sh, tl_ss; int tail_len;
+    int B, Hq, Hkv, S_kv, P, page;
+    float sm_scale;
+    float* part_o; float* part_lse; int n_split;      // (n_split, rows, D) fp32 and (n_split, rows): merged by fq_lse_merge
+};
+
+__device__ __forceinline__ float i8_ld(const void* p, int dtype, int64_t i) {
+    return dtype == FQ_F16 ? __half2float(static_cast<const __half*>(p)[i]) : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// Grid (n_split, Hq, B), 4 warps.  A warp takes pages of the row's compact list (entry index = split + n_split * (warp +
+// 4 * i)); lane owns CPL = D/32 consecutive channels of every token.  Each CTA writes a normalised partial (O, lse).
+template <int D>
+__global__ void __launch_bounds__(128) sparse_decode_int8_kernel(Int8AttnParams p) {
+    constexpr int CPL = D / 32;
+    __shared__ float s_m[4], s_l[4];
+    __shared__ float s_acc[4][D];
+    const int split = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+    const int hkv = hq / (p.Hq / p.Hkv);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float c = p.sm_scale * I8_LOG2E;
+    float q[CPL];
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) q[j] = i8_ld(p.Q, p.q_dtype, b * p.q_sb + hq * p.q_sh + CPL * lane + j) * c;
+    float m = -INFINITY, l = 0.f, acc[CPL];
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) acc[j] = 0.f;
+    const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
+    const uint8_t* Kb = p.K + b * p.kv_sb + hkv * p.kv_sh;
+    const uint8_t* Vb = p.V + b * p.kv_sb + hkv * p.kv_sh;
+    for (int e = split + p.n_split * warp; e < p.bucket; e += p.n_split * 4) {
+        const int pg = list[e];
+        if (pg < 0 || pg >= p.P || pg * p.page >= p.S_kv) continue;
+        const int64_t mo = b * p.km_sb + hkv * p.km_sh + (int64_t)pg * p.km_sp + CPL * lane;
+        float qs[CPL], qmn = 0.f;
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) {
+            qs[j] = q[j] * bf16_lo(p.K_scale[mo + j]);
+            qmn = fmaf(q[j], bf16_lo(p.K_mn[mo + j]), qmn);
+        }
+        qmn = warp_sum(qmn);
+        const int t_end = min((pg + 1) * p.page, p.S_kv);
+        for (int t = pg * p.page; t < t_end; ++t) {
+            const uint8_t* kr = Kb + (int64_t)t * p.kv_ss + CPL * lane;
+            const uint8_t* vr = Vb + (int64_t)t * p.kv_ss + CPL * lane;
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) s = fmaf(qs[j], (float)kr[j], s);
+            s = warp_sum(s) + qmn;
+            const float m_new = fmaxf(m, s);
+            const float al = i8_ex2(m - m_new), pr = i8_ex2(s - m_new);
+            const float vs = bf16_lo(p.V_scale[b * p.vm_sb + hkv * p.vm_sh + t]), vm = bf16_lo(p.V_mn[b * p.vm_sb + hkv * p.vm_sh + t]);
+            l = l * al + pr;
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) acc[j] = fmaf(pr, fmaf((float)vr[j], vs, vm), acc[j] * al);
+            m = m_new;
+        }
+    }
+    // the staged (unquantised) tail belongs to split 0
+    if (split == 0) {
+        for (int t = warp; t < p.tail_len; t += 4) {
+            const int64_t ro = b * p.tl_sb + hkv * p.tl_sh + (int64_t)t * p.tl_ss + CPL * lane;
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) s = fmaf(q[j], i8_ld(p.K_tail, p.tail_dtype, ro + j), s);
+            s = warp_sum(s);
+            const float m_new = fmaxf(m, s);
+            const float al = i8_ex2(m - m_new), pr = i8_ex2(s - m_new);
+            l = l * al + pr;
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) acc[j] = fmaf(pr, i8_ld(p.V_tail, p.tail_dtype, ro + j), acc[j] * al);
+            m = m_new;
+        }
+    }
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) s_acc[warp][CPL * lane + j] = acc[j];
+    __syncthreads();
+    float mx = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    float lsum = 0.f, o = 0.f;
+    const int d = threadIdx.x;
+    if (mx != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float wgt = i8_ex2(s_m[w] - mx);
+            lsum = fmaf(s_l[w], wgt, lsum);
+            if (d < D) o = fmaf(s_acc[w][d], wgt, o);
+        }
+    }
+    const int64_t row = (int64_t)b * p.Hq + hq, rows = (int64_t)p.B * p.Hq;
+    if (d < D) p.part_o[((int64_t)split * rows + row) * D + d] = lsum > 0.f ? o / lsum : 0.f;
+    if (d == 0) p.part_lse[(int64_t)split * rows + row] = lsum > 0.f ? (mx + log2f(lsum)) * I8_LN2 : -INFINITY;
+}
+
+// merge of the splits' normalised partial results (fp32) into O (q dtype) and lse; one warp per row
+__global__ void __launch_bounds__(128) int8_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_split,
+                                                         int64_t rows, int D, void* __restrict__ O, int q_dtype, float* __restrict__ lse) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    float m = -INFINITY;
+    for (int i = 0; i < n_split; ++i) m = fmaxf(m, part_lse[i * rows + r]);
+    float wsum = 0.f;
+    if (m != -INFINITY)
+        for (int i = 0; i < n_split; ++i) wsum += expf(part_lse[i * rows + r] - m);
+    for (int d = lane; d < D; d += 32) {
+        float a = 0.f;
+        if (m != -INFINITY)
+            for (int i = 0; i < n_split; ++i) a = fmaf(expf(part_lse[i * rows + r] - m), part_o[(i * rows + r) * D + d], a);
+        const float v = m != -INFINITY ? a / wsum : 0.f;
+        if (q_dtype == FQ_F16) static_cast<__half*>(O)[r * D + d] = __float2half_rn(v);
+        else static_cast<__nv_bfloat16*>(O)[r * D + d] = __float2bfloat16_rn(v);
+    }
+    if (lane == 0 && lse) lse[r] = m != -INFINITY ? m + logf(wsum) : -INFINITY;
+}
+
+template <typename T>
+static void launch_quant_int8(const void* K, const void* V, int64_t in_sb, int64_t in_sh, int64_t in_ss, int B, int H, int S, int D, int page,
+                              uint8_t* Kc, uint8_t* Vc, int64_t c_sb, int64_t c_sh, int64_t c_ss,
+                              uint16_t* Ks, uint16_t* Km, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+                              uint16_t* Vs, uint16_t* Vm, int64_t vm_sb, int64_t vm_sh, cudaStream_t st) {
+    if (K) {
+        const int64_t warps = (int64_t)B * H * ((S + page - 1) / page);
+        quant_k_int8_kernel<T><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(static_cast<const T*>(K), in_sb, in_sh, in_ss, B, H, S, D, page,
+                                                                          Kc, c_sb, c_sh, c_ss, Ks, Km, km_sb, km_sh, km_sp);
+    }
+    if (V) {
+        const int64_t warps = (int64_t)B * H * S;
+        quant_v_int8_kernel<T><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(static_cast<const T*>(V), in_sb, in_sh, in_ss, B, H, S, D,
+                                                                          Vc, c_sb, c_sh, c_ss, Vs, Vm, vm_sb, vm_sh);
+    }
+}
+
+}  // namespace fq
+
+extern "C" int fq_quantize_kv_int8(
+    const void* K, const void* V, int64_t in_sb, int64_t in_sh, int64_t in_ss, int dtype, int B, int H, int S, int D, int page,
+    uint8_t* K_uint8, uint8_t* V_uint8, int64_t c_sb, int64_t c_sh, int64_t c_ss,
+    void* K_scale, void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    void* V_scale, void* V_mn, int64_t vm_sb, int64_t vm_sh, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_quantize_kv_int8";
+    FQ_CHECK_ARG(B > 0 && H > 0 && S >= 0 && D > 0 && page > 0, FQ_ERR_ARG, "%s: bad sizes", fn);
+    FQ_CHECK_ARG(dtype == FQ_F32 || dtype == FQ_F16 || dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: dtype code %d", fn, dtype);
+    FQ_CHECK_ARG(!K || (K_uint8 && K_scale && K_mn), FQ_ERR_ARG, "%s: K given without its outputs", fn);
+    FQ_CHECK_ARG(!V || (V_uint8 && V_scale && V_mn), FQ_ERR_ARG, "%s: V given without its outputs", fn);
+    FQ_CHECK_ARG((int64_t)B * H * S <= 0x7fffffffLL * 4, FQ_ERR_ARG, "%s: too many tokens for one launch", fn);
+    if (S == 0) return FQ_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint16_t *ks = static_cast<uint16_t*>(K_scale), *km = static_cast<uint16_t*>(K_mn), *vs = static_cast<uint16_t*>(V_scale), *vm = static_cast<uint16_t*>(V_mn);
+    if (dtype == FQ_F32) launch_quant_int8<float>(K, V, in_sb, in_sh, in_ss, B, H, S, D, page, K_uint8, V_uint8, c_sb, c_sh, c_ss, ks, km, km_sb, km_sh, km_sp, vs, vm, vm_sb, vm_sh, st);
+    else if (dtype == FQ_F16) launch_quant_int8<__half>(K, V, in_sb, in_sh, in_ss, B, H, S, D, page, K_uint8, V_uint8, c_sb, c_sh, c_ss, ks, km, km_sb, km_sh, km_sp, vs, vm, vm_sb, vm_sh, st);
+    else launch_quant_int8<__nv_bfloat16>(K, V, in_sb, in_sh, in_ss, B, H, S, D, page, K_uint8, V_uint8, c_sb, c_sh, c_ss, ks, km, km_sb, km_sh, km_sp, vs, vm, vm_sb, vm_sh, st);
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+
+extern "C" int fq_dequantize_int8(
+    const uint8_t* codes, int64_t c_sb, int64_t c_sh, int64_t c_ss,
+    const void* scale, const void* mn, int64_t m_sb, int64_t m_sh, int64_t m_s2,
+    int per_page, int B, int H, int S, int D, int page, void* out, int64_t o_sb, int64_t o_sh, int64_t o_ss, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_dequantize_int8";
+    FQ_CHECK_ARG(B > 0 && H > 0 && S >= 0 && D > 0 && page > 0, FQ_ERR_ARG, "%s: bad sizes", fn);
+    if (S == 0) return FQ_OK;
+    FQ_CHECK_ARG(codes && scale && mn && out, FQ_ERR_ARG, "%s: null pointer", fn);
+    const int64_t total = (int64_t)B * H * S * D;
+    const int64_t want = (total + 255) / 256;
+    dequant_int8_kernel<<<(unsigned)(want < 148 * 16 ? want : 148 * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        codes, c_sb, c_sh, c_ss, static_cast<const uint16_t*>(scale), static_cast<const uint16_t*>(mn), m_sb, m_sh, m_s2, per_page,
+        B, H, S, D, page, static_cast<uint16_t*>(out), o_sb, o_sh, o_ss);
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}
+
+extern "C" size_t fq_sparse_decode_int8_workspace_bytes(int B, int Hq, int D, int n_split) {
+    if (B <= 0 || Hq <= 0 || D <= 0 || n_split < 1) return 0;
+    return (size_t)n_split * B * Hq * (D + 1) * 4;
+}
+
+extern "C" int fq_sparse_decode_int8(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_uint8, const uint8_t* V_uint8, int64_t kv_sb, int64_t kv_sh, int64_t kv_ss,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, float* lse, void* workspace, size_t workspace_bytes, int n_split, void* stream) {
+    using namespace fq;
+    const char* fn = "fq_sparse_decode_int8";
+    FQ_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && S_kv >= 0 && P >= 0 && bucket >= 0 && tail_len >= 0 && page > 0, FQ_ERR_ARG, "%s: bad sizes", fn);
+    FQ_CHECK_ARG(B <= 65535 && Hq <= 65535, FQ_ERR_ARG, "%s: B and H_q must be <= 65535", fn);
+    FQ_CHECK_ARG(Hq % Hkv == 0, FQ_ERR_ARG, "%s: H_q=%d must be divisible by H_kv=%d", fn, Hq, Hkv);
+    FQ_CHECK_ARG(D == 64 || D == 128, FQ_ERR_UNSUPPORTED, "%s: head_dim=%d not in (64, 128)", fn, D);
+    FQ_CHECK_ARG(q_dtype == FQ_F16 || q_dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: Q must be fp16 or bf16 (code %d)", fn, q_dtype);
+    FQ_CHECK_ARG(Q && O, FQ_ERR_ARG, "%s: null Q or O", fn);
+    FQ_CHECK_ARG(n_split >= 1 && n_split <= 1024, FQ_ERR_ARG, "%s: n_split=%d must be in [1, 1024]", fn, n_split);
+    const bool have_pages = bucket > 0 && P > 0 && S_kv > 0;
+    if (have_pages) FQ_CHECK_ARG(K_uint8 && V_uint8 && K_scale && K_mn && V_scale && V_mn && compact, FQ_ERR_ARG, "%s: null cache pointer", fn);
+    if (tail_len > 0) {
+        FQ_CHECK_ARG(K_tail && V_tail, FQ_ERR_ARG, "%s: null tail pointer", fn);
+        FQ_CHECK_ARG(tail_dtype == FQ_F16 || tail_dtype == FQ_BF16, FQ_ERR_DTYPE, "%s: tail must be fp16 or bf16", fn);
+    }
+    const size_t need = fq_sparse_decode_int8_workspace_bytes(B, Hq, D, n_split);
+    FQ_CHECK_ARG(workspace && workspace_bytes >= need, FQ_ERR_WORKSPACE, "%s: workspace of %zu B needed, %zu given", fn, need, workspace_bytes);
+    Int8AttnParams p;
+    p.Q = Q; p.q_dtype = q_dtype; p.q_sb = q_sb; p.q_sh = q_sh;
+    p.K = K_uint8; p.V = V_uint8; p.kv_sb = kv_sb; p.kv_sh = kv_sh; p.kv_ss = kv_ss;
+    p.K_scale = static_cast<const uint16_t*>(K_scale); p.K_mn = static_cast<const uint16_t*>(K_mn); p.km_sb = km_sb; p.km_sh = km_sh; p.km_sp = km_sp;
+    p.V_scale = static_cast<const uint16_t*>(V_scale); p.V_mn = static_cast<const uint16_t*>(V_mn); p.vm_sb = vm_sb; p.vm_sh = vm_sh;
+    p.compact = compact; p.cp_sb = cp_sb; p.cp_sh = cp_sh; p.bucket = have_pages ? bucket : 0;
+    p.K_tail = K_tail; p.V_tail = V_tail; p.tail_dtype = tail_dtype; p.tl_sb = tl_sb; p.tl_sh = tl_sh; p.tl_ss = tl_ss; p.tail_len = tail_len;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S_kv = S_kv; p.P = P; p.page = page; p.sm_scale = sm_scale;
+    p.n_split = n_split;
+    p.part_o = static_cast<float*>(workspace);
+    p.part_lse = p.part_o + (size_t)n_split * B * Hq * D;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid((unsigned)n_split, (unsigned)Hq, (unsigned)B);
+    if (D == 128) sparse_decode_int8_kernel<128><<<grid, 128, 0, st>>>(p);
+    else sparse_decode_int8_kernel<64><<<grid, 128, 0, st>>>(p);
+    FQ_CHECK_LAUNCH(fn);
+    const int64_t rows = (int64_t)B * Hq;
+    int8_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, n_split, rows, D, O, q_dtype, lse);
+    FQ_CHECK_LAUNCH(fn);
+    return FQ_OK;
+}

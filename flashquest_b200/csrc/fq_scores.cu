@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
     const uint16_t* __restrict__ K_scale, const uint16_t* __restrict__ K_mn,
     int64_t km_sb, int64_t km_sh, int64_t km_sp,
     int Hq, int Hkv, int P, int D, int head_off,
-    float* __restrict__ scores, int64_t sc_sb, int64_t sc_sh, const int* __restrict__ pos, int pos_new, int pos_page) {
+    float* __restrict__ scores, int64_t sc_sb, int64_t sc_sh, const int* __restrict__ pos, int pos_new, int pos_page, float levels) {
     const int b = blockIdx.z, hkv = blockIdx.y;
     const int n_rep = Hq / Hkv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
                 if (l == r) { v1 = t1[r]; v2 = t2[r]; }
             }
             const int hq = hkv * n_rep + head_off + l;
-            scores[b * sc_sb + hq * sc_sh + p] = __fadd_rn(v1, __fmul_rn(v2, 15.0f));
+            scores[b * sc_sb + hq * sc_sh + p] = __fadd_rn(v1, __fmul_rn(v2, levels));
         }
     }
 }
@@ -122,12 +122,12 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
 template <typename QT, int NR>
 static void launch_scores(int CH, dim3 grid, cudaStream_t st, const void* Q, int64_t q_sb, int64_t q_sh,
                           const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
-                          int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh, const DynPos& dp) {
+                          int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh, const DynPos& dp, float levels) {
 #define FQ_LAUNCH_SC(CHV)                                                                              \
     launch_k(PDL_SCORES, page_scores_kernel<QT, NR, CHV>, grid, dim3(SCORE_THREADS), 0, st,                        \
              static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),             \
              static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh,        \
-             dp.pos, dp.n_new, dp.page)
+             dp.pos, dp.n_new, dp.page, levels)
     if (CH == 1) FQ_LAUNCH_SC(1);
     else if (CH == 2) FQ_LAUNCH_SC(2);
     else FQ_LAUNCH_SC(4);
@@ -137,8 +137,8 @@ static void launch_scores(int CH, dim3 grid, cudaStream_t st, const void* Q, int
 template <typename QT>
 static void launch_scores_nr(int nr, int CH, dim3 grid, cudaStream_t st, const void* Q, int64_t q_sb, int64_t q_sh,
                              const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
-                             int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh, const DynPos& dp) {
-#define FQ_ARGS CH, grid, st, Q, q_sb, q_sh, K_scale, K_mn, km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh, dp
+                             int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh, const DynPos& dp, float levels) {
+#define FQ_ARGS CH, grid, st, Q, q_sb, q_sh, K_scale, K_mn, km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh, dp, levels
     if (nr == 1) launch_scores<QT, 1>(FQ_ARGS);
     else if (nr == 2) launch_scores<QT, 2>(FQ_ARGS);
     else if (nr == 3) launch_scores<QT, 3>(FQ_ARGS);
@@ -150,8 +150,8 @@ int page_scores_int4_launch(
     const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
     const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
     int B, int Hq, int Hkv, int P, int D,
-    float* scores, int64_t sc_sb, int64_t sc_sh, void* stream, const DynPos& dp) {
-    const char* fn = "fq_page_scores_int4";
+    float* scores, int64_t sc_sb, int64_t sc_sh, void* stream, const DynPos& dp, float levels) {
+    const char* fn = levels == 255.0f ? "fq_page_scores_int8" : "fq_page_scores_int4";
     FQ_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && P >= 0, FQ_ERR_ARG, "%s: bad sizes", fn);
     FQ_CHECK_ARG(Hq % Hkv == 0, FQ_ERR_ARG, "%s: H_q=%d must be divisible by H_kv=%d", fn, Hq, Hkv);
     FQ_CHECK_ARG(D == 32 || D == 64 || D == 128 || D == 256, FQ_ERR_UNSUPPORTED, "%s: head_dim %d not in {32,64,128,256}", fn, D);
@@ -169,7 +169,7 @@ int page_scores_int4_launch(
     // query heads of a group are served four at a time (one pass over the metadata per four)
     for (int off = 0; off < n_rep; off += 4) {
         const int nr = n_rep - off < 4 ? n_rep - off : 4;
-#define FQ_ARGS nr, CH, grid, st, Q, q_sb, q_sh, K_scale, K_mn, km_sb, km_sh, km_sp, Hq, Hkv, P, D, off, scores, sc_sb, sc_sh, dp
+#define FQ_ARGS nr, CH, grid, st, Q, q_sb, q_sh, K_scale, K_mn, km_sb, km_sh, km_sp, Hq, Hkv, P, D, off, scores, sc_sb, sc_sh, dp, levels
         if (q_dtype == FQ_F32) launch_scores_nr<float>(FQ_ARGS);
         else if (q_dtype == FQ_F16) launch_scores_nr<__half>(FQ_ARGS);
         else launch_scores_nr<__nv_bfloat16>(FQ_ARGS);
@@ -187,5 +187,14 @@ extern "C" int fq_page_scores_int4(
     int B, int Hq, int Hkv, int P, int D,
     float* scores, int64_t sc_sb, int64_t sc_sh, void* stream) {
     return fq::page_scores_int4_launch(Q, q_dtype, q_sb, q_sh, K_scale, K_mn, km_sb, km_sh, km_sp, B, Hq, Hkv, P, D,
-                                       scores, sc_sb, sc_sh, stream, fq::DynPos{});
+                                       scores, sc_sb, sc_sh, stream, fq::DynPos{}, 15.0f);
+}
+
+extern "C" int fq_page_scores_int8(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int B, int Hq, int Hkv, int P, int D,
+    float* scores, int64_t sc_sb, int64_t sc_sh, void* stream) {
+    return fq::page_scores_int4_launch(Q, q_dtype, q_sb, q_sh, K_scale, K_mn, km_sb, km_sh, km_sp, B, Hq, Hkv, P, D,
+                                       scores, sc_sb, sc_sh, stream, fq::DynPos{}, 255.0f);
 }

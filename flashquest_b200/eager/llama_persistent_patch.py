@@ -10,7 +10,7 @@ embedding, appends k/v to the persistent cache and attends:
   * decode (S_q == 1, reference :202-245): page scores from the quantised metadata, static-k_max
     top-k with per-head retention from the head pattern, sparse attention over the selected
     pages, tail attention over the staged tokens and the LSE merge.
-      kv_bits == 4, use_compact_kernel=False: the reference's own sequence of steps — bool
+      kv_bits == 4 or 8, use_compact_kernel=False: the reference's own sequence of steps — bool
         mask, sparse kernel, separate tail attention, two-way merge of bf16 partial results;
       kv_bits == 4, use_compact_kernel=True: ONE foreign call per layer (fq_decode_layer_int4:
         append + scores + top-k with compact index + attention with the tail in the same softmax);
@@ -26,10 +26,12 @@ from typing import Optional
 import torch
 from transformers.models.llama.modeling_llama import LlamaAttention, apply_rotary_pos_emb
 
-from ..kernel.kv_quant import dequantize_k_int4, dequantize_k_turbo, dequantize_v_int4, dequantize_v_turbo
+from ..kernel.kv_quant import (dequantize_k, dequantize_k_int4, dequantize_k_turbo, dequantize_v, dequantize_v_int4,
+                               dequantize_v_turbo)
 from ..kernel.prefill_attn import prefill_causal_attention
+from ..kernel.sparse_fwd import flash_attn_sparse_fwd
 from ..kernel.sparse_int4_fwd import flash_attn_sparse_int4_fwd
-from .criticality import page_scores_int4_fast
+from .criticality import page_scores_int4_fast, page_scores_int8_fast
 from .decode_step import QuestDecodeInt4, QuestDecodeTurbo
 from .selection import select_pages_vectorized
 from .tail_merge import _bf16_dense_attn_with_lse, _merge_two_attentions
@@ -91,7 +93,11 @@ def make_quest_persistent_forward(
         def _dequant_v_from_views(views):
             return dequantize_v_int4(views["V_packed"], views["V_scale"], views["V_mn"])
     elif kv_bits == 8:
-        raise NotImplementedError("cache.kv_bits=8 (INT8 KV) has no kernels in flashquest_b200; use kv_bits 4 or 3")
+        def _dequant_k_from_views(views):
+            return dequantize_k(views["K_uint8"], views["K_scale"], views["K_mn"], page_size=page_size)
+
+        def _dequant_v_from_views(views):
+            return dequantize_v(views["V_uint8"], views["V_scale"], views["V_mn"])
     else:
         raise ValueError(f"unsupported cache.kv_bits={kv_bits!r}")
     if page_size != cache.page_size:
@@ -165,13 +171,20 @@ def make_quest_persistent_forward(
                     torch.full((H_q,), retention, device=q.device),
                     torch.zeros(H_q, device=q.device),
                 )
-                scores = page_scores_int4_fast(q, views["K_scale"], views["K_mn"])
+                score_fn = page_scores_int4_fast if kv_bits == 4 else page_scores_int8_fast
+                scores = score_fn(q, views["K_scale"], views["K_mn"])
                 sel = select_pages_vectorized(scores, retention=retention_per_q, num_sinks=num_sinks,
                                               window_pages=window_pages, k_max_static=k_max_static)
-                O_sparse, lse_sparse = flash_attn_sparse_int4_fwd(
-                    q, views["K_packed"], views["K_scale"], views["K_mn"],
-                    views["V_packed"], views["V_scale"], views["V_mn"],
-                    selection_mask=sel, page_size=page_size, return_lse=True)
+                if kv_bits == 4:
+                    O_sparse, lse_sparse = flash_attn_sparse_int4_fwd(
+                        q, views["K_packed"], views["K_scale"], views["K_mn"],
+                        views["V_packed"], views["V_scale"], views["V_mn"],
+                        selection_mask=sel, page_size=page_size, return_lse=True)
+                else:
+                    O_sparse, lse_sparse = flash_attn_sparse_fwd(
+                        q, views["K_uint8"], views["K_scale"], views["K_mn"],
+                        views["V_uint8"], views["V_scale"], views["V_mn"],
+                        selection_mask=sel, page_size=page_size, return_lse=True)
                 if partial_len == 0:
                     attn_bhsd = O_sparse
                 else:

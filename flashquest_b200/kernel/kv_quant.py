@@ -121,6 +121,83 @@ def dequantize_v_int4(V_packed, scale, mn) -> torch.Tensor:
     return _dequantize_int4(V_packed, scale, mn, 1, False)
 
 
+# === INT8 KV variant (kernel/kv_quant.py:18-103) ===
+
+def quantize_kv_int8_into(K, V, page_size, *, K_uint8=None, K_scale=None, K_mn=None, V_uint8=None, V_scale=None, V_mn=None):
+    """One call of fq_quantize_kv_int8 writing into (possibly strided) output views; K or V may be None."""
+    ref = K if K is not None else V
+    require_cuda(ref)
+    B, H, S, D = ref.shape
+    K = inner_contiguous(K) if K is not None else None
+    V = inner_contiguous(V) if V is not None else None
+    if K is not None and V is not None and _strides3(K) != _strides3(V):
+        K, V = K.contiguous(), V.contiguous()
+    src = K if K is not None else V
+    cod = K_uint8 if K_uint8 is not None else V_uint8
+    if K_uint8 is not None and V_uint8 is not None and _strides3(K_uint8) != _strides3(V_uint8):
+        raise ValueError("K_uint8 and V_uint8 must share their strides")
+    z3 = (0, 0, 0)
+    with torch.cuda.device(ref.device):
+        check(lib().fq_quantize_kv_int8(
+            ptr(K), ptr(V), *_strides3(src), dtype_code(ref), B, H, S, D, int(page_size),
+            ptr(K_uint8), ptr(V_uint8), *_strides3(cod),
+            ptr(K_scale), ptr(K_mn), *(_strides3(K_scale) if K_scale is not None else z3),
+            ptr(V_scale), ptr(V_mn), *(V_scale.stride()[:2] if V_scale is not None else (0, 0)),
+            stream_ptr(ref.device)))
+
+
+def quantize_k(K: torch.Tensor, page_size: int):
+    """uint8 K with per-page per-channel (scale, mn) (kernel/kv_quant.py:45).
+    Returns (K_uint8 (B,H,S,D), scale (B,H,num_pages,D) bf16, mn (B,H,num_pages,D) bf16)."""
+    B, H, S, D = K.shape
+    require_cuda(K)
+    P = (S + page_size - 1) // page_size
+    codes = torch.empty(B, H, S, D, dtype=torch.uint8, device=K.device)
+    scale = torch.empty(B, H, P, D, dtype=torch.bfloat16, device=K.device)
+    mn = torch.empty(B, H, P, D, dtype=torch.bfloat16, device=K.device)
+    if S > 0:
+        quantize_kv_int8_into(K, None, page_size, K_uint8=codes, K_scale=scale, K_mn=mn)
+    return codes, scale, mn
+
+
+def quantize_v(V: torch.Tensor):
+    """uint8 V per token (kernel/kv_quant.py:81).  Returns (V_uint8 (B,H,S,D), scale (B,H,S,1) bf16, mn (B,H,S,1) bf16)."""
+    B, H, S, D = V.shape
+    require_cuda(V)
+    codes = torch.empty(B, H, S, D, dtype=torch.uint8, device=V.device)
+    scale = torch.empty(B, H, S, 1, dtype=torch.bfloat16, device=V.device)
+    mn = torch.empty(B, H, S, 1, dtype=torch.bfloat16, device=V.device)
+    if S > 0:
+        quantize_kv_int8_into(None, V, 16, V_uint8=codes, V_scale=scale, V_mn=mn)
+    return codes, scale, mn
+
+
+def _dequantize_int8(codes, scale, mn, page_size, per_page):
+    require_cuda(codes, scale, mn)
+    B, H, S, D = codes.shape
+    codes = inner_contiguous(codes)
+    scale, mn = inner_contiguous(scale), inner_contiguous(mn)
+    if _strides3(scale) != _strides3(mn):
+        scale, mn = scale.contiguous(), mn.contiguous()
+    out = torch.empty(B, H, S, D, dtype=torch.bfloat16, device=codes.device)
+    if S > 0:
+        with torch.cuda.device(codes.device):
+            check(lib().fq_dequantize_int8(ptr(codes), *_strides3(codes), ptr(scale), ptr(mn), *_strides3(scale),
+                                           1 if per_page else 0, B, H, S, D, int(page_size), ptr(out), *_strides3(out),
+                                           stream_ptr(codes.device)))
+    return out
+
+
+def dequantize_k(K_uint8, scale, mn, page_size: int) -> torch.Tensor:
+    """Inverse of quantize_k (kernel/kv_quant.py:65).  Returns bf16."""
+    return _dequantize_int8(K_uint8, scale, mn, page_size, True)
+
+
+def dequantize_v(V_uint8, scale, mn) -> torch.Tensor:
+    """Inverse of quantize_v (kernel/kv_quant.py:96).  Returns bf16."""
+    return _dequantize_int8(V_uint8, scale, mn, 1, False)
+
+
 # === TurboQuant K3-V3 (kernel/kv_quant.py:225-420) ===
 
 K_TURBO_CODEBOOK_VALUES = (-2.1519, -1.3439, -0.7560, -0.2451, 0.2451, 0.7560, 1.3439, 2.1519)

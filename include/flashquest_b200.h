@@ -139,6 +139,47 @@ int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
                      int32_t* compact, int64_t cp_sr, int bucket, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * INT8 KV variant (cache.kv_bits == 8): KIVI-style asymmetric uint8, one code per byte.
+ * fq_quantize_kv_int8 replaces quantize_k / quantize_v (kernel/kv_quant.py:45-62, :81-93):
+ *   K per page and channel, scale = (mx - mn) / 255 and mn in the INPUT dtype, eps clamp 1e-6,
+ *   codes = clamp(rint((K_f32 - mn) / scale), 0, 255); V per token in fp32; metadata stored bf16.
+ *   K, V (B,H,S,D) dtype with strides in_sb,in_sh,in_ss (either may be NULL); codes (B,H,S,D) u8
+ *   strides c_sb,c_sh,c_ss; K_scale,K_mn (B,H,P,D) bf16; V_scale,V_mn (B,H,S) bf16.
+ * fq_dequantize_int8 replaces dequantize_k / dequantize_v (:65-78, :96-103): bf16(code*scale + mn).
+ * fq_page_scores_int8 replaces page_scores_int8_fast (eager/criticality.py:77-125): the INT4 score
+ *   with 255 levels, same fixed summation order.
+ * fq_sparse_decode_int8 replaces flash_attn_sparse_fwd (kernel/sparse_fwd.py:140-228) over a compact
+ *   page list (as fq_sparse_decode_int4; a bool mask goes through fq_build_compact first), with the
+ *   optional staged tail in the same softmax.  O (B,Hq,D) q_dtype dense, lse (B,Hq) fp32 or NULL.
+ *   workspace: fq_sparse_decode_int8_workspace_bytes(B,Hq,D,n_split) bytes, always needed, no
+ *   initial contents required.
+ */
+int fq_quantize_kv_int8(
+    const void* K, const void* V, int64_t in_sb, int64_t in_sh, int64_t in_ss, int dtype, int B, int H, int S, int D, int page,
+    uint8_t* K_uint8, uint8_t* V_uint8, int64_t c_sb, int64_t c_sh, int64_t c_ss,
+    void* K_scale, void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    void* V_scale, void* V_mn, int64_t vm_sb, int64_t vm_sh, void* stream);
+int fq_dequantize_int8(
+    const uint8_t* codes, int64_t c_sb, int64_t c_sh, int64_t c_ss,
+    const void* scale, const void* mn, int64_t m_sb, int64_t m_sh, int64_t m_s2,
+    int per_page, int B, int H, int S, int D, int page, void* out, int64_t o_sb, int64_t o_sh, int64_t o_ss, void* stream);
+int fq_page_scores_int8(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int B, int Hq, int Hkv, int P, int D,
+    float* scores, int64_t sc_sb, int64_t sc_sh, void* stream);
+size_t fq_sparse_decode_int8_workspace_bytes(int B, int Hq, int D, int n_split);
+int fq_sparse_decode_int8(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_uint8, const uint8_t* V_uint8, int64_t kv_sb, int64_t kv_sh, int64_t kv_ss,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, float* lse, void* workspace, size_t workspace_bytes, int n_split, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Dense causal attention of the prefill branch (S_q > 1).
  * Replaces the torch.nn.functional.scaled_dot_product_attention(q, K_full, V_full,
  * is_causal=True, enable_gqa=True) call of the patched forward

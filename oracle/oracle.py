@@ -26,7 +26,8 @@ __all__ = [
     "k_page_meta_int4", "wht_along_head_dim", "quantize_k_turbo", "quantize_v_turbo",
     "dequantize_k_turbo", "dequantize_v_turbo", "turbo_codebook", "page_scores_int4_fast",
     "k_per_head", "select_pages_vectorized", "build_compact_selection", "sparse_attn_int4",
-    "sparse_attn_turbo", "sparse_attn_turbo_rotated", "lse_merge", "awq_gemv", "awq_pack", "set_num_threads",
+    "sparse_attn_turbo", "sparse_attn_turbo_rotated", "lse_merge", "quantize_k", "quantize_v", "dequantize_k", "dequantize_v",
+    "page_scores_int8_fast", "sparse_attn_int8", "awq_gemv", "awq_pack", "set_num_threads",
 ]
 
 
@@ -344,6 +345,94 @@ def lse_merge(O_parts: torch.Tensor, lse_parts: torch.Tensor):
     O = torch.empty(O_parts.shape[1:], dtype=torch.float32)
     lse = torch.empty(lse_parts.shape[1:], dtype=torch.float32)
     _load().orc_lse_merge(_p(Op), _p(lp), n, ctypes.c_long(rows), D, _p(O), _p(lse))
+    return O, lse
+
+
+# ---------------------------------------------------------------- INT8 KV variant
+
+def quantize_k(K: torch.Tensor, page_size: int):
+    """kernel/kv_quant.py:45 — (K_uint8 (B,H,S,D), scale, mn (B,H,P,D) bf16)."""
+    B, H, S, D = K.shape
+    P = (S + page_size - 1) // page_size
+    K = _c(K)
+    codes = torch.empty(B, H, S, D, dtype=torch.uint8)
+    scale = torch.empty(B, H, P, D, dtype=torch.bfloat16)
+    mn = torch.empty(B, H, P, D, dtype=torch.bfloat16)
+    _load().orc_quantize_k_int8(_p(K), _dt(K), B, H, S, D, page_size, _p(codes), _p(scale), _p(mn))
+    return codes, scale, mn
+
+
+def quantize_v(V: torch.Tensor):
+    """kernel/kv_quant.py:81 — (V_uint8 (B,H,S,D), scale, mn (B,H,S,1) bf16)."""
+    B, H, S, D = V.shape
+    V = _c(V)
+    codes = torch.empty(B, H, S, D, dtype=torch.uint8)
+    scale = torch.empty(B, H, S, 1, dtype=torch.bfloat16)
+    mn = torch.empty(B, H, S, 1, dtype=torch.bfloat16)
+    _load().orc_quantize_v_int8(_p(V), _dt(V), ctypes.c_long(B * H * S), D, _p(codes), _p(scale), _p(mn))
+    return codes, scale, mn
+
+
+def _dequantize_int8(codes, scale, mn, page_size, per_page):
+    B, H, S, D = codes.shape
+    out = torch.empty(B, H, S, D, dtype=torch.bfloat16)
+    _load().orc_dequantize_int8(_p(_c(codes)), _p(_c(scale)), _p(_c(mn)), ctypes.c_long(B * H), S, D, int(page_size),
+                                1 if per_page else 0, _p(out))
+    return out
+
+
+def dequantize_k(K_uint8, scale, mn, page_size: int):
+    """kernel/kv_quant.py:65."""
+    return _dequantize_int8(K_uint8, scale, mn, page_size, True)
+
+
+def dequantize_v(V_uint8, scale, mn):
+    """kernel/kv_quant.py:96."""
+    return _dequantize_int8(V_uint8, scale, mn, 1, False)
+
+
+def page_scores_int8_fast(Q, K_scale, K_mn):
+    """eager/criticality.py:77 — (B,H_q,1,P) fp32, same fixed summation order as page_scores_int4_fast."""
+    B, H_q, S_q, D = Q.shape
+    if S_q != 1:
+        raise NotImplementedError("oracle page scores are decode-only (S_q == 1)")
+    H_kv, P = K_scale.shape[1], K_scale.shape[2]
+    if H_q % H_kv != 0:
+        raise ValueError(f"H_q={H_q} must be divisible by H_kv={H_kv}")
+    Q = _c(Q)
+    out = torch.empty(B, H_q, 1, P, dtype=torch.float32)
+    _load().orc_page_scores_int8(_p(Q), _dt(Q), _p(_c(K_scale)), _p(_c(K_mn)), B, H_q, H_kv, P, D, _p(out))
+    return out
+
+
+def sparse_attn_int8(Q, K_uint8, K_scale, K_mn, V_uint8, V_scale, V_mn, *, selection_mask=None, selected_page_ids=None,
+                     page_size=64, sm_scale=None, K_partial=None, V_partial=None):
+    """kernel/sparse_fwd.py:140 semantics in fp64 accumulation (+ optional staged tail).  Returns (O fp32, lse)."""
+    B, H_q, S_q, D = Q.shape
+    if S_q != 1:
+        raise NotImplementedError(f"decode-only (S_q={S_q})")
+    H_kv, S_kv = K_uint8.shape[1], K_uint8.shape[2]
+    P = K_scale.shape[2]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    Q = _c(Q)
+    m8 = comp = None
+    bucket = 0
+    if selection_mask is not None:
+        m8 = _c(selection_mask.reshape(B, H_q, P).to(torch.uint8))
+    elif selected_page_ids is not None:
+        comp = _c(selected_page_ids.reshape(B, H_q, -1).to(torch.int32))
+        bucket = comp.shape[-1]
+    tail_len, kt, vt, tail_dt = 0, None, None, 2
+    if K_partial is not None and K_partial.shape[2] > 0:
+        kt, vt = _c(K_partial), _c(V_partial)
+        tail_len, tail_dt = kt.shape[2], _dt(kt)
+    O = torch.empty(B, H_q, 1, D, dtype=torch.float32)
+    lse = torch.empty(B, H_q, 1, dtype=torch.float32)
+    _load().orc_sparse_attn_int8(
+        _p(Q), _dt(Q), _p(_c(K_uint8)), _p(_c(K_scale)), _p(_c(K_mn)), _p(_c(V_uint8)), _p(_c(V_scale)), _p(_c(V_mn)),
+        _p(m8), _p(comp), bucket, _p(kt), _p(vt), tail_dt, tail_len,
+        B, H_q, H_kv, S_kv, P, D, int(page_size), ctypes.c_float(sm_scale), _p(O), _p(lse))
     return O, lse
 
 

@@ -55,6 +55,9 @@ class _OracleCheck:
             if self.bits == 4:
                 kq, vq = oracle.quantize_k_int4(K[:, :, :nq], page), oracle.quantize_v_int4(V[:, :, :nq])
                 Kd, Vd = oracle.dequantize_k_int4(*kq, page), oracle.dequantize_v_int4(*vq)
+            elif self.bits == 8:
+                kq, vq = oracle.quantize_k(K[:, :, :nq], page), oracle.quantize_v(V[:, :, :nq])
+                Kd, Vd = oracle.dequantize_k(*kq, page), oracle.dequantize_v(*vq)
             else:
                 kq, vq = oracle.quantize_k_turbo(K[:, :, :nq], page), oracle.quantize_v_turbo(V[:, :, :nq])
                 Kd = oracle.dequantize_k_turbo(kq[0], kq[1], kq[2], head_dim=K.shape[-1])
@@ -66,14 +69,16 @@ class _OracleCheck:
             return
         Kt, Vt = K[:, :, nq:], V[:, :, nq:]
         r = self.ret[li]
-        if self.bits == 4:
-            kv = oracle.quantize_k_int4(K[:, :, :nq], page) + oracle.quantize_v_int4(V[:, :, :nq])
+        if self.bits in (4, 8):
+            qk, qv, sc, at = ((oracle.quantize_k_int4, oracle.quantize_v_int4, oracle.page_scores_int4_fast, oracle.sparse_attn_int4)
+                              if self.bits == 4 else
+                              (oracle.quantize_k, oracle.quantize_v, oracle.page_scores_int8_fast, oracle.sparse_attn_int8))
+            kv = qk(K[:, :, :nq], page) + qv(V[:, :, :nq])
             if nq:
-                mask = oracle.select_pages_vectorized(oracle.page_scores_int4_fast(q, kv[1], kv[2]), r, self.sinks, self.window,
-                                                      k_max_static=self.kms)
+                mask = oracle.select_pages_vectorized(sc(q, kv[1], kv[2]), r, self.sinks, self.window, k_max_static=self.kms)
             else:
                 mask = torch.zeros(q.shape[0], q.shape[1], 1, 0, dtype=torch.bool)
-            want, _ = oracle.sparse_attn_int4(q, *kv, selection_mask=mask, page_size=page, K_partial=Kt, V_partial=Vt)
+            want, _ = at(q, *kv, selection_mask=mask, page_size=page, K_partial=Kt, V_partial=Vt)
             tol = 2e-3 + 2 ** -8 * want.abs() * (1 if self.fused else 3)   # separate bf16 partials + merge: two more roundings
         else:
             kq, vq = oracle.quantize_k_turbo(K[:, :, :nq], page), oracle.quantize_v_turbo(V[:, :, :nq])
@@ -106,14 +111,15 @@ def _run(model, cache, ids_prompt, ids_steps):
     return torch.cat(outs, 1)
 
 
-@pytest.mark.parametrize("kv_bits,page", [(4, 8), (4, 16), (3, 16)])
+@pytest.mark.parametrize("kv_bits,page", [(4, 8), (4, 16), (3, 16), (8, 16)])
 def test_patched_forward_paths_and_oracle(kv_bits, page):
     from flashquest_b200.cache.persistent_int4 import PersistentInt4KVCache
+    from flashquest_b200.cache.persistent_int8 import PersistentInt8KVCache
     from flashquest_b200.cache.persistent_turbo import PersistentTurboKVCache
     from flashquest_b200.eager import llama_persistent_patch as lpp
     from transformers.cache_utils import Cache
     cfg, model_a = _tiny_llama()
-    Cls = PersistentInt4KVCache if kv_bits == 4 else PersistentTurboKVCache
+    Cls = {4: PersistentInt4KVCache, 8: PersistentInt8KVCache, 3: PersistentTurboKVCache}[kv_bits]
     mk = lambda: Cls(num_layers=2, batch_size=1, num_kv_heads=2, head_dim=64, page_size=page, max_seq_len=128)
     cache_a = mk()
     assert isinstance(cache_a, Cache) and cache_a.kv_bits == kv_bits
