@@ -86,8 +86,7 @@ class LlamaModelDesc(ctypes.Structure):
 class LlamaScratchDesc(ctypes.Structure):
     """struct fq_llama_scratch."""
     _fields_ = [("resid0", P), ("resid1", P), ("normed", P), ("q", P), ("k", P), ("v", P), ("attn_out", P), ("down", P),
-                ("gate", P), ("up", P), ("act", P), ("logits", P), ("next_ids", P),
-                ("gemv_ws", P * 4), ("gemv_ws_bytes", Z * 4),
+                ("gate", P), ("up", P), ("logits", P), ("next_ids", P),
                 ("scores", P), ("sc_sl", L), ("compact", P), ("cp_sl", L), ("O", P), ("o_sl", L),
                 ("attn_ws", P), ("attn_ws_sl", Z), ("attn_ws_bytes", Z)]
 
@@ -95,9 +94,22 @@ class LlamaScratchDesc(ctypes.Structure):
 _PROTOTYPES["fq_llama_decode_step"] = (I, [ctypes.POINTER(LlamaModelDesc), ctypes.POINTER(Int4CacheDesc),
                                           ctypes.POINTER(DecodeParams), P, P, I, ctypes.POINTER(LlamaScratchDesc), P])
 _PROTOTYPES["fq_llama_decode_step_dev"] = _PROTOTYPES["fq_llama_decode_step"]
-_PROTOTYPES["fq_awq_gemv_workspace_bytes"] = (Z, [I, I, I])
+
+
+class GemvPrologue(ctypes.Structure):
+    """struct fq_gemv_prologue."""
+    _fields_ = [("kind", I), ("b", P), ("weight", P), ("eps", F), ("out", P)]
+
+
+class GemvRope(ctypes.Structure):
+    """struct fq_gemv_rope."""
+    _fields_ = [("proj_mask", ctypes.c_uint), ("pos_dev", P), ("pos", I), ("theta", F), ("head_dim", I)]
+
+
+GEMV_PLAIN, GEMV_ADD_RMSNORM, GEMV_SWIGLU = 0, 1, 2
 _PROTOTYPES["fq_awq_gemv_default_splits"] = (I, [I, I, I])
-_PROTOTYPES["fq_awq_gemv"] = (I, [P, I, I, I, I, P, P, P, P, P, P, I, P, Z, I, P])
+_PROTOTYPES["fq_awq_gemv"] = (I, [P, I, I, I, I, P, P, P, P, P, P, I, I, P])
+_PROTOTYPES["fq_awq_gemv_fused"] = (I, [P, I, I, I, I, P, P, P, P, P, P, I, ctypes.POINTER(GemvPrologue), ctypes.POINTER(GemvRope), I, P])
 _PROTOTYPES["fq_awq_gemm"] = (I, [P, I, I, I, I, P, P, P, P, P, P, I, P])
 _PROTOTYPES["fq_wht"] = (I, [P, P, I, L, I, P])
 _PROTOTYPES["fq_quantize_turbo"] = (I, [P, L, L, L, I, P, L, L, L, I, I, I, I, I, I, P, L, L, L, P, L, L, L, P, L, L, L, P])

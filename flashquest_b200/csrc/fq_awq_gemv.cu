@@ -1,38 +1,49 @@
 // AWQ W4A16 GEMV for decode shapes (M <= 8 rows of activations), several projections that
-// share the same input fused into one launch (QKV, gate/up).
+// share the same input fused into one launch (QKV, gate/up), optionally with the element-wise
+// operator in front of the linear (residual add + RMSNorm, or SwiGLU) computed while the input
+// is staged and the rotary embedding applied to the outputs before they are stored.
 //
 // Layout (AutoAWQ GEMM format, flashquest/quant/awq_layout.py:18-44): qweight (K, N/8) int32
 // with eight 4-bit codes per int32 along N, scales (K/G, N) fp16, qzeros (K/G, N/8) int32;
 // w[k,n] = (code[k,n] - zero[k/G,n]) * scale[k/G,n].  In the interleaved order nibble i of an
 // int32 holds column 8c + {0,2,4,6,1,3,5,7}[i].
 //
-// HBM-bound on the weights (0.5 byte per weight, read once), so what matters is bytes in
-// flight: a CTA owns a tile of 64 int32 column packs (256 B of a weight row, 512 outputs) of ONE
+// HBM-bound on the weights (0.5 byte per weight, read once) and, at these sizes (5-26 MB per
+// launch), on latency: what matters is bytes in flight early and a short chain after the last
+// byte.  A CTA owns a tile of 32 int32 column packs (128 B of a weight row, 256 outputs) of ONE
 // projection and a range of quantisation groups; it streams the tile one group (<= 128 rows,
-// 32 KiB) at a time into a 3-stage shared-memory ring with cp.async, so up to 96 KiB per CTA are
-// outstanding however many registers the arithmetic needs.  A thread owns one pack
-// (8 outputs); the 8 warps are 2 column halves x 4 interleaved row phases.
-// Inside a group the kernel accumulates sum_k x*code in fp32: the nibble is masked in place and
-// reinterpreted as an fp32 (sub)normal, x is pre-scaled by 2^100 and duplicated so that
-// fma.rn.f32x2 handles two nibbles per issue slot; the powers of two are undone once per group,
-// where scale and zero are applied: y += scale * (sum x*code - zero * sum x).
-// Split-K over ranges of groups: partial sums go to a workspace, the CTA that draws the last
-// ticket of its tile adds them in split order and writes fp16.
+// 16 KiB) at a time through a 3- or 6-stage shared-memory ring with cp.async, the first stages requested
+// before the dependency wait (weights never change).  A thread owns one pack (8 outputs); the 8
+// warps are 8 interleaved row phases.  Inside a group the kernel accumulates sum_k x*code in fp32:
+// the nibble is masked in place and reinterpreted as an fp32 (sub)normal, x is pre-scaled by 2^100
+// and duplicated so that fma.rn.f32x2 handles two nibbles per issue slot; the powers of two are
+// undone once per group, where scale and zero are applied: y += scale * (sum x*code - zero * sum x).
+// Split-K: the CTAs that share a tile form one thread-block cluster (<= 8); each sends its partial
+// sums into the shared memory of the cluster's first CTA, which adds them in rank order after one
+// cluster barrier — no global round trip, no atomics, a fixed summation order.
 #include "fq_common.cuh"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace fq {
 
 constexpr int GEMV_THREADS = 256;
-constexpr int GEMV_PACKS = 64;          // int32 column packs per CTA (512 outputs)
+constexpr int GEMV_WARPS = GEMV_THREADS / 32;
+constexpr int GEMV_PACKS = 32;          // int32 column packs per CTA (256 outputs)
+constexpr int GEMV_TILE = GEMV_PACKS * 8;
 constexpr int GEMV_MAX_PROJ = 4;
-constexpr int GEMV_STAGES = 3;
 constexpr int GEMV_ROWS = 128;          // rows per stage = largest group size
 constexpr int GEMV_STAGE_WORDS = GEMV_ROWS * GEMV_PACKS;
+constexpr int GEMV_MAX_STAGES = 6;       // ring depth: 3 (short K ranges) or 6 (long ones: more bytes in flight per CTA)
+constexpr int GEMV_MAX_CLUSTER = 8;
 
 struct GemvProj {
     const int32_t* qweight; const __half* scales; const int32_t* qzeros; const __half* bias; __half* y;
     int N;              // outputs of this projection
     int tile0;          // first tile of this projection in the grid
+    int rope;           // rotary embedding on the outputs of this projection
 };
 
 struct GemvParams {
@@ -41,8 +52,11 @@ struct GemvParams {
     int interleaved;
     int vec16;          // every weight row starts 16-byte aligned and N % 32 == 0: 16-byte copies
     int k_split, groups_per_split;
-    float* partials;    // [k_split][M][tiles_total*512]
-    int* tickets;       // per tile
+    // operator in front of the linear
+    int pro_kind;       // FQ_GEMV_PLAIN | FQ_GEMV_ADD_RMSNORM | FQ_GEMV_SWIGLU
+    const __half* pro_b; const __half* pro_weight; float eps; __half* pro_out;
+    // rotary embedding
+    const int* pos_dev; int pos; float theta; int head_dim;
 };
 
 __device__ __forceinline__ float pow2f_i(int n) { return __int_as_float((127 + n) << 23); }
@@ -56,33 +70,38 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// values held in nibble order -> 8 consecutive output columns as fp16.  In the interleaved
-// order column j comes from nibble {0,4,1,5,2,6,3,7}[j].
-__device__ __forceinline__ uint4 pack_columns(const float (&v)[8], int interleaved, const __half* bias) {
-    float c[8];
+// fixed-order sum over the CTA: lanes by butterfly, warps in index order
+__device__ __forceinline__ float gemv_block_sum(float v, float* s_red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) c[j] = interleaved ? v[(j >> 1) + (j & 1) * 4] : v[j];
-    if (bias) {
+    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) c[j] += __half2float(bias[j]);
-    }
-    __half2 h[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(c[2 * j], c[2 * j + 1]);
-    return *reinterpret_cast<uint4*>(h);
+    for (int w = 0; w < GEMV_WARPS; ++w) t += s_red[w];
+    return t;
 }
 
-template <int M>
+// Shared memory (dynamic), in this order:
+//   s_w    [STAGES][ROWS][PACKS] u32      weight ring; after the main loop: the row-phase partial sums
+//   s_xs   [range][M] float2              (x, x) * 2^100 of the CTA's K range
+//   s_slot [cluster][M][TILE] float       partial sums of the cluster's CTAs (used in the first CTA)
+//   s_xsum [groups_per_split][M] float    sum of x per group and row
+template <int M, int GEMV_STAGES>
 __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
     extern __shared__ __align__(16) unsigned char s_raw[];
-    uint32_t* s_w = reinterpret_cast<uint32_t*>(s_raw);                                   // [STAGES][ROWS][PACKS]
-    __half* s_xh = reinterpret_cast<__half*>(s_raw + GEMV_STAGES * GEMV_STAGE_WORDS * 4);   // [STAGES][M][ROWS]
-    float2* s_xs = reinterpret_cast<float2*>(s_xh + GEMV_STAGES * M * GEMV_ROWS);          // [ROWS][M] (x,x) * 2^100
-    __shared__ float s_xsum[M];
-    __shared__ int s_ticket;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int range = p.groups_per_split * p.group;
+    uint32_t* s_w = reinterpret_cast<uint32_t*>(s_raw);
+    float2* s_xs = reinterpret_cast<float2*>(s_raw + GEMV_STAGES * GEMV_STAGE_WORDS * 4);
+    float* s_slot = reinterpret_cast<float*>(s_xs + (size_t)range * M);
+    float* s_xsum = s_slot + (size_t)p.k_split * M * GEMV_TILE;
+    __shared__ float s_red8[GEMV_WARPS];
+    __shared__ float s_rstd[M];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wn = warp & 1, wk = warp >> 1;       // column half, row phase
-    const int tile = blockIdx.x, split = blockIdx.y;
+    const int tile = blockIdx.x, split = blockIdx.y;       // split == rank in the cluster
     int pi = 0;
 #pragma unroll
     for (int i = 1; i < GEMV_MAX_PROJ; ++i)
@@ -90,12 +109,13 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
     const GemvProj pr = p.proj[pi];
     const int npk = pr.N / 8;
     const int pk0 = (tile - pr.tile0) * GEMV_PACKS;          // first pack of the tile inside the projection
-    const int c = pk0 + wn * 32 + lane;                      // this thread's pack
+    const int c = pk0 + lane;                                // this thread's pack
     const bool valid = c < npk;
     const int g_begin = split * p.groups_per_split;
     const int g_end = min(p.n_groups, g_begin + p.groups_per_split);
-    const int n_chunks = g_end - g_begin;
+    const int n_chunks = max(g_end - g_begin, 0);
     const int G = p.group;
+    const int k0 = g_begin * G, k_len = n_chunks * G;
 
     // weights of a chunk (they never change: safe to request before the previous kernel is done)
     auto issue_w = [&](int chunk) {
@@ -103,40 +123,119 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
         uint32_t* dst = s_w + st * GEMV_STAGE_WORDS;
         const int32_t* src = pr.qweight + (int64_t)g * G * npk + pk0;
         if (p.vec16) {
-            // 256 threads = 16 rows x 16 pieces of 16 bytes: a thread keeps its piece and walks down the rows
-            const int r0 = tid >> 4, q = tid & 15;
+            // 256 threads = 32 rows x 8 pieces of 16 bytes: a thread keeps its piece and walks down the rows
+            const int r0 = tid >> 3, q = tid & 7;
             if (pk0 + q * 4 < npk) {
                 uint32_t* d = dst + r0 * GEMV_PACKS + q * 4;
                 const int32_t* sp = src + (int64_t)r0 * npk + q * 4;
-                for (int r = r0; r < G; r += 16, d += 16 * GEMV_PACKS, sp += 16 * (int64_t)npk) cp_async16(d, sp);
+                for (int r = r0; r < G; r += 32, d += 32 * GEMV_PACKS, sp += 32 * (int64_t)npk) cp_async16(d, sp);
             }
         } else {
-            const int r0 = tid >> 6, q = tid & 63;
+            const int r0 = tid >> 5, q = tid & 31;
             if (pk0 + q < npk) {
                 uint32_t* d = dst + r0 * GEMV_PACKS + q;
                 const int32_t* sp = src + (int64_t)r0 * npk + q;
-                for (int r = r0; r < G; r += 4, d += 4 * GEMV_PACKS, sp += 4 * (int64_t)npk) cp_async4(d, sp);
+                for (int r = r0; r < G; r += 8, d += 8 * GEMV_PACKS, sp += 8 * (int64_t)npk) cp_async4(d, sp);
             }
         }
     };
-    // activations of the group, fp16 as they are: M rows of G halves (16-byte pieces)
-    auto issue_x = [&](int chunk) {
-        const int g = g_begin + chunk, st = chunk % GEMV_STAGES;
-        for (int i = tid; i < M * (G / 8); i += GEMV_THREADS) {
-            const int m = i / (G / 8), q = i % (G / 8);
-            if (m < p.M) cp_async16(s_xh + (st * M + m) * GEMV_ROWS + q * 8, p.x + (int64_t)m * p.K + (int64_t)g * G + q * 8);
-        }
-    };
 
+    cluster.barrier_arrive();          // matched by the wait in front of the first access to another CTA's shared memory
 #pragma unroll
-    for (int s = 0; s < GEMV_STAGES - 1; ++s)
+    for (int s = 0; s < GEMV_STAGES; ++s) {
         if (s < n_chunks) issue_w(s);
+        cp_async_commit();             // group s = chunk s
+    }
     pdl_wait();        // x comes from the previous kernel
     pdl_trigger();
+
+    // ---- the CTA's K range of the input, through the operator in front of the linear ----
+    // 8 values (16 bytes) per thread and pass; s_xs[kk*M+m].x first holds the fp16 value as fp32
+    const int kv8 = p.K / 8;
+    if (p.pro_kind == FQ_GEMV_ADD_RMSNORM) {
+        // h = x (+ b) in fp16; rstd = rsqrt(mean(h^2) + eps) over the whole row, computed by every CTA
 #pragma unroll
-    for (int s = 0; s < GEMV_STAGES - 1; ++s) {
-        if (s < n_chunks) issue_x(s);
-        cp_async_commit();      // the first group also holds the weights of the later prologue stages: waits are only stricter
+        for (int m = 0; m < M; ++m) {
+            float ss = 0.f;
+            if (m < p.M) {
+                const uint4* xa = reinterpret_cast<const uint4*>(p.x + (int64_t)m * p.K);
+                const uint4* xb = p.pro_b ? reinterpret_cast<const uint4*>(p.pro_b + (int64_t)m * p.K) : nullptr;
+                for (int i = tid; i < kv8; i += GEMV_THREADS) {
+                    uint4 a = __ldcg(xa + i);
+                    __half2* ah = reinterpret_cast<__half2*>(&a);
+                    if (xb) {
+                        const uint4 b = __ldcg(xb + i);
+                        const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) ah[j] = __hadd2(ah[j], bh[j]);
+                    }
+                    const int kk = i * 8 - k0;
+                    const bool mine = kk >= 0 && kk < k_len;
+                    if (mine && tile == 0 && p.pro_out) *reinterpret_cast<uint4*>(p.pro_out + (int64_t)m * p.K + i * 8) = a;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(ah[j]);
+                        ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+                        if (mine) {
+                            s_xs[(kk + 2 * j) * M + m] = make_float2(f.x, 0.f);
+                            s_xs[(kk + 2 * j + 1) * M + m] = make_float2(f.y, 0.f);
+                        }
+                    }
+                }
+            }
+            const float tot = gemv_block_sum(ss, s_red8);
+            if (tid == 0) s_rstd[m] = rsqrtf(tot / (float)p.K + p.eps);
+        }
+        __syncthreads();
+        for (int i = tid; i < M * k_len; i += GEMV_THREADS) {
+            const int kk = i / M, m = i % M;
+            float v = 0.f;
+            if (m < p.M) {
+                const __half xh = __float2half_rn(s_xs[i].x * s_rstd[m]);
+                v = __half2float(__hmul(p.pro_weight[k0 + kk], xh));
+            }
+            const float vs = v * 1.2676506002282294e30f;
+            s_xs[i] = make_float2(vs, vs);
+        }
+    } else {
+        const int kl8 = k_len / 8;
+        for (int i = tid; i < M * kl8; i += GEMV_THREADS) {
+            const int m = i / kl8, kk = (i % kl8) * 8;
+            uint4 a = make_uint4(0, 0, 0, 0);
+            if (m < p.M) {
+                const int64_t gi = (int64_t)m * p.K + k0 + kk;
+                a = __ldcg(reinterpret_cast<const uint4*>(p.x + gi));
+                if (p.pro_kind == FQ_GEMV_SWIGLU) {
+                    const uint4 u = __ldcg(reinterpret_cast<const uint4*>(p.pro_b + gi));
+                    __half2* ah = reinterpret_cast<__half2*>(&a);
+                    const __half2* uh = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 g2 = __half22float2(ah[j]);
+                        ah[j] = __hmul2(__floats2half2_rn(g2.x / (1.0f + expf(-g2.x)), g2.y / (1.0f + expf(-g2.y))), uh[j]);
+                    }
+                    if (tile == 0 && p.pro_out) *reinterpret_cast<uint4*>(p.pro_out + gi) = a;
+                }
+            }
+            const __half2* ah = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(ah[j]);
+                const float v0 = f.x * 1.2676506002282294e30f, v1 = f.y * 1.2676506002282294e30f;
+                s_xs[(kk + 2 * j) * M + m] = make_float2(v0, v0);
+                s_xs[(kk + 2 * j + 1) * M + m] = make_float2(v1, v1);
+            }
+        }
+    }
+    __syncthreads();
+    // sum of x per group and row (fixed order): warp = row, lanes stride the group
+    for (int gm = warp; gm < n_chunks * M; gm += GEMV_WARPS) {
+        const int ch = gm / M, m = gm % M;
+        float s = 0.f;
+        for (int r = lane; r < G; r += 32) s += s_xs[(ch * G + r) * M + m].x;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) s_xsum[gm] = s * 7.888609052210118e-31f;      // * 2^-100 (exact)
     }
 
     float yacc[M][8];
@@ -153,33 +252,23 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
             z = (uint32_t)__ldg(pr.qzeros + (int64_t)g * npk + c);
             sc8 = __ldg(reinterpret_cast<const uint4*>(pr.scales + (int64_t)g * pr.N + c * 8));
         }
-        cp_async_wait<GEMV_STAGES - 2>();
-        __syncthreads();                 // chunk ch has landed for everybody; chunk ch-1 is consumed
-        if (ch + GEMV_STAGES - 1 < n_chunks) { issue_w(ch + GEMV_STAGES - 1); issue_x(ch + GEMV_STAGES - 1); }
-        cp_async_commit();
-        // x of the group: fp16 -> fp32 * 2^100, duplicated; sum per row of x (fixed order)
-        if (warp < M) {
-            float s = 0.f;
-            for (int r = lane; r < G; r += 32) {
-                const float v = warp < p.M ? __half2float(s_xh[(st * M + warp) * GEMV_ROWS + r]) : 0.f;
-                s += v;
-                const float vs = v * 1.2676506002282294e30f;
-                s_xs[r * M + warp] = make_float2(vs, vs);
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) s_xsum[warp] = s;
+        // groups committed so far: chunks 0 .. max(2, ch+1); chunk ch must have landed
+        if (ch == 0) cp_async_wait<GEMV_STAGES - 1>(); else cp_async_wait<GEMV_STAGES - 2>();
+        __syncthreads();                 // chunk ch has landed for everybody; chunk ch-1 is consumed; s_xsum is written
+        if (ch >= 1) {
+            if (ch + GEMV_STAGES - 1 < n_chunks) issue_w(ch + GEMV_STAGES - 1);    // into the stage chunk ch-1 has left
+            cp_async_commit();
         }
-        __syncthreads();
         if (!valid) continue;
         float2 acc[M][4];
 #pragma unroll
         for (int m = 0; m < M; ++m)
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[m][j] = make_float2(0.f, 0.f);
-        const uint32_t* wcol = s_w + st * GEMV_STAGE_WORDS + wn * 32 + lane;
-#pragma unroll 8
-        for (int r = wk; r < G; r += 4) {
+        const uint32_t* wcol = s_w + st * GEMV_STAGE_WORDS + lane;
+        const float2* xs = s_xs + (size_t)ch * G * M;
+#pragma unroll 4
+        for (int r = warp; r < G; r += GEMV_WARPS) {
             const uint32_t w = wcol[r * GEMV_PACKS];
             float2 f[4];
             f[0] = make_float2(__uint_as_float(w & 0x0000000fu), __uint_as_float(w & 0x000000f0u));
@@ -188,7 +277,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
             f[3] = make_float2(__uint_as_float(w >> 24), __uint_as_float(w >> 28));
 #pragma unroll
             for (int m = 0; m < M; ++m) {
-                const float2 xx = s_xs[r * M + m];
+                const float2 xx = xs[r * M + m];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[m][j] = __ffma2_rn(f[j], xx, acc[m][j]);
             }
@@ -212,123 +301,111 @@ __global__ void __launch_bounds__(GEMV_THREADS) awq_gemv_kernel(GemvParams p) {
                 else if (i == 6) a = fmaf(-16.f, acc[m][3].y, ai) * pow2f_i(49);
                 else a = ai * pow2f_i(49);
                 // the zero term belongs to the group once, not once per row phase
-                const float zterm = wk == 0 ? zero * s_xsum[m] : 0.f;
-                yacc[m][i] = fmaf(scv, a - zterm, yacc[m][i]);     // kept in nibble order until the store
+                const float zterm = warp == 0 ? zero * s_xsum[ch * M + m] : 0.f;
+                yacc[m][i] = fmaf(scv, a - zterm, yacc[m][i]);     // kept in nibble order until the columns are written
             }
         }
     }
     cp_async_wait<0>();
-    // reduce the 4 row phases through shared memory: s_red[wk-1][wn][lane][m][8]
+    // reduce the 8 row phases through shared memory: s_red[warp-1][lane][m][8]
     __syncthreads();
     float* s_red = reinterpret_cast<float*>(s_raw);
-    if (wk > 0) {
-#pragma unroll
-        for (int m = 0; m < M; ++m)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s_red[((((wk - 1) * 2 + wn) * 32 + lane) * M + m) * 8 + j] = yacc[m][j];
-    }
-    __syncthreads();
-    if (wk == 0) {
-#pragma unroll
-        for (int k = 0; k < 3; ++k)
-#pragma unroll
-            for (int m = 0; m < M; ++m)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) yacc[m][j] += s_red[(((k * 2 + wn) * 32 + lane) * M + m) * 8 + j];
-    }
-    const __half* bias = pr.bias ? pr.bias + c * 8 : nullptr;
-    if (p.k_split == 1) {
-        if (wk == 0 && valid) {
-#pragma unroll
-            for (int m = 0; m < M; ++m)
-                if (m < p.M) *reinterpret_cast<uint4*>(pr.y + (int64_t)m * pr.N + c * 8) = pack_columns(yacc[m], p.interleaved, bias);
-        }
-        return;
-    }
-    // split-K: publish, the CTA that draws the last ticket of the tile adds the splits in order
-    constexpr int TILE_F = GEMV_PACKS * 8;                     // floats per tile row
-    const int64_t n_pad = (int64_t)p.tiles_total * TILE_F;
-    const int64_t tpos = (int64_t)tile * TILE_F;
-    if (wk == 0 && valid) {
+    if (warp > 0) {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            float* dst = p.partials + ((int64_t)split * M + m) * n_pad + tpos + (wn * 32 + lane) * 8;
-            __stcg(reinterpret_cast<float4*>(dst), make_float4(yacc[m][0], yacc[m][1], yacc[m][2], yacc[m][3]));
-            __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(yacc[m][4], yacc[m][5], yacc[m][6], yacc[m][7]));
+            float4* d = reinterpret_cast<float4*>(s_red + (((warp - 1) * 32 + lane) * M + m) * 8);
+            d[0] = make_float4(yacc[m][0], yacc[m][1], yacc[m][2], yacc[m][3]);
+            d[1] = make_float4(yacc[m][4], yacc[m][5], yacc[m][6], yacc[m][7]);
         }
     }
     __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        s_ticket = atomicAdd(&p.tickets[tile], 1);
-        __threadfence();
-    }
-    __syncthreads();
-    if (s_ticket != p.k_split - 1) return;
-    // all 256 threads: a thread sums one float4 column piece of one row over the splits, eight
-    // independent loads at a time; packs past the end of the projection hold garbage nobody reads
-    float* s_out = reinterpret_cast<float*>(s_raw) + 3 * 2 * 32 * M * 8;      // [M][TILE_F], behind s_red
-    {
-        const int piece = tid & 127, mh = tid >> 7;
-        for (int m = mh; m < p.M; m += 2) {
-            const float* src = p.partials + (int64_t)m * n_pad + tpos + piece * 4;
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int sp0 = 0; sp0 < p.k_split; sp0 += 8) {
-                float4 v[8];
+    cluster.barrier_wait();            // every CTA of the cluster runs: the first one's shared memory may be addressed
+    if (warp == 0) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    v[u] = sp0 + u < p.k_split ? __ldcg(reinterpret_cast<const float4*>(src + (int64_t)(sp0 + u) * M * n_pad))
-                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < GEMV_WARPS - 1; ++k)
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { sum.x += v[u].x; sum.y += v[u].y; sum.z += v[u].z; sum.w += v[u].w; }
+            for (int m = 0; m < M; ++m) {
+                const float4* s = reinterpret_cast<const float4*>(s_red + ((k * 32 + lane) * M + m) * 8);
+                const float4 a = s[0], b = s[1];
+                yacc[m][0] += a.x; yacc[m][1] += a.y; yacc[m][2] += a.z; yacc[m][3] += a.w;
+                yacc[m][4] += b.x; yacc[m][5] += b.y; yacc[m][6] += b.z; yacc[m][7] += b.w;
             }
-            *reinterpret_cast<float4*>(s_out + m * TILE_F + piece * 4) = sum;
+        // columns in order into slot [split] of the cluster's first CTA (its own shared memory when split == 0)
+        float* slot = cluster.map_shared_rank(s_slot, 0) + (size_t)split * M * GEMV_TILE;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            float cv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cv[j] = p.interleaved ? yacc[m][(j >> 1) + (j & 1) * 4] : yacc[m][j];
+            float4* d = reinterpret_cast<float4*>(slot + m * GEMV_TILE + lane * 8);
+            d[0] = make_float4(cv[0], cv[1], cv[2], cv[3]);
+            d[1] = make_float4(cv[4], cv[5], cv[6], cv[7]);
         }
     }
+    cluster.sync();                    // every partial sum has arrived in the first CTA
+    if (split != 0) return;
+    // ---- first CTA of the cluster: add the splits in rank order, bias, rounding, rotary embedding, store ----
+    __half* s_y = reinterpret_cast<__half*>(s_raw);            // [M][TILE] fp16 (the ring is free)
+    const int col = tid;                                       // one output column per thread
+    const bool col_ok = pk0 * 8 + col < pr.N;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        float v = 0.f;
+        for (int s = 0; s < p.k_split; ++s) v += s_slot[((size_t)s * M + m) * GEMV_TILE + col];
+        if (pr.bias && col_ok) v += __half2float(pr.bias[pk0 * 8 + col]);
+        s_y[m * GEMV_TILE + col] = __float2half_rn(v);
+    }
+    if (!pr.rope) {
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+            if (m < p.M && col_ok) pr.y[(int64_t)m * pr.N + pk0 * 8 + col] = s_y[m * GEMV_TILE + col];
+        return;
+    }
     __syncthreads();
-    if (wk == 0 && valid) {
+    // Hugging Face "rotate_half" convention, cos/sin in fp32 from pos * theta^(-2i/D) rounded to fp16,
+    // products and sum in fp16: the arithmetic of rope_kernel
+    const int D = p.head_dim, half = D / 2;
+    const int pos = p.pos_dev ? *p.pos_dev : p.pos;
+    const int hd = col / D, i = col % D;
+    if (i < half && col_ok) {
+        const float inv_freq = 1.0f / powf(p.theta, (float)(2 * i) / (float)D);
+        const float ang = (float)pos * inv_freq;
+        const __half cs = __float2half_rn(cosf(ang)), sn = __float2half_rn(sinf(ang));
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             if (m >= p.M) break;
-            float sv[8];
-            const float4 a = *reinterpret_cast<const float4*>(s_out + m * TILE_F + (wn * 32 + lane) * 8);
-            const float4 b2 = *reinterpret_cast<const float4*>(s_out + m * TILE_F + (wn * 32 + lane) * 8 + 4);
-            sv[0] = a.x; sv[1] = a.y; sv[2] = a.z; sv[3] = a.w; sv[4] = b2.x; sv[5] = b2.y; sv[6] = b2.z; sv[7] = b2.w;
-            *reinterpret_cast<uint4*>(pr.y + (int64_t)m * pr.N + c * 8) = pack_columns(sv, p.interleaved, bias);
+            const __half x1 = s_y[m * GEMV_TILE + hd * D + i], x2 = s_y[m * GEMV_TILE + hd * D + i + half];
+            __half* yo = pr.y + (int64_t)m * pr.N + pk0 * 8 + hd * D;
+            yo[i] = __hadd(__hmul(x1, cs), __hmul(__hneg(x2), sn));
+            yo[i + half] = __hadd(__hmul(x2, cs), __hmul(x1, sn));
         }
     }
-    if (tid == 0) p.tickets[tile] = 0;
 }
 
 }  // namespace fq
 
 static inline int gemv_mp(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
-// upper bound of the tiles of a call whose projections sum to N_total outputs
-static inline size_t gemv_tiles_bound(int N_total) { return (size_t)N_total / (fq::GEMV_PACKS * 8) + fq::GEMV_MAX_PROJ; }
-
-extern "C" size_t fq_awq_gemv_workspace_bytes(int M, int N_total, int k_split) {
-    if (M <= 0 || N_total <= 0 || k_split <= 1) return 0;
-    const size_t tiles = gemv_tiles_bound(N_total);
-    const size_t tickets = (tiles * 4 + 255) & ~(size_t)255;
-    return tickets + (size_t)k_split * gemv_mp(M) * tiles * fq::GEMV_PACKS * 8 * 4;
-}
 
 extern "C" int fq_awq_gemv_default_splits(int K, int N_total, int group) {
     if (K <= 0 || N_total <= 0 || group <= 0) return 1;
     const int n_groups = K / group;
     const int tiles = (N_total / 8 + fq::GEMV_PACKS - 1) / fq::GEMV_PACKS;
-    int want = (2 * 148 + tiles - 1) / tiles;       // about two CTAs per SM
+    int want = (3 * 148 + tiles - 1) / tiles;       // about three CTAs per SM
+    if (want > fq::GEMV_MAX_CLUSTER) want = fq::GEMV_MAX_CLUSTER;
     if (want > n_groups) want = n_groups;
     if (want < 1) want = 1;
-    // groups per split must cover all groups: round the split count to ceil(n_groups / gps)
-    const int gps = (n_groups + want - 1) / want;
-    return (n_groups + gps - 1) / gps;
+    // cluster sizes are powers of two; every rank must own at least one group
+    int ks = 1;
+    while (ks * 2 <= want) ks *= 2;
+    const int gps = (n_groups + ks - 1) / ks;
+    while (ks > 1 && (ks - 1) * gps >= n_groups) ks /= 2;
+    return ks;
 }
 
-extern "C" int fq_awq_gemv(
+extern "C" int fq_awq_gemv_fused(
     const void* x, int M, int K, int group, int n_proj,
     const int32_t* const* qweight, const void* const* scales, const int32_t* const* qzeros, const void* const* bias,
-    const int* N, void* const* y, int interleaved, void* workspace, size_t workspace_bytes, int k_split, void* stream) {
+    const int* N, void* const* y, int interleaved, const fq_gemv_prologue* pro, const fq_gemv_rope* rope, int k_split, void* stream) {
     using namespace fq;
     const char* fn = "fq_awq_gemv";
     FQ_CHECK_ARG(M >= 1 && M <= 8, FQ_ERR_UNSUPPORTED, "%s: M=%d rows; the GEMV path takes 1..8 (larger M belongs to the GEMM path)", fn, M);
@@ -337,11 +414,30 @@ extern "C" int fq_awq_gemv(
     FQ_CHECK_ARG(n_proj >= 1 && n_proj <= GEMV_MAX_PROJ, FQ_ERR_ARG, "%s: 1..%d projections per call, got %d", fn, GEMV_MAX_PROJ, n_proj);
     FQ_CHECK_ARG(x && qweight && scales && qzeros && N && y, FQ_ERR_ARG, "%s: null pointer", fn);
     FQ_CHECK_ARG(aligned(x, 16), FQ_ERR_ALIGN, "%s: x must be 16-byte aligned", fn);
-    FQ_CHECK_ARG(k_split >= 1, FQ_ERR_ARG, "%s: k_split=%d", fn, k_split);
+    FQ_CHECK_ARG(k_split >= 1 && k_split <= GEMV_MAX_CLUSTER && (k_split & (k_split - 1)) == 0, FQ_ERR_ARG,
+                 "%s: k_split=%d must be 1, 2, 4 or 8 (the CTAs of one thread-block cluster)", fn, k_split);
     GemvParams p;
     p.x = static_cast<const __half*>(x); p.M = M; p.K = K; p.group = group; p.n_groups = K / group;
     p.n_proj = n_proj; p.interleaved = interleaved ? 1 : 0;
-    int tile0 = 0, n_total = 0, vec16 = 1;
+    p.pro_kind = FQ_GEMV_PLAIN; p.pro_b = nullptr; p.pro_weight = nullptr; p.eps = 0.f; p.pro_out = nullptr;
+    if (pro && pro->kind != FQ_GEMV_PLAIN) {
+        FQ_CHECK_ARG(pro->kind == FQ_GEMV_ADD_RMSNORM || pro->kind == FQ_GEMV_SWIGLU, FQ_ERR_ARG, "%s: prologue kind %d", fn, pro->kind);
+        FQ_CHECK_ARG(K % 8 == 0, FQ_ERR_ARG, "%s: a fused prologue needs K %% 8 == 0", fn);
+        if (pro->kind == FQ_GEMV_ADD_RMSNORM) FQ_CHECK_ARG(pro->weight, FQ_ERR_ARG, "%s: RMSNorm prologue without weight", fn);
+        else FQ_CHECK_ARG(pro->b, FQ_ERR_ARG, "%s: SwiGLU prologue without the up projection", fn);
+        FQ_CHECK_ARG(!pro->b || aligned(pro->b, 16), FQ_ERR_ALIGN, "%s: prologue operand must be 16-byte aligned", fn);
+        FQ_CHECK_ARG(pro->out != x && (!pro->out || pro->out != pro->b), FQ_ERR_ARG, "%s: the prologue's output must not alias its inputs", fn);
+        p.pro_kind = pro->kind; p.pro_b = static_cast<const __half*>(pro->b); p.pro_weight = static_cast<const __half*>(pro->weight);
+        p.eps = pro->eps; p.pro_out = static_cast<__half*>(pro->out);
+    }
+    p.pos_dev = nullptr; p.pos = 0; p.theta = 0.f; p.head_dim = 0;
+    if (rope) {
+        FQ_CHECK_ARG(rope->head_dim > 0 && GEMV_TILE % rope->head_dim == 0 && rope->head_dim % 2 == 0, FQ_ERR_UNSUPPORTED,
+                     "%s: rotary embedding needs a head_dim that divides %d (got %d)", fn, GEMV_TILE, rope->head_dim);
+        FQ_CHECK_ARG(rope->theta > 0.f, FQ_ERR_ARG, "%s: rope theta", fn);
+        p.pos_dev = rope->pos_dev; p.pos = rope->pos; p.theta = rope->theta; p.head_dim = rope->head_dim;
+    }
+    int tile0 = 0, vec16 = 1;
     for (int i = 0; i < n_proj; ++i) {
         FQ_CHECK_ARG(N[i] > 0 && N[i] % 8 == 0, FQ_ERR_ARG, "%s: N[%d]=%d must be a positive multiple of 8", fn, i, N[i]);
         FQ_CHECK_ARG(qweight[i] && scales[i] && qzeros[i] && y[i], FQ_ERR_ARG, "%s: null tensor in projection %d", fn, i);
@@ -352,45 +448,69 @@ extern "C" int fq_awq_gemv(
         q.qweight = qweight[i]; q.scales = static_cast<const __half*>(scales[i]); q.qzeros = qzeros[i];
         q.bias = bias ? static_cast<const __half*>(bias[i]) : nullptr; q.y = static_cast<__half*>(y[i]);
         q.N = N[i]; q.tile0 = tile0;
+        q.rope = rope && ((rope->proj_mask >> i) & 1) ? 1 : 0;
+        if (q.rope) FQ_CHECK_ARG(N[i] % rope->head_dim == 0, FQ_ERR_ARG, "%s: N[%d]=%d is not a multiple of head_dim %d", fn, i, N[i], rope->head_dim);
         tile0 += (N[i] / 8 + GEMV_PACKS - 1) / GEMV_PACKS;
-        n_total += N[i];
     }
-    for (int i = n_proj; i < GEMV_MAX_PROJ; ++i) p.proj[i] = GemvProj{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
+    for (int i = n_proj; i < GEMV_MAX_PROJ; ++i) p.proj[i] = GemvProj{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
     p.tiles_total = tile0; p.vec16 = vec16;
     const int tiles = tile0;
-    if (k_split > p.n_groups) k_split = p.n_groups;
-    p.groups_per_split = (p.n_groups + k_split - 1) / k_split;
-    k_split = (p.n_groups + p.groups_per_split - 1) / p.groups_per_split;
-    p.k_split = k_split;
-    FQ_CHECK_ARG(k_split <= 65535, FQ_ERR_ARG, "%s: k_split=%d", fn, k_split);
-    p.partials = nullptr; p.tickets = nullptr;
-    const int Mp = gemv_mp(M);
-    if (k_split > 1) {
-        const size_t need = fq_awq_gemv_workspace_bytes(M, n_total, k_split);
-        FQ_CHECK_ARG(workspace && workspace_bytes >= need, FQ_ERR_WORKSPACE, "%s: workspace of %zu B needed, %zu given", fn, need, workspace_bytes);
-        FQ_CHECK_ARG(aligned(workspace, 16), FQ_ERR_ALIGN, "%s: workspace must be 16-byte aligned", fn);
-        p.tickets = static_cast<int*>(workspace);
-        p.partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + ((gemv_tiles_bound(n_total) * 4 + 255) & ~(size_t)255));
+    if (k_split > p.n_groups) {
+        k_split = 1;
+        while (k_split * 2 <= p.n_groups) k_split *= 2;
     }
-    const size_t smem = (size_t)GEMV_STAGES * GEMV_STAGE_WORDS * 4 + (size_t)GEMV_STAGES * Mp * GEMV_ROWS * 2 + (size_t)GEMV_ROWS * Mp * 8;
-    dim3 grid((unsigned)tiles, (unsigned)k_split);
+    // ranks past the last group get no chunks and send zeros
+    const int Mp = gemv_mp(M);
+    // the CTA keeps its whole K range of the input in shared memory: a range too long for it is split further
+    size_t smem = 0;
+    int stages = 3;
+    for (;;) {
+        p.groups_per_split = (p.n_groups + k_split - 1) / k_split;
+        stages = p.groups_per_split > 3 ? GEMV_MAX_STAGES : 3;
+        const size_t range = (size_t)p.groups_per_split * group;
+        const size_t fixed = range * Mp * 8 + (size_t)k_split * Mp * GEMV_TILE * 4 + (size_t)p.groups_per_split * Mp * 4;
+        smem = (size_t)stages * GEMV_STAGE_WORDS * 4 + fixed;
+        // the deep ring only while two CTAs still fit on an SM
+        if (smem > 113 * 1024 && stages > 3) { stages = 3; smem = (size_t)stages * GEMV_STAGE_WORDS * 4 + fixed; }
+        if (smem <= 226 * 1024 || k_split >= GEMV_MAX_CLUSTER || k_split * 2 > p.n_groups) break;
+        k_split *= 2;
+    }
+    p.k_split = k_split;
+    FQ_CHECK_ARG(smem <= 226 * 1024, FQ_ERR_UNSUPPORTED, "%s: K=%d with %d rows needs %zu B of shared memory per CTA", fn, K, M, smem);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define FQ_GEMV(MV)                                                                                          \
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)tiles, (unsigned)k_split); cfg.blockDim = dim3(GEMV_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[2]{};
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = (unsigned)k_split; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl_enabled(PDL_GEMV) ? 2 : 1;
+#define FQ_GEMV(MV, SV)                                                                                      \
     do {                                                                                                     \
-        static bool attr_set[64] = {};                                                                       \
+        static std::atomic<size_t> attr_smem[64];                                                            \
         int dev = 0; cudaGetDevice(&dev);                                                                    \
-        if (dev < 0 || dev >= 64 || !attr_set[dev]) {                                                        \
-            cudaError_t e = cudaFuncSetAttribute(awq_gemv_kernel<MV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (dev < 0 || dev >= 64 || attr_smem[dev].load(std::memory_order_acquire) < smem) {                 \
+            cudaError_t e = cudaFuncSetAttribute(awq_gemv_kernel<MV, SV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve %zu B of shared memory: %s", fn, smem, cudaGetErrorString(e)); \
-            if (dev >= 0 && dev < 64) attr_set[dev] = true;                                                  \
+            if (dev >= 0 && dev < 64) attr_smem[dev].store(smem, std::memory_order_release);                 \
         }                                                                                                    \
-        launch_k(PDL_GEMV, awq_gemv_kernel<MV>, grid, dim3(GEMV_THREADS), smem, st, p);                                          \
+        cudaLaunchKernelEx(&cfg, awq_gemv_kernel<MV, SV>, p);                                                \
     } while (0)
-    if (Mp == 1) FQ_GEMV(1);
-    else if (Mp == 2) FQ_GEMV(2);
-    else if (Mp == 4) FQ_GEMV(4);
-    else FQ_GEMV(8);
+#define FQ_GEMV_M(MV) do { if (stages == 3) FQ_GEMV(MV, 3); else FQ_GEMV(MV, GEMV_MAX_STAGES); } while (0)
+    if (Mp == 1) FQ_GEMV_M(1);
+    else if (Mp == 2) FQ_GEMV_M(2);
+    else if (Mp == 4) FQ_GEMV_M(4);
+    else FQ_GEMV_M(8);
+#undef FQ_GEMV_M
 #undef FQ_GEMV
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
+}
+
+extern "C" int fq_awq_gemv(
+    const void* x, int M, int K, int group, int n_proj,
+    const int32_t* const* qweight, const void* const* scales, const int32_t* const* qzeros, const void* const* bias,
+    const int* N, void* const* y, int interleaved, int k_split, void* stream) {
+    return fq_awq_gemv_fused(x, M, K, group, n_proj, qweight, scales, qzeros, bias, N, y, interleaved, nullptr, nullptr, k_split, stream);
 }

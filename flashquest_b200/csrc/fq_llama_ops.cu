@@ -8,6 +8,8 @@
 // rest of the chain.
 #include "fq_common.cuh"
 
+#include <cooperative_groups.h>
+
 namespace fq {
 
 constexpr int NORM_THREADS = 256;
@@ -132,40 +134,65 @@ __global__ void __launch_bounds__(GEMVH_WARPS * 32) gemv_f16_kernel(const __half
     }
 }
 
-// index of the first maximum of each row (torch.argmax); one CTA per row
-__global__ void __launch_bounds__(1024) argmax_f16_kernel(const __half* __restrict__ x, int N, int32_t* __restrict__ out) {
+// index of the first maximum of each row (torch.argmax): a cluster of ARGMAX_CTAS CTAs per row, each scans
+// a contiguous slice and sends its best (value, index) to the first CTA through distributed shared memory
+constexpr int ARGMAX_CTAS = 8;
+constexpr int ARGMAX_THREADS = 512;
+
+__device__ __forceinline__ bool argmax_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_f16_kernel(const __half* __restrict__ x, int N, int32_t* __restrict__ out) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
     __shared__ float s_v[32];
     __shared__ int s_i[32];
-    const int64_t row = blockIdx.x;
+    __shared__ float s_cv[ARGMAX_CTAS];
+    __shared__ int s_ci[ARGMAX_CTAS];
+    const int64_t row = blockIdx.y;
+    const int rank = blockIdx.x;
+    cluster.barrier_arrive();
     pdl_wait();
     pdl_trigger();
+    const int per = (N + ARGMAX_CTAS - 1) / ARGMAX_CTAS;
+    const int lo = rank * per, hi = min(N, lo + per);
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < N; i += blockDim.x) {
-        const float v = __half2float(x[row * N + i]);
-        if (v > best || (v == best && i < bi) || bi == 0x7fffffff) { best = v; bi = i; }
+    const __half* xr = x + row * N;
+    for (int i = lo + threadIdx.x; i < hi; i += ARGMAX_THREADS) {
+        const float v = __half2float(xr[i]);
+        if (bi == 0x7fffffff || argmax_better(v, i, best, bi)) { best = v; bi = i; }
     }
-    auto better = [](float v, int i, float bv, int b2) { return v > bv || (v == bv && i < b2); };
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, off);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-        if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+        if (argmax_better(ov, oi, best, bi)) { best = ov; bi = oi; }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { s_v[warp] = best; s_i[warp] = bi; }
     __syncthreads();
+    cluster.barrier_wait();            // every CTA of the cluster runs: the first one's shared memory may be addressed
     if (warp == 0) {
-        const int nw = blockDim.x >> 5;
+        constexpr int nw = ARGMAX_THREADS / 32;
         best = lane < nw ? s_v[lane] : -INFINITY;
         bi = lane < nw ? s_i[lane] : 0x7fffffff;
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, off);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-            if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+            if (argmax_better(ov, oi, best, bi)) { best = ov; bi = oi; }
         }
-        if (lane == 0) out[row] = bi;
+        if (lane == 0) {
+            cluster.map_shared_rank(s_cv, 0)[rank] = best;
+            cluster.map_shared_rank(s_ci, 0)[rank] = bi;
+        }
+    }
+    cluster.sync();
+    if (rank == 0 && threadIdx.x == 0) {
+        best = s_cv[0]; bi = s_ci[0];
+        for (int r = 1; r < ARGMAX_CTAS; ++r)
+            if (argmax_better(s_cv[r], s_ci[r], best, bi)) { best = s_cv[r]; bi = s_ci[r]; }
+        out[row] = bi;
     }
 }
 
@@ -262,8 +289,16 @@ extern "C" int fq_argmax_f16(const void* x, int64_t rows, int N, int32_t* out, v
     const char* fn = "fq_argmax_f16";
     FQ_CHECK_ARG(x && out && rows >= 0 && N > 0, FQ_ERR_ARG, "%s: bad arguments", fn);
     if (rows == 0) return FQ_OK;
-    launch_k(PDL_GEMV, argmax_f16_kernel, dim3((unsigned)rows), dim3(1024), 0, static_cast<cudaStream_t>(stream),
-             static_cast<const __half*>(x), N, out);
+    FQ_CHECK_ARG(rows <= 65535, FQ_ERR_ARG, "%s: at most 65535 rows", fn);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ARGMAX_CTAS, (unsigned)rows); cfg.blockDim = dim3(ARGMAX_THREADS); cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute at[2]{};
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = ARGMAX_CTAS; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 2;
+    cudaLaunchKernelEx(&cfg, argmax_f16_kernel, static_cast<const __half*>(x), N, out);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
@@ -290,6 +325,13 @@ static int llama_step_impl(const fq_llama_model* m, const fq_int4_cache* cache, 
     const void* xin = x;          // residual stream; alternates between the two buffers
     const void* delta = nullptr;  // output of the previous block, added by the next norm
     int flip = 0;
+    // residual add + RMSNorm folded into the GEMV that consumes it: the prologue record and the buffer the sum goes to
+    auto norm_prologue = [&](const void* w, fq_gemv_prologue& pro) -> const void* {
+        pro.kind = FQ_GEMV_ADD_RMSNORM; pro.b = delta; pro.weight = w; pro.eps = m->rms_eps; pro.out = nullptr;
+        const void* src = xin;
+        if (delta) { pro.out = flip ? s->resid1 : s->resid0; flip ^= 1; xin = pro.out; }
+        return src;
+    };
     auto add_norm = [&](const void* w) -> int {
         void* out = nullptr;
         if (delta) { out = flip ? s->resid1 : s->resid0; flip ^= 1; }
@@ -302,27 +344,29 @@ static int llama_step_impl(const fq_llama_model* m, const fq_int4_cache* cache, 
         FQ_CHECK_ARG(L.q.K == H && L.q.N == nq && L.k.N == nkv && L.v.N == nkv && L.o.K == nq && L.o.N == H &&
                      L.gate.N == m->ffn && L.up.N == m->ffn && L.down.K == m->ffn && L.down.N == H, FQ_ERR_ARG,
                      "%s: layer %d has unexpected projection shapes", fn, l);
-        if ((rc = add_norm(L.input_norm)) != FQ_OK) return rc;
+        void* Ol = static_cast<char*>(s->O) + (size_t)l * s->o_sl * 2;
         {
+            // input_layernorm -> q/k/v -> rotary embedding of q and k: one launch
             const int32_t* qw[3] = {L.q.qweight, L.k.qweight, L.v.qweight};
             const void* sc[3] = {L.q.scales, L.k.scales, L.v.scales};
             const int32_t* qz[3] = {L.q.qzeros, L.k.qzeros, L.v.qzeros};
             const void* bs[3] = {L.q.bias, L.k.bias, L.v.bias};
             const int N[3] = {nq, nkv, nkv};
             void* y[3] = {s->q, s->k, s->v};
-            rc = fq_awq_gemv(s->normed, B, H, m->group, 3, qw, sc, qz, (bs[0] || bs[1] || bs[2]) ? bs : nullptr, N, y, m->interleaved,
-                             s->gemv_ws[0], s->gemv_ws_bytes[0], ks_qkv, stream);
+            fq_gemv_prologue pro;
+            const void* src = norm_prologue(L.input_norm, pro);
+            fq_gemv_rope rope;
+            rope.proj_mask = 3u; rope.pos_dev = pos_dev ? pos_dev + l : nullptr; rope.pos = pos_dev ? 0 : seen[l];
+            rope.theta = m->rope_theta; rope.head_dim = D;
+            rc = fq_awq_gemv_fused(src, B, H, m->group, 3, qw, sc, qz, (bs[0] || bs[1] || bs[2]) ? bs : nullptr, N, y, m->interleaved,
+                                   &pro, &rope, ks_qkv, stream);
             if (rc != FQ_OK) return rc;
         }
-        void* Ol = static_cast<char*>(s->O) + (size_t)l * s->o_sl * 2;
         if (pos_dev) {
-            rc = rope_launch(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, 0, m->rope_theta, stream, pos_dev + l, 0);
-            if (rc != FQ_OK) return rc;
             rc = decode_layer_int4_dyn(cache, l, pos_dev + l, s->k, s->v, nkv, D, D, 1, s->q, FQ_F16, nq, D, prm,
                                        s->scores + l * s->sc_sl, s->compact + l * s->cp_sl, Ol, nullptr,
                                        static_cast<char*>(s->attn_ws) + (size_t)l * s->attn_ws_sl, s->attn_ws_bytes, stream);
         } else {
-            if ((rc = fq_rope(s->q, nq, D, Hq, s->k, nkv, D, Hkv, B, D, seen[l], m->rope_theta, stream)) != FQ_OK) return rc;
             rc = fq_decode_layer_int4(cache, l, seen[l], s->k, s->v, nkv, D, D, 1, s->q, FQ_F16, nq, D, prm,
                                       s->scores + l * s->sc_sl, s->compact + l * s->cp_sl, Ol, nullptr,
                                       static_cast<char*>(s->attn_ws) + (size_t)l * s->attn_ws_sl, s->attn_ws_bytes, stream);
@@ -331,26 +375,29 @@ static int llama_step_impl(const fq_llama_model* m, const fq_int4_cache* cache, 
         {
             const int32_t* qw[1] = {L.o.qweight}; const void* sc[1] = {L.o.scales}; const int32_t* qz[1] = {L.o.qzeros};
             const void* bs[1] = {L.o.bias}; const int N[1] = {H}; void* y[1] = {s->attn_out};
-            rc = fq_awq_gemv(Ol, B, nq, m->group, 1, qw, sc, qz, bs[0] ? bs : nullptr, N, y, m->interleaved,
-                             s->gemv_ws[1], s->gemv_ws_bytes[1], ks_o, stream);
+            rc = fq_awq_gemv(Ol, B, nq, m->group, 1, qw, sc, qz, bs[0] ? bs : nullptr, N, y, m->interleaved, ks_o, stream);
             if (rc != FQ_OK) return rc;
         }
         delta = s->attn_out;
-        if ((rc = add_norm(L.post_norm)) != FQ_OK) return rc;
         {
+            // post_attention_layernorm -> gate/up: one launch
             const int32_t* qw[2] = {L.gate.qweight, L.up.qweight}; const void* sc[2] = {L.gate.scales, L.up.scales};
             const int32_t* qz[2] = {L.gate.qzeros, L.up.qzeros}; const void* bs[2] = {L.gate.bias, L.up.bias};
             const int N[2] = {m->ffn, m->ffn}; void* y[2] = {s->gate, s->up};
-            rc = fq_awq_gemv(s->normed, B, H, m->group, 2, qw, sc, qz, (bs[0] || bs[1]) ? bs : nullptr, N, y, m->interleaved,
-                             s->gemv_ws[2], s->gemv_ws_bytes[2], ks_gu, stream);
+            fq_gemv_prologue pro;
+            const void* src = norm_prologue(L.post_norm, pro);
+            rc = fq_awq_gemv_fused(src, B, H, m->group, 2, qw, sc, qz, (bs[0] || bs[1]) ? bs : nullptr, N, y, m->interleaved,
+                                   &pro, nullptr, ks_gu, stream);
             if (rc != FQ_OK) return rc;
         }
-        if ((rc = fq_swiglu(s->gate, s->up, (int64_t)B * m->ffn, s->act, stream)) != FQ_OK) return rc;
         {
+            // act_fn(gate) * up -> down: one launch
             const int32_t* qw[1] = {L.down.qweight}; const void* sc[1] = {L.down.scales}; const int32_t* qz[1] = {L.down.qzeros};
             const void* bs[1] = {L.down.bias}; const int N[1] = {H}; void* y[1] = {s->down};
-            rc = fq_awq_gemv(s->act, B, m->ffn, m->group, 1, qw, sc, qz, bs[0] ? bs : nullptr, N, y, m->interleaved,
-                             s->gemv_ws[3], s->gemv_ws_bytes[3], ks_dn, stream);
+            fq_gemv_prologue pro;
+            pro.kind = FQ_GEMV_SWIGLU; pro.b = s->up; pro.weight = nullptr; pro.eps = 0.f; pro.out = nullptr;
+            rc = fq_awq_gemv_fused(s->gate, B, m->ffn, m->group, 1, qw, sc, qz, bs[0] ? bs : nullptr, N, y, m->interleaved,
+                                   &pro, nullptr, ks_dn, stream);
             if (rc != FQ_OK) return rc;
         }
         delta = s->down;

@@ -120,7 +120,7 @@ class LlamaInt4Decoder:
         self._build_native()
 
     def _build_native(self):
-        """Descriptors of the one-call step (fq_llama_decode_step): weights, scratch, split-K workspaces."""
+        """Descriptors of the one-call step (fq_llama_decode_step): weights and scratch."""
         c, w, B, a = self.cfg, self.w, self.B, self.attn
         L = lib()
 
@@ -137,17 +137,10 @@ class LlamaInt4Decoder:
         nq, nkv = c.q_heads * c.head_dim, c.kv_heads * c.head_dim
         self._nat = dict(q=mk(B, nq), k=mk(B, nkv), v=mk(B, nkv), attn_out=mk(B, c.hidden), down=mk(B, c.hidden),
                          gate=mk(B, c.ffn), up=mk(B, c.ffn))
-        shapes = ((c.hidden, nq + 2 * nkv), (nq, c.hidden), (c.hidden, 2 * c.ffn), (c.ffn, c.hidden))
-        self._gemv_ws = []
-        with torch.cuda.device(self.dev):
-            for K, N in shapes:
-                ks = L.fq_awq_gemv_default_splits(K, N, c.group_size)
-                self._gemv_ws.append(torch.zeros(max(L.fq_awq_gemv_workspace_bytes(B, N, ks), 256), dtype=torch.uint8, device=self.dev))
         n = self._nat
         self._scratch = LlamaScratchDesc(
             ptr(self.resid[0]), ptr(self.resid[1]), ptr(self.normed), ptr(n["q"]), ptr(n["k"]), ptr(n["v"]),
-            ptr(n["attn_out"]), ptr(n["down"]), ptr(n["gate"]), ptr(n["up"]), ptr(self.act), ptr(self.logits), ptr(self.next_ids),
-            (ctypes.c_void_p * 4)(*[ptr(t) for t in self._gemv_ws]), (ctypes.c_size_t * 4)(*[t.numel() for t in self._gemv_ws]),
+            ptr(n["attn_out"]), ptr(n["down"]), ptr(n["gate"]), ptr(n["up"]), ptr(self.logits), ptr(self.next_ids),
             ptr(a.scores), a.scores.stride(0), ptr(a.compact), a.compact.stride(0), ptr(a.O), a.O.stride(0),
             ptr(a.workspace), a.workspace.stride(0), a.workspace.shape[1])
 
@@ -164,7 +157,7 @@ class LlamaInt4Decoder:
                                          seen, ptr(x), self.B, ctypes.byref(self._scratch), stream_ptr(self.dev)))
         for li in range(n_l):
             c._seen_tokens[li] += 1
-        self.launches += 12 * n_l + 3
+        self.launches += 8 * n_l + 3
         return self.next_ids
 
     def prefill(self, token_ids: torch.Tensor) -> torch.Tensor:
@@ -261,7 +254,7 @@ class LlamaInt4Decoder:
         self.attn.attend(torch.zeros(self.B, cfg.q_heads, 1, cfg.head_dim, dtype=torch.float16, device=self.dev), 0)
         lw = self.w.layers[0]
         awq_gemv_fused(self.normed.view(self.B, 1, -1), (lw.q_proj, lw.k_proj, lw.v_proj))
-        awq_gemv_fused(self.act.view(self.B, 1, -1), (lw.down_proj,))
+        awq_gemv_fused(self.act.view(self.B, 1, -1), (lw.down_proj,))       # shared memory size of the widest K range
         torch.cuda.synchronize(self.dev)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):
@@ -277,7 +270,7 @@ class LlamaInt4Decoder:
             graph.replay()
             for li in range(n_l):
                 c._seen_tokens[li] += 1
-            self.launches += 12 * n_l + 4
+            self.launches += 8 * n_l + 4
             return ids
 
         replay.graph, replay.ids, replay.pos = graph, ids, pos

@@ -7,34 +7,29 @@ rows, the tensor-core dequant-GEMM (`fq_awq_gemm`, tcgen05) for prefill / batche
 from __future__ import annotations
 
 import ctypes
-from typing import Sequence
+from typing import Optional, Sequence
 
 import torch
 
-from .._lib import check, lib, ptr, require_cuda, stream_ptr
+from .._lib import (GEMV_ADD_RMSNORM, GEMV_SWIGLU, GemvPrologue, GemvRope, check, lib, ptr, require_cuda,
+                    stream_ptr)
 
-_WS: dict = {}
-
-
-def _workspace(device: torch.device, nbytes: int, key) -> torch.Tensor:
-    """Zero-initialised split-K scratch per device; the kernel leaves its tickets at zero, so
-    the buffer is cleared only when it is created, grown, or used for another shape."""
-    ent = _WS.get(device)
-    if ent is None or ent[0].numel() < nbytes:
-        ent = [torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device), key]
-        _WS[device] = ent
-    elif ent[1] != key:
-        ent[0][:4096].zero_()
-        ent[1] = key
-    return ent[0]
-
-
-def awq_gemv_fused(hidden: torch.Tensor, projs: Sequence) -> tuple[torch.Tensor, ...]:
-    """y_i = hidden @ dequant(projs[i]) (+ bias) for up to 4 AWQ linears in one launch.
+def awq_gemv_fused(hidden: torch.Tensor, projs: Sequence, *, add: Optional[torch.Tensor] = None,
+                   norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-5, return_sum: bool = False,
+                   swiglu_up: Optional[torch.Tensor] = None, rope: Optional[dict] = None,
+                   k_split: Optional[int] = None) -> tuple[torch.Tensor, ...]:
+    """y_i = op(hidden) @ dequant(projs[i]) (+ bias) for up to 4 AWQ linears in one launch.
 
     hidden (..., K) fp16 with at most 8 rows in total; each proj has .qweight (K, N/8) int32,
     .scales (K/G, N) fp16, .qzeros (K/G, N/8) int32 and optionally .bias, .group_size,
-    .interleaved (default: AutoAWQ's nibble order)."""
+    .interleaved (default: AutoAWQ's nibble order).
+
+    op, folded into the launch (the Hugging Face modules in front of the linears):
+      norm_weight given: RMSNorm(hidden + add) * norm_weight (add optional); with return_sum the sum
+        hidden + add (the new residual stream) is appended to the returned tuple;
+      swiglu_up given: silu(hidden) * swiglu_up (hidden = gate).
+    rope: dict(mask=<bit i: rotate projection i>, theta=, head_dim=, pos=<int> or pos_dev=<int32 tensor>):
+      rotary embedding (rotate_half) of those outputs at one position for all rows."""
     require_cuda(hidden)
     if hidden.dtype != torch.float16:
         raise NotImplementedError(f"AWQ GEMV computes in fp16 (AutoAWQ's dtype), got {hidden.dtype}")
@@ -65,20 +60,47 @@ def awq_gemv_fused(hidden: torch.Tensor, projs: Sequence) -> tuple[torch.Tensor,
         if b is not None and (b.dtype != torch.float16 or b.numel() != N or not b.is_contiguous()):
             raise ValueError("bias must be a contiguous fp16 vector of out_features")
     bias_arr = VP(*[ptr(b) if b is not None else None for b in biases]) if any(b is not None for b in biases) else None
+    pro, keep, summed = None, [], None
+    if norm_weight is not None and swiglu_up is not None:
+        raise ValueError("norm_weight and swiglu_up are different operators; give one")
+    if norm_weight is not None:
+        if norm_weight.dtype != torch.float16 or norm_weight.numel() != K:
+            raise ValueError("norm_weight must be an fp16 vector of in_features")
+        if add is not None:
+            add = add.reshape(-1, K).to(torch.float16).contiguous()
+            if add.shape[0] != M:
+                raise ValueError("add must have the shape of hidden")
+        if return_sum:
+            summed = torch.empty_like(x)
+        keep = [add, norm_weight.contiguous(), summed]
+        pro = GemvPrologue(GEMV_ADD_RMSNORM, ptr(add), ptr(keep[1]), float(eps), ptr(summed))
+    elif swiglu_up is not None:
+        up = swiglu_up.reshape(-1, K).contiguous()
+        if up.dtype != torch.float16 or up.shape[0] != M:
+            raise ValueError("swiglu_up must be fp16 with the shape of hidden")
+        keep = [up]
+        pro = GemvPrologue(GEMV_SWIGLU, ptr(up), None, 0.0, None)
+    elif add is not None or return_sum:
+        raise ValueError("add / return_sum belong to the RMSNorm prologue: give norm_weight")
+    rp = None
+    if rope is not None:
+        pos_dev = rope.get("pos_dev")
+        if pos_dev is not None and (pos_dev.dtype != torch.int32 or not pos_dev.is_cuda):
+            raise ValueError("rope pos_dev must be an int32 CUDA tensor")
+        rp = GemvRope(int(rope["mask"]), ptr(pos_dev), int(rope.get("pos", 0)), float(rope["theta"]), int(rope["head_dim"]))
     L = lib()
     n_total = sum(Ns)
     with torch.cuda.device(hidden.device):
-        ks = L.fq_awq_gemv_default_splits(K, n_total, group)
-        need = L.fq_awq_gemv_workspace_bytes(M, n_total, ks)
-        ws = _workspace(hidden.device, need, (M, n_total, ks)) if need else None
-        check(L.fq_awq_gemv(
+        ks = int(k_split) if k_split is not None else L.fq_awq_gemv_default_splits(K, n_total, group)
+        check(L.fq_awq_gemv_fused(
             ptr(x), M, K, group, n,
             VP(*[ptr(pj.qweight) for pj in projs]), VP(*[ptr(pj.scales) for pj in projs]),
             VP(*[ptr(pj.qzeros) for pj in projs]), bias_arr, (ctypes.c_int * n)(*Ns), VP(*[ptr(o) for o in outs]),
-            int(inter), ptr(ws) if ws is not None else None, ws.numel() if ws is not None else 0, ks,
+            int(inter), ctypes.byref(pro) if pro is not None else None, ctypes.byref(rp) if rp is not None else None, ks,
             stream_ptr(hidden.device)))
     lead = hidden.shape[:-1]
-    return tuple(o.reshape(*lead, N) for o, N in zip(outs, Ns))
+    res = tuple(o.reshape(*lead, N) for o, N in zip(outs, Ns))
+    return res + (summed.reshape(hidden.shape),) if summed is not None else res
 
 
 def awq_gemm_fused(hidden: torch.Tensor, projs: Sequence) -> tuple[torch.Tensor, ...]:

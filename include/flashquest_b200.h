@@ -379,15 +379,47 @@ int fq_ctx_select_attend(
  *   x (M,K) fp16 dense, 1 <= M <= 8; arrays of n_proj (<= 4) HOST arrays holding device
  *   pointers / sizes; bias NULL, or n_proj entries each NULL or (N[i]) fp16, added in fp32
  *   before the rounding to fp16; y[i] (M,N[i]) fp16 dense.  fp32 accumulation.
- *   k_split > 1 needs fq_awq_gemv_workspace_bytes(M, sum N, k_split) bytes whose leading
- *   ticket words are zero (left zero again); k_split <= 0 is not accepted — ask
- *   fq_awq_gemv_default_splits. */
-size_t fq_awq_gemv_workspace_bytes(int M, int N_total, int k_split);
+ *   k_split (1, 2, 4 or 8; ask fq_awq_gemv_default_splits): the CTAs that share one tile of
+ *   256 outputs split K between them as one thread-block cluster and merge their partial sums
+ *   through distributed shared memory in rank order — no workspace, no atomics.
+ *
+ * fq_awq_gemv_fused is the same launch with the element-wise operator in front of the linear and
+ * the rotary embedding behind it folded in, for the decode step of a Llama-shaped layer (the
+ * Hugging Face modules around the patched attention, eager/llama_persistent_patch.py:164-190,
+ * 246-251: input_layernorm -> q/k/v_proj -> apply_rotary_pos_emb; post_attention_layernorm ->
+ * gate/up_proj; act_fn(gate) * up -> down_proj), with the same roundings to fp16 as the separate
+ * operators (fq_add_rmsnorm, fq_swiglu, fq_rope):
+ *   pro (NULL = none): FQ_GEMV_ADD_RMSNORM: input = weight * fp16((x + b) * rsqrt(mean((x+b)^2) + eps)),
+ *     b NULL or (M,K); x + b is also written to `out` (M,K) when given (the new residual stream; it
+ *     must not alias x or b).  FQ_GEMV_SWIGLU: input = fp16(silu(x)) * b with x = gate, b = up (M,K);
+ *     written to `out` when given.
+ *   rope (NULL = none): outputs of projection i with bit i of proj_mask set are rotated in place of
+ *     the plain store, rotate_half convention, position *pos_dev when pos_dev is given, else pos;
+ *     the same position for all M rows.  head_dim must divide 256, N[i] be a multiple of it. */
+enum { FQ_GEMV_PLAIN = 0, FQ_GEMV_ADD_RMSNORM = 1, FQ_GEMV_SWIGLU = 2 };
+typedef struct fq_gemv_prologue {
+    int kind;
+    const void* b;
+    const void* weight;
+    float eps;
+    void* out;
+} fq_gemv_prologue;
+typedef struct fq_gemv_rope {
+    unsigned proj_mask;
+    const int* pos_dev;
+    int pos;
+    float theta;
+    int head_dim;
+} fq_gemv_rope;
 int fq_awq_gemv_default_splits(int K, int N_total, int group);
 int fq_awq_gemv(
     const void* x, int M, int K, int group, int n_proj,
     const int32_t* const* qweight, const void* const* scales, const int32_t* const* qzeros, const void* const* bias,
-    const int* N, void* const* y, int interleaved, void* workspace, size_t workspace_bytes, int k_split, void* stream);
+    const int* N, void* const* y, int interleaved, int k_split, void* stream);
+int fq_awq_gemv_fused(
+    const void* x, int M, int K, int group, int n_proj,
+    const int32_t* const* qweight, const void* const* scales, const int32_t* const* qzeros, const void* const* bias,
+    const int* N, void* const* y, int interleaved, const fq_gemv_prologue* pro, const fq_gemv_rope* rope, int k_split, void* stream);
 
 /* AWQ W4A16 dequant-GEMM for prefill / batched shapes (any M >= 1): the same computation as
  * fq_awq_gemv — the linears kernel/fused_proj.py:36-39,51-53 and the patched forward
@@ -546,10 +578,11 @@ int fq_argmax_f16(const void* x, int64_t rows, int N, int32_t* out, void* stream
 /* ------------------------------------------------------------------------------------
  * One greedy decode step of a Llama-shaped model in ONE foreign call: the decoder-layer loop
  * around eager/llama_persistent_patch.py:164-305 (Hugging Face's LlamaDecoderLayer / LlamaMLP /
- * LlamaRMSNorm semantics) issued from native code, 12 launches per layer and no host work
- * between them.  Per layer: add+RMSNorm, fused AWQ q/k/v GEMV, RoPE, fq_decode_layer_int4
- * (append + score + select + attend), AWQ o GEMV, add+RMSNorm, fused AWQ gate/up GEMV, SwiGLU,
- * AWQ down GEMV; then add+RMSNorm, fp16 lm_head GEMV, argmax.  fp16 model, B <= 8 sequences.
+ * LlamaRMSNorm semantics) issued from native code, 8 launches per layer and no host work
+ * between them.  Per layer: fq_awq_gemv_fused (add+RMSNorm -> q/k/v -> RoPE), fq_decode_layer_int4
+ * (append + score + select + attend), AWQ o GEMV, fq_awq_gemv_fused (add+RMSNorm -> gate/up),
+ * fq_awq_gemv_fused (SwiGLU -> down); then add+RMSNorm, fp16 lm_head GEMV, argmax.  fp16 model,
+ * B <= 8 sequences.
  * All pointers inside the structs are device pointers except `layers` (host array). */
 typedef struct fq_awq_linear {
     const int32_t* qweight; const void* scales; const int32_t* qzeros; const void* bias;   /* bias may be NULL */
@@ -572,9 +605,8 @@ typedef struct fq_llama_scratch {
     void *resid0, *resid1, *normed;                /* (B, hidden) fp16 */
     void *q, *k, *v;                               /* (B, q_heads*D), (B, kv_heads*D) x2 fp16 */
     void *attn_out, *down;                         /* (B, hidden) fp16 */
-    void *gate, *up, *act;                         /* (B, ffn) fp16 */
+    void *gate, *up;                               /* (B, ffn) fp16 */
     void* logits; int32_t* next_ids;               /* (B, vocab) fp16, (B) */
-    void* gemv_ws[4]; size_t gemv_ws_bytes[4];     /* split-K scratch of the q/k/v, o, gate/up and down GEMVs, tickets zero */
     float* scores; int64_t sc_sl;                  /* per layer (B,Hq,P_max) fp32, layer stride in elements */
     int32_t* compact; int64_t cp_sl;               /* per layer (B,Hq,bucket) */
     void* O; int64_t o_sl;                         /* per layer (B,Hq,D) fp16 */

@@ -45,7 +45,5 @@ def test_host_only_entry_points_answer_without_a_gpu():
     so = ctypes.CDLL(path)
     so.fq_version.restype = ctypes.c_char_p
     assert so.fq_version()
-    so.fq_awq_gemv_workspace_bytes.restype = ctypes.c_size_t
-    assert so.fq_awq_gemv_workspace_bytes(1, 5120, 1) == 0
-    assert so.fq_awq_gemv_workspace_bytes(1, 5120, 4) >= 4 * 5120 * 4
-    assert 1 <= so.fq_awq_gemv_default_splits(3072, 5120, 128) <= 24
+    assert so.fq_awq_gemv_default_splits(3072, 5120, 128) in (1, 2, 4, 8)
+    assert so.fq_awq_gemv_default_splits(64, 256, 64) == 1          # one group: nothing to split

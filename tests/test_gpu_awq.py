@@ -85,6 +85,88 @@ def test_rejects_bad_arguments():
         awq_gemv_fused(torch.zeros(1, 128, dtype=torch.float16, device="cuda"), (dev,))
 
 
+def _sep_ops():
+    """The separate operators the fused launch must reproduce (fq_add_rmsnorm, fq_swiglu, fq_rope)."""
+    from flashquest_b200._lib import check, lib, ptr, stream_ptr
+    L = lib()
+    dev = torch.device("cuda")
+
+    def add_rmsnorm(x, delta, w, eps):
+        s, y = torch.empty_like(x), torch.empty_like(x)
+        check(L.fq_add_rmsnorm(ptr(x), ptr(delta), ptr(w), eps, x.shape[0], x.shape[1], ptr(s), ptr(y), stream_ptr(dev)))
+        return s, y
+
+    def swiglu(g, u):
+        a = torch.empty_like(g)
+        check(L.fq_swiglu(ptr(g), ptr(u), g.numel(), ptr(a), stream_ptr(dev)))
+        return a
+
+    def rope(q, Hq, k, Hkv, D, pos, theta):
+        q, k = q.clone(), k.clone()
+        check(L.fq_rope(ptr(q), Hq * D, D, Hq, ptr(k), Hkv * D, D, Hkv, q.shape[0], D, pos, theta, stream_ptr(dev)))
+        return q, k
+    return add_rmsnorm, swiglu, rope
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_fused_norm_qkv_rope(M):
+    """add + RMSNorm in front of the fused QKV launch and the rotary embedding behind it: the separate
+    operators on the same inputs give the same bits, except where the row's sum of squares (another
+    summation order) moves the normalised value by an fp16 ulp; the residual sum is exact."""
+    from flashquest_b200.kernel.fused_proj import awq_gemv_fused
+    add_rmsnorm, _, rope = _sep_ops()
+    K, group, D, theta, pos = 3072, 128, 128, 500000.0, 4321
+    lins = [_make_linear(K, N, group, 70 + i, True, bias=(i == 1)) for i, N in enumerate((3072, 1024, 1024))]
+    devs = [_to_dev(l, group, True) for l in lins]
+    g = torch.Generator().manual_seed(100 + M)
+    x = (torch.randn(M, K, generator=g) * 0.7).half().cuda()
+    delta = (torch.randn(M, K, generator=g) * 0.3).half().cuda()
+    w = (1.0 + 0.1 * torch.randn(K, generator=g)).half().cuda()
+    s_ref, normed = add_rmsnorm(x, delta, w, 1e-5)
+    q0, k0, v0 = awq_gemv_fused(normed, devs)
+    q0, k0 = rope(q0, 24, k0, 8, D, pos, theta)
+    pos_dev = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    for kw in (dict(pos=pos), dict(pos_dev=pos_dev)):
+        q1, k1, v1, s1 = awq_gemv_fused(x, devs, add=delta, norm_weight=w, eps=1e-5, return_sum=True,
+                                        rope=dict(mask=3, theta=theta, head_dim=D, **kw))
+        assert torch.equal(s1, s_ref)
+        for a, b in ((q1, q0), (k1, k0), (v1, v0)):
+            err = (a.float() - b.float()).abs()
+            assert err.max().item() <= 2e-3 * b.float().abs().max().item() + 1e-3
+            assert (err > 0).float().mean().item() < 0.2
+    # without the addition and without the sum: plain RMSNorm of x
+    _, normed_x = add_rmsnorm(x, None, w, 1e-5)
+    (v2,) = awq_gemv_fused(x, devs[2:], norm_weight=w, eps=1e-5)
+    (v3,) = awq_gemv_fused(normed_x, devs[2:])
+    assert (v2.float() - v3.float()).abs().max().item() <= 2e-3 * v3.float().abs().max().item() + 1e-3
+    # against the oracle end to end
+    _check(v3, normed_x.cpu(), lins[2], group, True)
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_fused_swiglu_down(M):
+    from flashquest_b200.kernel.fused_proj import awq_gemv_fused
+    _, swiglu, _ = _sep_ops()
+    K, N, group = 8192, 3072, 128
+    lin = _make_linear(K, N, group, 81, True)
+    dev = _to_dev(lin, group, True)
+    g = torch.Generator().manual_seed(200 + M)
+    gate = (torch.randn(M, K, generator=g) * 1.5).half().cuda()
+    up = (torch.randn(M, K, generator=g) * 0.5).half().cuda()
+    act = swiglu(gate, up)
+    (y0,) = awq_gemv_fused(act, (dev,))
+    (y1,) = awq_gemv_fused(gate, (dev,), swiglu_up=up)
+    assert torch.equal(y0, y1)            # same inputs, same summation order: same bits
+    _check(y1, act.cpu(), lin, group, True)
+    for ks in (1, 2, 4, 8):
+        (y2,) = awq_gemv_fused(gate, (dev,), swiglu_up=up, k_split=ks)
+        _check(y2, act.cpu(), lin, group, True)
+    with pytest.raises(ValueError):
+        awq_gemv_fused(gate, (dev,), swiglu_up=up, norm_weight=up[0])
+    with pytest.raises(ValueError, match="k_split"):
+        awq_gemv_fused(gate, (dev,), k_split=3)
+
+
 def _check_gemm(y_dev, x, lin, group, interleaved):
     """Tensor-core path: weights rounded once to fp16 (as AutoAWQ's GEMM kernels do), fp32 accumulation."""
     qw, sc, qz, b = lin
