@@ -31,6 +31,8 @@ _PROTOTYPES = {
     "fq_page_scores_int4": (I, [P, I, L, L, P, P, L, L, L, I, I, I, I, I, P, L, L, P]),
     "fq_select_pages": (I, [P, L, L, I, I, I, P, F, I, I, I, P, L, L, P, L, L, I, P, P]),
     "fq_build_compact": (I, [P, L, L, I, P, L, I, P]),
+    "fq_score_select_supported": (I, [I, I, I, I]),
+    "fq_score_select": (I, [P, I, L, L, P, P, L, L, L, I, I, I, I, I, I, P, L, L, P, F, I, I, I, P, L, L, I, P, I, P]),
     "fq_sparse_decode_workspace_bytes": (Z, [I, I, I, I]),
     "fq_sparse_decode_default_splits": (I, [I, I, I, I]),
     "fq_sparse_decode_int4": (I, [P, I, L, L, P, L, L, P, P, L, L, L, P, L, L, P, P, L, L,

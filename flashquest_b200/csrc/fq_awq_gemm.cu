@@ -185,12 +185,22 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
         uint32_t zsub[4];                             // (1024 + zero) for the four column pairs, half2 bits
         __half2 sc2[4];                               // scales of the four column pairs
         const int a_n = c >> 3, chunk = c & 7;        // 64-column atom and 16-byte chunk inside its rows
+        // scale and zero words of the NEXT group are requested one group ahead, so that their latency
+        // is hidden behind a whole group of dequantisation
+        const int n_grp = (num_kb + gpk - 1) / gpk;
+        auto load_meta = [&](int g, uint32_t& zw, uint4& s4) {
+            zw = (uint32_t)__ldg(P.qzeros + (int64_t)g * (P.N / 8) + n0 / 8 + c);
+            s4 = __ldg(reinterpret_cast<const uint4*>(P.scales + (int64_t)g * P.N + n0 + 8 * c));
+        };
+        uint32_t zw_nx = 0; uint4 s4_nx = make_uint4(0, 0, 0, 0);
+        load_meta(0, zw_nx, s4_nx);
         for (int kb = 0; kb < num_kb; ++kb) {
             const int s = kb % GM_STAGES;
             if (kb % gpk == 0) {                      // new group: scale and zero of this thread's 8 columns
-                const int g = (kb * GM_BK) / p.group;
-                const uint32_t zw = (uint32_t)__ldg(P.qzeros + (int64_t)g * (P.N / 8) + n0 / 8 + c);
-                const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(P.scales + (int64_t)g * P.N + n0 + 8 * c));
+                const int g = kb / gpk;
+                const uint32_t zw = zw_nx;
+                const uint4 s4 = s4_nx;
+                if (g + 1 < n_grp) load_meta(g + 1, zw_nx, s4_nx);
                 const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) zsub[q] = ((zw >> (4 * q)) & 0x000f000fu) | 0x64006400u;

@@ -78,6 +78,13 @@ int page_scores_int4_launch(
     const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
     int B, int Hq, int Hkv, int P, int D, float* scores, int64_t sc_sb, int64_t sc_sh, void* stream, const DynPos& dp,
     float levels = 15.0f);
+bool score_select_fusable(int Hq, int Hkv, int P, int D);
+int score_select_launch(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int B, int Hq, int Hkv, int P, int D, float levels, float* scores, int64_t sc_sb, int64_t sc_sh,
+    const float* retention_per_head, float retention, int k_max, int sinks, int window,
+    int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket, int32_t* count, void* stream, const DynPos& dp, int first_fresh);
 int select_pages_launch(
     const float* scores, int64_t sc_sb, int64_t sc_sh, int B, int H, int P,
     const float* retention_per_head, float retention, int k_max, int sinks, int window,

@@ -9,7 +9,7 @@
 // consecutive pages, so every warp load is one contiguous 512-byte run.  Each lane keeps
 // its slice of q for all NR query heads in registers; the per-page reduction is a 3-step
 // xor shuffle inside the quarter warp.
-#include "fq_common.cuh"
+#include "fq_score_lane.cuh"
 
 namespace fq {
 
@@ -45,77 +45,15 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
         const int p = p_base + it * 16 + warp * 4 + qw;
-#pragma unroll
-        for (int c = 0; c < CH; ++c) {
-            const int chunk = l + 8 * c;
-            if (p < P && chunk < n_chunks) {
-                m4[it][c] = ldg16(mn_base + (int64_t)p * km_sp + 8 * chunk);
-                s4[it][c] = ldg16(sc_base + (int64_t)p * km_sp + 8 * chunk);
-            } else {
-                m4[it][c] = make_uint4(0, 0, 0, 0);
-                s4[it][c] = make_uint4(0, 0, 0, 0);
-            }
-        }
+        score_load_meta<CH>(sc_base, mn_base, km_sp, p, p < P, l, n_chunks, m4[it], s4[it]);
     }
-
     float q[NR][CH][8];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-        const int hq = hkv * n_rep + head_off + min(r, nr - 1);
-#pragma unroll
-        for (int c = 0; c < CH; ++c) {
-            const int chunk = l + 8 * c;
-            if (chunk < n_chunks) {
-                load8<QT>(Q + b * q_sb + hq * q_sh + 8 * chunk, q[r][c]);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) q[r][c][e] = 0.f;
-            }
-        }
-    }
-
+    score_load_q<QT, NR, CH>(Q + b * q_sb, q_sh, hkv * n_rep + head_off, nr, l, n_chunks, q);
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
         const int p = p_base + it * 16 + warp * 4 + qw;
-        const bool live = p < P;
-        float t1[NR], t2[NR];
-#pragma unroll
-        for (int r = 0; r < NR; ++r) { t1[r] = 0.f; t2[r] = 0.f; }
-        {
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                const uint32_t mw[4] = {m4[it][c].x, m4[it][c].y, m4[it][c].z, m4[it][c].w};
-                const uint32_t sw[4] = {s4[it][c].x, s4[it][c].y, s4[it][c].z, s4[it][c].w};
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float mn = (e & 1) ? bf16_hi(mw[e >> 1]) : bf16_lo(mw[e >> 1]);
-                    const float sc = (e & 1) ? bf16_hi(sw[e >> 1]) : bf16_lo(sw[e >> 1]);
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) {
-                        const float qv = q[r][c][e];
-                        t1[r] = __fmaf_rn(qv, mn, t1[r]);
-                        t2[r] = __fmaf_rn(fmaxf(qv, 0.f), sc, t2[r]);
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int off = 4; off >= 1; off >>= 1) {
-#pragma unroll
-            for (int r = 0; r < NR; ++r) {
-                t1[r] = __fadd_rn(t1[r], __shfl_xor_sync(0xffffffffu, t1[r], off));
-                t2[r] = __fadd_rn(t2[r], __shfl_xor_sync(0xffffffffu, t2[r], off));
-            }
-        }
-        if (live && l < nr) {
-            float v1 = t1[0], v2 = t2[0];
-#pragma unroll
-            for (int r = 1; r < NR; ++r) {
-                if (l == r) { v1 = t1[r]; v2 = t2[r]; }
-            }
-            const int hq = hkv * n_rep + head_off + l;
-            scores[b * sc_sb + hq * sc_sh + p] = __fadd_rn(v1, __fmul_rn(v2, levels));
-        }
+        const float v = score_page<NR, CH>(q, m4[it], s4[it], l, levels);
+        if (p < P && l < nr) scores[b * sc_sb + (hkv * n_rep + head_off + l) * sc_sh + p] = v;
     }
 }
 

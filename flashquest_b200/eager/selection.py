@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from .._lib import check, lib, ptr, require_cuda, stream_ptr
+from .._lib import check, dtype_code, lib, ptr, require_cuda, stream_ptr
 
 
 def _select(scores, retention, num_sinks, window_pages, k_max_static, want_mask, bucket, want_count=False):
@@ -78,3 +78,41 @@ def build_compact_selection(mask: torch.Tensor, BUCKET_MAX: int) -> torch.Tensor
         check(lib().fq_build_compact(ptr(m), P, B * H * S_q, P, ptr(out), BUCKET_MAX, BUCKET_MAX,
                                      stream_ptr(mask.device)))
     return out
+
+
+def score_select_compact(Q: torch.Tensor, K_scale: torch.Tensor, K_mn: torch.Tensor, retention, num_sinks: int,
+                         window_pages: int, *, k_max_static: int, BUCKET_MAX: int, levels: int = 15,
+                         first_fresh_page: int = 0):
+    """page_scores_int4_fast (levels=15) / page_scores_int8_fast (levels=255) -> select_pages_vectorized ->
+    build_compact_selection in ONE launch (fq_score_select), the sequence the decode branch runs
+    (eager/llama_persistent_patch.py:214-228).  Q (B,H_q,1,D); K_scale, K_mn (B,H_kv,P,D) bf16;
+    retention a float or a (H_q,) tensor.  Returns (scores (B,H_q,1,P) fp32, compact (B,H_q,1,BUCKET_MAX)
+    int32), bit-identical to the separate calls.  first_fresh_page: see fq_score_select."""
+    B, H_q, S_q, D = Q.shape
+    if S_q != 1:
+        raise NotImplementedError(f"score_select_compact: decode-only (S_q={S_q})")
+    require_cuda(Q, K_scale, K_mn)
+    H_kv, P = K_scale.shape[1], K_scale.shape[2]
+    if not lib().fq_score_select_supported(H_q, H_kv, P, D):
+        raise NotImplementedError("score_select_compact: shape outside the fused launch (use the separate calls)")
+    Q3 = Q.reshape(B, H_q, D)
+    if Q3.stride(2) != 1:
+        Q3 = Q3.contiguous()
+    if K_scale.stride(3) != 1 or K_scale.stride() != K_mn.stride():
+        K_scale, K_mn = K_scale.contiguous(), K_mn.contiguous()
+    scores = torch.empty(B, H_q, max(P, 1), dtype=torch.float32, device=Q.device)
+    compact = torch.empty(B, H_q, BUCKET_MAX, dtype=torch.int32, device=Q.device)
+    r_t = None
+    r_f = 0.0
+    if isinstance(retention, torch.Tensor):
+        r_t = retention.to(device=Q.device, dtype=torch.float32).contiguous()
+    else:
+        r_f = float(retention)
+    with torch.cuda.device(Q.device):
+        check(lib().fq_score_select(
+            ptr(Q3), dtype_code(Q3), Q3.stride(0), Q3.stride(1), ptr(K_scale), ptr(K_mn), *K_scale.stride()[:3],
+            B, H_q, H_kv, P, D, int(levels), ptr(scores), scores.stride(0), scores.stride(1),
+            ptr(r_t), r_f, min(int(k_max_static), P), int(num_sinks), int(window_pages),
+            ptr(compact), compact.stride(0), compact.stride(1), int(BUCKET_MAX), None, int(first_fresh_page),
+            stream_ptr(Q.device)))
+    return scores[:, :, :P].unsqueeze(2), compact.unsqueeze(2)

@@ -138,6 +138,27 @@ int fq_select_pages(
 int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
                      int32_t* compact, int64_t cp_sr, int bucket, void* stream);
 
+/* Page scores, top-k and compact index in ONE launch: fq_page_scores_int4 (levels 15) or
+ * fq_page_scores_int8 (levels 255) followed by fq_select_pages with a compact list and no mask, i.e.
+ * page_scores_int4_fast / page_scores_int8_fast -> select_pages_vectorized -> build_compact_selection
+ * (eager/criticality.py:77-163, eager/selection.py:65-164) as the decode branch chains them
+ * (eager/llama_persistent_patch.py:214-228).  Same arguments and the same bits in `scores` and
+ * `compact` as the two separate calls.  A thread-block cluster of 8 CTAs per (batch, KV head) scores
+ * the pages once for the whole GQA group and hands each head's keys through distributed shared memory
+ * to the CTA that selects for it.  Shapes: at most 4 query heads per KV head, P <= 16384, head_dim in
+ * {32,64,128,256} (fq_score_select_supported tells; other shapes take the two separate calls).
+ * first_fresh_page: the caller's word that the metadata rows of pages below it were written BEFORE the
+ * launch that precedes this call in the stream (a decode step that appended one token passes the index
+ * of the page that token went to); their copies are then requested ahead of the dependency wait and
+ * overlap the previous kernel.  0 = no such promise. */
+int fq_score_select_supported(int Hq, int Hkv, int P, int D);
+int fq_score_select(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int B, int Hq, int Hkv, int P, int D, int levels, float* scores, int64_t sc_sb, int64_t sc_sh,
+    const float* retention_per_head, float retention, int k_max, int sinks, int window,
+    int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket, int32_t* count, int first_fresh_page, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * INT8 KV variant (cache.kv_bits == 8): KIVI-style asymmetric uint8, one code per byte.
  * fq_quantize_kv_int8 replaces quantize_k / quantize_v (kernel/kv_quant.py:45-62, :81-93):

@@ -135,3 +135,49 @@ def test_compact_sentinels_and_truncation(ops, golden):
     assert (ops.compact(torch.zeros(1, 1, 1, 8, dtype=torch.bool, device="cuda"), 4) == -1).all()
     full = ops.compact(torch.ones(1, 1, 1, 4, dtype=torch.bool, device="cuda"), 2)   # keeps the highest ids
     assert full.flatten().tolist() == [3, 2]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,Hq,Hkv,P,D", [(1, 24, 8, 2048, 128), (2, 6, 2, 37, 128), (1, 4, 4, 19, 64), (1, 8, 2, 257, 128),
+                                          (1, 2, 1, 1, 128), (1, 10, 5, 21, 32), (1, 6, 3, 300, 256), (1, 3, 1, 4100, 128)])
+def test_fused_score_select_equals_separate_calls(ops, dtype, B, Hq, Hkv, P, D):
+    """fq_score_select against the oracle and against the two separate launches: the same bits in the
+    scores, the same compact list, with and without the early metadata request."""
+    from flashquest_b200.eager.selection import score_select_compact
+    Ks, Km = _meta(3, B, Hkv, P, D)
+    Ks[:, :, P // 2] = Ks[:, :, 0]             # two pages with identical metadata: an exact score tie
+    Km[:, :, P // 2] = Km[:, :, 0]
+    Q = make_q(4, (B, Hq, 1, D), dtype)
+    want_s = oracle.page_scores_int4_fast(Q, Ks, Km)
+    r_head = torch.tensor([0.25 if h % 3 else 0.0 for h in range(Hq)])
+    for retention, sinks, window in ((0.25, 1, 1), (r_head, 4, 2), (1.0, 0, 0), (0.0, 0, 3)):
+        rmax = float(retention.max()) if isinstance(retention, torch.Tensor) else retention
+        kms = math.ceil(rmax * P)
+        bucket = max(1, kms + sinks + window)
+        want_m = oracle.select_pages_vectorized(want_s, retention, sinks, window, k_max_static=kms)
+        want_c = oracle.build_compact_selection(want_m, bucket)
+        r_dev = retention.cuda() if isinstance(retention, torch.Tensor) else retention
+        for fresh in (0, P, max(P - 1, 0), P // 2):
+            s, c = score_select_compact(Q.cuda(), Ks.cuda(), Km.cuda(), r_dev, sinks, window, k_max_static=kms,
+                                        BUCKET_MAX=bucket, first_fresh_page=fresh)
+            assert s.shape == (B, Hq, 1, P) and c.shape == (B, Hq, 1, bucket)
+            assert bit_equal(s.cpu(), want_s), (retention, fresh)
+            assert torch.equal(c.cpu(), want_c), (retention, fresh)
+    s2 = ops.scores(Q.cuda(), Ks.cuda(), Km.cuda())
+    assert bit_equal(s2.cpu(), want_s)
+
+
+def test_fused_score_select_int8_levels_and_errors():
+    from flashquest_b200.eager.selection import score_select_compact
+    K = make_kv(9, (1, 2, 40 * 16, 128), torch.bfloat16)
+    _, Ks, Km = oracle.quantize_k(K, 16)
+    Q = make_q(10, (1, 4, 1, 128), torch.bfloat16)
+    want_s = oracle.page_scores_int8_fast(Q, Ks, Km)
+    want_c = oracle.build_compact_selection(oracle.select_pages_vectorized(want_s, 0.3, 1, 1, k_max_static=12), 14)
+    s, c = score_select_compact(Q.cuda(), Ks.cuda(), Km.cuda(), 0.3, 1, 1, k_max_static=12, BUCKET_MAX=14, levels=255)
+    assert bit_equal(s.cpu(), want_s) and torch.equal(c.cpu(), want_c)
+    with pytest.raises(ValueError, match="levels"):
+        score_select_compact(Q.cuda(), Ks.cuda(), Km.cuda(), 0.3, 1, 1, k_max_static=12, BUCKET_MAX=14, levels=16)
+    with pytest.raises(NotImplementedError):      # 8 query heads per KV head: outside the fused launch
+        score_select_compact(make_q(1, (1, 16, 1, 128), torch.bfloat16).cuda(), Ks.cuda(), Km.cuda(), 0.3, 1, 1,
+                             k_max_static=12, BUCKET_MAX=14)
