@@ -940,6 +940,36 @@ def run_prefill_attn(args):
 
 # --------------------------------------------------------------------------- secondary workload: Llama decode
 
+def llama_batched_leg(torch, cfg, w, dev, Bb, S, steps):
+    """The Llama-shaped model decoding Bb sequences at once (not part of config 3): the weights are read once for all
+    rows (AWQ GEMV and lm_head on the tensor cores for 2..8 rows); caches filled with synthetic K/V of BASELINE's
+    distribution, no prefill."""
+    from flashquest_b200 import _lib
+    from flashquest_b200.eager.llama_decode import LlamaInt4Decoder
+    decb = LlamaInt4Decoder(cfg, w, batch_size=Bb, max_seq_len=S + 256, page_size=16, retention=0.25, num_sinks=1, window_pages=1,
+                            device=dev)
+    for li in range(cfg.layers):
+        for b in range(Bb):
+            fill_cache_random(torch, decb.cache, li, b, 5000 + 97 * li + b, S)
+        decb.cache._seen_tokens[li] = S
+    idb = torch.arange(Bb, dtype=torch.int32, device=dev) * 1000 + 17
+    for _ in range(2):
+        idb = decb.decode_step(idb).clone()
+    rb = decb.capture_decode_graph(idb)
+    for _ in range(3):
+        rb()
+    torch.cuda.synchronize()
+    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    b0.record()
+    for _ in range(steps):
+        rb()
+    b1.record()
+    torch.cuda.synchronize()
+    msb = b0.elapsed_time(b1) / steps
+    return {"batch": Bb, "value": Bb * 1e3 / msb, "unit": "tokens/s", "ms_per_step": msb, "steps": steps, "layers": cfg.layers,
+            "cache": f"synthetic K/V, {S} tokens per sequence (no prefill)", "device_status": _lib.lib().fq_device_status()}
+
+
 def run_llama(args):
     """BASELINE config 3: random-init Llama-3.2-3B architecture with AWQ 4-bit weights; the prompt is 32 768
     uniform-random token ids from Python's seeded generator (the reference's protocol, scripts/bench_flashquest.py:
@@ -960,6 +990,10 @@ def run_llama(args):
     S = args.ctx or 32768
     n_decode = 127
     w = random_llama_weights(cfg, dev, seed=3)
+    if args.batch and args.batch > 1:        # the batched decode leg alone (small captures: --layers, --ctx, --steps)
+        r = llama_batched_leg(torch, cfg, w, dev, args.batch, S, max(args.steps, 1))
+        r.update({"metric": "Llama-3.2-3B-shaped AWQ decode tokens/s, batched (synthetic cache)", "workload": "llama"})
+        return r
     dec = LlamaInt4Decoder(cfg, w, batch_size=1, max_seq_len=S + 256, page_size=16, retention=0.25, num_sinks=1, window_pages=1,
                            device=dev)
     from flashquest_b200 import bench_record as br
@@ -1031,6 +1065,13 @@ def run_llama(args):
         rec["provenance"] = br.provenance({"torch": torch.__version__}, [{"name": torch.cuda.get_device_name(dev)}])
         with open(record_path, "w") as f:
             json.dump(br.export_record(rec), f, indent=1)
+    launches = dec.launches + dec.attn.launches - l0
+    status = _lib.lib().fq_device_status()
+    batched = None
+    if not args.layers and not args.ctx:
+        del dec, replay
+        torch.cuda.empty_cache()
+        batched = llama_batched_leg(torch, cfg, w, dev, 8, S, 30)
     return {
         "metric": "Llama-3.2-3B-shaped AWQ decode tokens/s at 32k ctx (sparse INT4 attention)", "workload": "llama",
         "value": 1e3 / ms, "unit": "tokens/s", "ms_per_token": ms, "decode_steps_timed": timed, "decode_steps_total": n_decode,
@@ -1040,8 +1081,8 @@ def run_llama(args):
                    "ffn": cfg.ffn, "vocab": cfg.vocab, "context": S, "retention": 0.25, "weights": "random-init AWQ 4-bit, group 128",
                    "prompt": "32768 ids from random.Random(0).randrange(vocab), prefilled", "parity": "AWQ arithmetic unpinned"},
         "weight_bytes_per_token": wbytes, "weight_GBs": wbytes / ms / 1e6,
-        "gpu_launches": dec.launches + dec.attn.launches - l0, "clocks": clk.summary(),
-        "device_status": _lib.lib().fq_device_status()}
+        "gpu_launches": launches, "clocks": clk.summary(), "batch8": batched,
+        "device_status": status}
 
 
 # --------------------------------------------------------------------------- secondary workload: context split

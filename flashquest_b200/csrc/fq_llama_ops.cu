@@ -134,6 +134,58 @@ __global__ void __launch_bounds__(GEMVH_WARPS * 32) gemv_f16_kernel(const __half
     }
 }
 
+// The same product for 2..8 rows on the tensor cores (mma.sync m16n8k16, fp32 accumulation): on the CUDA cores every
+// weight costs one fma per row and a shared-memory read of x, which for 8 rows is several times the HBM time of W.
+// A warp owns 16 output rows (A = 16 rows of W, straight from global memory with 16-byte loads), B = the rows of x
+// (staged once per CTA as fp16, padded to 8 rows); lane (g, t) reads W[n0+g][k0+8t .. +7] and W[n0+g+8][...], i.e. the
+// k index inside an MMA is permuted the same way for A and B.  CTAs are persistent over tiles of 128 output rows.
+constexpr int GEMVM_WARPS = 8;
+constexpr int GEMVM_XPAD = 32;      // fp16 elements: row stride = 16 words mod 32, conflict-free 16-byte fragment loads
+
+__global__ void __launch_bounds__(GEMVM_WARPS * 32) gemv_f16_mma_kernel(const __half* __restrict__ x, const __half* __restrict__ W,
+                                                                        int Mrows, int K, int N, __half* __restrict__ y) {
+    extern __shared__ __align__(16) __half s_xh[];      // [8][K + XPAD]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int xs = K + GEMVM_XPAD;
+    pdl_wait();
+    pdl_trigger();
+    for (int i = threadIdx.x; i < 8 * (K / 8); i += GEMVM_WARPS * 32) {
+        const int m = i / (K / 8), kk = (i - m * (K / 8)) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (m < Mrows) v = __ldcg(reinterpret_cast<const uint4*>(x + (int64_t)m * K + kk));
+        *reinterpret_cast<uint4*>(s_xh + m * xs + kk) = v;
+    }
+    __syncthreads();
+    const int tiles = (N + 16 * GEMVM_WARPS - 1) / (16 * GEMVM_WARPS);
+    const __half* xrow = s_xh + g * xs + 8 * t;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int n0 = tile * 16 * GEMVM_WARPS + warp * 16;
+        if (n0 >= N) continue;
+        const __half* wa = W + (int64_t)min(n0 + g, N - 1) * K + 8 * t;
+        const __half* wb = W + (int64_t)min(n0 + g + 8, N - 1) * K + 8 * t;
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int k0 = 0; k0 < K; k0 += 32) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(wa + k0));
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(wb + k0));
+            const uint4 xv = *reinterpret_cast<const uint4*>(xrow + k0);
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a.x), "r"(b.x), "r"(a.y), "r"(b.y), "r"(xv.x), "r"(xv.y));
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a.z), "r"(b.z), "r"(a.w), "r"(b.w), "r"(xv.z), "r"(xv.w));
+        }
+        // c0, c1: output row n0+g for x rows 2t, 2t+1; c2, c3: output row n0+g+8
+        if (2 * t < Mrows) {
+            if (n0 + g < N) y[(int64_t)(2 * t) * N + n0 + g] = __float2half_rn(c[0]);
+            if (n0 + g + 8 < N) y[(int64_t)(2 * t) * N + n0 + g + 8] = __float2half_rn(c[2]);
+        }
+        if (2 * t + 1 < Mrows) {
+            if (n0 + g < N) y[(int64_t)(2 * t + 1) * N + n0 + g] = __float2half_rn(c[1]);
+            if (n0 + g + 8 < N) y[(int64_t)(2 * t + 1) * N + n0 + g + 8] = __float2half_rn(c[3]);
+        }
+    }
+}
+
 // index of the first maximum of each row (torch.argmax): a cluster of ARGMAX_CTAS CTAs per row, each scans
 // a contiguous slice and sends its best (value, index) to the first CTA through distributed shared memory
 constexpr int ARGMAX_CTAS = 8;
@@ -261,6 +313,19 @@ extern "C" int fq_gemv_f16(const void* x, const void* W, int M, int K, int N, vo
     FQ_CHECK_ARG(x && W && y && N > 0 && K > 0, FQ_ERR_ARG, "%s: bad arguments", fn);
     FQ_CHECK_ARG(M >= 1 && M <= 8, FQ_ERR_UNSUPPORTED, "%s: M=%d rows; 1..8 are built", fn, M);
     FQ_CHECK_ARG(K % 8 == 0 && aligned(W, 16) && aligned(x, 2), FQ_ERR_ALIGN, "%s: K must be a multiple of 8 and W 16-byte aligned", fn);
+    cudaStream_t st0 = static_cast<cudaStream_t>(stream);
+    if (M >= 2 && K % 32 == 0 && (size_t)8 * (K + GEMVM_XPAD) * 2 <= 100 * 1024) {
+        const size_t smem_m = (size_t)8 * (K + GEMVM_XPAD) * 2;
+        if (smem_m > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(gemv_f16_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_m);
+            if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));
+        }
+        const int tiles = (N + 16 * GEMVM_WARPS - 1) / (16 * GEMVM_WARPS);
+        launch_k(PDL_GEMV, gemv_f16_mma_kernel, dim3((unsigned)(tiles < 2 * 148 ? tiles : 2 * 148)), dim3(GEMVM_WARPS * 32), smem_m, st0,
+                 static_cast<const __half*>(x), static_cast<const __half*>(W), M, K, N, static_cast<__half*>(y));
+        FQ_CHECK_LAUNCH(fn);
+        return FQ_OK;
+    }
     const int Mp = M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
     const size_t smem = (size_t)Mp * K * 4;
     FQ_CHECK_ARG(smem <= 200 * 1024, FQ_ERR_UNSUPPORTED, "%s: M x K = %d x %d does not fit in shared memory", fn, M, K);

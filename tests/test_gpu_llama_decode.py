@@ -134,6 +134,14 @@ def test_small_ops_match_torch():
     check(L.fq_gemv_f16(ptr(xd), ptr(Wd), 3, 512, 1000, ptr(yv), st()))
     ref = (x.float() @ W.float().T)
     assert (yv.cpu().float() - ref).abs().max() <= 2e-3 * ref.abs().max() + 1e-3
+    # one row on the CUDA cores, 2..8 rows on the tensor cores, ragged N, a K the tensor-core path does not take
+    for Mr, Kr, Nr in ((1, 512, 1000), (2, 1024, 130), (8, 3072, 2056), (5, 520, 64), (8, 256, 7)):
+        xr, Wr = torch.randn(Mr, Kr, generator=g).half(), (torch.randn(Nr, Kr, generator=g) * 0.05).half()
+        yr = torch.full((Mr, Nr), float("nan"), dtype=torch.float16, device=dev)
+        xrd, Wrd = xr.cuda(), Wr.cuda()
+        check(L.fq_gemv_f16(ptr(xrd), ptr(Wrd), Mr, Kr, Nr, ptr(yr), st()))
+        rr = xr.float() @ Wr.float().T
+        assert (yr.cpu().float() - rr).abs().max() <= 2e-3 * rr.abs().max() + 1e-3, (Mr, Kr, Nr)
     idx = torch.empty(3, dtype=torch.int32, device=dev)
     yv[1, 7] = yv[1].max() ; yv[1, 500] = yv[1, 7]               # a tie: the first index wins
     check(L.fq_argmax_f16(ptr(yv), 3, 1000, ptr(idx), st()))
