@@ -1,22 +1,26 @@
 // AWQ W4A16 dequant-GEMM on the 5th-generation tensor cores (tcgen05) for prefill / batched
 // shapes: y[M,N] = x[M,K] @ W, W in AutoAWQ's GEMM format (4-bit codes, group scales and zeros).
-// The M <= 8 decode shapes stay with the CUDA-core GEMV (fq_awq_gemv.cu); this kernel is the dense
+// The M <= 8 decode shapes stay with the GEMV (fq_awq_gemv.cu); this kernel is the dense
 // contraction of the prefill branch (the q/k/v/o/gate/up/down linears over all prompt tokens).
 //
-// One CTA computes a 256 x 128 output tile (two 128 x 128 accumulators in tensor memory that share
-// every weight tile) and walks K in steps of 64:
-//   warp 0      : one thread issues the TMA loads of a stage — two x tiles of 128 rows x 64 k
-//                 (fp16, 128-byte swizzle, K-major) and the raw weight tile of 64 k x 16 int32;
-//   warps 1..4  : dequantise the raw tile to fp16 in shared memory, (code - zero) * scale rounded
-//                 once to fp16 like the reference's GEMM kernels, written N-contiguous in the
-//                 canonical MN-major 128-byte-swizzle layout (AWQ's nibble order makes every
-//                 masked word a pair of neighbouring columns, so a 32-bit word of codes becomes one
-//                 16-byte store); after the K loop the same warps drain the accumulators
-//                 (tcgen05.ld, lane quarter = warp id mod 4), convert to fp16 and store y;
-//   warp 5      : one thread issues tcgen05.mma (M 128, N 128, K 16, fp16 x fp16 -> fp32 in TMEM),
-//                 eight per stage, and commits the stage back to the producer.
-// Stages are handed over through mbarriers (TMA bytes -> dequantised -> consumed); every wait is
-// bounded and reports through the device status word instead of spinning forever.
+// A CTA is persistent: it walks output tiles of 256 x 128 (two 128 x 128 accumulators in tensor memory
+// that share every weight tile; two such sets, so that a finished tile is drained while the next one
+// is multiplied) and, inside a tile, K in steps of 64:
+//   warp 0       : one thread issues the TMA loads of a stage — two x tiles of 128 rows x 64 k
+//                  (fp16, 128-byte swizzle, K-major) and the raw weight tile of 64 k x 16 int32;
+//   warp 1       : one thread issues tcgen05.mma (M 128, N 128, K 16, fp16 x fp16 -> fp32 in TMEM),
+//                  eight per stage, commits the stage back to the producer and the accumulator set
+//                  to the epilogue; the warp also owns the tensor-memory allocation (512 columns);
+//   warps 2..9   : dequantise the raw tile to fp16 in shared memory, (code - zero) * scale rounded
+//                  once to fp16 like the reference's GEMM kernels, written N-contiguous in the
+//                  canonical MN-major 128-byte-swizzle layout (AWQ's nibble order makes every
+//                  masked word a pair of neighbouring columns, so a 32-bit word of codes becomes one
+//                  16-byte store);
+//   warps 10..13 : epilogue — drain an accumulator set (tcgen05.ld, lane quarter = warp id mod 4),
+//                  add the bias, convert to fp16, store y, hand the set back.
+// Stages and accumulator sets are handed over through mbarriers (TMA bytes -> dequantised ->
+// consumed; multiplied -> drained); every wait is bounded and reports through the device status
+// word instead of spinning forever.
 #include <cuda.h>
 
 #include "fq_common.cuh"
@@ -28,7 +32,10 @@ constexpr int GM_MT = 2;            // accumulators (M tiles) per CTA
 constexpr int GM_BN = 128;
 constexpr int GM_BK = 64;
 constexpr int GM_STAGES = 4;
-constexpr int GM_THREADS = 192;     // TMA warp, 4 dequant / epilogue warps, MMA warp
+constexpr int GM_DEQ_WARPS = 8;
+constexpr int GM_EPI_WARPS = 4;
+constexpr int GM_THREADS = (2 + GM_DEQ_WARPS + GM_EPI_WARPS) * 32;     // TMA warp, MMA warp, dequantise warps, epilogue warps
+constexpr int GM_ACC_SETS = 2;      // accumulator sets in tensor memory (2 x 2 x 128 columns = all 512)
 constexpr int GM_MAX_PROJ = 4;
 constexpr unsigned GM_SPIN_LIMIT = 1u << 26;
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;             // 16 KiB per M tile
@@ -36,6 +43,7 @@ constexpr int GM_RAW_BYTES = GM_BK * (GM_BN / 8) * 4;     // 4 KiB
 constexpr int GM_B_BYTES = GM_BK * GM_BN * 2;             // 16 KiB
 constexpr int GM_STAGE_BYTES = GM_MT * GM_A_BYTES + GM_B_BYTES + GM_RAW_BYTES;
 constexpr int GM_SMEM = GM_STAGES * GM_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers, tmem address */;
+static_assert((3 * GM_STAGES + 4) * 8 + 4 <= 256, "barrier block");
 
 struct GemmProj {
     const __half* scales; const int32_t* qzeros; const __half* bias; __half* y;
@@ -44,6 +52,7 @@ struct GemmProj {
 struct GemmParams {
     GemmProj proj[GM_MAX_PROJ];
     int n_proj, M, K, group, interleaved;
+    int n_tiles, m_tiles;   // N tiles over all projections, M tiles of 256 rows
     int* status;
 };
 
@@ -99,34 +108,30 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gm_raw_smem) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + GM_STAGES * GM_STAGE_BYTES);
     uint64_t* full_raw = bars;                       // [stages] TMA bytes landed (x tiles + raw codes)
-    uint64_t* b_ready = bars + GM_STAGES;            // [stages] dequantised tile written (128 arrivals)
+    uint64_t* b_ready = bars + GM_STAGES;            // [stages] dequantised tile written (256 arrivals)
     uint64_t* empty = bars + 2 * GM_STAGES;          // [stages] the MMAs that read the stage have completed
-    uint64_t* acc_ready = bars + 3 * GM_STAGES;      // all MMAs of the tile have completed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * GM_STAGES + 1);
+    uint64_t* acc_ready = bars + 3 * GM_STAGES;      // [sets] all MMAs of a tile have completed
+    uint64_t* acc_empty = acc_ready + GM_ACC_SETS;   // [sets] the epilogue has drained the set (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + GM_ACC_SETS);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // which projection this N tile belongs to
-    int pj = 0;
-#pragma unroll
-    for (int i = 1; i < GM_MAX_PROJ; ++i)
-        if (i < p.n_proj && (int)blockIdx.x >= p.proj[i].tile0) pj = i;
-    const GemmProj& P = p.proj[pj];
-    const CUtensorMap* map_w = pj == 0 ? &map_w0 : (pj == 1 ? &map_w1 : (pj == 2 ? &map_w2 : &map_w3));
-    const int n0 = ((int)blockIdx.x - P.tile0) * GM_BN;
-    const int m0 = (int)blockIdx.y * (GM_BM * GM_MT);
     const int num_kb = p.K / GM_BK;
+    const int total_tiles = p.n_tiles * p.m_tiles;
 
     if (tid == 0) {
         for (int s = 0; s < GM_STAGES; ++s) {
             gm_mbar_init(&full_raw[s], 1);
-            gm_mbar_init(&b_ready[s], 128);
+            gm_mbar_init(&b_ready[s], GM_DEQ_WARPS * 32);
             gm_mbar_init(&empty[s], 1);
         }
-        gm_mbar_init(acc_ready, 1);
+        for (int a = 0; a < GM_ACC_SETS; ++a) {
+            gm_mbar_init(&acc_ready[a], 1);
+            gm_mbar_init(&acc_empty[a], GM_EPI_WARPS * 32);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {     // tensor memory: two accumulators of 128 fp32 columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem(tmem_slot)), "r"(GM_MT * GM_BN) : "memory");
+    if (warp == 1) {     // tensor memory: two sets of two accumulators of 128 fp32 columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem(tmem_slot)), "r"(GM_ACC_SETS * GM_MT * GM_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -135,126 +140,162 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
 
+    // tile index -> projection, first column inside it, first row (N tiles vary fastest: neighbouring CTAs share x rows)
+    auto locate = [&](int tile, int& pj, int& n0, int& m0) {
+        const int nt = tile % p.n_tiles;
+        pj = 0;
+#pragma unroll
+        for (int i = 1; i < GM_MAX_PROJ; ++i)
+            if (i < p.n_proj && nt >= p.proj[i].tile0) pj = i;
+        n0 = (nt - p.proj[pj].tile0) * GM_BN;
+        m0 = (tile / p.n_tiles) * (GM_BM * GM_MT);
+    };
+
     if (warp == 0) {
         // =========================== TMA producer ===========================
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % GM_STAGES;
-                if (kb >= GM_STAGES && !gm_wait(&empty[s], (unsigned)(kb / GM_STAGES - 1) & 1u)) { failed = true; break; }
-                unsigned char* st = base + s * GM_STAGE_BYTES;
-                gm_mbar_expect_tx(&full_raw[s], GM_MT * GM_A_BYTES + GM_RAW_BYTES);
+            int g = 0;                                  // k blocks issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+                int pj, n0, m0;
+                locate(tile, pj, n0, m0);
+                const CUtensorMap* map_w = pj == 0 ? &map_w0 : (pj == 1 ? &map_w1 : (pj == 2 ? &map_w2 : &map_w3));
+                for (int kb = 0; kb < num_kb; ++kb, ++g) {
+                    const int s = g % GM_STAGES;
+                    if (g >= GM_STAGES && !gm_wait(&empty[s], (unsigned)(g / GM_STAGES - 1) & 1u)) { failed = true; break; }
+                    unsigned char* st = base + s * GM_STAGE_BYTES;
+                    gm_mbar_expect_tx(&full_raw[s], GM_MT * GM_A_BYTES + GM_RAW_BYTES);
 #pragma unroll
-                for (int mt = 0; mt < GM_MT; ++mt) gm_tma_2d(st + mt * GM_A_BYTES, &map_x, kb * GM_BK, m0 + mt * GM_BM, &full_raw[s]);
-                gm_tma_2d(st + GM_MT * GM_A_BYTES + GM_B_BYTES, map_w, n0 / 8, kb * GM_BK, &full_raw[s]);
+                    for (int mt = 0; mt < GM_MT; ++mt) gm_tma_2d(st + mt * GM_A_BYTES, &map_x, kb * GM_BK, m0 + mt * GM_BM, &full_raw[s]);
+                    gm_tma_2d(st + GM_MT * GM_A_BYTES + GM_B_BYTES, map_w, n0 / 8, kb * GM_BK, &full_raw[s]);
+                }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 1) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
             // instruction descriptor: fp32 accumulate, fp16 A (K-major) and B (MN-major), N = 128, M = 128
             const uint32_t idesc = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(GM_BN >> 3) << 17) |
                                    ((uint32_t)(GM_BM >> 4) << 24);
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % GM_STAGES;
-                const unsigned ph = (unsigned)(kb / GM_STAGES) & 1u;
-                if (!gm_wait(&full_raw[s], ph) || !gm_wait(&b_ready[s], ph)) { failed = true; break; }
+            int g = 0, it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++it) {
+                const int set = it & 1, use = it >> 1;
+                // the set must have been drained by the epilogue of the tile that used it last
+                if (use >= 1 && !gm_wait(&acc_empty[set], (unsigned)(use - 1) & 1u)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = gm_smem(base + s * GM_STAGE_BYTES);
-                const uint32_t b_addr = a_addr + GM_MT * GM_A_BYTES;
+                const uint32_t acc = tmem_base + (uint32_t)(set * GM_MT * GM_BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++g) {
+                    const int s = g % GM_STAGES;
+                    const unsigned ph = (unsigned)(g / GM_STAGES) & 1u;
+                    if (!gm_wait(&full_raw[s], ph) || !gm_wait(&b_ready[s], ph)) { failed = true; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = gm_smem(base + s * GM_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + GM_MT * GM_A_BYTES;
 #pragma unroll
-                for (int k = 0; k < GM_BK / 16; ++k) {
-                    // B: MN-major; 64 columns x 8 k = one 1 KiB atom; atoms 1 KiB apart along K, BK*128 B apart along N
-                    const uint64_t db = gm_desc(b_addr + k * 2048, GM_BK * 128, 1024);
+                    for (int k = 0; k < GM_BK / 16; ++k) {
+                        // B: MN-major; 64 columns x 8 k = one 1 KiB atom; atoms 1 KiB apart along K, BK*128 B apart along N
+                        const uint64_t db = gm_desc(b_addr + k * 2048, GM_BK * 128, 1024);
 #pragma unroll
-                    for (int mt = 0; mt < GM_MT; ++mt) {
-                        // A: K-major; 8 rows x 64 k = one 1 KiB atom; 16 k = 32 B further inside the swizzled row
-                        const uint64_t da = gm_desc(a_addr + mt * GM_A_BYTES + k * 32, 16, 1024);
-                        gm_mma(tmem_base + mt * GM_BN, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        for (int mt = 0; mt < GM_MT; ++mt) {
+                            // A: K-major; 8 rows x 64 k = one 1 KiB atom; 16 k = 32 B further inside the swizzled row
+                            const uint64_t da = gm_desc(a_addr + mt * GM_A_BYTES + k * 32, 16, 1024);
+                            gm_mma(acc + mt * GM_BN, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
+                    gm_commit(&empty[s]);          // arrives when the MMAs issued so far have read their operands
                 }
-                gm_commit(&empty[s]);          // arrives when the MMAs issued so far have read their operands
+                if (!failed) gm_commit(&acc_ready[set]);
             }
-            gm_commit(acc_ready);
         }
-    } else {
-        // =========================== dequantise, then epilogue ===========================
-        const int t = tid - 32;                       // 0..127
+    } else if (warp < 2 + GM_DEQ_WARPS) {
+        // =========================== dequantise ===========================
+        const int t = tid - 64;                       // 0..255
         const int c = t & 15;                         // int32 column of the raw tile = 8 output columns n0 + 8c ..
-        const int kr0 = t >> 4;                       // first k row of this thread; it takes rows kr0 + 8 i
+        const int kr0 = t >> 4;                       // first k row of this thread; it takes rows kr0 + 16 i
         const int gpk = p.group / GM_BK;              // k blocks per quantisation group
         uint32_t zsub[4];                             // (1024 + zero) for the four column pairs, half2 bits
         __half2 sc2[4];                               // scales of the four column pairs
         const int a_n = c >> 3, chunk = c & 7;        // 64-column atom and 16-byte chunk inside its rows
-        // scale and zero words of the NEXT group are requested one group ahead, so that their latency
-        // is hidden behind a whole group of dequantisation
         const int n_grp = (num_kb + gpk - 1) / gpk;
-        auto load_meta = [&](int g, uint32_t& zw, uint4& s4) {
-            zw = (uint32_t)__ldg(P.qzeros + (int64_t)g * (P.N / 8) + n0 / 8 + c);
-            s4 = __ldg(reinterpret_cast<const uint4*>(P.scales + (int64_t)g * P.N + n0 + 8 * c));
-        };
-        uint32_t zw_nx = 0; uint4 s4_nx = make_uint4(0, 0, 0, 0);
-        load_meta(0, zw_nx, s4_nx);
-        for (int kb = 0; kb < num_kb; ++kb) {
-            const int s = kb % GM_STAGES;
-            if (kb % gpk == 0) {                      // new group: scale and zero of this thread's 8 columns
-                const int g = kb / gpk;
-                const uint32_t zw = zw_nx;
-                const uint4 s4 = s4_nx;
-                if (g + 1 < n_grp) load_meta(g + 1, zw_nx, s4_nx);
-                const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+        int g = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+            int pj, n0, m0;
+            locate(tile, pj, n0, m0);
+            const GemmProj& P = p.proj[pj];
+            // scale and zero words of the NEXT group are requested one group ahead
+            auto load_meta = [&](int gi, uint32_t& zw, uint4& s4) {
+                zw = (uint32_t)__ldg(P.qzeros + (int64_t)gi * (P.N / 8) + n0 / 8 + c);
+                s4 = __ldg(reinterpret_cast<const uint4*>(P.scales + (int64_t)gi * P.N + n0 + 8 * c));
+            };
+            uint32_t zw_nx = 0; uint4 s4_nx = make_uint4(0, 0, 0, 0);
+            load_meta(0, zw_nx, s4_nx);
+            for (int kb = 0; kb < num_kb; ++kb, ++g) {
+                const int s = g % GM_STAGES;
+                if (kb % gpk == 0) {                      // new group: scale and zero of this thread's 8 columns
+                    const int gi = kb / gpk;
+                    const uint32_t zw = zw_nx;
+                    const uint4 s4 = s4_nx;
+                    if (gi + 1 < n_grp) load_meta(gi + 1, zw_nx, s4_nx);
+                    const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-                for (int q = 0; q < 4; ++q) zsub[q] = ((zw >> (4 * q)) & 0x000f000fu) | 0x64006400u;
-                if constexpr (INTERLEAVED) {
+                    for (int q = 0; q < 4; ++q) zsub[q] = ((zw >> (4 * q)) & 0x000f000fu) | 0x64006400u;
+                    if constexpr (INTERLEAVED) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) sc2[q] = *reinterpret_cast<const __half2*>(&sw[q]);      // columns (2q, 2q+1)
-                } else {
-                    // word q of the codes pairs columns (q, q+4)
-                    const __half* sh = reinterpret_cast<const __half*>(sw);
+                        for (int q = 0; q < 4; ++q) sc2[q] = *reinterpret_cast<const __half2*>(&sw[q]);      // columns (2q, 2q+1)
+                    } else {
+                        // word q of the codes pairs columns (q, q+4)
+                        const __half* sh = reinterpret_cast<const __half*>(sw);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) sc2[q] = __halves2half2(sh[q], sh[q + 4]);
+                        for (int q = 0; q < 4; ++q) sc2[q] = __halves2half2(sh[q], sh[q + 4]);
+                    }
                 }
+                if (!gm_wait(&full_raw[s], (unsigned)(g / GM_STAGES) & 1u)) { failed = true; break; }
+                unsigned char* st = base + s * GM_STAGE_BYTES;
+                const uint32_t* raw = reinterpret_cast<const uint32_t*>(st + GM_MT * GM_A_BYTES + GM_B_BYTES);
+                unsigned char* bt = st + GM_MT * GM_A_BYTES + a_n * (GM_BK * 128);
+#pragma unroll
+                for (int i = 0; i < GM_BK / 16; ++i) {
+                    const int kr = kr0 + 16 * i;
+                    const uint32_t w = raw[kr * (GM_BN / 8) + c];
+                    uint32_t o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t h = ((w >> (4 * q)) & 0x000f000fu) | 0x64006400u;                   // (1024 + code) pairs
+                        const __half2 d = __hsub2(*reinterpret_cast<const __half2*>(&h), *reinterpret_cast<const __half2*>(&zsub[q]));
+                        const __half2 r = __hmul2(d, sc2[q]);
+                        o[q] = *reinterpret_cast<const uint32_t*>(&r);
+                    }
+                    uint4 out;
+                    if constexpr (INTERLEAVED) {
+                        out = make_uint4(o[0], o[1], o[2], o[3]);
+                    } else {      // pairs (q, q+4) -> column order
+                        out = make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),
+                                         __byte_perm(o[0], o[1], 0x7632), __byte_perm(o[2], o[3], 0x7632));
+                    }
+                    // row kr of the atom column a_n: 128 B per row, 16-byte chunks swizzled by the row index
+                    *reinterpret_cast<uint4*>(bt + kr * 128 + ((chunk ^ (kr & 7)) << 4)) = out;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
+                gm_mbar_arrive(&b_ready[s]);
             }
-            if (!gm_wait(&full_raw[s], (unsigned)(kb / GM_STAGES) & 1u)) { failed = true; break; }
-            unsigned char* st = base + s * GM_STAGE_BYTES;
-            const uint32_t* raw = reinterpret_cast<const uint32_t*>(st + GM_MT * GM_A_BYTES + GM_B_BYTES);
-            unsigned char* bt = st + GM_MT * GM_A_BYTES + a_n * (GM_BK * 128);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int kr = kr0 + 8 * i;
-                const uint32_t w = raw[kr * (GM_BN / 8) + c];
-                uint32_t o[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t h = ((w >> (4 * q)) & 0x000f000fu) | 0x64006400u;                   // (1024 + code) pairs
-                    const __half2 d = __hsub2(*reinterpret_cast<const __half2*>(&h), *reinterpret_cast<const __half2*>(&zsub[q]));
-                    const __half2 r = __hmul2(d, sc2[q]);
-                    o[q] = *reinterpret_cast<const uint32_t*>(&r);
-                }
-                uint4 out;
-                if constexpr (INTERLEAVED) {
-                    out = make_uint4(o[0], o[1], o[2], o[3]);
-                } else {      // pairs (q, q+4) -> column order
-                    out = make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),
-                                     __byte_perm(o[0], o[1], 0x7632), __byte_perm(o[2], o[3], 0x7632));
-                }
-                // row kr of the atom column a_n: 128 B per row, 16-byte chunks swizzled by the row index
-                *reinterpret_cast<uint4*>(bt + kr * 128 + ((chunk ^ (kr & 7)) << 4)) = out;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
-            gm_mbar_arrive(&b_ready[s]);
         }
-        // ---- epilogue: this warp drains TMEM lanes 32 (warp % 4) .. +31 of both accumulators ----
-        if (!failed && !gm_wait(acc_ready, 0u)) failed = true;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (!failed) {
-            const int lq = warp & 3;
+    } else {
+        // =========================== epilogue ===========================
+        const int lq = warp & 3;                      // the TMEM lane quarter this warp may read
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++it) {
+            int pj, n0, m0;
+            locate(tile, pj, n0, m0);
+            const GemmProj& P = p.proj[pj];
+            const int set = it & 1, use = it >> 1;
+            if (!gm_wait(&acc_ready[set], (unsigned)use & 1u)) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int mt = 0; mt < GM_MT; ++mt) {
                 const int row = m0 + mt * GM_BM + lq * 32 + lane;
 #pragma unroll 1
                 for (int cb = 0; cb < GM_BN / 32; ++cb) {
                     uint32_t v[32];
-                    const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(mt * GM_BN + cb * 32);
+                    const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(set * GM_MT * GM_BN + mt * GM_BN + cb * 32);
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                         "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -284,13 +325,16 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
                     }
                 }
             }
+            // the set's columns have been read: hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            gm_mbar_arrive(&acc_empty[set]);
         }
     }
     if (failed) atomicExch(p.status, FQ_ERR_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 5) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GM_MT * GM_BN) : "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GM_ACC_SETS * GM_MT * GM_BN) : "memory");
     }
 }
 
@@ -357,8 +401,14 @@ extern "C" int fq_awq_gemm(
     }
     for (int i = n_proj; i < GM_MAX_PROJ; ++i) { maps[1 + i] = maps[1]; p.proj[i] = GemmProj{nullptr, nullptr, nullptr, nullptr, 0, 1 << 30}; }
     const int m_tiles = (M + GM_BM * GM_MT - 1) / (GM_BM * GM_MT);
-    FQ_CHECK_ARG(m_tiles <= 65535, FQ_ERR_ARG, "%s: M=%d too large for one launch", fn, M);
-    dim3 grid((unsigned)tile0, (unsigned)m_tiles);
+    FQ_CHECK_ARG((int64_t)m_tiles * tile0 <= 0x7fffffffLL, FQ_ERR_ARG, "%s: M=%d too large for one launch", fn, M);
+    p.n_tiles = tile0; p.m_tiles = m_tiles;
+    // one persistent CTA per SM (the shared memory of a CTA leaves room for no second one)
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const int total = m_tiles * tile0;
+    dim3 grid((unsigned)(total < sms ? total : sms));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto kern = interleaved ? awq_gemm_kernel<true> : awq_gemm_kernel<false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM);
