@@ -28,22 +28,29 @@
 namespace fq {
 
 constexpr int GM_BM = 128;          // rows per accumulator
-constexpr int GM_MT = 2;            // accumulators (M tiles) per CTA
-constexpr int GM_BN = 128;
+constexpr int GM_BN = 256;          // columns per tile: one MMA of N = 256 per 16 k and accumulator
 constexpr int GM_BK = 64;
-constexpr int GM_STAGES = 4;
+constexpr int GM_TMEM_COLS = 512;   // all of an SM's tensor memory: MT = 1: two accumulator sets, MT = 2: one
 constexpr int GM_DEQ_WARPS = 8;
 constexpr int GM_EPI_WARPS = 4;
 constexpr int GM_THREADS = (2 + GM_DEQ_WARPS + GM_EPI_WARPS) * 32;     // TMA warp, MMA warp, dequantise warps, epilogue warps
-constexpr int GM_ACC_SETS = 2;      // accumulator sets in tensor memory (2 x 2 x 128 columns = all 512)
+
 constexpr int GM_MAX_PROJ = 4;
 constexpr unsigned GM_SPIN_LIMIT = 1u << 26;
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;             // 16 KiB per M tile
-constexpr int GM_RAW_BYTES = GM_BK * (GM_BN / 8) * 4;     // 4 KiB
-constexpr int GM_B_BYTES = GM_BK * GM_BN * 2;             // 16 KiB
-constexpr int GM_STAGE_BYTES = GM_MT * GM_A_BYTES + GM_B_BYTES + GM_RAW_BYTES;
-constexpr int GM_SMEM = GM_STAGES * GM_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers, tmem address */;
-static_assert((3 * GM_STAGES + 4) * 8 + 4 <= 256, "barrier block");
+constexpr int GM_RAW_BYTES = GM_BK * (GM_BN / 8) * 4;     // 8 KiB
+constexpr int GM_B_BYTES = GM_BK * GM_BN * 2;             // 32 KiB
+// MT = accumulators (M tiles of 128 rows) per CTA tile.  MT = 2 (256 x 256 tiles, 3 stages): every byte fetched from L2
+// feeds twice the MMAs, the tile for long M; MT = 1 (128 x 256 tiles, 4 stages, two accumulator sets so that a
+// finished tile is drained while the next one is multiplied): more tiles, the one for short M.
+template <int MT> struct GmCfg {
+    static constexpr int STAGES = MT == 2 ? 3 : 4;
+    static constexpr int ACC_SETS = GM_TMEM_COLS / (MT * GM_BN);
+    static constexpr int STAGE_BYTES = MT * GM_A_BYTES + GM_B_BYTES + GM_RAW_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers, tmem address */;
+    static_assert((3 * STAGES + 2 * ACC_SETS) * 8 + 4 <= 256, "barrier block");
+    static_assert(SMEM <= 227 * 1024, "shared memory");
+};
 
 struct GemmProj {
     const __half* scales; const int32_t* qzeros; const __half* bias; __half* y;
@@ -99,12 +106,13 @@ __device__ __forceinline__ uint64_t gm_desc(uint32_t smem_addr, uint32_t lbo_byt
            ((uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32) | (1ull << 46) | (2ull << 61);
 }
 
-template <bool INTERLEAVED>
+template <bool INTERLEAVED, int GM_MT>
 __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
     const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_w3, const GemmParams p) {
+    constexpr int GM_STAGES = GmCfg<GM_MT>::STAGES, GM_ACC_SETS = GmCfg<GM_MT>::ACC_SETS, GM_STAGE_BYTES = GmCfg<GM_MT>::STAGE_BYTES;
     extern __shared__ unsigned char gm_raw_smem[];
-    // stage s: [A tile 0 | A tile 1 | B (dequantised) | raw codes]; every tile 1024-byte aligned
+    // stage s: [A tiles | B (dequantised) | raw codes]; every tile 1024-byte aligned
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gm_raw_smem) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + GM_STAGES * GM_STAGE_BYTES);
     uint64_t* full_raw = bars;                       // [stages] TMA bytes landed (x tiles + raw codes)
@@ -130,8 +138,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {     // tensor memory: two sets of two accumulators of 128 fp32 columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem(tmem_slot)), "r"(GM_ACC_SETS * GM_MT * GM_BN) : "memory");
+    if (warp == 1) {     // tensor memory: all 512 columns (ACC_SETS sets of MT accumulators of 256 fp32 columns)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem(tmem_slot)), "r"(GM_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -178,7 +186,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
                                    ((uint32_t)(GM_BM >> 4) << 24);
             int g = 0, it = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++it) {
-                const int set = it & 1, use = it >> 1;
+                const int set = it % GM_ACC_SETS, use = it / GM_ACC_SETS;
                 // the set must have been drained by the epilogue of the tile that used it last
                 if (use >= 1 && !gm_wait(&acc_empty[set], (unsigned)(use - 1) & 1u)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -192,7 +200,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
                     const uint32_t b_addr = a_addr + GM_MT * GM_A_BYTES;
 #pragma unroll
                     for (int k = 0; k < GM_BK / 16; ++k) {
-                        // B: MN-major; 64 columns x 8 k = one 1 KiB atom; atoms 1 KiB apart along K, BK*128 B apart along N
+                        // B: MN-major; 64 columns x 8 k = one 1 KiB atom; atoms 1 KiB apart along K, BK*128 B apart along N (4 atoms)
                         const uint64_t db = gm_desc(b_addr + k * 2048, GM_BK * 128, 1024);
 #pragma unroll
                         for (int mt = 0; mt < GM_MT; ++mt) {
@@ -209,8 +217,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
     } else if (warp < 2 + GM_DEQ_WARPS) {
         // =========================== dequantise ===========================
         const int t = tid - 64;                       // 0..255
-        const int c = t & 15;                         // int32 column of the raw tile = 8 output columns n0 + 8c ..
-        const int kr0 = t >> 4;                       // first k row of this thread; it takes rows kr0 + 16 i
+        const int c = t & 31;                         // int32 column of the raw tile = 8 output columns n0 + 8c ..
+        const int kr0 = t >> 5;                       // first k row of this thread; it takes rows kr0 + 8 i
         const int gpk = p.group / GM_BK;              // k blocks per quantisation group
         uint32_t zsub[4];                             // (1024 + zero) for the four column pairs, half2 bits
         __half2 sc2[4];                               // scales of the four column pairs
@@ -222,9 +230,13 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
             locate(tile, pj, n0, m0);
             const GemmProj& P = p.proj[pj];
             // scale and zero words of the NEXT group are requested one group ahead
+            const bool col_ok = n0 + 8 * c < P.N;      // a projection of 128 (mod 256) columns ends inside its last tile
             auto load_meta = [&](int gi, uint32_t& zw, uint4& s4) {
-                zw = (uint32_t)__ldg(P.qzeros + (int64_t)gi * (P.N / 8) + n0 / 8 + c);
-                s4 = __ldg(reinterpret_cast<const uint4*>(P.scales + (int64_t)gi * P.N + n0 + 8 * c));
+                zw = 0; s4 = make_uint4(0, 0, 0, 0);
+                if (col_ok) {
+                    zw = (uint32_t)__ldg(P.qzeros + (int64_t)gi * (P.N / 8) + n0 / 8 + c);
+                    s4 = __ldg(reinterpret_cast<const uint4*>(P.scales + (int64_t)gi * P.N + n0 + 8 * c));
+                }
             };
             uint32_t zw_nx = 0; uint4 s4_nx = make_uint4(0, 0, 0, 0);
             load_meta(0, zw_nx, s4_nx);
@@ -253,8 +265,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
                 const uint32_t* raw = reinterpret_cast<const uint32_t*>(st + GM_MT * GM_A_BYTES + GM_B_BYTES);
                 unsigned char* bt = st + GM_MT * GM_A_BYTES + a_n * (GM_BK * 128);
 #pragma unroll
-                for (int i = 0; i < GM_BK / 16; ++i) {
-                    const int kr = kr0 + 16 * i;
+                for (int i = 0; i < GM_BK / 8; ++i) {
+                    const int kr = kr0 + 8 * i;
                     const uint32_t w = raw[kr * (GM_BN / 8) + c];
                     uint32_t o[4];
 #pragma unroll
@@ -286,7 +298,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
             int pj, n0, m0;
             locate(tile, pj, n0, m0);
             const GemmProj& P = p.proj[pj];
-            const int set = it & 1, use = it >> 1;
+            const int set = it % GM_ACC_SETS, use = it / GM_ACC_SETS;
             if (!gm_wait(&acc_ready[set], (unsigned)use & 1u)) { failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -305,7 +317,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
                           "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                         : "r"(taddr));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (row < p.M) {
+                    if (row < p.M && n0 + cb * 32 < P.N) {
                         __half* yrow = P.y + (int64_t)row * P.N + n0 + cb * 32;
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
@@ -334,7 +346,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) awq_gemm_kernel(
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GM_ACC_SETS * GM_MT * GM_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(GM_TMEM_COLS) : "memory");
     }
 }
 
@@ -384,13 +396,13 @@ extern "C" int fq_awq_gemm(
     }
     int tile0 = 0;
     for (int i = 0; i < n_proj; ++i) {
-        FQ_CHECK_ARG(N[i] > 0 && N[i] % GM_BN == 0, FQ_ERR_UNSUPPORTED, "%s: N[%d]=%d must be a positive multiple of %d", fn, i, N[i], GM_BN);
+        FQ_CHECK_ARG(N[i] > 0 && N[i] % 128 == 0, FQ_ERR_UNSUPPORTED, "%s: N[%d]=%d must be a positive multiple of 128", fn, i, N[i]);
         FQ_CHECK_ARG(qweight[i] && scales[i] && qzeros[i] && y[i], FQ_ERR_ARG, "%s: null tensor in projection %d", fn, i);
         FQ_CHECK_ARG(aligned(y[i], 16) && aligned(scales[i], 16) && aligned(qweight[i], 16) && aligned(qzeros[i], 4), FQ_ERR_ALIGN,
                      "%s: y[%d], scales[%d] and qweight[%d] must be 16-byte aligned", fn, i, i, i);
         p.proj[i] = GemmProj{static_cast<const __half*>(scales[i]), qzeros[i], bias ? static_cast<const __half*>(bias[i]) : nullptr,
                              static_cast<__half*>(y[i]), N[i], tile0};
-        tile0 += N[i] / GM_BN;
+        tile0 += (N[i] + GM_BN - 1) / GM_BN;
         const cuuint64_t dims[2] = {(cuuint64_t)(N[i] / 8), (cuuint64_t)K};
         const cuuint64_t strides[1] = {(cuuint64_t)(N[i] / 8) * 4};
         const cuuint32_t box[2] = {(cuuint32_t)(GM_BN / 8), (cuuint32_t)GM_BK}, es[2] = {1, 1};
@@ -400,20 +412,27 @@ extern "C" int fq_awq_gemm(
         if (r != CUDA_SUCCESS) return fail(FQ_ERR_CUDA, "%s: tensor map for qweight[%d]: driver error %d", fn, i, (int)r);
     }
     for (int i = n_proj; i < GM_MAX_PROJ; ++i) { maps[1 + i] = maps[1]; p.proj[i] = GemmProj{nullptr, nullptr, nullptr, nullptr, 0, 1 << 30}; }
-    const int m_tiles = (M + GM_BM * GM_MT - 1) / (GM_BM * GM_MT);
-    FQ_CHECK_ARG((int64_t)m_tiles * tile0 <= 0x7fffffffLL, FQ_ERR_ARG, "%s: M=%d too large for one launch", fn, M);
-    p.n_tiles = tile0; p.m_tiles = m_tiles;
     // one persistent CTA per SM (the shared memory of a CTA leaves room for no second one)
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    // 256-row tiles once they fill at least one wave of the SMs, 128-row tiles (twice as many CTAs) below that
+    const int mt = ((int64_t)((M + 255) / 256) * tile0 >= (int64_t)sms) ? 2 : 1;
+    const int m_tiles = (M + GM_BM * mt - 1) / (GM_BM * mt);
+    FQ_CHECK_ARG((int64_t)m_tiles * tile0 <= 0x7fffffffLL, FQ_ERR_ARG, "%s: M=%d too large for one launch", fn, M);
+    p.n_tiles = tile0; p.m_tiles = m_tiles;
     const int total = m_tiles * tile0;
     dim3 grid((unsigned)(total < sms ? total : sms));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    auto kern = interleaved ? awq_gemm_kernel<true> : awq_gemm_kernel<false>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM);
-    if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve %d B of shared memory: %s", fn, GM_SMEM, cudaGetErrorString(e));
-    kern<<<grid, GM_THREADS, GM_SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+#define FQ_GM(IL, MTV)                                                                                                       \
+    do {                                                                                                                     \
+        cudaError_t e = cudaFuncSetAttribute(awq_gemm_kernel<IL, MTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, GmCfg<MTV>::SMEM); \
+        if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve %d B of shared memory: %s", fn, GmCfg<MTV>::SMEM, cudaGetErrorString(e)); \
+        awq_gemm_kernel<IL, MTV><<<grid, GM_THREADS, GmCfg<MTV>::SMEM, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);  \
+    } while (0)
+    if (interleaved) { if (mt == 2) FQ_GM(true, 2); else FQ_GM(true, 1); }
+    else { if (mt == 2) FQ_GM(false, 2); else FQ_GM(false, 1); }
+#undef FQ_GM
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
