@@ -219,6 +219,11 @@ static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
     return FQ_OK;
 }
 
+// tcgen05 kernel for head_dim 128 (fq_prefill_attn_tc.cu); false: shape not served there
+bool prefill_attention_tc_launch(const void* Q, int64_t q_sb, int64_t q_sh, int64_t q_ss, const void* K, int64_t k_sb, int64_t k_sh, int64_t k_ss,
+                                 const void* V, int64_t v_sb, int64_t v_sh, int64_t v_ss, int bf16, int B, int Hq, int Hkv, int Sq, int Skv,
+                                 float sm_scale, void* O, int64_t o_sb, int64_t o_sh, int64_t o_ss, cudaStream_t st, int* rc);
+
 }  // namespace fq
 
 extern "C" int fq_prefill_attention(
@@ -248,6 +253,14 @@ extern "C" int fq_prefill_attention(
     p.scale_log2 = sm_scale * 1.4426950408889634f;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
+    // head_dim 128 with at least one full query tile: the tcgen05 kernel; everything else: mma.sync
+    if (D == 128 && Sq >= 128 && Skv >= 1 &&
+        prefill_attention_tc_launch(Q, q_sb, q_sh, q_ss, K, k_sb, k_sh, k_ss, V, v_sb, v_sh, v_ss, dtype == FQ_BF16 ? 1 : 0, B, Hq, Hkv, Sq, Skv,
+                                    sm_scale, O, o_sb, o_sh, o_ss, st, &rc)) {
+        if (rc != FQ_OK) return rc;
+        FQ_CHECK_LAUNCH(fn);
+        return FQ_OK;
+    }
     if (dtype == FQ_BF16) rc = D == 128 ? launch_prefill<__nv_bfloat16, 128>(p, st) : launch_prefill<__nv_bfloat16, 64>(p, st);
     else rc = D == 128 ? launch_prefill<__half, 128>(p, st) : launch_prefill<__half, 64>(p, st);
     if (rc != FQ_OK) return rc;

@@ -1,0 +1,344 @@
+// Dense causal attention of the prefill branch on the 5th-generation tensor cores (tcgen05), head_dim 128.
+// Same contract as prefill_attn_kernel (fq_prefill_attn.cu): queries of the new tokens over the dequantised
+// completed pages followed by the staged tail, grouped-query heads, causal mask aligned at the top left
+// (query i sees keys 0..i), fp16 or bf16 operands, fp32 accumulation and softmax.
+//
+// One CTA = 128 queries of one query head, walking key tiles of 128:
+//   warp 0      : one thread issues the TMA loads (4-D tensor maps over Q, K, V; 128-byte swizzle): Q once,
+//                 then K and V tiles into a two-deep ring;
+//   warp 1      : one thread issues tcgen05.mma: S = Q K^T (M 128, N 128, K 16 x 8) into one of two S buffers in
+//                 tensor memory, and O_tile = P V (P from shared memory, V as the MN-major operand) into a third;
+//                 S of the next key tile is issued before the softmax of the current one is awaited;
+//   warps 2..5  : softmax — thread r owns query row r (TMEM lane r): reads S (tcgen05.ld), scales, masks, keeps the
+//                 running maximum and denominator in base 2, writes P as fp16/bf16 into the swizzled K-major
+//                 operand layout, then adds O_tile (rescaled by the change of the maximum) to its fp32 row of O
+//                 in registers; stores the normalised row at the end.
+// Every mbarrier wait is bounded and reports through the device status word.
+#include <cuda.h>
+
+#include "fq_common.cuh"
+
+namespace fq {
+
+constexpr int PT_BM = 128, PT_BN = 128, PT_D = 128;
+constexpr int PT_THREADS = 192;
+constexpr int PT_TILE_BYTES = 128 * PT_D * 2;                 // 32 KiB: two halves of [128 rows][64 elements]
+constexpr int PT_HALF_BYTES = PT_TILE_BYTES / 2;
+constexpr int PT_KV_STAGES = 2;
+constexpr int PT_SMEM = PT_TILE_BYTES * (2 + 2 * PT_KV_STAGES) + 1024 + 256;   // Q, P, K/V ring, alignment slack, barriers
+constexpr unsigned PT_SPIN_LIMIT = 1u << 26;
+constexpr int PT_TMEM_COLS = 512;                              // S0 @0, S1 @128, O_tile @256
+
+struct PrefillTcParams {
+    void* O; int64_t o_sb, o_sh, o_ss;
+    int B, Hq, Hkv, Sq, Skv, bf16;
+    float scale_log2;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t pt_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void pt_mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pt_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void pt_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pt_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void pt_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pt_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool pt_mbar_try(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(pt_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool pt_wait(uint64_t* bar, unsigned parity) {
+    unsigned spins = 0;
+    while (!pt_mbar_try(bar, parity)) {
+        if (++spins > PT_SPIN_LIMIT) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void pt_tma_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(pt_smem(dst)), "l"(map), "r"(pt_smem(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void pt_mma(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void pt_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pt_smem(bar)) : "memory");
+}
+// shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100); offsets in bytes
+__device__ __forceinline__ uint64_t pt_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void pt_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float pt_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pt_pack(float lo, float hi, int bf16) {
+    if (bf16) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v); }
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+    const PrefillTcParams p) {
+    extern __shared__ unsigned char pt_raw_smem[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pt_raw_smem) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = base;                                         // [2 halves][128 rows][128 B]
+    unsigned char* sP = base + PT_TILE_BYTES;                         // same layout, keys instead of channels
+    unsigned char* sK = base + 2 * PT_TILE_BYTES;                     // [stages] same layout
+    unsigned char* sV = sK + PT_KV_STAGES * PT_TILE_BYTES;            // [stages][2 halves of d][128 keys][128 B]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + PT_KV_STAGES * PT_TILE_BYTES);
+    uint64_t* q_full = bars;                 // Q landed
+    uint64_t* kv_full = bars + 1;            // [stages] K and V tiles landed
+    uint64_t* kv_empty = bars + 3;           // [stages] both MMAs that read the stage have completed
+    uint64_t* s_ready = bars + 5;            // [2] S buffer written by the tensor core
+    uint64_t* p_ready = bars + 7;            // P written (and S read) by the 128 softmax threads
+    uint64_t* o_ready = bars + 8;            // O_tile written by the tensor core
+    uint64_t* o_taken = bars + 9;            // O_tile read by the 128 softmax threads
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // the heaviest query tiles (most keys under the causal mask) are scheduled first
+    const int qt = gridDim.x - 1 - blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+    const int hkv = hq / (p.Hq / p.Hkv);
+    const int q0 = qt * PT_BM;
+    const int kv_tiles_all = (p.Skv + PT_BN - 1) / PT_BN;
+    const int n_tiles = min(kv_tiles_all, qt + 1);                    // keys 0 .. q0 + 127
+
+    if (tid == 0) {
+        pt_mbar_init(q_full, 1);
+        for (int s = 0; s < PT_KV_STAGES; ++s) { pt_mbar_init(&kv_full[s], 1); pt_mbar_init(&kv_empty[s], 1); }
+        pt_mbar_init(&s_ready[0], 1); pt_mbar_init(&s_ready[1], 1);
+        pt_mbar_init(p_ready, 128); pt_mbar_init(o_ready, 1); pt_mbar_init(o_taken, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pt_smem(tmem_slot)), "r"(PT_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        // =========================== TMA producer ===========================
+        if (lane == 0 && n_tiles > 0) {
+            pt_mbar_expect_tx(q_full, PT_TILE_BYTES);
+            pt_tma_4d(sQ, &map_q, 0, q0, hq, b, q_full);
+            pt_tma_4d(sQ + PT_HALF_BYTES, &map_q, 64, q0, hq, b, q_full);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % PT_KV_STAGES;
+                if (j >= PT_KV_STAGES && !pt_wait(&kv_empty[s], (unsigned)(j / PT_KV_STAGES - 1) & 1u)) { failed = true; break; }
+                pt_mbar_expect_tx(&kv_full[s], 2 * PT_TILE_BYTES);
+                pt_tma_4d(sK + s * PT_TILE_BYTES, &map_k, 0, j * PT_BN, hkv, b, &kv_full[s]);
+                pt_tma_4d(sK + s * PT_TILE_BYTES + PT_HALF_BYTES, &map_k, 64, j * PT_BN, hkv, b, &kv_full[s]);
+                pt_tma_4d(sV + s * PT_TILE_BYTES, &map_v, 0, j * PT_BN, hkv, b, &kv_full[s]);
+                pt_tma_4d(sV + s * PT_TILE_BYTES + PT_HALF_BYTES, &map_v, 64, j * PT_BN, hkv, b, &kv_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // =========================== MMA issuer ===========================
+        if (lane == 0 && n_tiles > 0) {
+            const uint32_t fmt = p.bf16 ? 1u : 0u;
+            // fp32 accumulate; A K-major; B K-major (S = Q K^T) or MN-major (O = P V); N = 128, M = 128
+            const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(PT_BN >> 3) << 17) |
+                                     ((uint32_t)(PT_BM >> 4) << 24);
+            const uint32_t idesc_o = idesc_s | (1u << 16);
+            const uint32_t q_addr = pt_smem(sQ), p_addr = pt_smem(sP);
+            auto issue_s = [&](int j) -> bool {           // S[j & 1] = Q K_j^T
+                const int s = j % PT_KV_STAGES;
+                if (!pt_wait(&kv_full[s], (unsigned)(j / PT_KV_STAGES) & 1u)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t k_addr = pt_smem(sK + s * PT_TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < PT_D / 16; ++kk) {
+                    // K-major, 128-byte swizzle: 8 rows x 64 elements = one 1 KiB atom; 16 k = 32 B inside the row; second half 16 KiB on
+                    const uint32_t off = (uint32_t)(kk >> 2) * PT_HALF_BYTES + (uint32_t)(kk & 3) * 32;
+                    pt_mma(tmem_base + (uint32_t)((j & 1) * PT_BN), pt_desc(q_addr + off, 16, 1024), pt_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+                }
+                pt_commit(&s_ready[j & 1]);
+                return true;
+            };
+            if (!pt_wait(q_full, 0u) || !issue_s(0)) failed = true;
+            for (int j = 0; j < n_tiles && !failed; ++j) {
+                const int s = j % PT_KV_STAGES;
+                // S of the next key tile while the softmax of this one runs: its buffer was read two tiles ago (p_ready of j-1 seen below)
+                if (j + 1 < n_tiles && !issue_s(j + 1)) { failed = true; break; }
+                if (!pt_wait(p_ready, (unsigned)j & 1u)) { failed = true; break; }
+                if (j >= 1 && !pt_wait(o_taken, (unsigned)(j - 1) & 1u)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t v_addr = pt_smem(sV + s * PT_TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < PT_BN / 16; ++kk) {
+                    // A = P, K-major over the keys; B = V, MN-major: 64 channels x 8 keys = one atom, 16 keys = 2 KiB, channel halves 16 KiB apart
+                    const uint32_t offp = (uint32_t)(kk >> 2) * PT_HALF_BYTES + (uint32_t)(kk & 3) * 32;
+                    pt_mma(tmem_base + 2 * PT_BN, pt_desc(p_addr + offp, 16, 1024), pt_desc(v_addr + (uint32_t)kk * 2048, PT_HALF_BYTES, 1024), idesc_o,
+                           kk != 0 ? 1u : 0u);
+                }
+                pt_commit(o_ready);
+                pt_commit(&kv_empty[s]);
+            }
+        }
+    } else {
+        // =========================== softmax and output ===========================
+        const int lq = warp & 3;                  // the TMEM lane quarter this warp may read
+        const int r = lq * 32 + lane;             // query row inside the tile
+        const int qi = q0 + r;                    // global query index
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(lq * 32) << 16);
+        float acc[PT_D];
+#pragma unroll
+        for (int i = 0; i < PT_D; ++i) acc[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        for (int j = 0; j < n_tiles; ++j) {
+            if (!pt_wait(&s_ready[j & 1], (unsigned)(j >> 1) & 1u)) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * PT_BN);
+            const int k0 = j * PT_BN;
+            const int k_lim = min(qi, p.Skv - 1);         // last key this row may see
+            uint32_t v[32];
+            // pass 1: the row's maximum over this tile
+            float m_tile = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < PT_BN / 32; ++c) {
+                pt_tmem_ld32(s_addr + (uint32_t)(c * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (k0 + c * 32 + i <= k_lim) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+            }
+            const float m_new = fmaxf(m_run, m_tile * p.scale_log2);
+            const float alpha = m_new == -INFINITY ? 1.f : pt_ex2(m_run - m_new);
+            const float m_sub = m_new == -INFINITY ? 0.f : m_new;
+            // pass 2: probabilities into the operand layout (row r of half h: 128 B, 16-byte chunks swizzled by r & 7)
+            float l_tile = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < PT_BN / 32; ++c) {
+                pt_tmem_ld32(s_addr + (uint32_t)(c * 32), v);
+                unsigned char* prow = sP + (c >> 1) * PT_HALF_BYTES + r * 128;
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) {
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i0 = q8 * 8 + 2 * e;
+                        float p0 = 0.f, p1 = 0.f;
+                        if (k0 + c * 32 + i0 <= k_lim) p0 = pt_ex2(fmaf(__uint_as_float(v[i0]), p.scale_log2, -m_sub));
+                        if (k0 + c * 32 + i0 + 1 <= k_lim) p1 = pt_ex2(fmaf(__uint_as_float(v[i0 + 1]), p.scale_log2, -m_sub));
+                        pk[e] = pt_pack(p0, p1, p.bf16);
+                        // the denominator sums what the tensor core multiplies: the rounded probabilities
+                        if (p.bf16) { const __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&pk[e]); l_tile += __low2float(h) + __high2float(h); }
+                        else { const __half2 h = *reinterpret_cast<__half2*>(&pk[e]); l_tile += __low2float(h) + __high2float(h); }
+                    }
+                    const int chunk = (c & 1) * 4 + q8;       // 16-byte chunk inside the 128-byte row
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            pt_mbar_arrive(p_ready);
+            l_run = l_run * alpha + l_tile;
+            m_run = m_new;
+            // O += P V: the tile's product, with the row's earlier sum rescaled to the new maximum
+            if (!pt_wait(o_ready, (unsigned)j & 1u)) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < PT_D / 32; ++c) {
+                pt_tmem_ld32(lane_addr + (uint32_t)(2 * PT_BN + c * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(v[i]));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            pt_mbar_arrive(o_taken);
+        }
+        if (!failed && qi < p.Sq) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            unsigned char* orow = static_cast<unsigned char*>(p.O) + ((int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + (int64_t)qi * p.o_ss) * 2;
+#pragma unroll
+            for (int i = 0; i < PT_D; i += 2) *reinterpret_cast<uint32_t*>(orow + i * 2) = pt_pack(acc[i] * inv, acc[i + 1] * inv, p.bf16);
+        }
+    }
+    if (failed) atomicExch(p.status, FQ_ERR_TIMEOUT);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(PT_TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*PtEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static PtEncodeTiledFn pt_encode_fn() {
+    static std::atomic<void*> cached{nullptr};
+    void* fn = cached.load(std::memory_order_relaxed);
+    if (fn == nullptr) {
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess) return nullptr;
+        cached.store(fn, std::memory_order_relaxed);
+    }
+    return reinterpret_cast<PtEncodeTiledFn>(fn);
+}
+
+// (B, H, S, 128) tensor with element strides sb, sh, ss -> 4-D map {128, S, H, B}, boxes of 64 elements x 128 rows
+static bool pt_make_map(PtEncodeTiledFn enc, CUtensorMap* map, const void* ptr, int bf16, int S, int H, int B, int64_t sb, int64_t sh, int64_t ss) {
+    const cuuint64_t dims[4] = {(cuuint64_t)PT_D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1}, es[4] = {1, 1, 1, 1};
+    return enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, es,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// true when the launch was made; false: the shape is not served here (the caller falls back to the mma.sync kernel)
+bool prefill_attention_tc_launch(const void* Q, int64_t q_sb, int64_t q_sh, int64_t q_ss, const void* K, int64_t k_sb, int64_t k_sh, int64_t k_ss,
+                                 const void* V, int64_t v_sb, int64_t v_sh, int64_t v_ss, int bf16, int B, int Hq, int Hkv, int Sq, int Skv,
+                                 float sm_scale, void* O, int64_t o_sb, int64_t o_sh, int64_t o_ss, cudaStream_t st, int* rc) {
+    *rc = FQ_OK;
+    // strides of a tensor map are 40-bit multiples of 16 bytes; a size-1 axis may carry any stride, so give it a valid one
+    auto ok_stride = [](int64_t s) { return s > 0 && (s * 2) % 16 == 0 && s * 2 < (1ll << 40); };
+    if (Sq < 1 || Skv < 1 || !aligned(O, 4) || o_ss % 2 != 0 || o_sh % 2 != 0 || o_sb % 2 != 0) return false;
+    if (B == 1) { q_sb = (int64_t)Hq * q_sh; k_sb = (int64_t)Hkv * k_sh; v_sb = k_sb; }
+    if (!ok_stride(q_ss) || !ok_stride(q_sh) || !ok_stride(q_sb) || !ok_stride(k_ss) || !ok_stride(k_sh) || !ok_stride(k_sb) ||
+        !ok_stride(v_ss) || !ok_stride(v_sh) || !ok_stride(v_sb)) return false;
+    PtEncodeTiledFn enc = pt_encode_fn();
+    if (!enc) return false;
+    CUtensorMap mq, mk, mv;
+    if (!pt_make_map(enc, &mq, Q, bf16, Sq, Hq, B, q_sb, q_sh, q_ss) || !pt_make_map(enc, &mk, K, bf16, Skv, Hkv, B, k_sb, k_sh, k_ss) ||
+        !pt_make_map(enc, &mv, V, bf16, Skv, Hkv, B, v_sb, v_sh, v_ss)) return false;
+    PrefillTcParams p;
+    p.O = O; p.o_sb = o_sb; p.o_sh = o_sh; p.o_ss = o_ss;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv; p.bf16 = bf16;
+    p.scale_log2 = sm_scale * 1.4426950408889634f;
+    p.status = device_status_ptr();
+    if (p.status == nullptr) { *rc = FQ_ERR_CUDA; return true; }
+    cudaError_t e = cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM);
+    if (e != cudaSuccess) { *rc = fail(FQ_ERR_CUDA, "fq_prefill_attention: cannot reserve %d B of shared memory: %s", PT_SMEM, cudaGetErrorString(e)); return true; }
+    dim3 grid((unsigned)((Sq + PT_BM - 1) / PT_BM), (unsigned)Hq, (unsigned)B);
+    prefill_attn_tc_kernel<<<grid, PT_THREADS, PT_SMEM, st>>>(mq, mk, mv, p);
+    return true;
+}
+
+}  // namespace fq
