@@ -9,10 +9,12 @@
 //   warp 1      : one thread issues tcgen05.mma: S = Q K^T (M 128, N 128, K 16 x 8) into one of two S buffers in
 //                 tensor memory, and O_tile = P V (P from shared memory, V as the MN-major operand) into a third;
 //                 S of the next key tile is issued before the softmax of the current one is awaited;
-//   warps 2..5  : softmax — thread r owns query row r (TMEM lane r): reads S (tcgen05.ld), scales, masks, keeps the
-//                 running maximum and denominator in base 2, writes P as fp16/bf16 into the swizzled K-major
-//                 operand layout, then adds O_tile (rescaled by the change of the maximum) to its fp32 row of O
-//                 in registers; stores the normalised row at the end.
+//   warps 2..9  : softmax — two threads per query row (TMEM lane = row; warps 2..5 own the key / channel columns
+//                 0..63, warps 6..9 the columns 64..127): read S once (tcgen05.ld), scale, mask (diagonal tile only),
+//                 exchange the row maximum through shared memory, keep the running maximum and denominator in base
+//                 2, write P as fp16/bf16 into the swizzled K-major operand layout, then add their half of O_tile
+//                 (with the row's earlier sum rescaled by the change of the maximum) to an fp32 half row of O in
+//                 registers; store the normalised row at the end.
 // Every mbarrier wait is bounded and reports through the device status word.
 #include <cuda.h>
 
@@ -21,7 +23,8 @@
 namespace fq {
 
 constexpr int PT_BM = 128, PT_BN = 128, PT_D = 128;
-constexpr int PT_THREADS = 192;
+constexpr int PT_SOFTMAX_WARPS = 8;      // two threads per query row: each owns 64 of the 128 columns
+constexpr int PT_THREADS = (2 + PT_SOFTMAX_WARPS) * 32;
 constexpr int PT_TILE_BYTES = 128 * PT_D * 2;                 // 32 KiB: two halves of [128 rows][64 elements]
 constexpr int PT_HALF_BYTES = PT_TILE_BYTES / 2;
 constexpr int PT_KV_STAGES = 2;
@@ -113,10 +116,12 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
     uint64_t* kv_full = bars + 1;            // [stages] K and V tiles landed
     uint64_t* kv_empty = bars + 3;           // [stages] both MMAs that read the stage have completed
     uint64_t* s_ready = bars + 5;            // [2] S buffer written by the tensor core
-    uint64_t* p_ready = bars + 7;            // P written (and S read) by the 128 softmax threads
+    uint64_t* p_ready = bars + 7;            // P written (and S read) by the softmax threads
     uint64_t* o_ready = bars + 8;            // O_tile written by the tensor core
-    uint64_t* o_taken = bars + 9;            // O_tile read by the 128 softmax threads
+    uint64_t* o_taken = bars + 9;            // O_tile read by the softmax threads
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);      // a wait gave up somewhere: nobody waits any more
+    __shared__ float s_xch[2][PT_BM];                                          // row maxima / denominators of the two column halves
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // the heaviest query tiles (most keys under the causal mask) are scheduled first
@@ -130,7 +135,8 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
         pt_mbar_init(q_full, 1);
         for (int s = 0; s < PT_KV_STAGES; ++s) { pt_mbar_init(&kv_full[s], 1); pt_mbar_init(&kv_empty[s], 1); }
         pt_mbar_init(&s_ready[0], 1); pt_mbar_init(&s_ready[1], 1);
-        pt_mbar_init(p_ready, 128); pt_mbar_init(o_ready, 1); pt_mbar_init(o_taken, 128);
+        pt_mbar_init(p_ready, PT_SOFTMAX_WARPS * 32); pt_mbar_init(o_ready, 1); pt_mbar_init(o_taken, PT_SOFTMAX_WARPS * 32);
+        *s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -205,53 +211,68 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
     } else {
         // =========================== softmax and output ===========================
         const int lq = warp & 3;                  // the TMEM lane quarter this warp may read
+        const int hf = (warp - 2) >> 2;           // column half owned by this thread
         const int r = lq * 32 + lane;             // query row inside the tile
         const int qi = q0 + r;                    // global query index
         const uint32_t lane_addr = tmem_base + ((uint32_t)(lq * 32) << 16);
-        float acc[PT_D];
+        float acc[PT_D / 2];
 #pragma unroll
-        for (int i = 0; i < PT_D; ++i) acc[i] = 0.f;
+        for (int i = 0; i < PT_D / 2; ++i) acc[i] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
+        // a wait that gives up is remembered by everybody: the loop then runs on without waiting, so that the
+        // named barrier below still sees all 256 threads
+        auto wait_ok = [&](uint64_t* bar, unsigned parity) {
+            if (*s_fail) return;
+            if (!pt_wait(bar, parity)) { failed = true; *s_fail = 1; }
+        };
         for (int j = 0; j < n_tiles; ++j) {
-            if (!pt_wait(&s_ready[j & 1], (unsigned)(j >> 1) & 1u)) { failed = true; break; }
+            wait_ok(&s_ready[j & 1], (unsigned)(j >> 1) & 1u);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * PT_BN);
-            const int k0 = j * PT_BN;
+            const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * PT_BN + hf * 64);
+            const int k0 = j * PT_BN + hf * 64;           // first key of this thread's columns
             const int k_lim = min(qi, p.Skv - 1);         // last key this row may see
-            uint32_t v[32];
-            // pass 1: the row's maximum over this tile
+            const bool full = k0 + 63 <= min(q0, p.Skv - 1);     // no column of this half is masked for any row of the tile
+            uint32_t v0[32], v1[32];
+            pt_tmem_ld32(s_addr, v0);
+            pt_tmem_ld32(s_addr + 32, v1);
             float m_tile = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < PT_BN / 32; ++c) {
-                pt_tmem_ld32(s_addr + (uint32_t)(c * 32), v);
+            if (full) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (k0 + c * 32 + i <= k_lim) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+                for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (k0 + i > k_lim) v0[i] = 0xff800000u;          // -inf: masked
+                    if (k0 + 32 + i > k_lim) v1[i] = 0xff800000u;
+                    m_tile = fmaxf(m_tile, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+                }
             }
+            // the row's maximum over both halves
+            s_xch[hf][r] = m_tile;
+            asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
+            m_tile = fmaxf(m_tile, s_xch[hf ^ 1][r]);
             const float m_new = fmaxf(m_run, m_tile * p.scale_log2);
             const float alpha = m_new == -INFINITY ? 1.f : pt_ex2(m_run - m_new);
             const float m_sub = m_new == -INFINITY ? 0.f : m_new;
-            // pass 2: probabilities into the operand layout (row r of half h: 128 B, 16-byte chunks swizzled by r & 7)
+            // probabilities into the operand layout (row r of half hf: 128 B, 16-byte chunks swizzled by r & 7)
             float l_tile = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < PT_BN / 32; ++c) {
-                pt_tmem_ld32(s_addr + (uint32_t)(c * 32), v);
-                unsigned char* prow = sP + (c >> 1) * PT_HALF_BYTES + r * 128;
+            unsigned char* prow = sP + hf * PT_HALF_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const uint32_t (&v)[32] = c == 0 ? v0 : v1;
 #pragma unroll
                 for (int q8 = 0; q8 < 4; ++q8) {
                     uint32_t pk[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int i0 = q8 * 8 + 2 * e;
-                        float p0 = 0.f, p1 = 0.f;
-                        if (k0 + c * 32 + i0 <= k_lim) p0 = pt_ex2(fmaf(__uint_as_float(v[i0]), p.scale_log2, -m_sub));
-                        if (k0 + c * 32 + i0 + 1 <= k_lim) p1 = pt_ex2(fmaf(__uint_as_float(v[i0 + 1]), p.scale_log2, -m_sub));
+                        // ex2(-inf) = 0 for masked columns
+                        const float p0 = pt_ex2(fmaf(__uint_as_float(v[i0]), p.scale_log2, -m_sub));
+                        const float p1 = pt_ex2(fmaf(__uint_as_float(v[i0 + 1]), p.scale_log2, -m_sub));
+                        l_tile += p0 + p1;
                         pk[e] = pt_pack(p0, p1, p.bf16);
-                        // the denominator sums what the tensor core multiplies: the rounded probabilities
-                        if (p.bf16) { const __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&pk[e]); l_tile += __low2float(h) + __high2float(h); }
-                        else { const __half2 h = *reinterpret_cast<__half2*>(&pk[e]); l_tile += __low2float(h) + __high2float(h); }
                     }
-                    const int chunk = (c & 1) * 4 + q8;       // 16-byte chunk inside the 128-byte row
+                    const int chunk = c * 4 + q8;       // 16-byte chunk inside the 128-byte row
                     *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
             }
@@ -260,23 +281,30 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
             pt_mbar_arrive(p_ready);
             l_run = l_run * alpha + l_tile;
             m_run = m_new;
-            // O += P V: the tile's product, with the row's earlier sum rescaled to the new maximum
-            if (!pt_wait(o_ready, (unsigned)j & 1u)) { failed = true; break; }
+            // O += P V: this thread's half of the tile's product, with the row's earlier sum rescaled to the new maximum
+            wait_ok(o_ready, (unsigned)j & 1u);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t o_addr = lane_addr + (uint32_t)(2 * PT_BN + hf * 64);
+            pt_tmem_ld32(o_addr, v0);
+            pt_tmem_ld32(o_addr + 32, v1);
 #pragma unroll
-            for (int c = 0; c < PT_D / 32; ++c) {
-                pt_tmem_ld32(lane_addr + (uint32_t)(2 * PT_BN + c * 32), v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(v[i]));
+            for (int i = 0; i < 32; ++i) {
+                acc[i] = fmaf(acc[i], alpha, __uint_as_float(v0[i]));
+                acc[32 + i] = fmaf(acc[32 + i], alpha, __uint_as_float(v1[i]));
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             pt_mbar_arrive(o_taken);
         }
-        if (!failed && qi < p.Sq) {
+        // the row's denominator over both halves
+        asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
+        s_xch[hf][r] = l_run;
+        asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
+        l_run += s_xch[hf ^ 1][r];
+        if (*s_fail == 0 && qi < p.Sq) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            unsigned char* orow = static_cast<unsigned char*>(p.O) + ((int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + (int64_t)qi * p.o_ss) * 2;
+            unsigned char* orow = static_cast<unsigned char*>(p.O) + ((int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + (int64_t)qi * p.o_ss) * 2 + hf * 128;
 #pragma unroll
-            for (int i = 0; i < PT_D; i += 2) *reinterpret_cast<uint32_t*>(orow + i * 2) = pt_pack(acc[i] * inv, acc[i + 1] * inv, p.bf16);
+            for (int i = 0; i < PT_D / 2; i += 2) *reinterpret_cast<uint32_t*>(orow + i * 2) = pt_pack(acc[i] * inv, acc[i + 1] * inv, p.bf16);
         }
     }
     if (failed) atomicExch(p.status, FQ_ERR_TIMEOUT);
