@@ -932,7 +932,7 @@ def run_prefill_attn(args):
             tpeak = float(json.load(f)["bf16_tflops_sustained"])
     except Exception:
         tpeak = 1400.0
-    return {"metric": "prefill causal attention", "workload": "prefill_attn", "kernel": "prefill_attn_kernel (mma.sync m16n8k16, fp32 accumulate)",
+    return {"metric": "prefill causal attention", "workload": "prefill_attn", "kernel": "prefill_attn_tc_kernel (tcgen05.mma, S / O in tensor memory, TMA-staged Q/K/V; fp32 softmax)",
             "config": {"q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "S_q": S, "S_kv": S, "dtype": "f16"},
             "us_per_call": us, "TFLOPs": flops / us / 1e6, "frac_of_tensor_peak": flops / us / 1e6 / tpeak, "peak_TFLOPs": tpeak,
             "device_status": _lib.lib().fq_device_status()}

@@ -4,17 +4,19 @@
 // (query i sees keys 0..i), fp16 or bf16 operands, fp32 accumulation and softmax.
 //
 // One CTA = 128 queries of one query head, walking key tiles of 128:
-//   warp 0      : one thread issues the TMA loads (4-D tensor maps over Q, K, V; 128-byte swizzle): Q once,
-//                 then K and V tiles into a two-deep ring;
+//   warp 0      : two threads issue the TMA loads (4-D tensor maps over Q, K, V; 128-byte swizzle): Q once, then one
+//                 thread the K tiles and one the V tiles, each into its own two-deep ring (a K stage is free again as
+//                 soon as S has been computed, long before the V stage of the same tile);
 //   warp 1      : one thread issues tcgen05.mma: S = Q K^T (M 128, N 128, K 16 x 8) into one of two S buffers in
-//                 tensor memory, and O_tile = P V (P from shared memory, V as the MN-major operand) into a third;
-//                 S of the next key tile is issued before the softmax of the current one is awaited;
+//                 tensor memory, and O_tile = P V (P from one of two shared-memory buffers, V as the MN-major
+//                 operand) into one of two O buffers; S runs up to two key tiles ahead of P V;
 //   warps 2..9  : softmax — two threads per query row (TMEM lane = row; warps 2..5 own the key / channel columns
 //                 0..63, warps 6..9 the columns 64..127): read S once (tcgen05.ld), scale, mask (diagonal tile only),
 //                 exchange the row maximum through shared memory, keep the running maximum and denominator in base
 //                 2, write P as fp16/bf16 into the swizzled K-major operand layout, then add their half of O_tile
 //                 (with the row's earlier sum rescaled by the change of the maximum) to an fp32 half row of O in
-//                 registers; store the normalised row at the end.
+//                 registers; store the normalised row at the end.  The softmax of tile j+1 is computed BEFORE O_tile of
+//                 tile j is collected, so that P V of tile j overlaps it.
 // Every mbarrier wait is bounded and reports through the device status word.
 #include <cuda.h>
 
@@ -28,9 +30,9 @@ constexpr int PT_THREADS = (2 + PT_SOFTMAX_WARPS) * 32;
 constexpr int PT_TILE_BYTES = 128 * PT_D * 2;                 // 32 KiB: two halves of [128 rows][64 elements]
 constexpr int PT_HALF_BYTES = PT_TILE_BYTES / 2;
 constexpr int PT_KV_STAGES = 2;
-constexpr int PT_SMEM = PT_TILE_BYTES * (2 + 2 * PT_KV_STAGES) + 1024 + 256;   // Q, P, K/V ring, alignment slack, barriers
+constexpr int PT_SMEM = PT_TILE_BYTES * (3 + 2 * PT_KV_STAGES) + 1024 + 256;   // Q, P x 2, K ring, V ring, alignment slack, barriers
 constexpr unsigned PT_SPIN_LIMIT = 1u << 26;
-constexpr int PT_TMEM_COLS = 512;                              // S0 @0, S1 @128, O_tile @256
+constexpr int PT_TMEM_COLS = 512;                              // S0 @0, S1 @128, O0 @256, O1 @384
 
 struct PrefillTcParams {
     void* O; int64_t o_sb, o_sh, o_ss;
@@ -108,20 +110,22 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
     extern __shared__ unsigned char pt_raw_smem[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pt_raw_smem) + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;                                         // [2 halves][128 rows][128 B]
-    unsigned char* sP = base + PT_TILE_BYTES;                         // same layout, keys instead of channels
-    unsigned char* sK = base + 2 * PT_TILE_BYTES;                     // [stages] same layout
+    unsigned char* sP = base + PT_TILE_BYTES;                         // [2 buffers] same layout, keys instead of channels
+    unsigned char* sK = base + 3 * PT_TILE_BYTES;                     // [stages] same layout
     unsigned char* sV = sK + PT_KV_STAGES * PT_TILE_BYTES;            // [stages][2 halves of d][128 keys][128 B]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + PT_KV_STAGES * PT_TILE_BYTES);
     uint64_t* q_full = bars;                 // Q landed
-    uint64_t* kv_full = bars + 1;            // [stages] K and V tiles landed
-    uint64_t* kv_empty = bars + 3;           // [stages] both MMAs that read the stage have completed
-    uint64_t* s_ready = bars + 5;            // [2] S buffer written by the tensor core
-    uint64_t* p_ready = bars + 7;            // P written (and S read) by the softmax threads
-    uint64_t* o_ready = bars + 8;            // O_tile written by the tensor core
-    uint64_t* o_taken = bars + 9;            // O_tile read by the softmax threads
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* k_full = bars + 1;             // [stages] K tile landed
+    uint64_t* k_empty = bars + 3;            // [stages] S = Q K^T of the tile has completed
+    uint64_t* v_full = bars + 5;             // [stages] V tile landed
+    uint64_t* v_empty = bars + 7;            // [stages] O_tile = P V of the tile has completed
+    uint64_t* s_ready = bars + 9;            // [2] S buffer written by the tensor core
+    uint64_t* p_ready = bars + 11;           // [2] P buffer written (and the S buffer read) by the softmax threads
+    uint64_t* o_ready = bars + 13;           // [2] O buffer written by the tensor core
+    uint64_t* o_taken = bars + 15;           // [2] O buffer read by the softmax threads
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);      // a wait gave up somewhere: nobody waits any more
-    __shared__ float s_xch[2][PT_BM];                                          // row maxima / denominators of the two column halves
+    __shared__ float s_xch[2 * PT_BM];                                         // [column half][row]: row maxima / denominators
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // the heaviest query tiles (most keys under the causal mask) are scheduled first
@@ -133,9 +137,11 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
 
     if (tid == 0) {
         pt_mbar_init(q_full, 1);
-        for (int s = 0; s < PT_KV_STAGES; ++s) { pt_mbar_init(&kv_full[s], 1); pt_mbar_init(&kv_empty[s], 1); }
-        pt_mbar_init(&s_ready[0], 1); pt_mbar_init(&s_ready[1], 1);
-        pt_mbar_init(p_ready, PT_SOFTMAX_WARPS * 32); pt_mbar_init(o_ready, 1); pt_mbar_init(o_taken, PT_SOFTMAX_WARPS * 32);
+        for (int s = 0; s < 2; ++s) {
+            pt_mbar_init(&k_full[s], 1); pt_mbar_init(&k_empty[s], 1); pt_mbar_init(&v_full[s], 1); pt_mbar_init(&v_empty[s], 1);
+            pt_mbar_init(&s_ready[s], 1); pt_mbar_init(&o_ready[s], 1);
+            pt_mbar_init(&p_ready[s], PT_SOFTMAX_WARPS * 32); pt_mbar_init(&o_taken[s], PT_SOFTMAX_WARPS * 32);
+        }
         *s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -151,18 +157,24 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
 
     if (warp == 0) {
         // =========================== TMA producer ===========================
-        if (lane == 0 && n_tiles > 0) {
+        if (lane == 0 && n_tiles > 0) {           // Q, then the K tiles
             pt_mbar_expect_tx(q_full, PT_TILE_BYTES);
             pt_tma_4d(sQ, &map_q, 0, q0, hq, b, q_full);
             pt_tma_4d(sQ + PT_HALF_BYTES, &map_q, 64, q0, hq, b, q_full);
             for (int j = 0; j < n_tiles; ++j) {
-                const int s = j % PT_KV_STAGES;
-                if (j >= PT_KV_STAGES && !pt_wait(&kv_empty[s], (unsigned)(j / PT_KV_STAGES - 1) & 1u)) { failed = true; break; }
-                pt_mbar_expect_tx(&kv_full[s], 2 * PT_TILE_BYTES);
-                pt_tma_4d(sK + s * PT_TILE_BYTES, &map_k, 0, j * PT_BN, hkv, b, &kv_full[s]);
-                pt_tma_4d(sK + s * PT_TILE_BYTES + PT_HALF_BYTES, &map_k, 64, j * PT_BN, hkv, b, &kv_full[s]);
-                pt_tma_4d(sV + s * PT_TILE_BYTES, &map_v, 0, j * PT_BN, hkv, b, &kv_full[s]);
-                pt_tma_4d(sV + s * PT_TILE_BYTES + PT_HALF_BYTES, &map_v, 64, j * PT_BN, hkv, b, &kv_full[s]);
+                const int s = j & 1;
+                if (j >= 2 && !pt_wait(&k_empty[s], (unsigned)((j >> 1) - 1) & 1u)) { failed = true; break; }
+                pt_mbar_expect_tx(&k_full[s], PT_TILE_BYTES);
+                pt_tma_4d(sK + s * PT_TILE_BYTES, &map_k, 0, j * PT_BN, hkv, b, &k_full[s]);
+                pt_tma_4d(sK + s * PT_TILE_BYTES + PT_HALF_BYTES, &map_k, 64, j * PT_BN, hkv, b, &k_full[s]);
+            }
+        } else if (lane == 1 && n_tiles > 0) {    // the V tiles
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                if (j >= 2 && !pt_wait(&v_empty[s], (unsigned)((j >> 1) - 1) & 1u)) { failed = true; break; }
+                pt_mbar_expect_tx(&v_full[s], PT_TILE_BYTES);
+                pt_tma_4d(sV + s * PT_TILE_BYTES, &map_v, 0, j * PT_BN, hkv, b, &v_full[s]);
+                pt_tma_4d(sV + s * PT_TILE_BYTES + PT_HALF_BYTES, &map_v, 64, j * PT_BN, hkv, b, &v_full[s]);
             }
         }
     } else if (warp == 1) {
@@ -173,39 +185,42 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
             const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(PT_BN >> 3) << 17) |
                                      ((uint32_t)(PT_BM >> 4) << 24);
             const uint32_t idesc_o = idesc_s | (1u << 16);
-            const uint32_t q_addr = pt_smem(sQ), p_addr = pt_smem(sP);
-            auto issue_s = [&](int j) -> bool {           // S[j & 1] = Q K_j^T
-                const int s = j % PT_KV_STAGES;
-                if (!pt_wait(&kv_full[s], (unsigned)(j / PT_KV_STAGES) & 1u)) return false;
+            const uint32_t q_addr = pt_smem(sQ);
+            auto issue_s = [&](int j) -> bool {           // S[j & 1] = Q K_j^T; the buffer was read by the softmax of tile j-2
+                const int s = j & 1;
+                if (!pt_wait(&k_full[s], (unsigned)(j >> 1) & 1u)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t k_addr = pt_smem(sK + s * PT_TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < PT_D / 16; ++kk) {
                     // K-major, 128-byte swizzle: 8 rows x 64 elements = one 1 KiB atom; 16 k = 32 B inside the row; second half 16 KiB on
                     const uint32_t off = (uint32_t)(kk >> 2) * PT_HALF_BYTES + (uint32_t)(kk & 3) * 32;
-                    pt_mma(tmem_base + (uint32_t)((j & 1) * PT_BN), pt_desc(q_addr + off, 16, 1024), pt_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+                    pt_mma(tmem_base + (uint32_t)(s * PT_BN), pt_desc(q_addr + off, 16, 1024), pt_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
                 }
-                pt_commit(&s_ready[j & 1]);
+                pt_commit(&s_ready[s]);
+                pt_commit(&k_empty[s]);
                 return true;
             };
             if (!pt_wait(q_full, 0u) || !issue_s(0)) failed = true;
+            if (!failed && n_tiles > 1 && !issue_s(1)) failed = true;
             for (int j = 0; j < n_tiles && !failed; ++j) {
-                const int s = j % PT_KV_STAGES;
-                // S of the next key tile while the softmax of this one runs: its buffer was read two tiles ago (p_ready of j-1 seen below)
-                if (j + 1 < n_tiles && !issue_s(j + 1)) { failed = true; break; }
-                if (!pt_wait(p_ready, (unsigned)j & 1u)) { failed = true; break; }
-                if (j >= 1 && !pt_wait(o_taken, (unsigned)(j - 1) & 1u)) { failed = true; break; }
+                const int s = j & 1;
+                const unsigned ph = (unsigned)(j >> 1) & 1u;
+                if (!pt_wait(&p_ready[s], ph) || !pt_wait(&v_full[s], ph)) { failed = true; break; }
+                if (j >= 2 && !pt_wait(&o_taken[s], (unsigned)((j >> 1) - 1) & 1u)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v_addr = pt_smem(sV + s * PT_TILE_BYTES);
+                const uint32_t v_addr = pt_smem(sV + s * PT_TILE_BYTES), p_addr = pt_smem(sP + s * PT_TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < PT_BN / 16; ++kk) {
                     // A = P, K-major over the keys; B = V, MN-major: 64 channels x 8 keys = one atom, 16 keys = 2 KiB, channel halves 16 KiB apart
                     const uint32_t offp = (uint32_t)(kk >> 2) * PT_HALF_BYTES + (uint32_t)(kk & 3) * 32;
-                    pt_mma(tmem_base + 2 * PT_BN, pt_desc(p_addr + offp, 16, 1024), pt_desc(v_addr + (uint32_t)kk * 2048, PT_HALF_BYTES, 1024), idesc_o,
-                           kk != 0 ? 1u : 0u);
+                    pt_mma(tmem_base + (uint32_t)(2 * PT_BN + s * PT_D), pt_desc(p_addr + offp, 16, 1024),
+                           pt_desc(v_addr + (uint32_t)kk * 2048, PT_HALF_BYTES, 1024), idesc_o, kk != 0 ? 1u : 0u);
                 }
-                pt_commit(o_ready);
-                pt_commit(&kv_empty[s]);
+                pt_commit(&o_ready[s]);
+                pt_commit(&v_empty[s]);
+                // S two tiles ahead: its buffer has just been released by p_ready of tile j
+                if (j + 2 < n_tiles && !issue_s(j + 2)) { failed = true; break; }
             }
         }
     } else {
@@ -225,10 +240,12 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
             if (*s_fail) return;
             if (!pt_wait(bar, parity)) { failed = true; *s_fail = 1; }
         };
-        for (int j = 0; j < n_tiles; ++j) {
-            wait_ok(&s_ready[j & 1], (unsigned)(j >> 1) & 1u);
+        // softmax of key tile j: reads S[j & 1], writes P[j & 1]; returns the factor the row's earlier sums shrink by
+        auto softmax_tile = [&](int j) -> float {
+            const int sb = j & 1;
+            wait_ok(&s_ready[sb], (unsigned)(j >> 1) & 1u);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * PT_BN + hf * 64);
+            const uint32_t s_addr = lane_addr + (uint32_t)(sb * PT_BN + hf * 64);
             const int k0 = j * PT_BN + hf * 64;           // first key of this thread's columns
             const int k_lim = min(qi, p.Skv - 1);         // last key this row may see
             const bool full = k0 + 63 <= min(q0, p.Skv - 1);     // no column of this half is masked for any row of the tile
@@ -247,16 +264,17 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
                     m_tile = fmaxf(m_tile, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
                 }
             }
-            // the row's maximum over both halves
-            s_xch[hf][r] = m_tile;
+            // the row's maximum over both halves; the second barrier keeps the next tile's write behind this tile's read
+            s_xch[hf * PT_BM + r] = m_tile;
             asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
-            m_tile = fmaxf(m_tile, s_xch[hf ^ 1][r]);
+            m_tile = fmaxf(m_tile, s_xch[(hf ^ 1) * PT_BM + r]);
+            asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
             const float m_new = fmaxf(m_run, m_tile * p.scale_log2);
             const float alpha = m_new == -INFINITY ? 1.f : pt_ex2(m_run - m_new);
             const float m_sub = m_new == -INFINITY ? 0.f : m_new;
             // probabilities into the operand layout (row r of half hf: 128 B, 16-byte chunks swizzled by r & 7)
             float l_tile = 0.f;
-            unsigned char* prow = sP + hf * PT_HALF_BYTES + r * 128;
+            unsigned char* prow = sP + sb * PT_TILE_BYTES + hf * PT_HALF_BYTES + r * 128;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const uint32_t (&v)[32] = c == 0 ? v0 : v1;
@@ -278,13 +296,18 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            pt_mbar_arrive(p_ready);
+            pt_mbar_arrive(&p_ready[sb]);
             l_run = l_run * alpha + l_tile;
             m_run = m_new;
-            // O += P V: this thread's half of the tile's product, with the row's earlier sum rescaled to the new maximum
-            wait_ok(o_ready, (unsigned)j & 1u);
+            return alpha;
+        };
+        // O += P V of key tile j: this thread's half of O[j & 1], the row's earlier sum first rescaled by alpha
+        auto collect_tile = [&](int j, float alpha) {
+            const int ob = j & 1;
+            wait_ok(&o_ready[ob], (unsigned)(j >> 1) & 1u);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t o_addr = lane_addr + (uint32_t)(2 * PT_BN + hf * 64);
+            const uint32_t o_addr = lane_addr + (uint32_t)(2 * PT_BN + ob * PT_D + hf * 64);
+            uint32_t v0[32], v1[32];
             pt_tmem_ld32(o_addr, v0);
             pt_tmem_ld32(o_addr + 32, v1);
 #pragma unroll
@@ -293,13 +316,21 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
                 acc[32 + i] = fmaf(acc[32 + i], alpha, __uint_as_float(v1[i]));
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            pt_mbar_arrive(o_taken);
+            pt_mbar_arrive(&o_taken[ob]);
+        };
+        // P[j & 1] is free when the softmax of tile j starts: O_tile of tile j-2 was collected (hence P V of j-2 complete) before
+        float alpha_cur = n_tiles > 0 ? softmax_tile(0) : 1.f;
+        for (int j = 0; j < n_tiles; ++j) {
+            float alpha_next = 1.f;
+            if (j + 1 < n_tiles) alpha_next = softmax_tile(j + 1);     // overlaps P V of tile j on the tensor core
+            collect_tile(j, alpha_cur);
+            alpha_cur = alpha_next;
         }
         // the row's denominator over both halves
         asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
-        s_xch[hf][r] = l_run;
+        s_xch[hf * PT_BM + r] = l_run;
         asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
-        l_run += s_xch[hf ^ 1][r];
+        l_run += s_xch[(hf ^ 1) * PT_BM + r];
         if (*s_fail == 0 && qi < p.Sq) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             unsigned char* orow = static_cast<unsigned char*>(p.O) + ((int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + (int64_t)qi * p.o_ss) * 2 + hf * 128;
