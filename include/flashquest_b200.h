@@ -206,8 +206,9 @@ int fq_sparse_decode_int8(
  * is_causal=True, enable_gqa=True) call of the patched forward
  * (eager/llama_persistent_patch.py:196-201), where K_full / V_full are the dequantised
  * completed pages followed by the staged tail.  The causal mask is aligned at the top left,
- * as torch aligns it when S_q != S_kv: query i attends keys 0..i.  Tensor-core kernel
- * (mma.sync, fp32 accumulation, softmax in fp32).
+ * as torch aligns it when S_q != S_kv: query i attends keys 0..i.  Tensor-core kernels, fp32
+ * accumulation and softmax: tcgen05 (S and P.V in tensor memory, TMA-staged operands) for head_dim 128
+ * with at least 128 queries, mma.sync otherwise.
  *   Q (B,Hq,Sq,D), K,V (B,Hkv,Skv,D), O (B,Hq,Sq,D): all `dtype` (F16|BF16), element strides
  *   *_sb,*_sh,*_ss (head_dim contiguous; pass O's strides to write a (B,Sq,Hq*D) buffer).
  * D in {64,128}; Q/K/V rows 16-byte aligned.
