@@ -8,7 +8,9 @@ import json
 import os
 import sys
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_bench_record_keys.py /path/to/reference")
+ref = sys.argv[1]
 path = sorted(glob.glob(os.path.join(ref, "benchmarks/validation/ablation/*/cells/c32768-s0-sparse.json")))[0]
 rec = json.load(open(path))
 out = {"source": "benchmarks/validation/ablation/<hash>/cells/c32768-s0-sparse.json", "schema_version": rec["schema_version"],
