@@ -12,12 +12,15 @@
 // accumulation, split-K partials merged by the CTA that draws the last ticket of its row (no
 // CTA waits for another).  Bound by the ALU/LSU work of the index assembly and look-ups
 // (about 3 instructions per 3-bit element), not by HBM.
+#include <atomic>
+
 #include "fq_common.cuh"
 
 namespace fq {
 
 constexpr int TQ_WARPS = 8;
 constexpr int TQ_THREADS = TQ_WARPS * 32;
+constexpr int TQ_LIST_MAX = 4096;        // page-list entries a CTA packs in shared memory
 constexpr float TQ_LOG2E = 1.4426950408889634f;
 constexpr float TQ_LN2 = 0.6931471805599453f;
 
@@ -83,7 +86,7 @@ __device__ __forceinline__ void tq_reduce(float (&s)[N], int c) {
 }
 
 template <typename QT, int D>
-__global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAttnParams p) {
+__global__ void __launch_bounds__(TQ_THREADS, 3) sparse_decode_turbo_kernel(TurboAttnParams p) {
     constexpr int TOK = 16;
     constexpr int LPT = D / 8;           // lanes per token, 8 channels each
     constexpr int NTP = 32 / LPT;        // tokens a warp works on at once
@@ -96,6 +99,8 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
     __shared__ __align__(16) unsigned char s_stage[TQ_WARPS][2][UNIT_BYTES];
     __shared__ float s_m[TQ_WARPS], s_l[TQ_WARPS], s_acc[TQ_WARPS][D];
     __shared__ int s_ticket;
+    extern __shared__ int s_pages[];                                       // the row's valid pages: min(bucket, TQ_LIST_MAX) entries, or none
+    __shared__ int s_cnt[TQ_WARPS];
 
     const int split = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
     const int n_rep = p.Hq / p.Hkv, hkv = hq / n_rep;
@@ -126,12 +131,46 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
         for (int j = 0; j < 4; ++j) q2[j] = make_float2(Dt<QT>::to_f32(qp[2 * j]) * sc, Dt<QT>::to_f32(qp[2 * j + 1]) * sc);
     }
 
-    // Units are dealt round-robin to the splits (unit g belongs to split g % n_split): a list
-    // whose valid entries sit at the front and padding at the back stays balanced.
-    const int cpp = p.page / TOK;
-    const int total_units = p.bucket * cpp;
-    const int n_units = split < total_units ? (total_units - split + p.n_split - 1) / p.n_split : 0;   // of this CTA
+    // A list made from a selection mask is as wide as the page count and mostly padding.  Every CTA of a row
+    // therefore first packs the row's valid entries, in their order, into shared memory (a warp per contiguous
+    // eighth of the list: 16 independent loads per lane, ballots, one exchange of the warps' counts); the walk below
+    // then meets real pages only.  Lists wider than TQ_LIST_MAX are walked as they are, padding skipped per unit.
     const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
+    const bool packed = p.bucket <= TQ_LIST_MAX;
+    int n_entries = p.bucket;
+    if (packed) {
+        constexpr int PER_LANE = TQ_LIST_MAX / TQ_THREADS;
+        const int seg = (p.bucket + TQ_WARPS - 1) / TQ_WARPS;
+        const int e_begin = warp * seg, e_end = min(p.bucket, e_begin + seg);
+        int pg[PER_LANE], pos[PER_LANE];
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int e = e_begin + i * 32 + lane;
+            pg[i] = e < e_end ? __ldg(list + e) : -1;
+        }
+        int cnt = 0;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const bool ok = pg[i] >= 0 && pg[i] < p.P && (int64_t)pg[i] * p.page < p.S_kv;
+            const unsigned bal = __ballot_sync(0xffffffffu, ok);
+            pos[i] = ok ? cnt + __popc(bal & ((1u << lane) - 1u)) : -1;
+            cnt += __popc(bal);
+        }
+        if (lane == 0) s_cnt[warp] = cnt;
+        __syncthreads();
+        int off = 0, tot = 0;
+#pragma unroll
+        for (int w = 0; w < TQ_WARPS; ++w) { const int n = s_cnt[w]; off += w < warp ? n : 0; tot += n; }
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i)
+            if (pos[i] >= 0) s_pages[off + pos[i]] = pg[i];
+        __syncthreads();
+        n_entries = tot;
+    }
+    // Units are dealt round-robin to the splits (unit g belongs to split g % n_split).
+    const int cpp = p.page / TOK;
+    const int total_units = n_entries * cpp;
+    const int n_units = split < total_units ? (total_units - split + p.n_split - 1) / p.n_split : 0;   // of this CTA
 
     const uint8_t* Kmsb = p.K_msb + b * p.km_sb + hkv * p.km_sh;
     const uint8_t* Klsb = p.K_lsb + b * p.kl_sb + hkv * p.kl_sh;
@@ -144,13 +183,18 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
 
     // unit -> first token and number of valid tokens (0: nothing to do)
     // page id of this warp's unit u (-1 past the end); requested two units ahead of its use
+    const int cpp_shift = (cpp & (cpp - 1)) == 0 ? __ffs(cpp) - 1 : -1;      // units per page as a shift, where it is one
     auto page_of = [&](int u) -> int {
-        return u < n_units ? __ldg(list + (u * p.n_split + split) / cpp) : -1;
+        const int g = u * p.n_split + split;
+        if (u >= n_units) return -1;
+        const int e = cpp_shift >= 0 ? g >> cpp_shift : g / cpp;
+        return packed ? s_pages[e] : __ldg(list + e);
     };
     auto locate = [&](int u, int pg, int& tok0, int& n_tok) {
         tok0 = 0; n_tok = 0;
         if (pg < 0 || pg >= p.P) return;
-        tok0 = pg * p.page + ((u * p.n_split + split) % cpp) * TOK;
+        const int g = u * p.n_split + split;
+        tok0 = pg * p.page + (cpp_shift >= 0 ? g & (cpp - 1) : g % cpp) * TOK;
         n_tok = max(0, min(TOK, p.S_kv - tok0));
     };
     // this lane's three 16-byte pieces of a full unit: plane, offset inside the unit, bytes per token
@@ -192,9 +236,11 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
             }
         }
     };
-    // codebook pair of channels (2j, 2j+1) of this lane: M = msb byte << 12, Lw = lsb halfword << 8
-    auto pair_at = [&](uint32_t M, uint32_t Lw, int j) -> float2 {
-        return tq_lds_f2(lut_addr + ((M >> (2 * j)) & 0x3000u) + ((Lw >> (4 * j)) & 0x0f00u));
+    // codebook pair of channels (2j, 2j+1) of this lane from the raw plane bytes: mask, then shift-and-add
+    auto pair_at = [&](uint32_t M, uint32_t L, int j) -> float2 {
+        const uint32_t a = lut_addr + ((M & (3u << (2 * j))) << (12 - 2 * j));
+        const uint32_t b = j < 2 ? ((L & (15u << (4 * j))) << (8 - 4 * j)) : j == 2 ? (L & 0x0f00u) : ((L >> 4) & 0x0f00u);
+        return tq_lds_f2(a + b);
     };
 
     float m_run = -INFINITY, l_run = 0.f;
@@ -225,16 +271,27 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
         __syncwarp();
         if (cur_n > 0) {                                   // warp-uniform
             const uint32_t buf = (uint32_t)__cvta_generic_to_shared(s_stage[warp][it & 1]);
+            // plane bytes of this lane's tokens, K and V, are requested before the first look-up depends on one
+            // of them: their latencies overlap each other and the V planes arrive during the softmax
+            const uint32_t row_m = buf + tp * MROW + c, row_l = buf + tp * LROW + 2 * c;
+            uint32_t Mk[TPL], Lk[TPL], Mv[TPL], Lv[TPL];
+#pragma unroll
+            for (int k = 0; k < TPL; ++k) {
+                Mk[k] = tq_lds_u8(row_m + KM_OFF + NTP * k * MROW);
+                Lk[k] = tq_lds_u16(row_l + KL_OFF + NTP * k * LROW);
+            }
+#pragma unroll
+            for (int k = 0; k < TPL; ++k) {
+                Mv[k] = tq_lds_u8(row_m + VM_OFF + NTP * k * MROW);
+                Lv[k] = tq_lds_u16(row_l + VL_OFF + NTP * k * LROW);
+            }
             // ---------------- K ----------------
             float dots[TPL];
 #pragma unroll
             for (int k = 0; k < TPL; ++k) {
-                const int t = NTP * k + tp;
-                const uint32_t M = tq_lds_u8(buf + KM_OFF + t * MROW + c) << 12;
-                const uint32_t Lw = tq_lds_u16(buf + KL_OFF + t * LROW + 2 * c) << 8;
                 float2 a = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) a = __ffma2_rn(pair_at(M, Lw, j), q2[j], a);
+                for (int j = 0; j < 4; ++j) a = __ffma2_rn(pair_at(Mk[k], Lk[k], j), q2[j], a);
                 dots[k] = a.x + a.y;
             }
             tq_reduce<TPL, LPT>(dots, c);
@@ -258,13 +315,10 @@ __global__ void __launch_bounds__(TQ_THREADS) sparse_decode_turbo_kernel(TurboAt
             for (int j = 0; j < 4; ++j) acc[j] = __fmul2_rn(acc[j], al2);
 #pragma unroll
             for (int k = 0; k < TPL; ++k) {
-                const int t = NTP * k + tp;
                 const float pv = __shfl_sync(0xffffffffu, pv_mine, tp * LPT + 2 * k);
                 const float2 pv2 = make_float2(pv, pv);
-                const uint32_t M = tq_lds_u8(buf + VM_OFF + t * MROW + c) << 12;
-                const uint32_t Lw = tq_lds_u16(buf + VL_OFF + t * LROW + 2 * c) << 8;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[j] = __ffma2_rn(pair_at(M, Lw, j), pv2, acc[j]);
+                for (int j = 0; j < 4; ++j) acc[j] = __ffma2_rn(pair_at(Mv[k], Lv[k], j), pv2, acc[j]);
             }
         }
         __syncwarp();                                      // the buffer is refilled in the next iteration
@@ -418,13 +472,24 @@ extern "C" int fq_sparse_decode_turbo(
     }
     dim3 grid((unsigned)n_split, (unsigned)Hq, (unsigned)B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (q_dtype == FQ_F16) {
-        if (D == 128) launch_k(PDL_ATTN, sparse_decode_turbo_kernel<__half, 128>, grid, dim3(TQ_THREADS), 0, st, p);
-        else launch_k(PDL_ATTN, sparse_decode_turbo_kernel<__half, 64>, grid, dim3(TQ_THREADS), 0, st, p);
-    } else {
-        if (D == 128) launch_k(PDL_ATTN, sparse_decode_turbo_kernel<__nv_bfloat16, 128>, grid, dim3(TQ_THREADS), 0, st, p);
-        else launch_k(PDL_ATTN, sparse_decode_turbo_kernel<__nv_bfloat16, 64>, grid, dim3(TQ_THREADS), 0, st, p);
+    const size_t smem = p.bucket <= TQ_LIST_MAX ? (size_t)p.bucket * sizeof(int) : 0;       // the packed page list
+    void (*kern)(TurboAttnParams) =
+        q_dtype == FQ_F16 ? (D == 128 ? sparse_decode_turbo_kernel<__half, 128> : sparse_decode_turbo_kernel<__half, 64>)
+                          : (D == 128 ? sparse_decode_turbo_kernel<__nv_bfloat16, 128> : sparse_decode_turbo_kernel<__nv_bfloat16, 64>);
+    {
+        // static + dynamic shared memory pass 48 KB: each of the four kernels opts in once per device
+        constexpr int MAX_DEV = 64;
+        static std::atomic<bool> prepared[MAX_DEV][4];     // relaxed: concurrent host threads may repeat the idempotent set-up
+        const int which = (q_dtype == FQ_F16 ? 0 : 2) + (D == 128 ? 0 : 1);
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return fail(FQ_ERR_CUDA, "%s: cannot identify the current device", fn);
+        if (!prepared[dev][which].load(std::memory_order_relaxed)) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TQ_LIST_MAX * (int)sizeof(int));
+            if (e != cudaSuccess) return fail(FQ_ERR_CUDA, "%s: cannot reserve shared memory for the page list: %s", fn, cudaGetErrorString(e));
+            prepared[dev][which].store(true, std::memory_order_relaxed);
+        }
     }
+    launch_k(PDL_ATTN, kern, grid, dim3(TQ_THREADS), smem, st, p);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
 }
