@@ -231,6 +231,129 @@ __global__ void __launch_bounds__(128) turbo_quant_kernel(TurboParams p) {
     if (lane == 0) p.scale[b * p.sc_sb + h * p.sc_sh + (int64_t)t * p.sc_ss] = f32_to_bf16_bits(s);
 }
 
+// The same coding for the shape that matters (head_dim 128, 16-bit values, 8-byte aligned rows) with about half the
+// instructions; results are bit-identical to turbo_quant_kernel (the tests compare both with the reference's planes).
+//  * the row stays packed (two values per register) from the load to the end of the butterflies; a butterfly with a
+//    partner lane is one shuffle and one packed fma(mine, +-1, other), which rounds once like the add it replaces;
+//  * x / fp32(sqrt(128)) rounded to the dtype: for every one of the 65 536 bit patterns the quotient, once rounded to
+//    the dtype, equals the rounding of q1 = fma(fma(-q0, cd, x), 1/cd, q0), q0 = x * (1/cd) (fp16), resp. of q0
+//    itself (bf16) -- checked exhaustively on the host; only the sign of a zero can differ, which no later step sees;
+//  * the nearest codebook entry of y = v / s is found without the division: |v| against the three midpoints times s.
+//    A value within 3e-5 (relative) of a midpoint, or that close to zero, takes the exact path (division, the
+//    reference's fp32 distances, first index on ties) -- the reference's decision can differ from the midpoint
+//    comparison only within a few fp32 roundings (1e-7 relative) of a midpoint;
+//  * a warp codes four consecutive tokens, so the row addresses are set up once.
+template <typename T>
+__global__ void __launch_bounds__(128) turbo_quant128_kernel(TurboParams p) {
+    using P2 = typename Pk2<T>::type;
+    constexpr int TPW = 4, D = 128;
+    constexpr bool IS_HALF = sizeof(T) == 2 && Dt<T>::code == FQ_F16;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int t0 = (blockIdx.x * 4 + warp) * TPW;
+    if (t0 >= p.n_quant) return;
+    const int nt = min(TPW, p.n_quant - t0);
+    const T* head = static_cast<const T*>(p.head) + b * p.hd_sb + h * p.hd_sh;
+    const T* nw = static_cast<const T*>(p.nw) + b * p.nw_sb + h * p.nw_sh;
+    uint8_t* msb = p.msb + b * p.ms_sb + h * p.ms_sh;
+    uint8_t* lsb = p.lsb + b * p.ls_sb + h * p.ls_sh;
+    uint16_t* scale = p.scale + b * p.sc_sb + h * p.sc_sh;
+
+    uint2 raw[TPW];
+#pragma unroll
+    for (int i = 0; i < TPW; ++i) {
+        const int t = t0 + i;
+        raw[i] = make_uint2(0u, 0u);
+        if (i < nt) {
+            const T* row = t < p.n_head ? head + (int64_t)t * p.hd_ss : nw + (int64_t)(t - p.n_head) * p.nw_ss;
+            raw[i] = *reinterpret_cast<const uint2*>(row + 4 * lane);
+        }
+    }
+    const uint32_t one = IS_HALF ? 0x3c003c00u : 0x3f803f80u, neg = one | 0x80008000u;
+    const P2 pm = p2_from<P2>(IS_HALF ? 0xbc003c00u : 0xbf803f80u);              // (+1, -1)
+    P2 sgn[5];                                                                   // (+-1, +-1): -1 in the upper lane of a pair
+#pragma unroll
+    for (int st = 0; st < 5; ++st) sgn[st] = p2_from<P2>((lane >> st) & 1 ? neg : one);
+    constexpr float cd = 11.313708498984761f;                                    // fp32(sqrt(128)), the reference's divisor
+    constexpr float rcd = 1.0f / cd;
+    // midpoints between neighbouring codebook magnitudes
+    constexpr float M0 = 0.50055f, M1 = 1.04995f, M2 = 1.7479f, GUARD = 3e-5f;
+
+#pragma unroll
+    for (int i = 0; i < TPW; ++i) {
+        if (i >= nt) break;
+        const int t = t0 + i;
+        P2 x[2] = {p2_from<P2>(raw[i].x), p2_from<P2>(raw[i].y)};
+        // stride 1: (a, b) -> (a + b, a - b)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t u = p2_bits(x[r]);
+            x[r] = __hfma2(p2_from<P2>(__byte_perm(u, u, 0x3232)), pm, p2_from<P2>(__byte_perm(u, u, 0x1010)));
+        }
+        // stride 2: the lane's two registers
+        {
+            const P2 a = x[0], c = x[1];
+            x[0] = __hadd2(a, c);
+            x[1] = __hsub2(a, c);
+        }
+        // strides 4 .. 64: partner lane
+#pragma unroll
+        for (int st = 0; st < 5; ++st) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const P2 other = p2_from<P2>(__shfl_xor_sync(0xffffffffu, p2_bits(x[r]), 1 << st));
+                x[r] = __hfma2(x[r], sgn[st], other);
+            }
+        }
+        // divide by sqrt(128), round to the dtype
+        float v[4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float2 f = Pk2<T>::unpack(x[r]);
+            float qx = __fmul_rn(f.x, rcd), qy = __fmul_rn(f.y, rcd);
+            if constexpr (IS_HALF) {
+                qx = __fmaf_rn(__fmaf_rn(-qx, cd, f.x), rcd, qx);
+                qy = __fmaf_rn(__fmaf_rn(-qy, cd, f.y), rcd, qy);
+            }
+            const float2 g = Pk2<T>::unpack(Pk2<T>::make(qx, qy));
+            v[2 * r] = g.x; v[2 * r + 1] = g.y;
+        }
+        float a = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a = __fmaf_rn(v[j], v[j], a);
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, off));
+        const float s = fmaxf(__fsqrt_rn(__fmul_rn(a, 1.0f / D)), 1e-6f);           // a / 128 is exact either way
+        const float th0 = M0 * s, th1 = M1 * s, th2 = M2 * s;
+        const float g0 = GUARD * th0, g1 = GUARD * th1, g2 = GUARD * th2, gz = GUARD * s;
+        unsigned idx[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float av = fabsf(v[j]);
+            const int m = (av > th0 ? 1 : 0) + (av > th1 ? 1 : 0) + (av > th2 ? 1 : 0);
+            idx[j] = (unsigned)(v[j] < 0.f ? 3 - m : 4 + m);
+            const bool risky = fabsf(av - th0) < g0 || fabsf(av - th1) < g1 || fabsf(av - th2) < g2 || av < gz;
+            if (risky) {
+                // the reference's own decision (kernel/kv_quant.py:253-279): fp32 quotient, fp32 distances, first index on ties
+                const float y = __fdiv_rn(v[j], s);
+                int k = y >= 0.2451f ? 4 : 0;
+                k += y >= (k ? 1.3439f : -0.7560f) ? 2 : 0;
+                k += y >= c_turbo_codebook[k + 1] ? 1 : 0;
+                k = min(k, 6);
+                const float d0 = fabsf(__fsub_rn(y, c_turbo_codebook[k])), d1 = fabsf(__fsub_rn(y, c_turbo_codebook[k + 1]));
+                idx[j] = (unsigned)(k + (d1 < d0 ? 1 : 0));
+            }
+        }
+        unsigned l8 = 0, m4 = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { l8 |= (idx[j] & 3u) << (2 * j); m4 |= ((idx[j] >> 2) & 1u) << j; }
+        const unsigned hi = __shfl_down_sync(0xffffffffu, m4, 1);
+        lsb[(int64_t)t * p.ls_ss + lane] = (uint8_t)l8;
+        if ((lane & 1) == 0) msb[(int64_t)t * p.ms_ss + (lane >> 1)] = (uint8_t)(m4 | (hi << 4));
+        if (lane == 0) scale[(int64_t)t * p.sc_ss] = f32_to_bf16_bits(s);
+    }
+}
+
 // dequantize_k_turbo / dequantize_v_turbo (kernel/kv_quant.py:366-378, :408-420):
 // codebook[idx] * scale in fp32, WHT in fp32, cast to bf16.
 template <int EPL>
@@ -337,8 +460,19 @@ extern "C" int fq_quantize_turbo(
     p.nw_sb = nw_sb; p.nw_sh = nw_sh; p.nw_ss = nw_ss; p.n_head = n_head; p.n_quant = n_quant; p.D = D;
     p.msb = msb; p.lsb = lsb; p.ms_sb = ms_sb; p.ms_sh = ms_sh; p.ms_ss = ms_ss; p.ls_sb = ls_sb; p.ls_sh = ls_sh; p.ls_ss = ls_ss;
     p.scale = static_cast<uint16_t*>(scale); p.sc_sb = sc_sb; p.sc_sh = sc_sh; p.sc_ss = sc_ss;
-    dim3 grid((unsigned)((n_quant + 3) / 4), (unsigned)H, (unsigned)B);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    {
+        // head_dim 128, 16-bit values, every row 8-byte aligned: the short kernel (four tokens per warp)
+        auto rows8 = [](const void* q, int64_t a, int64_t b2, int64_t c) { return q == nullptr || (aligned(q, 8) && a % 4 == 0 && b2 % 4 == 0 && c % 4 == 0); };
+        if (D == 128 && dtype != FQ_F32 && rows8(head, hd_sb, hd_sh, hd_ss) && rows8(nw, nw_sb, nw_sh, nw_ss)) {
+            dim3 grid16((unsigned)((n_quant + 15) / 16), (unsigned)H, (unsigned)B);
+            if (dtype == FQ_F16) turbo_quant128_kernel<__half><<<grid16, 128, 0, st>>>(p);
+            else turbo_quant128_kernel<__nv_bfloat16><<<grid16, 128, 0, st>>>(p);
+            FQ_CHECK_LAUNCH(fn);
+            return FQ_OK;
+        }
+    }
+    dim3 grid((unsigned)((n_quant + 3) / 4), (unsigned)H, (unsigned)B);
     if (dtype == FQ_F32) launch_turbo<float>(p, grid, st);
     else if (dtype == FQ_F16) launch_turbo<__half>(p, grid, st);
     else launch_turbo<__nv_bfloat16>(p, grid, st);

@@ -155,6 +155,38 @@ def _student_t_kv(seed, shape, dtype, df=3, dims=(3, 17, 29, 41, 64, 77, 100, 11
     return torch.from_numpy(x).to(dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_turbo_quant_head_dim_128_rows(T, dtype):
+    """The head_dim-128 kernel (packed butterflies, division-free codebook search with an exact path near the
+    decision points) against the oracle, bit for bit: heavy-tailed rows at several magnitudes, rows of zeros, of one
+    value, of values sitting on codebook midpoints, a token count that is no multiple of the 16 tokens a CTA codes,
+    and a strided source (odd token stride falls back to the general kernel; an even one does not)."""
+    H, S, D = 2, 4099, 128
+    x = _student_t_kv(901, (1, H, S, D), torch.float32)
+    x[:, :, 0:256] *= 1e-3
+    x[:, :, 256:512] *= 60.0
+    x[:, :, 512] = 0.0
+    x[:, :, 513] = 0.75
+    x[:, :, 514] = 6e-8
+    # rows whose rotated values land on / next to midpoints times the row scale: one large entry, the rest equal
+    x[:, :, 515] = 0.50055
+    x[:, :, 515, 0] = 1.04995
+    x = x.to(dtype)
+    want = oracle.quantize_v_turbo(x)
+    got = T.kvq.quantize_v_turbo(x.cuda())
+    for g, w, key in zip(got, want, ("msb", "lsb", "scale")):
+        assert bit_equal(g.cpu(), w), key
+    wide = torch.zeros(1, H, S, 2 * D, dtype=dtype)
+    wide[..., :D] = x
+    got2 = T.kvq.quantize_v_turbo(wide.cuda()[..., :D])            # token stride 256: still the short kernel
+    for g, w, key in zip(got2, want, ("msb", "lsb", "scale")):
+        assert bit_equal(g.cpu(), w), key
+    wk = oracle.quantize_k_turbo(x[:, :, :4096], 16)
+    gk = T.kvq.quantize_k_turbo(x[:, :, :4096].cuda(), 16)
+    for g, w, key in zip(gk, wk, ("Kmsb", "Klsb", "Kst", "Ksr", "Kmr")):
+        assert bit_equal(g.cpu(), w), key
+
+
 def test_turbo_config2_shape(T):
     """BASELINE config 2 as stated: batch 16, 8 KV heads x 128, context 32k, page 16, retention 0.25,
     heavy-tailed outlier channels.  Pack-on-append over the whole batch on the GPU; planes and scales
