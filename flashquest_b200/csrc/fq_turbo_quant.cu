@@ -242,7 +242,20 @@ __global__ void __launch_bounds__(128) turbo_quant_kernel(TurboParams p) {
 //    A value within 3e-5 (relative) of a midpoint, or that close to zero, takes the exact path (division, the
 //    reference's fp32 distances, first index on ties) -- the reference's decision can differ from the midpoint
 //    comparison only within a few fp32 roundings (1e-7 relative) of a midpoint;
-//  * a warp codes four consecutive tokens, so the row addresses are set up once.
+//  * a warp codes four consecutive tokens in a loop that is NOT unrolled (a short body keeps instruction fetch off
+//    the stall list), the next row requested while the current one is coded.
+// The reference's own decision (kernel/kv_quant.py:253-279): fp32 quotient, fp32 distances, first index on ties.
+// Out of line: it runs for a few values in 10^4 and should not lengthen the loop body.
+__device__ __noinline__ unsigned turbo_idx_exact(float v, float s) {
+    const float y = __fdiv_rn(v, s);
+    int k = y >= 0.2451f ? 4 : 0;
+    k += y >= (k ? 1.3439f : -0.7560f) ? 2 : 0;
+    k += y >= c_turbo_codebook[k + 1] ? 1 : 0;
+    k = min(k, 6);
+    const float d0 = fabsf(__fsub_rn(y, c_turbo_codebook[k])), d1 = fabsf(__fsub_rn(y, c_turbo_codebook[k + 1]));
+    return (unsigned)(k + (d1 < d0 ? 1 : 0));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) turbo_quant128_kernel(TurboParams p) {
     using P2 = typename Pk2<T>::type;
@@ -259,16 +272,11 @@ __global__ void __launch_bounds__(128) turbo_quant128_kernel(TurboParams p) {
     uint8_t* lsb = p.lsb + b * p.ls_sb + h * p.ls_sh;
     uint16_t* scale = p.scale + b * p.sc_sb + h * p.sc_sh;
 
-    uint2 raw[TPW];
-#pragma unroll
-    for (int i = 0; i < TPW; ++i) {
-        const int t = t0 + i;
-        raw[i] = make_uint2(0u, 0u);
-        if (i < nt) {
-            const T* row = t < p.n_head ? head + (int64_t)t * p.hd_ss : nw + (int64_t)(t - p.n_head) * p.nw_ss;
-            raw[i] = *reinterpret_cast<const uint2*>(row + 4 * lane);
-        }
-    }
+    auto load_row8 = [&](int t) -> uint2 {
+        const T* row = t < p.n_head ? head + (int64_t)t * p.hd_ss : nw + (int64_t)(t - p.n_head) * p.nw_ss;
+        return *reinterpret_cast<const uint2*>(row + 4 * lane);
+    };
+    uint2 raw_next = load_row8(t0);
     const uint32_t one = IS_HALF ? 0x3c003c00u : 0x3f803f80u, neg = one | 0x80008000u;
     const P2 pm = p2_from<P2>(IS_HALF ? 0xbc003c00u : 0xbf803f80u);              // (+1, -1)
     P2 sgn[5];                                                                   // (+-1, +-1): -1 in the upper lane of a pair
@@ -279,11 +287,12 @@ __global__ void __launch_bounds__(128) turbo_quant128_kernel(TurboParams p) {
     // midpoints between neighbouring codebook magnitudes
     constexpr float M0 = 0.50055f, M1 = 1.04995f, M2 = 1.7479f, GUARD = 3e-5f;
 
-#pragma unroll
-    for (int i = 0; i < TPW; ++i) {
-        if (i >= nt) break;
+#pragma unroll 1
+    for (int i = 0; i < nt; ++i) {
         const int t = t0 + i;
-        P2 x[2] = {p2_from<P2>(raw[i].x), p2_from<P2>(raw[i].y)};
+        const uint2 raw = raw_next;
+        if (i + 1 < nt) raw_next = load_row8(t + 1);       // in flight while this token is coded
+        P2 x[2] = {p2_from<P2>(raw.x), p2_from<P2>(raw.y)};
         // stride 1: (a, b) -> (a + b, a - b)
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -333,16 +342,7 @@ __global__ void __launch_bounds__(128) turbo_quant128_kernel(TurboParams p) {
             const int m = (av > th0 ? 1 : 0) + (av > th1 ? 1 : 0) + (av > th2 ? 1 : 0);
             idx[j] = (unsigned)(v[j] < 0.f ? 3 - m : 4 + m);
             const bool risky = fabsf(av - th0) < g0 || fabsf(av - th1) < g1 || fabsf(av - th2) < g2 || av < gz;
-            if (risky) {
-                // the reference's own decision (kernel/kv_quant.py:253-279): fp32 quotient, fp32 distances, first index on ties
-                const float y = __fdiv_rn(v[j], s);
-                int k = y >= 0.2451f ? 4 : 0;
-                k += y >= (k ? 1.3439f : -0.7560f) ? 2 : 0;
-                k += y >= c_turbo_codebook[k + 1] ? 1 : 0;
-                k = min(k, 6);
-                const float d0 = fabsf(__fsub_rn(y, c_turbo_codebook[k])), d1 = fabsf(__fsub_rn(y, c_turbo_codebook[k + 1]));
-                idx[j] = (unsigned)(k + (d1 < d0 ? 1 : 0));
-            }
+            if (risky) idx[j] = turbo_idx_exact(v[j], s);
         }
         unsigned l8 = 0, m4 = 0;
 #pragma unroll
