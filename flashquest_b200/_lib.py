@@ -38,6 +38,10 @@ _PROTOTYPES = {
     "fq_sparse_decode_int4": (I, [P, I, L, L, P, L, L, P, P, L, L, L, P, L, L, P, P, L, L,
                                   P, L, L, I, P, P, I, L, L, L, I,
                                   I, I, I, I, I, I, I, F, P, L, L, P, P, Z, I, P]),
+    "fq_sparse_decode_int4_counted": (I, [P, I, L, L, P, L, L, P, P, L, L, L, P, L, L, P, P, L, L,
+                                          P, L, L, I, P, P, P, I, L, L, L, I,
+                                          I, I, I, I, I, I, I, F, P, L, L, P, P, Z, I, P]),
+    "fq_build_compact_counted": (I, [P, L, L, I, P, L, I, P, P]),
 }
 
 

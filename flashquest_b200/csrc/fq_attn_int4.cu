@@ -53,6 +53,7 @@ struct AttnParams {
     const uint8_t* V_packed; int64_t vp_sb, vp_sh;
     const uint16_t *V_scale, *V_mn; int64_t vm_sb, vm_sh;
     const int32_t* compact; int64_t cp_sb, cp_sh; int bucket;
+    const int32_t* list_count;        // non-null: per (b,hq) row, only the first list_count[row] list entries can be valid
     const void *K_tail, *V_tail; int tail_dtype; int64_t tl_sb, tl_sh, tl_ss; int tail_len;
     int B, Hq, Hkv, S_kv, P, page, cpp_log2;
     float sm_scale;
@@ -232,10 +233,7 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     // Units are dealt round-robin to the splits (unit g belongs to split g % n_split), so a
     // list with its valid entries at the front and -1 padding behind them stays balanced.
     const int cpp_log2 = p.cpp_log2;                    // log2(chunks (units) per page)
-    const int total_units = p.bucket << cpp_log2;
-    const int n_units = split < total_units ? (total_units - split + p.n_split - 1) / p.n_split : 0;
     constexpr int units_per_iter = ATT_WARPS * 4;
-    const int n_iter = (n_units + units_per_iter - 1) / units_per_iter;
     const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
 
     if (tid == 0) {
@@ -248,6 +246,13 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     __syncthreads();
     pdl_wait();        // the page list (and, in the fused step, the freshly packed page) come from the previous kernels
     pdl_trigger();
+    // A list made from a selection mask is as wide as the page count; its builder says how many entries at the
+    // front are real, and the padding behind them is not walked at all.
+    int n_list = p.bucket;
+    if (p.list_count) n_list = max(0, min(n_list, __ldg(p.list_count + b * p.Hq + hq)));
+    const int total_units = n_list << cpp_log2;
+    const int n_units = split < total_units ? (total_units - split + p.n_split - 1) / p.n_split : 0;
+    const int n_iter = (n_units + units_per_iter - 1) / units_per_iter;
     // tokens in completed pages; read on the device when the launch must not depend on the sequence length
     int dyn_S = p.S_kv;
     if constexpr (DYN) {
@@ -750,7 +755,7 @@ int sparse_decode_int4_launch(
     int tail_len,
     int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
     void* O, int64_t o_sb, int64_t o_sh, float* lse,
-    void* workspace, size_t workspace_bytes, int n_split, void* stream, const DynPos& dp) {
+    void* workspace, size_t workspace_bytes, int n_split, void* stream, const DynPos& dp, const int32_t* list_count) {
     const char* fn = "fq_sparse_decode_int4";
     FQ_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && S_kv >= 0 && P >= 0 && bucket >= 0 && tail_len >= 0, FQ_ERR_ARG, "%s: bad sizes", fn);
     FQ_CHECK_ARG(B <= 65535 && Hq <= 65535, FQ_ERR_ARG, "%s: B and H_q must be <= 65535", fn);
@@ -788,6 +793,7 @@ int sparse_decode_int4_launch(
     p.V_scale = static_cast<const uint16_t*>(V_scale); p.V_mn = static_cast<const uint16_t*>(V_mn);
     p.vm_sb = vm_sb; p.vm_sh = vm_sh;
     p.compact = compact; p.cp_sb = cp_sb; p.cp_sh = cp_sh; p.bucket = have_pages ? bucket : 0;
+    p.list_count = list_count;
     p.K_tail = K_tail; p.V_tail = V_tail; p.tail_dtype = tail_dtype; p.tl_sb = tl_sb; p.tl_sh = tl_sh; p.tl_ss = tl_ss;
     p.tail_len = tail_len;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S_kv = S_kv; p.P = P; p.page = page;
@@ -844,6 +850,25 @@ extern "C" int fq_sparse_decode_int4(
         K_tail, V_tail, tail_dtype, tl_sb, tl_sh, tl_ss, tail_len,
         B, Hq, Hkv, S_kv, P, D, page, sm_scale, O, o_sb, o_sh, lse,
         workspace, workspace_bytes, n_split, stream, fq::DynPos{});
+}
+
+extern "C" int fq_sparse_decode_int4_counted(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket, const int32_t* list_count,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, float* lse,
+    void* workspace, size_t workspace_bytes, int n_split, void* stream) {
+    return fq::sparse_decode_int4_launch(
+        Q, q_dtype, q_sb, q_sh, K_packed, kp_sb, kp_sh, K_scale, K_mn, km_sb, km_sh, km_sp,
+        V_packed, vp_sb, vp_sh, V_scale, V_mn, vm_sb, vm_sh, compact, cp_sb, cp_sh, bucket,
+        K_tail, V_tail, tail_dtype, tl_sb, tl_sh, tl_ss, tail_len,
+        B, Hq, Hkv, S_kv, P, D, page, sm_scale, O, o_sb, o_sh, lse,
+        workspace, workspace_bytes, n_split, stream, fq::DynPos{}, list_count);
 }
 
 namespace fq {

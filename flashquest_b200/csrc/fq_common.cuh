@@ -100,7 +100,7 @@ int sparse_decode_int4_launch(
     const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
     int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
     void* O, int64_t o_sb, int64_t o_sh, float* lse,
-    void* workspace, size_t workspace_bytes, int n_split, void* stream, const DynPos& dp);
+    void* workspace, size_t workspace_bytes, int n_split, void* stream, const DynPos& dp, const int32_t* list_count = nullptr);
 
 // One layer of the graph-capturable step (append + score + select + attend with the sequence
 // length read from *pos) and the closing increment of the positions; defined in fq_decode_layer.cu.

@@ -407,7 +407,7 @@ __global__ void __launch_bounds__(FUSED_THREADS) score_select_kernel(ScoreSelect
 
 // mask (rows,P) u8 -> compact (rows,bucket) int32, descending ids, -1 padded.
 __global__ void build_compact_kernel(const uint8_t* __restrict__ mask, int64_t mk_sr, int P,
-                                     int32_t* __restrict__ compact, int64_t cp_sr, int bucket) {
+                                     int32_t* __restrict__ compact, int64_t cp_sr, int bucket, int32_t* __restrict__ count) {
     __shared__ SelShared sh;
     const int64_t r = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -434,6 +434,7 @@ __global__ void build_compact_kernel(const uint8_t* __restrict__ mask, int64_t m
         run += __popc(ballot);
     }
     for (int i = (int)total + tid; i < bucket; i += blockDim.x) crow[i] = -1;
+    if (count && tid == 0) count[r] = (int32_t)min(total, (unsigned)bucket);      // entries at the front of the list
 }
 
 static int select_threads(int P) { return P <= 512 ? 128 : (P <= 1024 ? 256 : (P <= 4096 ? 512 : 1024)); }
@@ -568,8 +569,8 @@ extern "C" int fq_select_pages(
                                    mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, stream, fq::DynPos{});
 }
 
-extern "C" int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
-                                int32_t* compact, int64_t cp_sr, int bucket, void* stream) {
+extern "C" int fq_build_compact_counted(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
+                                        int32_t* compact, int64_t cp_sr, int bucket, int32_t* count, void* stream) {
     using namespace fq;
     const char* fn = "fq_build_compact";
     FQ_CHECK_ARG(bucket >= 1, FQ_ERR_ARG, "%s: BUCKET_MAX must be >= 1, got %d", fn, bucket);
@@ -577,9 +578,14 @@ extern "C" int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows
     if (rows == 0) return FQ_OK;
     FQ_CHECK_ARG(rows <= 0x7fffffffLL, FQ_ERR_ARG, "%s: too many rows", fn);
     build_compact_kernel<<<(unsigned)rows, select_threads(P), 0, static_cast<cudaStream_t>(stream)>>>(
-        mask, mk_sr, P, compact, cp_sr, bucket);
+        mask, mk_sr, P, compact, cp_sr, bucket, count);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
+}
+
+extern "C" int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
+                                int32_t* compact, int64_t cp_sr, int bucket, void* stream) {
+    return fq_build_compact_counted(mask, mk_sr, rows, P, compact, cp_sr, bucket, nullptr, stream);
 }
 
 extern "C" int fq_score_select(

@@ -63,9 +63,10 @@ def select_pages_compact(scores, retention, num_sinks, window_pages, *, k_max_st
     return out[0] if len(out) == 1 else out
 
 
-def build_compact_selection(mask: torch.Tensor, BUCKET_MAX: int) -> torch.Tensor:
+def build_compact_selection(mask: torch.Tensor, BUCKET_MAX: int, *, return_count: bool = False):
     """(B,H,S_q,P) bool -> (B,H,S_q,BUCKET_MAX) int32: selected ids descending, -1 padded
-    (eager/selection.py:129)."""
+    (eager/selection.py:129).  return_count=True also returns (B,H,S_q) int32: how many entries at the
+    front of each list are real (what the counted attention call wants)."""
     if BUCKET_MAX < 1:
         raise ValueError(f"BUCKET_MAX must be >= 1, got {BUCKET_MAX}")
     if mask.dtype != torch.bool:
@@ -74,10 +75,11 @@ def build_compact_selection(mask: torch.Tensor, BUCKET_MAX: int) -> torch.Tensor
     B, H, S_q, P = mask.shape
     m = mask.contiguous().view(torch.uint8)
     out = torch.empty(B, H, S_q, BUCKET_MAX, dtype=torch.int32, device=mask.device)
+    count = torch.empty(B, H, S_q, dtype=torch.int32, device=mask.device) if return_count else None
     with torch.cuda.device(mask.device):
-        check(lib().fq_build_compact(ptr(m), P, B * H * S_q, P, ptr(out), BUCKET_MAX, BUCKET_MAX,
-                                     stream_ptr(mask.device)))
-    return out
+        check(lib().fq_build_compact_counted(ptr(m), P, B * H * S_q, P, ptr(out), BUCKET_MAX, BUCKET_MAX, ptr(count),
+                                             stream_ptr(mask.device)))
+    return (out, count) if return_count else out
 
 
 def score_select_compact(Q: torch.Tensor, K_scale: torch.Tensor, K_mn: torch.Tensor, retention, num_sinks: int,

@@ -67,8 +67,9 @@ def _packed(t: torch.Tensor, Dp):
 
 
 def sparse_decode_int4(Q, K_packed, K_scale, K_mn, V_packed, V_scale, V_mn, sel_3d, *, page_size, sm_scale,
-                       return_lse, K_partial=None, V_partial=None, n_split=None):
-    """Shared launcher: sel_3d is (B,H_q,bucket) int32 with -1 sentinels."""
+                       return_lse, K_partial=None, V_partial=None, n_split=None, list_count=None):
+    """Shared launcher: sel_3d is (B,H_q,bucket) int32 with -1 sentinels; list_count (B*H_q int32, contiguous)
+    bounds the entries walked per row when the real ones sit at the front."""
     B, H_q, S_q, D = Q.shape
     Bk, H_kv, S_kv, Dp = K_packed.shape
     P = K_scale.shape[2]
@@ -115,13 +116,16 @@ def sparse_decode_int4(Q, K_packed, K_scale, K_mn, V_packed, V_scale, V_mn, sel_
         if n_split > 1:
             ws_bytes = lib().fq_sparse_decode_workspace_bytes(B, H_q, D, n_split)
             ws = _workspace(dev, ws_bytes, B * H_q)
-        check(lib().fq_sparse_decode_int4(
+        if list_count is not None:
+            require_cuda(list_count)
+            assert list_count.dtype == torch.int32 and list_count.numel() == B * H_q and list_count.is_contiguous()
+        check(lib().fq_sparse_decode_int4_counted(
             ptr(Q_2d), dtype_code(Q_2d), Q_2d.stride(0), Q_2d.stride(1),
             ptr(K_packed), K_packed.stride(0), K_packed.stride(1),
             ptr(K_scale), ptr(K_mn), K_scale.stride(0), K_scale.stride(1), K_scale.stride(2),
             ptr(V_packed), V_packed.stride(0), V_packed.stride(1),
             ptr(V_scale), ptr(V_mn), V_scale.stride(0), V_scale.stride(1),
-            ptr(sel), sel.stride(0), sel.stride(1), bucket,
+            ptr(sel), sel.stride(0), sel.stride(1), bucket, ptr(list_count),
             ptr(K_partial), ptr(V_partial), tail_code, *tl, tail_len,
             B, H_q, H_kv, S_kv, P, D, int(page_size), float(sm_scale),
             ptr(O_2d), O_2d.stride(0), O_2d.stride(1), ptr(L),

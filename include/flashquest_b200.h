@@ -137,6 +137,11 @@ int fq_select_pages(
  * mask (rows,P) u8 with row stride mk_sr; compact (rows,bucket) int32 with stride cp_sr. */
 int fq_build_compact(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
                      int32_t* compact, int64_t cp_sr, int bucket, void* stream);
+/* The same, and count (rows) int32 receives min(selected pages, bucket) per row: the number of real entries at
+ * the front of the row's list (or NULL).  Hand it to fq_sparse_decode_int4_counted so that the padding of a list as
+ * wide as the page count -- what a mask-driven call produces -- is not walked. */
+int fq_build_compact_counted(const uint8_t* mask, int64_t mk_sr, int64_t rows, int P,
+                             int32_t* compact, int64_t cp_sr, int bucket, int32_t* count, void* stream);
 
 /* Page scores, top-k and compact index in ONE launch: fq_page_scores_int4 (levels 15) or
  * fq_page_scores_int8 (levels 255) followed by fq_select_pages with a compact list and no mask, i.e.
@@ -248,6 +253,22 @@ int fq_sparse_decode_int4(
     const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
     const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
     const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss,
+    int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, int64_t o_sb, int64_t o_sh, float* lse,
+    void* workspace, size_t workspace_bytes, int n_split, void* stream);
+/* fq_sparse_decode_int4 for a list whose real entries sit at the front: list_count (B*Hq) int32, contiguous, gives per
+ * (b,hq) row how many leading entries to walk (clamped to [0, bucket]); NULL = all of them.  This is how
+ * flash_attn_sparse_int4_fwd (kernel/sparse_int4_fwd.py:160-248, the bool-mask form) runs: fq_build_compact_counted,
+ * then this call. */
+int fq_sparse_decode_int4_counted(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_packed, int64_t kp_sb, int64_t kp_sh,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const uint8_t* V_packed, int64_t vp_sb, int64_t vp_sh,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket, const int32_t* list_count,
     const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss,
     int tail_len,
     int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,

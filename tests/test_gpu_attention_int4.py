@@ -262,3 +262,40 @@ def test_many_ctas_with_refills_and_empty_trailing_units(att):
             assert (lse - outs[0][1]).abs().max() <= 1e-4
         Ow, lw = oracle.sparse_attn_int4(Q[:1, :3].cpu(), *cpu, selected_page_ids=comp[:1, :3].cpu(), page_size=page)
         _close(outs[0][0][:1, :3], outs[0][1][:1, :3], Ow, lw, torch.float16)
+
+
+def test_counted_list_walks_only_the_front(att):
+    """The mask form builds a list as wide as the page count plus the number of real entries per row; the
+    attention call walks only that many.  The count equals the row's selected pages, the result equals the
+    tight-list result bit for bit at one split, and a smaller count drops exactly the entries behind it
+    (checked against the oracle with those pages removed from the mask)."""
+    from flashquest_b200.eager.selection import build_compact_selection
+    from flashquest_b200.kernel.sparse_int4_fwd_compact import sparse_decode_int4
+    B, Hq, Hkv, S, D, page, dtype = 2, 6, 2, 2048, 128, 16, torch.float16
+    Q, kv, mask = _case(41, B, Hq, Hkv, S, D, page, dtype, retention=0.2)
+    mask[1, 3] = False                                     # a row with nothing selected
+    dev = [t.cuda() for t in kv]
+    wide, count = build_compact_selection(mask.cuda(), S // page, return_count=True)
+    assert torch.equal(count.cpu().long(), mask.sum(-1))
+    assert torch.equal(wide.cpu(), oracle.build_compact_selection(mask, S // page))
+    tight = oracle.build_compact_selection(mask, int(mask.sum(-1).max())).cuda()
+    O1, l1 = att.compact(Q.cuda(), *dev, selected_page_ids=tight, page_size=page, n_split=1)
+    O2, l2 = sparse_decode_int4(Q.cuda(), *dev, wide.squeeze(2), page_size=page, sm_scale=None, return_lse=True,
+                                n_split=1, list_count=count)
+    assert torch.equal(O1, O2) and torch.equal(l1, l2)
+    O3, l3 = att.mask(Q.cuda(), *dev, selection_mask=mask.cuda(), page_size=page)          # default split count
+    Ow, lw = oracle.sparse_attn_int4(Q, *kv, selection_mask=mask, page_size=page)
+    _close(O3, l3, Ow, lw, dtype)
+    # half the count: the list is descending, so the lowest page ids of every row fall away
+    half = (count // 2).contiguous()
+    m2 = torch.zeros_like(mask)
+    ids = wide.cpu().long()
+    for b in range(B):
+        for h in range(Hq):
+            keep = ids[b, h, 0, :int(half[b, h, 0])]
+            m2[b, h, 0, keep] = True
+    O4, l4 = sparse_decode_int4(Q.cuda(), *dev, wide.squeeze(2), page_size=page, sm_scale=None, return_lse=True,
+                                list_count=half)
+    Ow2, lw2 = oracle.sparse_attn_int4(Q, *kv, selection_mask=m2, page_size=page)
+    _close(O4, l4, Ow2, lw2, dtype)
+    assert att.status() == 0
