@@ -633,7 +633,7 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     float* mw = reinterpret_cast<float*>(smem);            // [n_split] max, then weight
     float* lw = mw + p.n_split;                             // [n_split] denominators
     __shared__ float s_red[ATT_WARPS + 1];
-    constexpr int PRE = 16;    // partial accumulators requested up front, with the maxima
+    constexpr int PRE = 20;    // partial accumulators requested up front, with the maxima
     float pre[PRE];
     if (tid < D) {
 #pragma unroll
