@@ -36,9 +36,10 @@ struct SelShared {
 
 // Exclusive scan of one value per warp (value valid on every lane of the warp).
 // Returns this warp's exclusive prefix; *total receives the block total.  Uses sh.warp_tot.
-__device__ __forceinline__ unsigned block_warp_scan(unsigned warp_val, SelShared& sh, unsigned* total) {
+// lead_sync = false where a barrier already separates this call from the last reader of sh.warp_tot.
+__device__ __forceinline__ unsigned block_warp_scan(unsigned warp_val, SelShared& sh, unsigned* total, bool lead_sync = true) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    __syncthreads();
+    if (lead_sync) __syncthreads();
     if (lane == 0) sh.warp_tot[warp] = warp_val;
     __syncthreads();
     unsigned v = lane < nwarps ? sh.warp_tot[lane] : 0u;
@@ -65,6 +66,10 @@ __device__ __forceinline__ void select_row(
     auto key_at = [&](int i) -> unsigned { return SMEM_KEYS ? s_keys[i] : score_key(row[i]); };
 
     // ---- load the row once; block min / max of the keys ----
+    // (the histogram of the first round and the candidate counter are cleared while the loads are in flight; the
+    // barrier behind the min / max exchange covers them)
+    for (int i = tid; i < SEL_BINS; i += T_) sh.hist[i] = 0u;
+    if (tid == 0) sh.ncand = 0u;
     unsigned kmin = 0xffffffffu, kmax = 0u;
 #pragma unroll 4
     for (int i = tid; i < P; i += T_) {
@@ -103,8 +108,6 @@ __device__ __forceinline__ void select_row(
             if (width == 0u) { T = lo; need_eq = remaining; eq_total = in_range; break; }
             if (in_range <= (unsigned)SEL_CAND_MAX) {
                 // ---- few candidates left: rank them directly ----
-                if (tid == 0) sh.ncand = 0u;
-                __syncthreads();
                 for (int i = tid; i < P; i += T_) {
                     const unsigned key = key_at(i);
                     if (key >= lo && key <= hi) sh.cand[atomicAdd(&sh.ncand, 1u)] = key;
@@ -127,8 +130,10 @@ __device__ __forceinline__ void select_row(
             }
             const int nb = 32 - __clz(width);
             const int shift = nb > 11 ? nb - 11 : 0;           // (width >> shift) <= 2047
-            for (int i = tid; i < SEL_BINS; i += T_) sh.hist[i] = 0u;
-            __syncthreads();
+            if (round > 0) {
+                for (int i = tid; i < SEL_BINS; i += T_) sh.hist[i] = 0u;
+                __syncthreads();
+            }
             for (int i = tid; i < P; i += T_) {
                 const unsigned key = key_at(i);
                 if (key >= lo && key <= hi) atomicAdd(&sh.hist[(key - lo) >> shift], 1u);
@@ -144,7 +149,7 @@ __device__ __forceinline__ void select_row(
                 if (lane >= off) incl += n;
             }
             unsigned tot_unused;
-            const unsigned wprefix = block_warp_scan(__shfl_sync(0xffffffffu, incl, 31), sh, &tot_unused);
+            const unsigned wprefix = block_warp_scan(__shfl_sync(0xffffffffu, incl, 31), sh, &tot_unused, false);   // the barrier above
             unsigned run = wprefix + incl - own;               // keys in bins above this thread's bins
             if (run < remaining && remaining <= run + own) {
                 for (int j = 0; j < bpt; ++j) {
@@ -220,7 +225,7 @@ __device__ __forceinline__ void select_row(
         }
     }
     unsigned total = 0u;
-    const unsigned sel_before = block_warp_scan(sel_cnt, sh, &total);
+    const unsigned sel_before = block_warp_scan(sel_cnt, sh, &total, rank_ties);      // every earlier use of the scan is behind a barrier, except the tie count's
 
     // pass C: write mask and compact list (descending page id: position = total-1-ascending rank)
     {
