@@ -61,6 +61,7 @@ struct AttnParams {
     float* lse;
     int* tickets; float* partials; int n_split;
     const int* pos; int pos_new;      // non-null: S_kv, P and tail_len are derived from *pos on the device (see DynPos)
+    int pos_early;                    // *pos may be read before the dependency wait (DynPos::early)
     int* status;
 };
 
@@ -243,9 +244,16 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    int pos_v = 0;
+    if constexpr (DYN) {
+        if (p.pos_early) pos_v = __ldcg(p.pos);        // in flight during the barrier and the wait
+    }
     __syncthreads();
     pdl_wait();        // the page list (and, in the fused step, the freshly packed page) come from the previous kernels
     pdl_trigger();
+    if constexpr (DYN) {
+        if (!p.pos_early) pos_v = *p.pos;
+    }
     // A list made from a selection mask is as wide as the page count; its builder says how many entries at the
     // front are real, and the padding behind them is not walked at all.
     int n_list = p.bucket;
@@ -256,7 +264,7 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     // tokens in completed pages; read on the device when the launch must not depend on the sequence length
     int dyn_S = p.S_kv;
     if constexpr (DYN) {
-        const int now = *p.pos + p.pos_new;
+        const int now = pos_v + p.pos_new;
         dyn_S = now - now % p.page;
     }
 
@@ -536,7 +544,7 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     float tm = -INFINITY, tl = 0.f, tacc[TD];
 #pragma unroll
     for (int j = 0; j < TD; ++j) tacc[j] = 0.f;
-    const int dyn_tail = DYN ? (*p.pos + p.pos_new) % p.page : p.tail_len;
+    const int dyn_tail = DYN ? (pos_v + p.pos_new) % p.page : p.tail_len;
     if (split == 0 && dyn_tail > 0 && !is_producer) {
         float qt[TD];
         const QT* qp = static_cast<const QT*>(p.Q) + b * p.q_sb + hq * p.q_sh + TD * lane;
@@ -807,7 +815,7 @@ int sparse_decode_int4_launch(
     if (n_split > p.bucket) n_split = p.bucket > 0 ? p.bucket : 1;
     p.n_split = n_split;
     p.tickets = nullptr; p.partials = nullptr;
-    p.pos = dp.pos; p.pos_new = dp.n_new;
+    p.pos = dp.pos; p.pos_new = dp.n_new; p.pos_early = dp.early ? 1 : 0;
     p.status = device_status_ptr();
     if (p.status == nullptr) return FQ_ERR_CUDA;
     if (n_split > 1) {

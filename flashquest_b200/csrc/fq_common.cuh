@@ -62,7 +62,11 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 // `pos` derives page count, tail length and append offsets from *pos (tokens cached before this
 // step) instead of from its host-side arguments, which in that mode only size the grid (maximum
 // values).  The public entry points pass an empty record.
-struct DynPos { const int* pos = nullptr; int n_new = 0; int page = 1; int max_tokens = 0; };
+// `early`: the kernel may read *pos BEFORE its dependency wait, overlapping the load with the wait.  Safe only for a
+// kernel at least two launches behind the one that last wrote *pos: a dependent launch starts no earlier than its
+// predecessor's own wait has returned, i.e. after the writer has completed.  The decode layer sets it for scores,
+// selection and attention, which always follow the append launch; the append itself reads after its wait.
+struct DynPos { const int* pos = nullptr; int n_new = 0; int page = 1; int max_tokens = 0; bool early = false; };
 
 // Launch functions behind the public entry points of the same names, with the position record explicit.
 int quantize_kv_int4_launch(

@@ -131,6 +131,8 @@ int decode_layer_int4_dyn(const fq_int4_cache* c, int l, const int* pos, const v
     char* Kt = static_cast<char*>(c->K_partial) + l * c->pt_sl * kv_esz;
     char* Vt = static_cast<char*>(c->V_partial) + l * c->pt_sl * kv_esz;
     // host-side sizes are the maxima (they size grids and pass validation); the kernels read *pos
+    DynPos dp_early = dp;          // scores, selection and attention come at least two launches after any writer of *pos
+    dp_early.early = true;
     int rc = FQ_OK;
     if (append)
         rc = quantize_kv_int4_launch(Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, page - n_new, Kn, Vn, nw_sb, nw_sh, nw_ss, n_new,
@@ -139,11 +141,11 @@ int decode_layer_int4_dyn(const fq_int4_cache* c, int l, const int* pos, const v
                                      Vs, Vm, c->vm_sb, c->vm_sh, 1, Kt, Vt, c->pt_sb, c->pt_sh, c->pt_ss, stream, dp);
     if (rc != FQ_OK) return rc;
     rc = page_scores_int4_launch(Ql, q_dtype, q_sb, q_sh, Ks, Km, c->km_sb, c->km_sh, c->km_sp, B, Hq, Hkv, P_max, D,
-                                 sc, (int64_t)Hq * P_max, P_max, stream, dp);
+                                 sc, (int64_t)Hq * P_max, P_max, stream, dp_early);
     if (rc != FQ_OK) return rc;
     rc = select_pages_launch(sc, (int64_t)Hq * P_max, P_max, B, Hq, P_max, pl->retention_per_head, pl->retention,
                              pl->k_max_static < P_max ? pl->k_max_static : P_max, pl->sinks, pl->window, nullptr, 0, 0,
-                             cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket, nullptr, stream, dp);
+                             cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket, nullptr, stream, dp_early);
     if (rc != FQ_OK) return rc;
     const int n_split = pl->n_split > 0 ? pl->n_split : fq_sparse_decode_default_splits(B, Hq, pl->bucket, page);
     return sparse_decode_int4_launch(
@@ -152,7 +154,7 @@ int decode_layer_int4_dyn(const fq_int4_cache* c, int l, const int* pos, const v
         cp, (int64_t)Hq * pl->bucket, pl->bucket, pl->bucket,
         Kt, Vt, c->kv_dtype, c->pt_sb, c->pt_sh, c->pt_ss, page - 1,
         B, Hq, Hkv, P_max * page, P_max, D, page, pl->sm_scale,
-        O, (int64_t)Hq * D, D, lse, workspace, workspace_bytes, n_split, stream, dp);
+        O, (int64_t)Hq * D, D, lse, workspace, workspace_bytes, n_split, stream, dp_early);
 }
 }  // namespace fq
 

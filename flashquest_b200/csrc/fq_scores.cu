@@ -24,16 +24,21 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
     const uint16_t* __restrict__ K_scale, const uint16_t* __restrict__ K_mn,
     int64_t km_sb, int64_t km_sh, int64_t km_sp,
     int Hq, int Hkv, int P, int D, int head_off,
-    float* __restrict__ scores, int64_t sc_sb, int64_t sc_sh, const int* __restrict__ pos, int pos_new, int pos_page, float levels) {
+    float* __restrict__ scores, int64_t sc_sb, int64_t sc_sh, const int* __restrict__ pos, int pos_new, int pos_page, int pos_early, float levels) {
     const int b = blockIdx.z, hkv = blockIdx.y;
     const int n_rep = Hq / Hkv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int l = lane & 7, qw = lane >> 3;
     const int n_chunks = D >> 3;
     const int nr = min(NR, n_rep - head_off);   // heads actually present in this pass
+    int pos_v = 0;
+    if (pos && pos_early) pos_v = __ldcg(pos);             // in flight during the wait (see DynPos::early)
     pdl_wait();        // Q and the newest metadata row come from the kernels before this one
     pdl_trigger();
-    if (pos) P = min(P, (*pos + pos_new) / pos_page);      // completed pages after this step's append
+    if (pos) {
+        if (!pos_early) pos_v = *pos;
+        P = min(P, (pos_v + pos_new) / pos_page);          // completed pages after this step's append
+    }
 
     // Metadata loads of every page this quarter warp will score are issued first, the q loads
     // after them, so the two global-memory latencies overlap instead of adding up.
@@ -65,7 +70,7 @@ static void launch_scores(int CH, dim3 grid, cudaStream_t st, const void* Q, int
     launch_k(PDL_SCORES, page_scores_kernel<QT, NR, CHV>, grid, dim3(SCORE_THREADS), 0, st,                        \
              static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),             \
              static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh,        \
-             dp.pos, dp.n_new, dp.page, levels)
+             dp.pos, dp.n_new, dp.page, dp.early ? 1 : 0, levels)
     if (CH == 1) FQ_LAUNCH_SC(1);
     else if (CH == 2) FQ_LAUNCH_SC(2);
     else FQ_LAUNCH_SC(4);

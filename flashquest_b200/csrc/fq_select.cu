@@ -258,14 +258,17 @@ __global__ void select_pages_kernel(
     const float* __restrict__ retention_per_head, float retention, int k_max, int sinks, int window,
     uint8_t* __restrict__ mask, int64_t mk_sb, int64_t mk_sh,
     int32_t* __restrict__ compact, int64_t cp_sb, int64_t cp_sh, int bucket,
-    int32_t* __restrict__ count, const int* __restrict__ pos, int pos_new, int pos_page) {
+    int32_t* __restrict__ count, const int* __restrict__ pos, int pos_new, int pos_page, int pos_early) {
     __shared__ SelShared sh;
     extern __shared__ unsigned s_keys[];                        // [P] keys (SMEM_KEYS only)
     const int b = blockIdx.y, h = blockIdx.x;
+    int pos_v = 0;
+    if (pos && pos_early) pos_v = __ldcg(pos);                  // in flight during the wait (see DynPos::early)
     pdl_wait();        // the scores come from the previous kernel
     pdl_trigger();
     if (pos) {         // row length read on the device: completed pages after this step's append
-        P = min(P, (*pos + pos_new) / pos_page);
+        if (!pos_early) pos_v = *pos;
+        P = min(P, (pos_v + pos_new) / pos_page);
         k_max = min(k_max, P);
     }
     select_row<SMEM_KEYS, false>(sh, s_keys, scores + b * sc_sb + h * sc_sh, b, h, H, P, retention_per_head, retention, k_max,
@@ -469,11 +472,11 @@ int select_pages_launch(
         }
         launch_k(PDL_SELECT, select_pages_kernel<true>, grid, dim3(select_threads(P)), smem, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
-            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dp.pos, dp.n_new, dp.page);
+            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dp.pos, dp.n_new, dp.page, dp.early ? 1 : 0);
     } else {
         launch_k(PDL_SELECT, select_pages_kernel<false>, grid, dim3(select_threads(P)), 0, st,
             scores, sc_sb, sc_sh, H, P, retention_per_head, retention, k_max, sinks, window,
-            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dp.pos, dp.n_new, dp.page);
+            mask, mk_sb, mk_sh, compact, cp_sb, cp_sh, bucket, count, dp.pos, dp.n_new, dp.page, dp.early ? 1 : 0);
     }
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;

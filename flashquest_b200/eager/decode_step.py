@@ -184,12 +184,11 @@ class QuestDecodeInt4:
                 after()
 
         def replay():
-            for li in range(Ln):
-                if c._seen_tokens[li] + n_new > c.max_seq_len:
-                    raise RuntimeError(f"PersistentInt4KVCache: seen+new={c._seen_tokens[li] + n_new} exceeds max_seq_len={c.max_seq_len}")
+            seen = max(c._seen_tokens[:Ln])
+            if seen + n_new > c.max_seq_len:
+                raise RuntimeError(f"PersistentInt4KVCache: seen+new={seen + n_new} exceeds max_seq_len={c.max_seq_len}")
             graph.replay()
-            for li in range(Ln):
-                c._seen_tokens[li] += n_new
+            c._seen_tokens[:Ln] = [t + n_new for t in c._seen_tokens[:Ln]]
             self.launches += 3 * Ln + 2          # one append for all layers, 3 per layer, the position update
             return self.O.unsqueeze(3), self.lse.unsqueeze(3)
 
