@@ -629,9 +629,11 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) sparse_decode_in
     __syncthreads();           // the CTA's stores are ordered before thread 0's fence below
     __shared__ int s_ticket;
     if (tid == 0) {
-        __threadfence();       // one device-scope fence per CTA (cumulative over the barrier)
-        s_ticket = atomicAdd(&p.tickets[row], 1);
-        __threadfence();
+        // one device-scope release + acquire per CTA, carried by the ticket itself (cumulative over the barrier above;
+        // the barrier below hands what the last CTA acquired to its other threads)
+        int t;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(t) : "l"(p.tickets + row) : "memory");
+        s_ticket = t;
     }
     __syncthreads();
     if (s_ticket != p.n_split - 1) return;

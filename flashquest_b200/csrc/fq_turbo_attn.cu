@@ -367,9 +367,10 @@ __global__ void __launch_bounds__(TQ_THREADS, 3) sparse_decode_turbo_kernel(Turb
     if (tid == 0) { part[0] = m_cta; part[1] = l_cta; }
     __syncthreads();
     if (tid == 0) {
-        __threadfence();
-        s_ticket = atomicAdd(&p.tickets[row], 1);
-        __threadfence();
+        // one device-scope release + acquire per CTA, carried by the ticket itself (cumulative over the barrier above)
+        int t;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(t) : "l"(p.tickets + row) : "memory");
+        s_ticket = t;
     }
     __syncthreads();
     if (s_ticket != p.n_split - 1) return;
