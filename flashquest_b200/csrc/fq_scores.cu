@@ -62,15 +62,69 @@ __global__ void __launch_bounds__(SCORE_THREADS) page_scores_kernel(
     }
 }
 
+// page_scores_kernel for the decode step, where the position may be read before the dependency wait
+// (DynPos::early): the rows of the pages completed before this step -- nothing in flight writes them -- are
+// requested before the wait as well, so the CTA spends the end of the previous kernel fetching instead of waiting.
+template <typename QT, int NR, int CH>
+__global__ void __launch_bounds__(SCORE_THREADS) page_scores_early_kernel(
+    const QT* __restrict__ Q, int64_t q_sb, int64_t q_sh,
+    const uint16_t* __restrict__ K_scale, const uint16_t* __restrict__ K_mn,
+    int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    int Hq, int Hkv, int P, int D, int head_off,
+    float* __restrict__ scores, int64_t sc_sb, int64_t sc_sh, const int* __restrict__ pos, int pos_new, int pos_page, float levels) {
+    const int b = blockIdx.z, hkv = blockIdx.y;
+    const int n_rep = Hq / Hkv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int l = lane & 7, qw = lane >> 3;
+    const int n_chunks = D >> 3;
+    const int nr = min(NR, n_rep - head_off);   // heads actually present in this pass
+    constexpr int ITERS = SCORE_PAGES_PER_CTA / 16;
+    const int p_base = blockIdx.x * SCORE_PAGES_PER_CTA;
+    const uint16_t* sc_base = K_scale + b * km_sb + hkv * km_sh;
+    const uint16_t* mn_base = K_mn + b * km_sb + hkv * km_sh;
+    uint4 m4[ITERS][CH], s4[ITERS][CH];
+    const int pos_v = __ldcg(pos);
+    const int P_old = min(P, pos_v / pos_page);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int p = p_base + it * 16 + warp * 4 + qw;
+        if (p < P_old) score_load_meta<CH>(sc_base, mn_base, km_sp, p, true, l, n_chunks, m4[it], s4[it]);
+    }
+    pdl_wait();        // Q and the newest metadata row come from the kernels before this one
+    pdl_trigger();
+    P = min(P, (pos_v + pos_new) / pos_page);              // completed pages after this step's append
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int p = p_base + it * 16 + warp * 4 + qw;
+        if (p >= P_old) score_load_meta<CH>(sc_base, mn_base, km_sp, p, p < P, l, n_chunks, m4[it], s4[it]);
+    }
+    float q[NR][CH][8];
+    score_load_q<QT, NR, CH>(Q + b * q_sb, q_sh, hkv * n_rep + head_off, nr, l, n_chunks, q);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int p = p_base + it * 16 + warp * 4 + qw;
+        const float v = score_page<NR, CH>(q, m4[it], s4[it], l, levels);
+        if (p < P && l < nr) scores[b * sc_sb + (hkv * n_rep + head_off + l) * sc_sh + p] = v;
+    }
+}
+
 template <typename QT, int NR>
 static void launch_scores(int CH, dim3 grid, cudaStream_t st, const void* Q, int64_t q_sb, int64_t q_sh,
                           const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
                           int Hq, int Hkv, int P, int D, int head_off, float* scores, int64_t sc_sb, int64_t sc_sh, const DynPos& dp, float levels) {
 #define FQ_LAUNCH_SC(CHV)                                                                              \
-    launch_k(PDL_SCORES, page_scores_kernel<QT, NR, CHV>, grid, dim3(SCORE_THREADS), 0, st,                        \
-             static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),             \
-             static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh,        \
-             dp.pos, dp.n_new, dp.page, dp.early ? 1 : 0, levels)
+    do {                                                                                               \
+        if (dp.pos != nullptr && dp.early)                                                             \
+            launch_k(PDL_SCORES, page_scores_early_kernel<QT, NR, CHV>, grid, dim3(SCORE_THREADS), 0, st,              \
+                     static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),     \
+                     static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh, \
+                     dp.pos, dp.n_new, dp.page, levels);                                               \
+        else                                                                                           \
+            launch_k(PDL_SCORES, page_scores_kernel<QT, NR, CHV>, grid, dim3(SCORE_THREADS), 0, st,    \
+                     static_cast<const QT*>(Q), q_sb, q_sh, static_cast<const uint16_t*>(K_scale),     \
+                     static_cast<const uint16_t*>(K_mn), km_sb, km_sh, km_sp, Hq, Hkv, P, D, head_off, scores, sc_sb, sc_sh, \
+                     dp.pos, dp.n_new, dp.page, 0, levels);                                            \
+    } while (0)
     if (CH == 1) FQ_LAUNCH_SC(1);
     else if (CH == 2) FQ_LAUNCH_SC(2);
     else FQ_LAUNCH_SC(4);
