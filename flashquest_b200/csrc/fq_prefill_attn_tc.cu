@@ -93,6 +93,17 @@ __device__ __forceinline__ void pt_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) 
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void pt_tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float pt_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -121,8 +132,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
     uint64_t* v_empty = bars + 7;            // [stages] O_tile = P V of the tile has completed
     uint64_t* s_ready = bars + 9;            // [2] S buffer written by the tensor core
     uint64_t* p_ready = bars + 11;           // [2] P buffer written (and the S buffer read) by the softmax threads
-    uint64_t* o_ready = bars + 13;           // [2] O buffer written by the tensor core
-    uint64_t* o_taken = bars + 15;           // [2] O buffer read by the softmax threads
+    uint64_t* pv_done = bars + 13;           // [2] O += P V of a tile has completed: its P buffer is free, O is up to date
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);      // a wait gave up somewhere: nobody waits any more
     __shared__ float s_xch[2 * PT_BM];                                         // [column half][row]: row maxima / denominators
@@ -139,8 +149,8 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
         pt_mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
             pt_mbar_init(&k_full[s], 1); pt_mbar_init(&k_empty[s], 1); pt_mbar_init(&v_full[s], 1); pt_mbar_init(&v_empty[s], 1);
-            pt_mbar_init(&s_ready[s], 1); pt_mbar_init(&o_ready[s], 1);
-            pt_mbar_init(&p_ready[s], PT_SOFTMAX_WARPS * 32); pt_mbar_init(&o_taken[s], PT_SOFTMAX_WARPS * 32);
+            pt_mbar_init(&s_ready[s], 1); pt_mbar_init(&pv_done[s], 1);
+            pt_mbar_init(&p_ready[s], PT_SOFTMAX_WARPS * 32);
         }
         *s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -206,18 +216,18 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
             for (int j = 0; j < n_tiles && !failed; ++j) {
                 const int s = j & 1;
                 const unsigned ph = (unsigned)(j >> 1) & 1u;
+                // p_ready also says that the softmax threads have rescaled O where a row's maximum moved
                 if (!pt_wait(&p_ready[s], ph) || !pt_wait(&v_full[s], ph)) { failed = true; break; }
-                if (j >= 2 && !pt_wait(&o_taken[s], (unsigned)((j >> 1) - 1) & 1u)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = pt_smem(sV + s * PT_TILE_BYTES), p_addr = pt_smem(sP + s * PT_TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < PT_BN / 16; ++kk) {
                     // A = P, K-major over the keys; B = V, MN-major: 64 channels x 8 keys = one atom, 16 keys = 2 KiB, channel halves 16 KiB apart
                     const uint32_t offp = (uint32_t)(kk >> 2) * PT_HALF_BYTES + (uint32_t)(kk & 3) * 32;
-                    pt_mma(tmem_base + (uint32_t)(2 * PT_BN + s * PT_D), pt_desc(p_addr + offp, 16, 1024),
-                           pt_desc(v_addr + (uint32_t)kk * 2048, PT_HALF_BYTES, 1024), idesc_o, kk != 0 ? 1u : 0u);
+                    pt_mma(tmem_base + (uint32_t)(2 * PT_BN), pt_desc(p_addr + offp, 16, 1024),
+                           pt_desc(v_addr + (uint32_t)kk * 2048, PT_HALF_BYTES, 1024), idesc_o, (kk != 0 || j != 0) ? 1u : 0u);
                 }
-                pt_commit(&o_ready[s]);
+                pt_commit(&pv_done[s]);
                 pt_commit(&v_empty[s]);
                 // S two tiles ahead: its buffer has just been released by p_ready of tile j
                 if (j + 2 < n_tiles && !issue_s(j + 2)) { failed = true; break; }
@@ -230,18 +240,19 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
         const int r = lq * 32 + lane;             // query row inside the tile
         const int qi = q0 + r;                    // global query index
         const uint32_t lane_addr = tmem_base + ((uint32_t)(lq * 32) << 16);
-        float acc[PT_D / 2];
-#pragma unroll
-        for (int i = 0; i < PT_D / 2; ++i) acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        // m_used is the maximum the row's probabilities and O are currently expressed against; it follows the true
+        // running maximum only when that has moved by more than 8 (in base 2), so P stays below 2^8 and O in tensor
+        // memory is rescaled rarely (the first few tiles of a row) instead of being read back after every tile
+        float m_used = -INFINITY, l_run = 0.f;
+        constexpr float PT_LAZY = 8.0f;
         // a wait that gives up is remembered by everybody: the loop then runs on without waiting, so that the
-        // named barrier below still sees all 256 threads
+        // named barriers below still see all 256 threads
         auto wait_ok = [&](uint64_t* bar, unsigned parity) {
             if (*s_fail) return;
             if (!pt_wait(bar, parity)) { failed = true; *s_fail = 1; }
         };
-        // softmax of key tile j: reads S[j & 1], writes P[j & 1]; returns the factor the row's earlier sums shrink by
-        auto softmax_tile = [&](int j) -> float {
+        const uint32_t o_addr = lane_addr + (uint32_t)(2 * PT_BN + hf * 64);      // this thread's half row of O
+        for (int j = 0; j < n_tiles; ++j) {
             const int sb = j & 1;
             wait_ok(&s_ready[sb], (unsigned)(j >> 1) & 1u);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -269,9 +280,31 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
             asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
             m_tile = fmaxf(m_tile, s_xch[(hf ^ 1) * PT_BM + r]);
             asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
-            const float m_new = fmaxf(m_run, m_tile * p.scale_log2);
-            const float alpha = m_new == -INFINITY ? 1.f : pt_ex2(m_run - m_new);
-            const float m_sub = m_new == -INFINITY ? 0.f : m_new;
+            // both threads of a row see the same m_tile and m_used, so they take the same decision
+            const float m_true = m_tile * p.scale_log2;
+            float alpha = 1.f;
+            if (m_true > m_used + PT_LAZY || m_used == -INFINITY) {
+                const float m_new = fmaxf(m_used, m_true);
+                alpha = (m_used == -INFINITY) ? (m_new == -INFINITY ? 1.f : 0.f) : pt_ex2(m_used - m_new);
+                m_used = m_new;
+            }
+            // rescale this thread's half row of O where the reference maximum moved (warp-collective tensor-memory
+            // access: the whole warp goes when one lane must); O is complete only once P V of tile j-1 is
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                wait_ok(&pv_done[(j - 1) & 1], (unsigned)((j - 1) >> 1) & 1u);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t o[32];
+                    pt_tmem_ld32(o_addr + (uint32_t)(c * 32), o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    pt_tmem_st32(o_addr + (uint32_t)(c * 32), o);
+                }
+            }
+            const float m_sub = m_used == -INFINITY ? 0.f : m_used;
+            // P[sb] was the operand of P V of tile j-2
+            if (j >= 2) wait_ok(&pv_done[sb], (unsigned)((j >> 1) - 1) & 1u);
             // probabilities into the operand layout (row r of half hf: 128 B, 16-byte chunks swizzled by r & 7)
             float l_tile = 0.f;
             unsigned char* prow = sP + sb * PT_TILE_BYTES + hf * PT_HALF_BYTES + r * 128;
@@ -298,44 +331,34 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             pt_mbar_arrive(&p_ready[sb]);
             l_run = l_run * alpha + l_tile;
-            m_run = m_new;
-            return alpha;
-        };
-        // O += P V of key tile j: this thread's half of O[j & 1], the row's earlier sum first rescaled by alpha
-        auto collect_tile = [&](int j, float alpha) {
-            const int ob = j & 1;
-            wait_ok(&o_ready[ob], (unsigned)(j >> 1) & 1u);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t o_addr = lane_addr + (uint32_t)(2 * PT_BN + ob * PT_D + hf * 64);
-            uint32_t v0[32], v1[32];
-            pt_tmem_ld32(o_addr, v0);
-            pt_tmem_ld32(o_addr + 32, v1);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                acc[i] = fmaf(acc[i], alpha, __uint_as_float(v0[i]));
-                acc[32 + i] = fmaf(acc[32 + i], alpha, __uint_as_float(v1[i]));
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            pt_mbar_arrive(&o_taken[ob]);
-        };
-        // P[j & 1] is free when the softmax of tile j starts: O_tile of tile j-2 was collected (hence P V of j-2 complete) before
-        float alpha_cur = n_tiles > 0 ? softmax_tile(0) : 1.f;
-        for (int j = 0; j < n_tiles; ++j) {
-            float alpha_next = 1.f;
-            if (j + 1 < n_tiles) alpha_next = softmax_tile(j + 1);     // overlaps P V of tile j on the tensor core
-            collect_tile(j, alpha_cur);
-            alpha_cur = alpha_next;
         }
         // the row's denominator over both halves
         asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
         s_xch[hf * PT_BM + r] = l_run;
         asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
         l_run += s_xch[(hf ^ 1) * PT_BM + r];
-        if (*s_fail == 0 && qi < p.Sq) {
+        // O is final once P V of the last tile has completed
+        if (n_tiles > 0) wait_ok(&pv_done[(n_tiles - 1) & 1], (unsigned)((n_tiles - 1) >> 1) & 1u);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const bool store = *s_fail == 0 && qi < p.Sq && n_tiles > 0;
             unsigned char* orow = static_cast<unsigned char*>(p.O) + ((int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + (int64_t)qi * p.o_ss) * 2 + hf * 128;
 #pragma unroll
-            for (int i = 0; i < PT_D / 2; i += 2) *reinterpret_cast<uint32_t*>(orow + i * 2) = pt_pack(acc[i] * inv, acc[i + 1] * inv, p.bf16);
+            for (int c = 0; c < 2; ++c) {
+                uint32_t o[32];
+                pt_tmem_ld32(o_addr + (uint32_t)(c * 32), o);       // warp-collective: every lane loads, the rows in range store
+                if (store) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        *reinterpret_cast<uint4*>(orow + (c * 32 + i) * 2) =
+                            make_uint4(pt_pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv, p.bf16),
+                                       pt_pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv, p.bf16),
+                                       pt_pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv, p.bf16),
+                                       pt_pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv, p.bf16));
+                    }
+                }
+            }
         }
     }
     if (failed) atomicExch(p.status, FQ_ERR_TIMEOUT);
