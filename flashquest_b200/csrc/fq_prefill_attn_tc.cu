@@ -135,7 +135,9 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
     uint64_t* pv_done = bars + 13;           // [2] O += P V of a tile has completed: its P buffer is free, O is up to date
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);      // a wait gave up somewhere: nobody waits any more
-    __shared__ float s_xch[2 * PT_BM];                                         // [column half][row]: row maxima / denominators
+    // exchange between the two threads of a row, private to each pair of warps that shares 32 rows (256 B per pair):
+    // the tile maxima as bf16 [tile parity][column half][lane], at the end the denominators as fp32 [column half][lane]
+    __shared__ __align__(16) unsigned char s_xch[4 * 256];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // the heaviest query tiles (most keys under the causal mask) are scheduled first
@@ -246,12 +248,15 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
         float m_used = -INFINITY, l_run = 0.f;
         constexpr float PT_LAZY = 8.0f;
         // a wait that gives up is remembered by everybody: the loop then runs on without waiting, so that the
-        // named barriers below still see all 256 threads
+        // named barriers below still see both warps of every pair
         auto wait_ok = [&](uint64_t* bar, unsigned parity) {
             if (*s_fail) return;
             if (!pt_wait(bar, parity)) { failed = true; *s_fail = 1; }
         };
         const uint32_t o_addr = lane_addr + (uint32_t)(2 * PT_BN + hf * 64);      // this thread's half row of O
+        __nv_bfloat16* xch_m = reinterpret_cast<__nv_bfloat16*>(s_xch + lq * 256);
+        float* xch_l = reinterpret_cast<float*>(s_xch + lq * 256);
+        const int pair_bar = 1 + lq;              // named barrier of the two warps that share these 32 rows
         for (int j = 0; j < n_tiles; ++j) {
             const int sb = j & 1;
             wait_ok(&s_ready[sb], (unsigned)(j >> 1) & 1u);
@@ -275,11 +280,16 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
                     m_tile = fmaxf(m_tile, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
                 }
             }
-            // the row's maximum over both halves; the second barrier keeps the next tile's write behind this tile's read
-            s_xch[hf * PT_BM + r] = m_tile;
-            asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
-            m_tile = fmaxf(m_tile, s_xch[(hf ^ 1) * PT_BM + r]);
-            asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
+            // The row's maximum over both halves, to bf16 precision (it only serves as the reference point of the
+            // exponentials, and both threads must arrive at the same value).  One named barrier per pair of warps; the
+            // slot alternates with the tile parity, so the write of tile j+2 cannot overtake the partner's read of tile j
+            // (the partner reads before it arrives at the barrier of tile j+1).
+            {
+                const __nv_bfloat16 mine = __float2bfloat16_rn(m_tile);
+                xch_m[(sb * 2 + hf) * 32 + lane] = mine;
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+                m_tile = fmaxf(__bfloat162float(mine), __bfloat162float(xch_m[(sb * 2 + (hf ^ 1)) * 32 + lane]));
+            }
             // both threads of a row see the same m_tile and m_used, so they take the same decision
             const float m_true = m_tile * p.scale_log2;
             float alpha = 1.f;
@@ -332,11 +342,11 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
             pt_mbar_arrive(&p_ready[sb]);
             l_run = l_run * alpha + l_tile;
         }
-        // the row's denominator over both halves
-        asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
-        s_xch[hf * PT_BM + r] = l_run;
-        asm volatile("bar.sync 1, %0;" ::"n"(PT_SOFTMAX_WARPS * 32) : "memory");
-        l_run += s_xch[(hf ^ 1) * PT_BM + r];
+        // the row's denominator over both halves (the pair's exchange area again, as fp32)
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        xch_l[hf * 32 + lane] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        l_run += xch_l[(hf ^ 1) * 32 + lane];
         // O is final once P V of the last tile has completed
         if (n_tiles > 0) wait_ok(&pv_done[(n_tiles - 1) & 1], (unsigned)((n_tiles - 1) >> 1) & 1u);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
