@@ -8,15 +8,16 @@
 //                 thread the K tiles and one the V tiles, each into its own two-deep ring (a K stage is free again as
 //                 soon as S has been computed, long before the V stage of the same tile);
 //   warp 1      : one thread issues tcgen05.mma: S = Q K^T (M 128, N 128, K 16 x 8) into one of two S buffers in
-//                 tensor memory, and O_tile = P V (P from one of two shared-memory buffers, V as the MN-major
-//                 operand) into one of two O buffers; S runs up to two key tiles ahead of P V;
-//   warps 2..9  : softmax — two threads per query row (TMEM lane = row; warps 2..5 own the key / channel columns
-//                 0..63, warps 6..9 the columns 64..127): read S once (tcgen05.ld), scale, mask (diagonal tile only),
-//                 exchange the row maximum through shared memory, keep the running maximum and denominator in base
-//                 2, write P as fp16/bf16 into the swizzled K-major operand layout, then add their half of O_tile
-//                 (with the row's earlier sum rescaled by the change of the maximum) to an fp32 half row of O in
-//                 registers; store the normalised row at the end.  The softmax of tile j+1 is computed BEFORE O_tile of
-//                 tile j is collected, so that P V of tile j overlaps it.
+//                 tensor memory, and O += P V into the one O accumulator in tensor memory, with P read from tensor
+//                 memory as the A operand and V from shared memory as the MN-major B operand; S runs up to two key
+//                 tiles ahead of P V;
+//   warps 2..9  : softmax — two threads per query row (TMEM lane = row; warps 2..5 own the key columns 0..63, warps
+//                 6..9 the columns 64..127): read S once (tcgen05.ld), scale, mask (diagonal tile only), agree on the
+//                 row maximum through shared memory (one named barrier per pair of warps), write P as fp16/bf16, two
+//                 values per 32-bit column, over the S columns they have just read (tcgen05.st).  The exponentials
+//                 are taken against a reference maximum that follows the running maximum only when it has moved by
+//                 more than 2^8; only then do the threads rescale their half row of O in tensor memory, so O is read
+//                 back once, at the end, where it is normalised and stored.
 // Every mbarrier wait is bounded and reports through the device status word.
 #include <cuda.h>
 
@@ -30,9 +31,9 @@ constexpr int PT_THREADS = (2 + PT_SOFTMAX_WARPS) * 32;
 constexpr int PT_TILE_BYTES = 128 * PT_D * 2;                 // 32 KiB: two halves of [128 rows][64 elements]
 constexpr int PT_HALF_BYTES = PT_TILE_BYTES / 2;
 constexpr int PT_KV_STAGES = 2;
-constexpr int PT_SMEM = PT_TILE_BYTES * (3 + 2 * PT_KV_STAGES) + 1024 + 256;   // Q, P x 2, K ring, V ring, alignment slack, barriers
+constexpr int PT_SMEM = PT_TILE_BYTES * (1 + 2 * PT_KV_STAGES) + 1024 + 256;   // Q, K ring, V ring, alignment slack, barriers
 constexpr unsigned PT_SPIN_LIMIT = 1u << 26;
-constexpr int PT_TMEM_COLS = 512;                              // S0 @0, S1 @128, O0 @256, O1 @384
+constexpr int PT_TMEM_COLS = 512;                              // S0 / P0 @0, S1 / P1 @128, O @256 (allocation sizes are powers of two)
 
 struct PrefillTcParams {
     void* O; int64_t o_sb, o_sh, o_ss;
@@ -73,6 +74,13 @@ __device__ __forceinline__ void pt_mma(uint32_t tmem_c, uint64_t desc_a, uint64_
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the same with the A operand read from tensor memory (row m of A in lane m, two 16-bit elements per 32-bit column)
+__device__ __forceinline__ void pt_mma_ta(uint32_t tmem_c, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void pt_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pt_smem(bar)) : "memory");
@@ -121,8 +129,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
     extern __shared__ unsigned char pt_raw_smem[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pt_raw_smem) + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;                                         // [2 halves][128 rows][128 B]
-    unsigned char* sP = base + PT_TILE_BYTES;                         // [2 buffers] same layout, keys instead of channels
-    unsigned char* sK = base + 3 * PT_TILE_BYTES;                     // [stages] same layout
+    unsigned char* sK = base + PT_TILE_BYTES;                         // [stages] same layout
     unsigned char* sV = sK + PT_KV_STAGES * PT_TILE_BYTES;            // [stages][2 halves of d][128 keys][128 B]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + PT_KV_STAGES * PT_TILE_BYTES);
     uint64_t* q_full = bars;                 // Q landed
@@ -221,13 +228,15 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
                 // p_ready also says that the softmax threads have rescaled O where a row's maximum moved
                 if (!pt_wait(&p_ready[s], ph) || !pt_wait(&v_full[s], ph)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v_addr = pt_smem(sV + s * PT_TILE_BYTES), p_addr = pt_smem(sP + s * PT_TILE_BYTES);
+                const uint32_t v_addr = pt_smem(sV + s * PT_TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < PT_BN / 16; ++kk) {
-                    // A = P, K-major over the keys; B = V, MN-major: 64 channels x 8 keys = one atom, 16 keys = 2 KiB, channel halves 16 KiB apart
-                    const uint32_t offp = (uint32_t)(kk >> 2) * PT_HALF_BYTES + (uint32_t)(kk & 3) * 32;
-                    pt_mma(tmem_base + (uint32_t)(2 * PT_BN), pt_desc(p_addr + offp, 16, 1024),
-                           pt_desc(v_addr + (uint32_t)kk * 2048, PT_HALF_BYTES, 1024), idesc_o, (kk != 0 || j != 0) ? 1u : 0u);
+                    // A = P of tile j in tensor memory, written over the S buffer it came from: keys 0..63 in columns 0..31
+                    // of the buffer, keys 64..127 in columns 64..95 (each half under the S columns its writer owns);
+                    // B = V, MN-major: 64 channels x 8 keys = one atom, 16 keys = 2 KiB, channel halves 16 KiB apart
+                    const uint32_t p_taddr = tmem_base + (uint32_t)(s * PT_BN + (kk >> 2) * 64 + (kk & 3) * 8);
+                    pt_mma_ta(tmem_base + (uint32_t)(2 * PT_BN), p_taddr,
+                              pt_desc(v_addr + (uint32_t)kk * 2048, PT_HALF_BYTES, 1024), idesc_o, (kk != 0 || j != 0) ? 1u : 0u);
                 }
                 pt_commit(&pv_done[s]);
                 pt_commit(&v_empty[s]);
@@ -313,31 +322,23 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_attn_tc_kernel(
                 }
             }
             const float m_sub = m_used == -INFINITY ? 0.f : m_used;
-            // P[sb] was the operand of P V of tile j-2
-            if (j >= 2) wait_ok(&pv_done[sb], (unsigned)((j >> 1) - 1) & 1u);
-            // probabilities into the operand layout (row r of half hf: 128 B, 16-byte chunks swizzled by r & 7)
+            // probabilities, two per 32-bit column, over the first half of this thread's own S columns (the S values
+            // are in registers by now; the next S into this buffer is issued behind the P V that reads these)
             float l_tile = 0.f;
-            unsigned char* prow = sP + sb * PT_TILE_BYTES + hf * PT_HALF_BYTES + r * 128;
+            uint32_t pk[32];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const uint32_t (&v)[32] = c == 0 ? v0 : v1;
 #pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {
-                    uint32_t pk[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i0 = q8 * 8 + 2 * e;
-                        // ex2(-inf) = 0 for masked columns
-                        const float p0 = pt_ex2(fmaf(__uint_as_float(v[i0]), p.scale_log2, -m_sub));
-                        const float p1 = pt_ex2(fmaf(__uint_as_float(v[i0 + 1]), p.scale_log2, -m_sub));
-                        l_tile += p0 + p1;
-                        pk[e] = pt_pack(p0, p1, p.bf16);
-                    }
-                    const int chunk = c * 4 + q8;       // 16-byte chunk inside the 128-byte row
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                for (int i = 0; i < 32; i += 2) {
+                    // ex2(-inf) = 0 for masked columns
+                    const float p0 = pt_ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_sub));
+                    const float p1 = pt_ex2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_sub));
+                    l_tile += p0 + p1;
+                    pk[c * 16 + i / 2] = pt_pack(p0, p1, p.bf16);
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
+            pt_tmem_st32(s_addr, pk);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             pt_mbar_arrive(&p_ready[sb]);
             l_run = l_run * alpha + l_tile;
