@@ -154,6 +154,8 @@ _PROTOTYPES["fq_page_scores_int8"] = (I, [P, I, L, L, P, P, L, L, L, I, I, I, I,
 _PROTOTYPES["fq_sparse_decode_int8_workspace_bytes"] = (Z, [I, I, I, I])
 _PROTOTYPES["fq_sparse_decode_int8"] = (I, [P, I, L, L, P, P, L, L, L, P, P, L, L, L, P, P, L, L, P, L, L, I,
                                            P, P, I, L, L, L, I, I, I, I, I, I, I, I, F, P, P, P, Z, I, P])
+_PROTOTYPES["fq_sparse_decode_int8_counted"] = (I, [P, I, L, L, P, P, L, L, L, P, P, L, L, L, P, P, L, L, P, L, L, I, P,
+                                                   P, P, I, L, L, L, I, I, I, I, I, I, I, I, F, P, P, P, Z, I, P])
 _PROTOTYPES["fq_prefill_attention"] = (I, [P, L, L, L, P, L, L, L, P, L, L, L, I, I, I, I, I, I, I, F, P, L, L, L, P])
 
 # entry points added by later sources register themselves here (name -> (restype, argtypes))

@@ -118,6 +118,8 @@ struct Int8AttnParams {
     const uint16_t *K_scale, *K_mn; int64_t km_sb, km_sh, km_sp;
     const uint16_t *V_scale, *V_mn; int64_t vm_sb, vm_sh;
     const int32_t* compact; int64_t cp_sb, cp_sh; int bucket;
+    const int32_t* list_count;      // non-null: only the first list_count[row] list entries can be valid
+    int vec4;                       // code rows allow 4-byte loads
     const void *K_tail, *V_tail; int tail_dtype; int64_t tl_sb, tl_sh, tl_ss; int tail_len;
     int B, Hq, Hkv, S_kv, P, page;
     float sm_scale;
@@ -148,7 +150,21 @@ __global__ void __launch_bounds__(128) sparse_decode_int8_kernel(Int8AttnParams 
     const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
     const uint8_t* Kb = p.K + b * p.kv_sb + hkv * p.kv_sh;
     const uint8_t* Vb = p.V + b * p.kv_sb + hkv * p.kv_sh;
-    for (int e = split + p.n_split * warp; e < p.bucket; e += p.n_split * 4) {
+    int n_list = p.bucket;
+    if (p.list_count) n_list = max(0, min(n_list, __ldg(p.list_count + b * p.Hq + hq)));
+    // four code bytes of this lane's channels as fp32
+    auto codes4 = [&](const uint8_t* row, float (&out)[CPL]) {
+        if (p.vec4 && CPL == 4) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(row);
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) out[j] = (float)((w >> (8 * j)) & 0xffu);
+        } else {
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) out[j] = (float)row[j];
+        }
+    };
+    constexpr int TCH = 8;       // tokens whose logits are formed side by side: their warp reductions overlap
+    for (int e = split + p.n_split * warp; e < n_list; e += p.n_split * 4) {
         const int pg = list[e];
         if (pg < 0 || pg >= p.P || pg * p.page >= p.S_kv) continue;
         const int64_t mo = b * p.km_sb + hkv * p.km_sh + (int64_t)pg * p.km_sp + CPL * lane;
@@ -160,19 +176,42 @@ __global__ void __launch_bounds__(128) sparse_decode_int8_kernel(Int8AttnParams 
         }
         qmn = warp_sum(qmn);
         const int t_end = min((pg + 1) * p.page, p.S_kv);
-        for (int t = pg * p.page; t < t_end; ++t) {
-            const uint8_t* kr = Kb + (int64_t)t * p.kv_ss + CPL * lane;
-            const uint8_t* vr = Vb + (int64_t)t * p.kv_ss + CPL * lane;
-            float s = 0.f;
+        for (int t0 = pg * p.page; t0 < t_end; t0 += TCH) {
+            float sc[TCH], vs[TCH], vm[TCH];
 #pragma unroll
-            for (int j = 0; j < CPL; ++j) s = fmaf(qs[j], (float)kr[j], s);
-            s = warp_sum(s) + qmn;
-            const float m_new = fmaxf(m, s);
-            const float al = i8_ex2(m - m_new), pr = i8_ex2(s - m_new);
-            const float vs = bf16_lo(p.V_scale[b * p.vm_sb + hkv * p.vm_sh + t]), vm = bf16_lo(p.V_mn[b * p.vm_sb + hkv * p.vm_sh + t]);
-            l = l * al + pr;
+            for (int u = 0; u < TCH; ++u) {
+                const int t = min(t0 + u, t_end - 1);        // past the end: a repeat of the last token, masked below
+                float kf[CPL];
+                codes4(Kb + (int64_t)t * p.kv_ss + CPL * lane, kf);
+                float a = 0.f;
 #pragma unroll
-            for (int j = 0; j < CPL; ++j) acc[j] = fmaf(pr, fmaf((float)vr[j], vs, vm), acc[j] * al);
+                for (int j = 0; j < CPL; ++j) a = fmaf(qs[j], kf[j], a);
+                sc[u] = a;
+                vs[u] = bf16_lo(p.V_scale[b * p.vm_sb + hkv * p.vm_sh + t]);
+                vm[u] = bf16_lo(p.V_mn[b * p.vm_sb + hkv * p.vm_sh + t]);
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < TCH; ++u) {
+                sc[u] = t0 + u < t_end ? warp_sum(sc[u]) + qmn : -INFINITY;
+                mx = fmaxf(mx, sc[u]);
+            }
+            const float m_new = fmaxf(m, mx);                  // finite: token t0 is valid
+            const float al = i8_ex2(m - m_new);
+            l *= al;
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) acc[j] *= al;
+#pragma unroll
+            for (int u = 0; u < TCH; ++u) {
+                const int t = min(t0 + u, t_end - 1);
+                const float pr = i8_ex2(sc[u] - m_new);        // 0 past the end
+                float vf[CPL];
+                codes4(Vb + (int64_t)t * p.kv_ss + CPL * lane, vf);
+                l += pr;
+                const float ps = pr * vs[u], pm = pr * vm[u];
+#pragma unroll
+                for (int j = 0; j < CPL; ++j) acc[j] += fmaf(vf[j], ps, pm);
+            }
             m = m_new;
         }
     }
@@ -298,12 +337,12 @@ extern "C" size_t fq_sparse_decode_int8_workspace_bytes(int B, int Hq, int D, in
     return (size_t)n_split * B * Hq * (D + 1) * 4;
 }
 
-extern "C" int fq_sparse_decode_int8(
+extern "C" int fq_sparse_decode_int8_counted(
     const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
     const uint8_t* K_uint8, const uint8_t* V_uint8, int64_t kv_sb, int64_t kv_sh, int64_t kv_ss,
     const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
     const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
-    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket, const int32_t* list_count,
     const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
     int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
     void* O, float* lse, void* workspace, size_t workspace_bytes, int n_split, void* stream) {
@@ -330,6 +369,8 @@ extern "C" int fq_sparse_decode_int8(
     p.K_scale = static_cast<const uint16_t*>(K_scale); p.K_mn = static_cast<const uint16_t*>(K_mn); p.km_sb = km_sb; p.km_sh = km_sh; p.km_sp = km_sp;
     p.V_scale = static_cast<const uint16_t*>(V_scale); p.V_mn = static_cast<const uint16_t*>(V_mn); p.vm_sb = vm_sb; p.vm_sh = vm_sh;
     p.compact = compact; p.cp_sb = cp_sb; p.cp_sh = cp_sh; p.bucket = have_pages ? bucket : 0;
+    p.list_count = list_count;
+    p.vec4 = (have_pages && aligned(K_uint8, 4) && aligned(V_uint8, 4) && kv_sb % 4 == 0 && kv_sh % 4 == 0 && kv_ss % 4 == 0) ? 1 : 0;
     p.K_tail = K_tail; p.V_tail = V_tail; p.tail_dtype = tail_dtype; p.tl_sb = tl_sb; p.tl_sh = tl_sh; p.tl_ss = tl_ss; p.tail_len = tail_len;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S_kv = S_kv; p.P = P; p.page = page; p.sm_scale = sm_scale;
     p.n_split = n_split;
@@ -344,4 +385,19 @@ extern "C" int fq_sparse_decode_int8(
     int8_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, n_split, rows, D, O, q_dtype, lse);
     FQ_CHECK_LAUNCH(fn);
     return FQ_OK;
+}
+
+extern "C" int fq_sparse_decode_int8(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_uint8, const uint8_t* V_uint8, int64_t kv_sb, int64_t kv_sh, int64_t kv_ss,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, float* lse, void* workspace, size_t workspace_bytes, int n_split, void* stream) {
+    return fq_sparse_decode_int8_counted(Q, q_dtype, q_sb, q_sh, K_uint8, V_uint8, kv_sb, kv_sh, kv_ss, K_scale, K_mn, km_sb, km_sh, km_sp,
+                                         V_scale, V_mn, vm_sb, vm_sh, compact, cp_sb, cp_sh, bucket, nullptr,
+                                         K_tail, V_tail, tail_dtype, tl_sb, tl_sh, tl_ss, tail_len, B, Hq, Hkv, S_kv, P, D, page, sm_scale,
+                                         O, lse, workspace, workspace_bytes, n_split, stream);
 }

@@ -37,7 +37,8 @@ def flash_attn_sparse_fwd(Q, K_uint8, K_scale, K_mn, V_uint8, V_scale, V_mn, *, 
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
     dev = Q.device
-    compact = build_compact_selection(selection_mask, max(num_pages, 1)).squeeze(2)
+    compact, count = build_compact_selection(selection_mask, max(num_pages, 1), return_count=True)
+    compact = compact.squeeze(2)
     bucket = compact.shape[-1]
     Q3 = Q.reshape(B, H_q, D).contiguous()
     K_uint8, V_uint8 = inner_contiguous(K_uint8), inner_contiguous(V_uint8)
@@ -60,14 +61,17 @@ def flash_attn_sparse_fwd(Q, K_uint8, K_scale, K_mn, V_uint8, V_scale, V_mn, *, 
     O = torch.empty(B, H_q, D, dtype=Q.dtype, device=dev)
     L = torch.empty(B, H_q, dtype=torch.float32, device=dev) if return_lse else None
     if n_split is None:
-        n_split = max(1, min(64, (2 * 148) // max(B * H_q, 1), (bucket + 3) // 4))
+        # a warp should walk about six to eight pages: the list made from a mask is as wide as the page count and
+        # about a quarter of it is real, so one split per 96 entries (measured: 16-24 splits best at 2048 pages,
+        # batch 1 and 16 alike)
+        n_split = max(1, min(64, bucket // 96))
     with torch.cuda.device(dev):
         ws = torch.empty(lib().fq_sparse_decode_int8_workspace_bytes(B, H_q, D, n_split), dtype=torch.uint8, device=dev)
-        check(lib().fq_sparse_decode_int8(
+        check(lib().fq_sparse_decode_int8_counted(
             ptr(Q3), dtype_code(Q3), Q3.stride(0), Q3.stride(1),
             ptr(K_uint8), ptr(V_uint8), *K_uint8.stride()[:3],
             ptr(K_scale), ptr(K_mn), *K_scale.stride()[:3], ptr(Vs), ptr(Vm), Vs.stride(0), Vs.stride(1),
-            ptr(compact), compact.stride(0), compact.stride(1), bucket,
+            ptr(compact), compact.stride(0), compact.stride(1), bucket, ptr(count),
             ptr(K_partial), ptr(V_partial), tcode, *tl, tail_len,
             B, H_q, H_kv, S_kv, num_pages, D, int(page_size), float(sm_scale),
             ptr(O), ptr(L), ptr(ws), ws.numel(), int(n_split), stream_ptr(dev)))

@@ -204,6 +204,17 @@ int fq_sparse_decode_int8(
     const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
     int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
     void* O, float* lse, void* workspace, size_t workspace_bytes, int n_split, void* stream);
+/* The same for a list whose real entries sit at the front (what fq_build_compact_counted makes from a mask):
+ * list_count (B*Hq) int32 bounds the entries walked per row; NULL = all of them. */
+int fq_sparse_decode_int8_counted(
+    const void* Q, int q_dtype, int64_t q_sb, int64_t q_sh,
+    const uint8_t* K_uint8, const uint8_t* V_uint8, int64_t kv_sb, int64_t kv_sh, int64_t kv_ss,
+    const void* K_scale, const void* K_mn, int64_t km_sb, int64_t km_sh, int64_t km_sp,
+    const void* V_scale, const void* V_mn, int64_t vm_sb, int64_t vm_sh,
+    const int32_t* compact, int64_t cp_sb, int64_t cp_sh, int bucket, const int32_t* list_count,
+    const void* K_tail, const void* V_tail, int tail_dtype, int64_t tl_sb, int64_t tl_sh, int64_t tl_ss, int tail_len,
+    int B, int Hq, int Hkv, int S_kv, int P, int D, int page, float sm_scale,
+    void* O, float* lse, void* workspace, size_t workspace_bytes, int n_split, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * Dense causal attention of the prefill branch (S_q > 1).
