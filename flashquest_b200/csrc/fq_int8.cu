@@ -251,6 +251,161 @@ __global__ void __launch_bounds__(128) sparse_decode_int8_kernel(Int8AttnParams 
     if (d == 0) p.part_lse[(int64_t)split * rows + row] = lsum > 0.f ? (mx + log2f(lsum)) * I8_LN2 : -INFINITY;
 }
 
+// The same computation for 16-byte aligned code and metadata rows.  Eight lanes (a quarter warp) own one token: lane l
+// holds D/8 consecutive channels (one 16-byte load of codes at head_dim 128), so a page of 16 tokens is four tokens per
+// quarter warp, their loads in flight together, a 3-step shuffle reduction per logit and ONE online-softmax update per
+// 16 tokens.  acc holds sum (p * v_scale) * code, the sum of p * v_mn is kept apart and added once at the end; the four
+// quarter warps accumulate different tokens of the same channels and are added up before the CTA merge.
+template <int D>
+__global__ void __launch_bounds__(128) sparse_decode_int8_q_kernel(Int8AttnParams p) {
+    constexpr int DPL = D / 8;          // channels per lane
+    constexpr int NW = DPL / 4;         // 32-bit words of codes per lane and token
+    __shared__ float s_m[4], s_l[4];
+    __shared__ float s_acc[4][D];
+    const int split = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+    const int hkv = hq / (p.Hq / p.Hkv);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int l = lane & 7, qw = lane >> 3;
+    const float c = p.sm_scale * I8_LOG2E;
+    float q[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) q[j] = i8_ld(p.Q, p.q_dtype, b * p.q_sb + hq * p.q_sh + DPL * l + j) * c;
+    float m = -INFINITY, lsum = 0.f, mnacc = 0.f, acc[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) acc[j] = 0.f;
+    auto quarter_sum = [](float v) {
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        return v;
+    };
+    auto warp_max4 = [](float v) {       // over the four quarter warps (lanes of a quarter hold equal values)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+        return v;
+    };
+    auto load_codes = [&](const uint8_t* row, uint32_t (&w)[NW]) {
+        if constexpr (NW == 4) { const uint4 u = *reinterpret_cast<const uint4*>(row); w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w; }
+        else { const uint2 u = *reinterpret_cast<const uint2*>(row); w[0] = u.x; w[1] = u.y; }
+    };
+    const int32_t* list = p.compact + b * p.cp_sb + hq * p.cp_sh;
+    const uint8_t* Kb = p.K + b * p.kv_sb + hkv * p.kv_sh + DPL * l;
+    const uint8_t* Vb = p.V + b * p.kv_sb + hkv * p.kv_sh + DPL * l;
+    const uint16_t* Vsc = p.V_scale + b * p.vm_sb + hkv * p.vm_sh;
+    const uint16_t* Vmn = p.V_mn + b * p.vm_sb + hkv * p.vm_sh;
+    int n_list = p.bucket;
+    if (p.list_count) n_list = max(0, min(n_list, __ldg(p.list_count + b * p.Hq + hq)));
+    for (int e = split + p.n_split * warp; e < n_list; e += p.n_split * 4) {
+        const int pg = list[e];
+        if (pg < 0 || pg >= p.P || pg * p.page >= p.S_kv) continue;
+        const int64_t mo = b * p.km_sb + hkv * p.km_sh + (int64_t)pg * p.km_sp + DPL * l;
+        float qs[DPL], qmn = 0.f;
+#pragma unroll
+        for (int c8 = 0; c8 < DPL / 8; ++c8) {
+            float sc8[8], mn8[8];
+            load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.K_scale + mo) + 8 * c8, sc8);
+            load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.K_mn + mo) + 8 * c8, mn8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                qs[8 * c8 + j] = q[8 * c8 + j] * sc8[j];
+                qmn = fmaf(q[8 * c8 + j], mn8[j], qmn);
+            }
+        }
+        qmn = quarter_sum(qmn);
+        const int t_end = min((pg + 1) * p.page, p.S_kv);
+        for (int t0 = pg * p.page; t0 < t_end; t0 += 16) {
+            uint32_t kw[4][NW], vw[4][NW];
+            float vs[4], vm[4], sc[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int t = min(t0 + qw + 4 * u, t_end - 1);      // past the end: a repeat of the last token, masked below
+                load_codes(Kb + (int64_t)t * p.kv_ss, kw[u]);
+                load_codes(Vb + (int64_t)t * p.kv_ss, vw[u]);
+                vs[u] = bf16_lo(Vsc[t]);
+                vm[u] = bf16_lo(Vmn[t]);
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                float a = 0.f;
+#pragma unroll
+                for (int w = 0; w < NW; ++w)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) a = fmaf(qs[4 * w + k], (float)((kw[u][w] >> (8 * k)) & 0xffu), a);
+                a = quarter_sum(a);
+                sc[u] = t0 + qw + 4 * u < t_end ? a + qmn : -INFINITY;
+                mx = fmaxf(mx, sc[u]);
+            }
+            mx = warp_max4(mx);
+            const float m_new = fmaxf(m, mx);                  // finite: token t0 is valid
+            const float al = i8_ex2(m - m_new);
+            lsum *= al; mnacc *= al;
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) acc[j] *= al;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float pr = i8_ex2(sc[u] - m_new);        // 0 past the end
+                const float ps = pr * vs[u];
+                lsum += pr;
+                mnacc = fmaf(pr, vm[u], mnacc);
+#pragma unroll
+                for (int w = 0; w < NW; ++w)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc[4 * w + k] = fmaf(ps, (float)((vw[u][w] >> (8 * k)) & 0xffu), acc[4 * w + k]);
+            }
+            m = m_new;
+        }
+    }
+    // the staged (unquantised) tail belongs to split 0: a quarter warp per token
+    if (split == 0) {
+        for (int t0 = 4 * warp; t0 < p.tail_len; t0 += 16) {       // warp-uniform trip count
+            const int t = t0 + qw;
+            const bool live = t < p.tail_len;
+            const int64_t ro = b * p.tl_sb + hkv * p.tl_sh + (int64_t)(live ? t : 0) * p.tl_ss + DPL * l;
+            float a = 0.f;
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) a = fmaf(q[j], i8_ld(p.K_tail, p.tail_dtype, ro + j), a);
+            a = quarter_sum(a);
+            const float s = live ? a : -INFINITY;
+            const float m_new = fmaxf(m, warp_max4(s));        // finite: token t0 is live
+            const float al = i8_ex2(m - m_new), pr = i8_ex2(s - m_new);
+            lsum = lsum * al + pr;
+            mnacc *= al;
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) acc[j] = fmaf(pr, live ? i8_ld(p.V_tail, p.tail_dtype, ro + j) : 0.f, acc[j] * al);
+            m = m_new;
+        }
+    }
+    // the four quarter warps hold partial sums over different tokens of the same channels
+#pragma unroll
+    for (int off = 8; off <= 16; off <<= 1) {
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
+        mnacc += __shfl_xor_sync(0xffffffffu, mnacc, off);
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+    }
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = lsum; }
+    if (qw == 0) {
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) s_acc[warp][DPL * l + j] = acc[j] + mnacc;
+    }
+    __syncthreads();
+    float mx = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    float ltot = 0.f, o = 0.f;
+    const int d = threadIdx.x;
+    if (mx != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float wgt = i8_ex2(s_m[w] - mx);
+            ltot = fmaf(s_l[w], wgt, ltot);
+            if (d < D) o = fmaf(s_acc[w][d], wgt, o);
+        }
+    }
+    const int64_t row = (int64_t)b * p.Hq + hq, rows = (int64_t)p.B * p.Hq;
+    if (d < D) p.part_o[((int64_t)split * rows + row) * D + d] = ltot > 0.f ? o / ltot : 0.f;
+    if (d == 0) p.part_lse[(int64_t)split * rows + row] = ltot > 0.f ? (mx + log2f(ltot)) * I8_LN2 : -INFINITY;
+}
+
 // merge of the splits' normalised partial results (fp32) into O (q dtype) and lse; one warp per row
 __global__ void __launch_bounds__(128) int8_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_split,
                                                          int64_t rows, int D, void* __restrict__ O, int q_dtype, float* __restrict__ lse) {
@@ -378,8 +533,16 @@ extern "C" int fq_sparse_decode_int8_counted(
     p.part_lse = p.part_o + (size_t)n_split * B * Hq * D;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid((unsigned)n_split, (unsigned)Hq, (unsigned)B);
-    if (D == 128) sparse_decode_int8_kernel<128><<<grid, 128, 0, st>>>(p);
-    else sparse_decode_int8_kernel<64><<<grid, 128, 0, st>>>(p);
+    // 16-byte aligned code and metadata rows: the quarter-warp-per-token kernel
+    const bool vec16 = have_pages && aligned(K_uint8, 16) && aligned(V_uint8, 16) && kv_sb % 16 == 0 && kv_sh % 16 == 0 && kv_ss % 16 == 0 &&
+                       aligned(K_scale, 16) && aligned(K_mn, 16) && km_sb % 8 == 0 && km_sh % 8 == 0 && km_sp % 8 == 0;
+    if (vec16) {
+        if (D == 128) sparse_decode_int8_q_kernel<128><<<grid, 128, 0, st>>>(p);
+        else sparse_decode_int8_q_kernel<64><<<grid, 128, 0, st>>>(p);
+    } else {
+        if (D == 128) sparse_decode_int8_kernel<128><<<grid, 128, 0, st>>>(p);
+        else sparse_decode_int8_kernel<64><<<grid, 128, 0, st>>>(p);
+    }
     FQ_CHECK_LAUNCH(fn);
     const int64_t rows = (int64_t)B * Hq;
     int8_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p.part_o, p.part_lse, n_split, rows, D, O, q_dtype, lse);
