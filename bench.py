@@ -401,7 +401,7 @@ def run_ours(args):
         secondary = None
         if rank == 0 and world == 1 and not args.no_secondary:
             secondary = {}
-            for name, fn in (("awq", run_awq), ("turbo", run_turbo), ("prefill_attn", run_prefill_attn), ("llama", run_llama)):
+            for name, fn in (("awq", run_awq), ("turbo", run_turbo), ("int8", run_int8), ("prefill_attn", run_prefill_attn), ("llama", run_llama)):
                 torch.cuda.empty_cache()
                 try:
                     secondary[name] = fn(args)
@@ -895,6 +895,71 @@ def run_turbo(args):
         "peak": peak, "peak_kind": peak_kind, "device_status": _lib.lib().fq_device_status()}
 
 
+# --------------------------------------------------------------------------- secondary workload: INT8 KV and the mask-driven INT4 form
+
+def run_int8(args):
+    """The reference's mask-driven decode attention (its default path, `use_compact_kernel=False`) at the BASELINE config 1
+    shape, batch 16 (overridable): INT8 KV (`flash_attn_sparse_fwd`) and INT4 KV (`flash_attn_sparse_int4_fwd`), each
+    call = mask -> page list + attention (+ merge), replayed from a CUDA graph."""
+    import torch
+    from flashquest_b200 import _lib
+    from flashquest_b200.eager.criticality import page_scores_int4_fast, page_scores_int8_fast
+    from flashquest_b200.eager.selection import select_pages_vectorized
+    from flashquest_b200.kernel.kv_quant import quantize_k, quantize_k_int4, quantize_v, quantize_v_int4
+    from flashquest_b200.kernel.sparse_fwd import flash_attn_sparse_fwd
+    from flashquest_b200.kernel.sparse_int4_fwd import flash_attn_sparse_int4_fwd
+    _lib.lib()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, Hq, Hkv, D, S, page = args.batch or 16, 24, 8, 128, args.ctx or 32768, 16
+    peak, peak_kind = measured_peak()
+    n_rep = Hq // Hkv
+    out = {"metric": "mask-driven sparse decode attention (INT8 and INT4 KV)", "workload": "int8",
+           "config": {"batch": B, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "context": S, "page_size": page, "retention": 0.25},
+           "peak": peak, "peak_kind": peak_kind}
+    for name, qk, qv, score, attend, tok_bytes in (
+            ("int8", quantize_k, quantize_v, page_scores_int8_fast, flash_attn_sparse_fwd, 2 * D + 4),
+            ("int4", quantize_k_int4, quantize_v_int4, page_scores_int4_fast, flash_attn_sparse_int4_fwd, D + 4)):
+        g = torch.Generator(device=dev).manual_seed(1)
+        kvs = []
+        for _ in range(B):
+            K = torch.randn(1, Hkv, S, D, device=dev, generator=g)
+            K[..., [3, 17, 64, 100]] *= 8.0
+            V = torch.randn(1, Hkv, S, D, device=dev, generator=g)
+            kvs.append(qk(K.half(), page) + qv(V.half()))
+            del K, V
+        kv = tuple(torch.cat([k[i] for k in kvs]) for i in range(6))
+        del kvs
+        Q = torch.randn(B, Hq, 1, D, device=dev, generator=g).half()
+        mask = select_pages_vectorized(score(Q, kv[1], kv[2]), 0.25, 1, 1)
+
+        def call():
+            return attend(Q, *kv, selection_mask=mask, page_size=page)
+
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            call()
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps
+        pages = int(mask.view(B, Hkv, n_rep, -1).any(2).sum())
+        union = pages * (page * tok_bytes + 2 * D * 2)                # codes + V metadata per token, K metadata per page
+        out[name] = {"us_per_call": us, "union_bytes": union, "GBs_union": union / us / 1e3, "frac": union / us / 1e3 / peak}
+        del kv, Q, mask, graph
+        torch.cuda.empty_cache()
+    out["device_status"] = _lib.lib().fq_device_status()
+    return out
+
+
 # --------------------------------------------------------------------------- secondary workload: prefill attention
 
 def run_prefill_attn(args):
@@ -1116,7 +1181,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=0, help="override the context length (small captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch per GPU (profiles of batched shapes)")
     ap.add_argument("--n-split", type=int, default=0, help="override the split-K factor of the attention kernel")
-    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo", "llama", "ctxsplit", "prefill_attn"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "awq", "turbo", "int8", "llama", "ctxsplit", "prefill_attn"],
                     help="decode = the headline metric; awq = secondary table for the W4A16 GEMV (1 GPU)")
     ap.add_argument("--no-batched", action="store_true", help="skip the batched-attention leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -1130,6 +1195,8 @@ def main():
         print(json.dumps(run_awq(args)))
     elif args.workload == "turbo":
         print(json.dumps(run_turbo(args)))
+    elif args.workload == "int8":
+        print(json.dumps(run_int8(args)))
     elif args.workload == "llama":
         print(json.dumps(run_llama(args)))
     elif args.workload == "prefill_attn":
