@@ -284,6 +284,10 @@ __global__ void __launch_bounds__(128) sparse_decode_int8_q_kernel(Int8AttnParam
         v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
         return v;
     };
+    // byte k of w as fp32: the byte becomes the low mantissa byte of 2^23 (one byte permute), which is then subtracted
+    auto code_f32 = [](uint32_t w, int k) -> float {
+        return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7540u | (unsigned)k)) - 8388608.0f;
+    };
     auto load_codes = [&](const uint8_t* row, uint32_t (&w)[NW]) {
         if constexpr (NW == 4) { const uint4 u = *reinterpret_cast<const uint4*>(row); w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w; }
         else { const uint2 u = *reinterpret_cast<const uint2*>(row); w[0] = u.x; w[1] = u.y; }
@@ -331,7 +335,7 @@ __global__ void __launch_bounds__(128) sparse_decode_int8_q_kernel(Int8AttnParam
 #pragma unroll
                 for (int w = 0; w < NW; ++w)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) a = fmaf(qs[4 * w + k], (float)((kw[u][w] >> (8 * k)) & 0xffu), a);
+                    for (int k = 0; k < 4; ++k) a = fmaf(qs[4 * w + k], code_f32(kw[u][w], k), a);
                 a = quarter_sum(a);
                 sc[u] = t0 + qw + 4 * u < t_end ? a + qmn : -INFINITY;
                 mx = fmaxf(mx, sc[u]);
@@ -351,7 +355,7 @@ __global__ void __launch_bounds__(128) sparse_decode_int8_q_kernel(Int8AttnParam
 #pragma unroll
                 for (int w = 0; w < NW; ++w)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) acc[4 * w + k] = fmaf(ps, (float)((vw[u][w] >> (8 * k)) & 0xffu), acc[4 * w + k]);
+                    for (int k = 0; k < 4; ++k) acc[4 * w + k] = fmaf(ps, code_f32(vw[u][w], k), acc[4 * w + k]);
             }
             m = m_new;
         }
