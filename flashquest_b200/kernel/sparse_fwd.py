@@ -61,10 +61,10 @@ def flash_attn_sparse_fwd(Q, K_uint8, K_scale, K_mn, V_uint8, V_scale, V_mn, *, 
     O = torch.empty(B, H_q, D, dtype=Q.dtype, device=dev)
     L = torch.empty(B, H_q, dtype=torch.float32, device=dev) if return_lse else None
     if n_split is None:
-        # a warp should walk about six to eight pages: the list made from a mask is as wide as the page count and
-        # about a quarter of it is real, so one split per 96 entries (measured: 16-24 splits best at 2048 pages,
-        # batch 1 and 16 alike)
-        n_split = max(1, min(64, bucket // 96))
+        # a warp should walk at least six to eight pages (the list made from a mask is as wide as the page count and
+        # about a quarter of it is real: one split per 96 entries at most), and about sixteen 128-thread CTAs per SM
+        # are enough to fill the GPU (measured at 2048 pages: 16-24 splits best at batch 1, 4-8 at batch 16)
+        n_split = max(1, min(64, bucket // 96, max(1, (16 * 148) // max(B * H_q, 1))))
     with torch.cuda.device(dev):
         ws = torch.empty(lib().fq_sparse_decode_int8_workspace_bytes(B, H_q, D, n_split), dtype=torch.uint8, device=dev)
         check(lib().fq_sparse_decode_int8_counted(
