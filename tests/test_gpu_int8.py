@@ -192,3 +192,25 @@ def test_cache_allocation_and_streaming(kq):
         cache.get_views(2)
     with pytest.raises(NotImplementedError):
         cache.update(None, None, 0)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+def test_attention_with_rows_that_are_not_16_byte_aligned(D):
+    """Code rows cut out of a wider tensor (token stride D + 4 bytes) are 4-byte but not 16-byte aligned: the call
+    takes the warp-per-token kernel instead of the quarter-warp one; both agree with the oracle."""
+    from flashquest_b200.kernel.sparse_fwd import flash_attn_sparse_fwd
+    from flashquest_b200 import _lib
+    B, Hq, Hkv, S, page, dtype = 1, 4, 2, 640, 16, torch.bfloat16
+    Q, kv, mask = _att_case(33, B, Hq, Hkv, S, D, page, dtype)
+    Ow, lw = oracle.sparse_attn_int8(Q, *kv, selection_mask=mask, page_size=page)
+    dev = [t.cuda() for t in kv]
+    wideK = torch.zeros(B, Hkv, S, D + 4, dtype=torch.uint8, device="cuda")
+    wideV = torch.zeros_like(wideK)
+    wideK[..., :D], wideV[..., :D] = dev[0], dev[3]
+    Kc, Vc = wideK[..., :D], wideV[..., :D]
+    assert Kc.stride(2) == D + 4 and Kc.stride(3) == 1
+    O, lse = flash_attn_sparse_fwd(Q.cuda(), Kc, dev[1], dev[2], Vc, dev[4], dev[5], selection_mask=mask.cuda(), page_size=page)
+    _close(O, lse, Ow, lw, dtype)
+    O2, lse2 = flash_attn_sparse_fwd(Q.cuda(), *dev, selection_mask=mask.cuda(), page_size=page)
+    _close(O2, lse2, Ow, lw, dtype)
+    assert _lib.lib().fq_device_status() == 0
