@@ -146,6 +146,30 @@ def test_turbo_attention_rotated_basis(T, dtype, B, Hq, Hkv, S, D, page):
         _close_rot(O, lse, Ow, lw, dtype)
 
 
+def test_turbo_attention_list_wider_than_the_packing_limit(T):
+    """A page list wider than the 4096 entries a CTA packs into shared memory is walked as it is, padding and
+    out-of-order entries skipped per unit: 4200 pages, a few of them selected, against the oracle."""
+    from flashquest_b200.kernel.sparse_turbo_fwd import sparse_decode_turbo_rotated
+    B, Hq, Hkv, D, page, dtype = 1, 2, 1, 128, 16, torch.float16
+    S = page * 4200
+    K = make_kv(81, (B, Hkv, S, D), torch.bfloat16)
+    V = make_kv(82, (B, Hkv, S, D), torch.bfloat16, outliers=())
+    Q_rot = oracle.wht_along_head_dim(make_q(83, (B, Hq, 1, D), dtype))
+    Km, Kl, Kst, Ksr, Kmr = oracle.quantize_k_turbo(K, page)
+    Vm, Vl, Vst = oracle.quantize_v_turbo(V)
+    mask = torch.zeros(B, Hq, 1, S // page, dtype=torch.bool)
+    g = torch.Generator().manual_seed(5)
+    for h in range(Hq):
+        mask[0, h, 0, torch.randperm(S // page, generator=g)[:48]] = True
+    mask[..., 0] = True
+    mask[..., -1] = True
+    Ow, lw = oracle.sparse_attn_turbo_rotated(Q_rot, Km, Kl, Kst, Vm, Vl, Vst, selection_mask=mask, page_size=page)
+    dev = [t.cuda() for t in (Km, Kl, Kst, Vm, Vl, Vst)]
+    for n_split in (1, 5, None):
+        O, lse = sparse_decode_turbo_rotated(Q_rot.cuda(), *dev, selection_mask=mask.cuda(), page_size=page, n_split=n_split)
+        _close_rot(O, lse, Ow, lw, dtype)
+
+
 def _student_t_kv(seed, shape, dtype, df=3, dims=(3, 17, 29, 41, 64, 77, 100, 119)):
     """BASELINE config 2's distribution: N(0,1) with Student-t (df 3) values on 8 of the 128 channels."""
     import numpy as np
